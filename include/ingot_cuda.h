@@ -1,0 +1,142 @@
+/* ingot_cuda.h — C ABI of the B200 (sm_100a) attention path for the Ingot inference engine.
+ *
+ * The library replaces, for a Backend implementation, the per-layer attention stage that sits
+ * between the Q/K/V projections and the output projection of Ingot's forward pass:
+ *     rope(q), rope(k) -> KV-cache append -> causal GQA attention
+ * (CPU reference: src/cpu_backend.cpp:43-69; Metal reference: src/metal_backend.mm:443-445).
+ *
+ * Conventions
+ *   - Every entry point returns an int status (INGOT_OK == 0); nothing throws or aborts.
+ *   - Pointers named *_dev are device pointers on the device the cache was created on; pointers
+ *     named *_host are host pointers. `stream` is a cudaStream_t passed as void* (NULL = default
+ *     stream). Calls are asynchronous on `stream` unless stated otherwise.
+ *   - head_dim is 128 (the reference's flash kernels are specialised the same way,
+ *     src/metal_backend.mm:340,361). Query heads are grouped onto KV heads as h / (n_head / n_head_kv)
+ *     (src/cpu_backend.cpp:29,53).
+ *   - Query / output activations are row-major [token][head][128].
+ *   - The KV cache is f16 (as the Metal reference's, src/metal_backend.mm:197-198). Layouts:
+ *       contiguous: K and V each [n_layer][n_head_kv][n_ctx][128]            (one sequence)
+ *       paged:      K and V each [n_layer][n_blocks][n_head_kv][16][128]     (16-token blocks,
+ *                   any number of sequences, each described by a row of a block table)
+ *   - The cache is a pure function of (layer, position): positions may be rewritten in any order
+ *     and the caller owns the notion of sequence length (src/main.cpp:295,374-375 rewind `pos`
+ *     without telling the backend).
+ */
+#ifndef INGOT_CUDA_H
+#define INGOT_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+    INGOT_OK = 0,
+    INGOT_ERR_INVALID = 1,      /* bad argument (null pointer, range, unsupported shape) */
+    INGOT_ERR_CUDA = 2,         /* a CUDA runtime/driver call failed; see ingot_last_error() */
+    INGOT_ERR_UNSUPPORTED = 3,  /* shape or dtype outside what the kernels are built for */
+    INGOT_ERR_NOMEM = 4,
+    INGOT_ERR_DEVICE = 5        /* a kernel reported a problem through its status word */
+};
+
+enum { INGOT_F32 = 0, INGOT_F16 = 1, INGOT_BF16 = 2 };
+enum { INGOT_KV_CONTIGUOUS = 0, INGOT_KV_PAGED = 1 };
+#define INGOT_BLOCK_TOKENS 16
+#define INGOT_HEAD_DIM 128
+
+typedef struct ingot_kv ingot_kv;
+
+/* Human-readable text for a status code / for the last failure on the calling thread. */
+const char* ingot_status_string(int status);
+const char* ingot_last_error(void);
+/* Library build: compiled architecture string, e.g. "sm_100a". */
+const char* ingot_build_arch(void);
+
+/* ---- KV cache ------------------------------------------------------------------------------
+ * Replaces the cache the reference backends own (src/backend.h:1; CPU: src/cpu_backend.h:23,
+ * src/cpu_backend.cpp:18-19; Metal: src/metal_backend.mm:197-198).
+ * capacity = n_ctx positions (contiguous) or number of 16-token blocks (paged).
+ * max_seqs = most sequences one decode call will carry (sizes the split-KV scratch); 1 for a
+ * single-sequence backend. Allocates on the current device. Synchronous. */
+int ingot_kv_create(ingot_kv** out, int layout, int n_layer, int n_head_kv, int head_dim, int capacity,
+                    int max_seqs);
+void ingot_kv_destroy(ingot_kv* kv);
+/* Device base pointers of one layer's K / V storage (layouts above), e.g. to import a cache. */
+void* ingot_kv_k_dev(ingot_kv* kv, int layer);
+void* ingot_kv_v_dev(ingot_kv* kv, int layer);
+size_t ingot_kv_layer_bytes(const ingot_kv* kv);
+/* Reads and clears the device status word (0 = no kernel reported a problem). Synchronises `stream`. */
+int ingot_kv_status(ingot_kv* kv, void* stream, int* status_out);
+
+/* ---- K1: fused RoPE + K/V append -------------------------------------------------------------
+ * Replaces ops::rope on q and k plus the cache memcpy (src/ops.cpp:243-255,
+ * src/cpu_backend.cpp:43-49); on Metal: rope + rope_k_to_cache + to_half
+ * (shaders/kernels.metal:256-282,779-782; src/metal_backend.mm:324-334,395-409).
+ * For each token t in [0, n_tok): position p = positions_dev ? positions_dev[t] : pos0 + t.
+ *   q_dev  [n_tok][n_head][128]   f32, may be NULL (no query work);  rotated q is written as f16
+ *          to q_out_dev [n_tok][n_head][128].
+ *   k_dev, v_dev [n_tok][n_head_kv][128] f32; rotated k and raw v are written as f16 into the cache
+ *          at position p.
+ *   inv_freq_dev [64] f32: Model::rope_inv_freq (src/model.cpp:59-69). Rotation is on adjacent
+ *          pairs (x[2i], x[2i+1]) by angle float(p) * inv_freq[i], in f32.
+ * Paged caches: token t belongs to sequence s = seq_ids_dev ? seq_ids_dev[t] : 0 and its block is
+ * block_tables_dev[s * max_blocks_per_seq + p / 16]. Contiguous caches ignore those arguments. */
+int ingot_rope_kv_append(ingot_kv* kv, int layer, const float* q_dev, void* q_out_dev, const float* k_dev,
+                         const float* v_dev, const float* inv_freq_dev, int n_head, int pos0, int n_tok,
+                         const int32_t* positions_dev, const int32_t* seq_ids_dev,
+                         const int32_t* block_tables_dev, int max_blocks_per_seq, void* stream);
+
+/* Import of already-rotated f16 K/V rows [n_tok][n_head_kv][128] into the cache at positions
+ * pos0..pos0+n_tok-1 of one sequence (block_table_dev: that sequence's row, paged only).
+ * No reference counterpart on the CPU path (its cache is f32); mirrors the layout transform of
+ * the Metal KV store (src/metal_backend.mm:395-409) without the arithmetic. */
+int ingot_kv_import_f16(ingot_kv* kv, int layer, const void* k_f16_dev, const void* v_f16_dev, int pos0,
+                        int n_tok, const int32_t* block_table_dev, void* stream);
+
+/* ---- K3: split-KV flash decoding -------------------------------------------------------------
+ * Replaces the attention lambda for one-token queries (src/cpu_backend.cpp:51-69) and Metal's
+ * attn_decode_g3 + attn_combine (shaders/kernels.metal:428-516; src/metal_backend.mm:340-360).
+ * n_seq sequences, one query token each:
+ *   q_dev   [n_seq][n_head][128]  q_dtype in {F32, F16, BF16}, already rotated
+ *   out_dev [n_seq][n_head][128]  out_dtype in {F32, F16}
+ *   seq_lens_dev [n_seq] int32: keys 0..len-1 of each sequence are attended (len >= 1).
+ *          NULL with n_seq == 1 means the single length max_seq_len.
+ *   max_seq_len: host-side upper bound of every length (sizes the launch grid).
+ *   block_tables_dev [n_seq][max_blocks_per_seq]: paged caches only.
+ * chunk_keys: keys per split (multiple of 16), or 0 to let the library choose. */
+int ingot_attn_decode(ingot_kv* kv, int layer, const void* q_dev, int q_dtype, void* out_dev, int out_dtype,
+                      int n_head, int n_seq, const int32_t* seq_lens_dev, int max_seq_len,
+                      const int32_t* block_tables_dev, int max_blocks_per_seq, int chunk_keys, void* stream);
+
+/* ---- K2: causal GQA flash-attention prefill / chunked prefill -----------------------------------
+ * Replaces n_tok iterations of the attention lambda (src/backend.h:16-20 + src/cpu_backend.cpp:51-69)
+ * and Metal's attn_prefill (shaders/kernels.metal:518-633; src/metal_backend.mm:361-372).
+ * Query token i (0 <= i < n_tok) sits at position q_pos0 + i and attends to keys 0..q_pos0+i, which
+ * must already be in the cache (append first).
+ *   q_dev   [n_tok][n_head][128]  q_dtype in {F32, F16, BF16}, already rotated
+ *   out_dev [n_tok][n_head][128]  out_dtype in {F32, F16}
+ *   block_table_dev: the sequence's block-table row (paged caches), else NULL.
+ * impl: 0 = library's choice, 1 = force the warp-MMA kernel, 2 = force the tcgen05/TMEM/TMA kernel
+ *       (contiguous caches only). */
+int ingot_attn_prefill(ingot_kv* kv, int layer, const void* q_dev, int q_dtype, void* out_dev, int out_dtype,
+                       int n_head, int q_pos0, int n_tok, const int32_t* block_table_dev, int impl,
+                       void* stream);
+
+/* ---- Host-buffer convenience call ---------------------------------------------------------------
+ * One layer of the reference's attention stage with HOST inputs/outputs, as a CPU-side caller sees
+ * it (q,k,v from the projections in; attention output for the wo projection out):
+ * copies q/k/v f32 rows host->device, runs K1 then K3 (n_tok == 1) or K2 (n_tok > 1) on a contiguous
+ * cache at positions pos0..pos0+n_tok-1, copies the f32 output device->host. All on `stream`,
+ * asynchronous: call ingot_stream_sync (or cudaStreamSynchronize) before reading out_host.
+ * Host buffers should be pinned for the copies to overlap. inv_freq_dev is a device pointer. */
+int ingot_attn_layer_host(ingot_kv* kv, int layer, const float* q_host, const float* k_host, const float* v_host,
+                          float* out_host, const float* inv_freq_dev, int n_head, int pos0, int n_tok,
+                          void* stream);
+int ingot_stream_sync(void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* INGOT_CUDA_H */

@@ -1,0 +1,95 @@
+// Internal declarations shared by the .cu files of libingot_cuda.so. Not installed.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_fp16.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <string>
+
+#include "ingot_cuda.h"
+
+constexpr int kHeadDim = INGOT_HEAD_DIM;
+constexpr int kBlockTokens = INGOT_BLOCK_TOKENS;
+// Floats per (split, head) partial of the split-KV decode: o[128], running max m, running sum l,
+// padded to a 16-byte multiple. The Metal reference keeps the same triple with stride 130
+// (shaders/kernels.metal:291).
+constexpr int kPartStride = 132;
+// Most 16-key units a decode split may be asked to cover is unbounded; the smallest split the
+// library picks is one unit, which bounds the number of partials per (sequence, head).
+constexpr int kMinChunkKeys = 16;
+
+// Bits of the device status word (ingot_kv::status_dev).
+enum : int {
+    kDevErrPosRange = 1,      // K1: a position fell outside the cache; the row was skipped
+    kDevErrBlockRange = 2,    // a block-table entry fell outside the pool; the access was skipped
+    kDevErrBarrierTimeout = 4 // prefill: a bounded mbarrier wait expired; the CTA gave up cleanly
+};
+
+struct ingot_kv {
+    int device = 0;
+    int layout = INGOT_KV_CONTIGUOUS;
+    int n_layer = 0, n_head_kv = 0, head_dim = kHeadDim;
+    int capacity = 0;   // positions (contiguous) or blocks (paged)
+    int max_seqs = 1;
+    size_t layer_elems = 0;  // f16 elements per layer in each of K and V
+    __half* k = nullptr;
+    __half* v = nullptr;
+    int* status_dev = nullptr;
+    // split-KV decode scratch: partials [max_seqs][max_parts][n_head_max][kPartStride] and
+    // arrival counters [max_seqs][n_head_kv]
+    float* part = nullptr;
+    size_t part_floats = 0;
+    unsigned int* counters = nullptr;
+    // staging for the host-buffer entry point (grown on demand)
+    void* stage = nullptr;
+    size_t stage_bytes = 0;
+    // tensor maps for the TMA prefill kernel, one per layer and per tile height, built on first use
+    void* tmaps = nullptr;  // host array, see attn_prefill_sm100.cu
+};
+
+void ingot_set_error(const std::string& msg);
+int ingot_cuda_fail(cudaError_t e, const char* what);
+
+#define INGOT_CUDA_TRY(expr)                                          \
+    do {                                                              \
+        cudaError_t e__ = (expr);                                     \
+        if (e__ != cudaSuccess) return ingot_cuda_fail(e__, #expr);   \
+    } while (0)
+
+#define INGOT_REQUIRE(cond, msg)                                      \
+    do {                                                              \
+        if (!(cond)) {                                                \
+            ingot_set_error(msg);                                     \
+            return INGOT_ERR_INVALID;                                 \
+        }                                                             \
+    } while (0)
+
+// Element offset of (layer-local) row `pos` of kv head `h` — contiguous layout.
+__host__ __device__ inline size_t kv_row_offset_contig(int n_ctx, int h, int pos) {
+    return (size_t(h) * n_ctx + pos) * kHeadDim;
+}
+// Element offset of token slot `pos % 16` of kv head `h` in physical block `blk` — paged layout.
+__host__ __device__ inline size_t kv_row_offset_paged(int n_head_kv, int blk, int h, int pos) {
+    return ((size_t(blk) * n_head_kv + h) * kBlockTokens + (pos % kBlockTokens)) * kHeadDim;
+}
+
+// Launchers implemented in the kernel files.
+int launch_rope_kv_append(ingot_kv* kv, int layer, const float* q, __half* q_out, const float* k, const float* v,
+                          const float* inv_freq, int n_head, int pos0, int n_tok, const int32_t* positions,
+                          const int32_t* seq_ids, const int32_t* block_tables, int max_blocks_per_seq,
+                          cudaStream_t stream);
+int launch_kv_import_f16(ingot_kv* kv, int layer, const __half* k, const __half* v, int pos0, int n_tok,
+                         const int32_t* block_table, cudaStream_t stream);
+int launch_attn_decode(ingot_kv* kv, int layer, const void* q, int q_dtype, void* out, int out_dtype, int n_head,
+                       int n_seq, const int32_t* seq_lens, int max_seq_len, const int32_t* block_tables,
+                       int max_blocks_per_seq, int chunk_keys, float* part, unsigned int* counters,
+                       cudaStream_t stream);
+int launch_attn_prefill_mma(ingot_kv* kv, int layer, const void* q, int q_dtype, void* out, int out_dtype,
+                            int n_head, int q_pos0, int n_tok, const int32_t* block_table, cudaStream_t stream);
+int launch_attn_prefill_sm100(ingot_kv* kv, int layer, const void* q, int q_dtype, void* out, int out_dtype,
+                              int n_head, int q_pos0, int n_tok, cudaStream_t stream);
+void free_prefill_sm100_state(ingot_kv* kv);
+size_t decode_part_floats(int max_seqs, int capacity_keys, int n_head_kv);

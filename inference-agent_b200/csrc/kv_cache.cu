@@ -1,0 +1,284 @@
+// KV-cache handle, error reporting and the host-buffer convenience entry point of libingot_cuda.so.
+//
+// The cache replaces the one each reference backend owns (src/backend.h:1): f32
+// [n_layer][n_ctx][n_head_kv*head_dim] on the CPU (src/cpu_backend.h:23) and f16 with the same
+// order on Metal (src/metal_backend.mm:197-198). Here it is f16 in HBM and head-major, so that one
+// KV head's keys are a dense [positions][128] matrix: a decode split reads one contiguous byte
+// range, a prefill tile is one 2-D TMA box, and a KV-head shard of the cache is one slab.
+#include <cstdio>
+#include <cstring>
+#include <new>
+
+#include "ingot_internal.cuh"
+
+static thread_local std::string g_last_error;
+
+void ingot_set_error(const std::string& msg) { g_last_error = msg; }
+
+int ingot_cuda_fail(cudaError_t e, const char* what) {
+    g_last_error = std::string(what) + ": " + cudaGetErrorString(e);
+    return e == cudaErrorMemoryAllocation ? INGOT_ERR_NOMEM : INGOT_ERR_CUDA;
+}
+
+extern "C" {
+
+const char* ingot_status_string(int status) {
+    switch (status) {
+        case INGOT_OK: return "ok";
+        case INGOT_ERR_INVALID: return "invalid argument";
+        case INGOT_ERR_CUDA: return "CUDA call failed";
+        case INGOT_ERR_UNSUPPORTED: return "unsupported shape or dtype";
+        case INGOT_ERR_NOMEM: return "out of device memory";
+        case INGOT_ERR_DEVICE: return "a kernel reported an error";
+        default: return "unknown status";
+    }
+}
+
+const char* ingot_last_error(void) { return g_last_error.c_str(); }
+
+const char* ingot_build_arch(void) { return "sm_100a"; }
+
+int ingot_kv_create(ingot_kv** out, int layout, int n_layer, int n_head_kv, int head_dim, int capacity,
+                    int max_seqs) {
+    INGOT_REQUIRE(out != nullptr, "ingot_kv_create: out is null");
+    *out = nullptr;
+    INGOT_REQUIRE(layout == INGOT_KV_CONTIGUOUS || layout == INGOT_KV_PAGED, "ingot_kv_create: bad layout");
+    INGOT_REQUIRE(n_layer >= 1 && n_head_kv >= 1 && capacity >= 1 && max_seqs >= 1, "ingot_kv_create: bad sizes");
+    if (head_dim != kHeadDim) {
+        ingot_set_error("ingot_kv_create: head_dim must be 128");
+        return INGOT_ERR_UNSUPPORTED;
+    }
+    ingot_kv* kv = new (std::nothrow) ingot_kv();
+    if (!kv) return INGOT_ERR_NOMEM;
+    cudaError_t e = cudaGetDevice(&kv->device);
+    if (e != cudaSuccess) { delete kv; return ingot_cuda_fail(e, "cudaGetDevice"); }
+    kv->layout = layout;
+    kv->n_layer = n_layer;
+    kv->n_head_kv = n_head_kv;
+    kv->capacity = capacity;
+    kv->max_seqs = max_seqs;
+    const size_t rows = layout == INGOT_KV_CONTIGUOUS ? size_t(capacity) : size_t(capacity) * kBlockTokens;
+    kv->layer_elems = rows * n_head_kv * kHeadDim;
+    const size_t bytes = kv->layer_elems * n_layer * sizeof(__half);
+    auto fail = [&](cudaError_t err, const char* what) {
+        int rc = ingot_cuda_fail(err, what);
+        ingot_kv_destroy(kv);
+        return rc;
+    };
+    if ((e = cudaMalloc(&kv->k, bytes)) != cudaSuccess) return fail(e, "cudaMalloc(K cache)");
+    if ((e = cudaMalloc(&kv->v, bytes)) != cudaSuccess) return fail(e, "cudaMalloc(V cache)");
+    if ((e = cudaMalloc(&kv->status_dev, sizeof(int))) != cudaSuccess) return fail(e, "cudaMalloc(status)");
+    if ((e = cudaMalloc(&kv->counters, sizeof(unsigned int) * size_t(max_seqs) * n_head_kv)) != cudaSuccess)
+        return fail(e, "cudaMalloc(counters)");
+    // Zero-filled cache: rows that were never appended hold finite values, so a masked key can never
+    // inject NaN through 0 * garbage.
+    if ((e = cudaMemset(kv->k, 0, bytes)) != cudaSuccess) return fail(e, "cudaMemset(K)");
+    if ((e = cudaMemset(kv->v, 0, bytes)) != cudaSuccess) return fail(e, "cudaMemset(V)");
+    if ((e = cudaMemset(kv->status_dev, 0, sizeof(int))) != cudaSuccess) return fail(e, "cudaMemset(status)");
+    if ((e = cudaMemset(kv->counters, 0, sizeof(unsigned int) * size_t(max_seqs) * n_head_kv)) != cudaSuccess)
+        return fail(e, "cudaMemset(counters)");
+    if ((e = cudaDeviceSynchronize()) != cudaSuccess) return fail(e, "cudaDeviceSynchronize");
+    *out = kv;
+    return INGOT_OK;
+}
+
+void ingot_kv_destroy(ingot_kv* kv) {
+    if (!kv) return;
+    free_prefill_sm100_state(kv);
+    cudaFree(kv->k);
+    cudaFree(kv->v);
+    cudaFree(kv->status_dev);
+    cudaFree(kv->part);
+    cudaFree(kv->counters);
+    cudaFree(kv->stage);
+    delete kv;
+}
+
+void* ingot_kv_k_dev(ingot_kv* kv, int layer) {
+    if (!kv || layer < 0 || layer >= kv->n_layer) return nullptr;
+    return kv->k + size_t(layer) * kv->layer_elems;
+}
+
+void* ingot_kv_v_dev(ingot_kv* kv, int layer) {
+    if (!kv || layer < 0 || layer >= kv->n_layer) return nullptr;
+    return kv->v + size_t(layer) * kv->layer_elems;
+}
+
+size_t ingot_kv_layer_bytes(const ingot_kv* kv) { return kv ? kv->layer_elems * sizeof(__half) : 0; }
+
+int ingot_kv_status(ingot_kv* kv, void* stream, int* status_out) {
+    INGOT_REQUIRE(kv && status_out, "ingot_kv_status: null argument");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    int host = 0;
+    INGOT_CUDA_TRY(cudaMemcpyAsync(&host, kv->status_dev, sizeof(int), cudaMemcpyDeviceToHost, s));
+    INGOT_CUDA_TRY(cudaMemsetAsync(kv->status_dev, 0, sizeof(int), s));
+    INGOT_CUDA_TRY(cudaStreamSynchronize(s));
+    *status_out = host;
+    return INGOT_OK;
+}
+
+int ingot_rope_kv_append(ingot_kv* kv, int layer, const float* q_dev, void* q_out_dev, const float* k_dev,
+                         const float* v_dev, const float* inv_freq_dev, int n_head, int pos0, int n_tok,
+                         const int32_t* positions_dev, const int32_t* seq_ids_dev,
+                         const int32_t* block_tables_dev, int max_blocks_per_seq, void* stream) {
+    INGOT_REQUIRE(kv != nullptr, "ingot_rope_kv_append: kv is null");
+    INGOT_REQUIRE(layer >= 0 && layer < kv->n_layer, "ingot_rope_kv_append: layer out of range");
+    INGOT_REQUIRE(n_tok >= 0, "ingot_rope_kv_append: n_tok < 0");
+    if (n_tok == 0) return INGOT_OK;
+    INGOT_REQUIRE(k_dev && v_dev && inv_freq_dev, "ingot_rope_kv_append: null k/v/inv_freq");
+    INGOT_REQUIRE((q_dev == nullptr) == (q_out_dev == nullptr), "ingot_rope_kv_append: q and q_out must both be given or both be null");
+    INGOT_REQUIRE(q_dev == nullptr || (n_head >= kv->n_head_kv && n_head % kv->n_head_kv == 0),
+                  "ingot_rope_kv_append: n_head must be a multiple of n_head_kv");
+    if (kv->layout == INGOT_KV_CONTIGUOUS) {
+        INGOT_REQUIRE(positions_dev != nullptr || (pos0 >= 0 && size_t(pos0) + n_tok <= size_t(kv->capacity)),
+                      "context window exceeded");
+    } else {
+        INGOT_REQUIRE(block_tables_dev != nullptr && max_blocks_per_seq >= 1,
+                      "ingot_rope_kv_append: paged cache needs a block table");
+        INGOT_REQUIRE(positions_dev != nullptr ||
+                          (pos0 >= 0 && (size_t(pos0) + n_tok + kBlockTokens - 1) / kBlockTokens <= size_t(max_blocks_per_seq)),
+                      "context window exceeded");
+    }
+    return launch_rope_kv_append(kv, layer, q_dev, static_cast<__half*>(q_out_dev), k_dev, v_dev, inv_freq_dev, n_head,
+                                 pos0, n_tok, positions_dev, seq_ids_dev, block_tables_dev, max_blocks_per_seq,
+                                 static_cast<cudaStream_t>(stream));
+}
+
+int ingot_kv_import_f16(ingot_kv* kv, int layer, const void* k_f16_dev, const void* v_f16_dev, int pos0,
+                        int n_tok, const int32_t* block_table_dev, void* stream) {
+    INGOT_REQUIRE(kv != nullptr, "ingot_kv_import_f16: kv is null");
+    INGOT_REQUIRE(layer >= 0 && layer < kv->n_layer, "ingot_kv_import_f16: layer out of range");
+    INGOT_REQUIRE(n_tok >= 0 && pos0 >= 0, "ingot_kv_import_f16: negative range");
+    if (n_tok == 0) return INGOT_OK;
+    INGOT_REQUIRE(k_f16_dev && v_f16_dev, "ingot_kv_import_f16: null k/v");
+    if (kv->layout == INGOT_KV_CONTIGUOUS)
+        INGOT_REQUIRE(size_t(pos0) + n_tok <= size_t(kv->capacity), "context window exceeded");
+    else
+        INGOT_REQUIRE(block_table_dev != nullptr, "ingot_kv_import_f16: paged cache needs a block table");
+    return launch_kv_import_f16(kv, layer, static_cast<const __half*>(k_f16_dev), static_cast<const __half*>(v_f16_dev),
+                                pos0, n_tok, block_table_dev, static_cast<cudaStream_t>(stream));
+}
+
+static int ensure_decode_scratch(ingot_kv* kv, size_t floats) {
+    if (floats <= kv->part_floats) return INGOT_OK;
+    // Growing the scratch frees the old one: wait for kernels that may still read it.
+    INGOT_CUDA_TRY(cudaDeviceSynchronize());
+    cudaFree(kv->part);
+    kv->part = nullptr;
+    kv->part_floats = 0;
+    INGOT_CUDA_TRY(cudaMalloc(&kv->part, floats * sizeof(float)));
+    kv->part_floats = floats;
+    return INGOT_OK;
+}
+
+int ingot_attn_decode(ingot_kv* kv, int layer, const void* q_dev, int q_dtype, void* out_dev, int out_dtype,
+                      int n_head, int n_seq, const int32_t* seq_lens_dev, int max_seq_len,
+                      const int32_t* block_tables_dev, int max_blocks_per_seq, int chunk_keys, void* stream) {
+    INGOT_REQUIRE(kv != nullptr, "ingot_attn_decode: kv is null");
+    INGOT_REQUIRE(layer >= 0 && layer < kv->n_layer, "ingot_attn_decode: layer out of range");
+    INGOT_REQUIRE(q_dev && out_dev, "ingot_attn_decode: null q/out");
+    INGOT_REQUIRE(n_seq >= 1 && n_seq <= kv->max_seqs, "ingot_attn_decode: n_seq exceeds max_seqs of the cache");
+    INGOT_REQUIRE(seq_lens_dev != nullptr || n_seq == 1, "ingot_attn_decode: seq_lens_dev required for n_seq > 1");
+    INGOT_REQUIRE(max_seq_len >= 1, "ingot_attn_decode: max_seq_len < 1");
+    INGOT_REQUIRE(n_head >= kv->n_head_kv && n_head % kv->n_head_kv == 0, "ingot_attn_decode: n_head must be a multiple of n_head_kv");
+    INGOT_REQUIRE(chunk_keys >= 0 && chunk_keys % 16 == 0, "ingot_attn_decode: chunk_keys must be a multiple of 16");
+    if (n_head / kv->n_head_kv > 8 || (q_dtype != INGOT_F32 && q_dtype != INGOT_F16 && q_dtype != INGOT_BF16) ||
+        (out_dtype != INGOT_F32 && out_dtype != INGOT_F16)) {
+        ingot_set_error("ingot_attn_decode: group size > 8 or unsupported dtype");
+        return INGOT_ERR_UNSUPPORTED;
+    }
+    if (kv->layout == INGOT_KV_CONTIGUOUS) {
+        INGOT_REQUIRE(n_seq == 1, "ingot_attn_decode: a contiguous cache holds one sequence");
+        INGOT_REQUIRE(max_seq_len <= kv->capacity, "context window exceeded");
+    } else {
+        INGOT_REQUIRE(block_tables_dev != nullptr && max_blocks_per_seq >= 1, "ingot_attn_decode: paged cache needs block tables");
+        INGOT_REQUIRE((max_seq_len + kBlockTokens - 1) / kBlockTokens <= max_blocks_per_seq, "ingot_attn_decode: max_seq_len exceeds the block table");
+    }
+    const size_t need = decode_part_floats(n_seq, max_seq_len, n_head);
+    int rc = ensure_decode_scratch(kv, need);
+    if (rc != INGOT_OK) return rc;
+    return launch_attn_decode(kv, layer, q_dev, q_dtype, out_dev, out_dtype, n_head, n_seq, seq_lens_dev, max_seq_len,
+                              block_tables_dev, max_blocks_per_seq, chunk_keys, kv->part, kv->counters,
+                              static_cast<cudaStream_t>(stream));
+}
+
+int ingot_attn_prefill(ingot_kv* kv, int layer, const void* q_dev, int q_dtype, void* out_dev, int out_dtype,
+                       int n_head, int q_pos0, int n_tok, const int32_t* block_table_dev, int impl, void* stream) {
+    INGOT_REQUIRE(kv != nullptr, "ingot_attn_prefill: kv is null");
+    INGOT_REQUIRE(layer >= 0 && layer < kv->n_layer, "ingot_attn_prefill: layer out of range");
+    INGOT_REQUIRE(n_tok >= 0 && q_pos0 >= 0, "ingot_attn_prefill: negative range");
+    if (n_tok == 0) return INGOT_OK;
+    INGOT_REQUIRE(q_dev && out_dev, "ingot_attn_prefill: null q/out");
+    INGOT_REQUIRE(n_head >= kv->n_head_kv && n_head % kv->n_head_kv == 0, "ingot_attn_prefill: n_head must be a multiple of n_head_kv");
+    INGOT_REQUIRE(impl >= 0 && impl <= 2, "ingot_attn_prefill: impl must be 0, 1 or 2");
+    if ((q_dtype != INGOT_F32 && q_dtype != INGOT_F16 && q_dtype != INGOT_BF16) ||
+        (out_dtype != INGOT_F32 && out_dtype != INGOT_F16)) {
+        ingot_set_error("ingot_attn_prefill: unsupported dtype");
+        return INGOT_ERR_UNSUPPORTED;
+    }
+    if (kv->layout == INGOT_KV_CONTIGUOUS)
+        INGOT_REQUIRE(size_t(q_pos0) + n_tok <= size_t(kv->capacity), "context window exceeded");
+    else
+        INGOT_REQUIRE(block_table_dev != nullptr, "ingot_attn_prefill: paged cache needs a block table");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const bool tma_ok = kv->layout == INGOT_KV_CONTIGUOUS;
+    if (impl == 2 && !tma_ok) {
+        ingot_set_error("ingot_attn_prefill: the tcgen05 kernel needs a contiguous cache");
+        return INGOT_ERR_UNSUPPORTED;
+    }
+    // The tcgen05 kernel works on 256-row tiles; below a few tiles per SM the warp-MMA kernel's
+    // finer 64-row tiles fill the GPU better.
+    const bool use_sm100 = impl == 2 || (impl == 0 && tma_ok && size_t(n_tok) * n_head >= 16384);
+    if (use_sm100) return launch_attn_prefill_sm100(kv, layer, q_dev, q_dtype, out_dev, out_dtype, n_head, q_pos0, n_tok, s);
+    return launch_attn_prefill_mma(kv, layer, q_dev, q_dtype, out_dev, out_dtype, n_head, q_pos0, n_tok, block_table_dev, s);
+}
+
+int ingot_attn_layer_host(ingot_kv* kv, int layer, const float* q_host, const float* k_host, const float* v_host,
+                          float* out_host, const float* inv_freq_dev, int n_head, int pos0, int n_tok, void* stream) {
+    INGOT_REQUIRE(kv != nullptr, "ingot_attn_layer_host: kv is null");
+    INGOT_REQUIRE(kv->layout == INGOT_KV_CONTIGUOUS, "ingot_attn_layer_host: contiguous cache only");
+    INGOT_REQUIRE(q_host && k_host && v_host && out_host && inv_freq_dev, "ingot_attn_layer_host: null argument");
+    INGOT_REQUIRE(n_tok >= 1 && pos0 >= 0, "ingot_attn_layer_host: bad range");
+    INGOT_REQUIRE(n_head >= kv->n_head_kv && n_head % kv->n_head_kv == 0, "ingot_attn_layer_host: n_head must be a multiple of n_head_kv");
+    INGOT_REQUIRE(size_t(pos0) + n_tok <= size_t(kv->capacity), "context window exceeded");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const size_t q_elems = size_t(n_tok) * n_head * kHeadDim, kv_elems = size_t(n_tok) * kv->n_head_kv * kHeadDim;
+    // Staging is per layer so that consecutive layers can be queued without waiting on each other.
+    const size_t per_layer = q_elems * 4 + kv_elems * 8 + q_elems * 2 + q_elems * 4;
+    const size_t per_layer_al = (per_layer + 255) / 256 * 256;
+    const size_t need = per_layer_al * kv->n_layer;
+    if (need > kv->stage_bytes) {
+        INGOT_CUDA_TRY(cudaDeviceSynchronize());
+        cudaFree(kv->stage);
+        kv->stage = nullptr;
+        kv->stage_bytes = 0;
+        INGOT_CUDA_TRY(cudaMalloc(&kv->stage, need));
+        kv->stage_bytes = need;
+    }
+    char* base = static_cast<char*>(kv->stage) + per_layer_al * layer;
+    float* q_d = reinterpret_cast<float*>(base);
+    float* k_d = q_d + q_elems;
+    float* v_d = k_d + kv_elems;
+    float* o_d = v_d + kv_elems;
+    __half* qh_d = reinterpret_cast<__half*>(o_d + q_elems);
+    INGOT_CUDA_TRY(cudaMemcpyAsync(q_d, q_host, q_elems * 4, cudaMemcpyHostToDevice, s));
+    INGOT_CUDA_TRY(cudaMemcpyAsync(k_d, k_host, kv_elems * 4, cudaMemcpyHostToDevice, s));
+    INGOT_CUDA_TRY(cudaMemcpyAsync(v_d, v_host, kv_elems * 4, cudaMemcpyHostToDevice, s));
+    int rc = ingot_rope_kv_append(kv, layer, q_d, qh_d, k_d, v_d, inv_freq_dev, n_head, pos0, n_tok, nullptr, nullptr,
+                                  nullptr, 0, stream);
+    if (rc != INGOT_OK) return rc;
+    if (n_tok == 1)
+        rc = ingot_attn_decode(kv, layer, qh_d, INGOT_F16, o_d, INGOT_F32, n_head, 1, nullptr, pos0 + 1, nullptr, 0, 0, stream);
+    else
+        rc = ingot_attn_prefill(kv, layer, qh_d, INGOT_F16, o_d, INGOT_F32, n_head, pos0, n_tok, nullptr, 0, stream);
+    if (rc != INGOT_OK) return rc;
+    INGOT_CUDA_TRY(cudaMemcpyAsync(out_host, o_d, q_elems * 4, cudaMemcpyDeviceToHost, s));
+    return INGOT_OK;
+}
+
+int ingot_stream_sync(void* stream) {
+    INGOT_CUDA_TRY(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+    return INGOT_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,180 @@
+"""Python harness over libingot_cuda.so (the C ABI declared in include/ingot_cuda.h).
+
+Used by the tests and bench.py. torch supplies device memory and streams only: every compute
+call goes through the C ABI with raw device pointers. There is no fallback: importing this
+module raises if the CUDA library has not been built.
+"""
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(os.path.dirname(_HERE), "libingot_cuda.so")
+
+F32, F16, BF16 = 0, 1, 2
+KV_CONTIGUOUS, KV_PAGED = 0, 1
+BLOCK_TOKENS = 16
+HEAD_DIM = 128
+
+# name -> (restype, argtypes); every symbol include/ingot_cuda.h declares.
+_P, _I, _SZ = C.c_void_p, C.c_int, C.c_size_t
+ABI = {
+    "ingot_status_string": (C.c_char_p, [_I]),
+    "ingot_last_error": (C.c_char_p, []),
+    "ingot_build_arch": (C.c_char_p, []),
+    "ingot_kv_create": (_I, [C.POINTER(_P), _I, _I, _I, _I, _I, _I]),
+    "ingot_kv_destroy": (None, [_P]),
+    "ingot_kv_k_dev": (_P, [_P, _I]),
+    "ingot_kv_v_dev": (_P, [_P, _I]),
+    "ingot_kv_layer_bytes": (_SZ, [_P]),
+    "ingot_kv_status": (_I, [_P, _P, C.POINTER(_I)]),
+    "ingot_rope_kv_append": (_I, [_P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _P, _P, _P, _I, _P]),
+    "ingot_kv_import_f16": (_I, [_P, _I, _P, _P, _I, _I, _P, _P]),
+    "ingot_attn_decode": (_I, [_P, _I, _P, _I, _P, _I, _I, _I, _P, _I, _P, _I, _I, _P]),
+    "ingot_attn_prefill": (_I, [_P, _I, _P, _I, _P, _I, _I, _I, _I, _P, _I, _P]),
+    "ingot_attn_layer_host": (_I, [_P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _P]),
+    "ingot_stream_sync": (_I, [_P]),
+}
+
+
+class IngotError(RuntimeError):
+    def __init__(self, status, message):
+        super().__init__(f"ingot status {status}: {message}")
+        self.status = status
+
+
+def load_library(path=LIB_PATH):
+    if not os.path.exists(path):
+        raise FileNotFoundError(
+            f"{path} not found: build it with `make -C inference-agent_b200` or __graft_entry__.build(); "
+            "there is no CPU fallback")
+    lib = C.CDLL(path)
+    for name, (res, args) in ABI.items():
+        fn = getattr(lib, name)
+        fn.restype = res
+        fn.argtypes = args
+    return lib
+
+
+_lib = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        _lib = load_library()
+    return _lib
+
+
+def _check(status):
+    if status != 0:
+        raise IngotError(status, lib().ingot_last_error().decode() or lib().ingot_status_string(status).decode())
+
+
+def _dtype_code(t):
+    import torch
+    return {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16}[t.dtype]
+
+
+def _ptr(t):
+    return None if t is None else C.c_void_p(t.data_ptr())
+
+
+def _stream():
+    import torch
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+class KVCache:
+    """Owns an ingot_kv handle on the current CUDA device."""
+
+    def __init__(self, layout, n_layer, n_head_kv, capacity, max_seqs=1, head_dim=HEAD_DIM):
+        self.layout, self.n_layer, self.n_head_kv, self.capacity, self.max_seqs = layout, n_layer, n_head_kv, capacity, max_seqs
+        h = C.c_void_p()
+        _check(lib().ingot_kv_create(C.byref(h), layout, n_layer, n_head_kv, head_dim, capacity, max_seqs))
+        self.handle = h
+
+    def close(self):
+        if self.handle:
+            lib().ingot_kv_destroy(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def layer_view(self, layer, which="k"):
+        """torch view of one layer's K or V storage in its native layout (no copy)."""
+        import torch
+        fn = lib().ingot_kv_k_dev if which == "k" else lib().ingot_kv_v_dev
+        ptr = fn(self.handle, layer)
+        if self.layout == KV_CONTIGUOUS:
+            shape = (self.n_head_kv, self.capacity, HEAD_DIM)
+        else:
+            shape = (self.capacity, self.n_head_kv, BLOCK_TOKENS, HEAD_DIM)
+
+        class _DeviceArray:  # wraps the raw device pointer for torch through the CUDA array interface
+            __cuda_array_interface__ = {"shape": shape, "typestr": "<f2", "data": (ptr, False), "version": 2}
+
+        return torch.as_tensor(_DeviceArray(), device=torch.device("cuda", torch.cuda.current_device()))
+
+    def status(self):
+        out = C.c_int(0)
+        _check(lib().ingot_kv_status(self.handle, _stream(), C.byref(out)))
+        return out.value
+
+    def import_f16(self, layer, k, v, pos0, block_table=None):
+        """k, v: [n_tok, n_head_kv, 128] f16 cuda tensors."""
+        assert k.is_contiguous() and v.is_contiguous() and _dtype_code(k) == F16 and _dtype_code(v) == F16
+        _check(lib().ingot_kv_import_f16(self.handle, layer, _ptr(k), _ptr(v), pos0, k.shape[0], _ptr(block_table), _stream()))
+
+
+def rope_kv_append(kv, layer, q, k, v, inv_freq, pos0=0, positions=None, seq_ids=None, block_tables=None):
+    """q [n,H,128] f32 or None; k, v [n,Hkv,128] f32. Returns rotated q as f16 (or None)."""
+    import torch
+    n_tok = k.shape[0]
+    q_out = None
+    n_head = kv.n_head_kv
+    if q is not None:
+        assert q.is_contiguous() and q.dtype == torch.float32
+        n_head = q.shape[1]
+        q_out = torch.empty(q.shape, dtype=torch.float16, device=q.device)
+    assert k.is_contiguous() and v.is_contiguous() and k.dtype == torch.float32 and v.dtype == torch.float32
+    mb = 0 if block_tables is None else block_tables.shape[-1]
+    _check(lib().ingot_rope_kv_append(kv.handle, layer, _ptr(q), _ptr(q_out), _ptr(k), _ptr(v), _ptr(inv_freq), n_head,
+                                      pos0, n_tok, _ptr(positions), _ptr(seq_ids), _ptr(block_tables), mb, _stream()))
+    return q_out
+
+
+def attn_decode(kv, layer, q, out=None, out_dtype=None, seq_lens=None, max_seq_len=None, block_tables=None,
+                chunk_keys=0):
+    """q [n_seq,H,128]; returns out [n_seq,H,128] (f32 unless out_dtype given)."""
+    import torch
+    assert q.is_contiguous()
+    n_seq, n_head = q.shape[0], q.shape[1]
+    if out is None:
+        out = torch.empty(q.shape, dtype=out_dtype or torch.float32, device=q.device)
+    mb = 0 if block_tables is None else block_tables.shape[-1]
+    _check(lib().ingot_attn_decode(kv.handle, layer, _ptr(q), _dtype_code(q), _ptr(out), _dtype_code(out), n_head, n_seq,
+                                   _ptr(seq_lens), int(max_seq_len), _ptr(block_tables), mb, chunk_keys, _stream()))
+    return out
+
+
+def attn_prefill(kv, layer, q, q_pos0, out=None, out_dtype=None, block_table=None, impl=0):
+    """q [n_tok,H,128]; returns out [n_tok,H,128]."""
+    import torch
+    assert q.is_contiguous()
+    n_tok, n_head = q.shape[0], q.shape[1]
+    if out is None:
+        out = torch.empty(q.shape, dtype=out_dtype or torch.float32, device=q.device)
+    _check(lib().ingot_attn_prefill(kv.handle, layer, _ptr(q), _dtype_code(q), _ptr(out), _dtype_code(out), n_head,
+                                    q_pos0, n_tok, _ptr(block_table), impl, _stream()))
+    return out
+
+
+def attn_layer_host(kv, layer, q_host, k_host, v_host, out_host, inv_freq_dev, pos0):
+    """Pinned host tensors in/out; asynchronous on the current stream."""
+    n_tok, n_head = q_host.shape[0], q_host.shape[1]
+    _check(lib().ingot_attn_layer_host(kv.handle, layer, _ptr(q_host), _ptr(k_host), _ptr(v_host), _ptr(out_host),
+                                       _ptr(inv_freq_dev), n_head, pos0, n_tok, _stream()))

@@ -1,0 +1,125 @@
+"""K2 (causal GQA flash-attention prefill / chunked prefill) against the CPU reference."""
+import numpy as np
+import pytest
+
+import helpers
+from helpers import D, H, HKV
+from ingot_b200 import workloads as W
+
+pytestmark = pytest.mark.gpu
+
+IMPLS = [1, 2]  # 1 = warp-MMA kernel, 2 = tcgen05/TMEM/TMA kernel
+
+
+@pytest.mark.parametrize("impl", IMPLS)
+def test_c1_prefill_128(impl):
+    wl = W.c1_prefill128()
+    want, q_rot, _ = helpers.oracle_prefill(wl)
+    out, _, _ = helpers.gpu_prefill(wl, impl=impl)
+    helpers.assert_parity(out.cpu().numpy(), want, f"C1 prefill 128 impl={impl}")
+
+
+@pytest.mark.parametrize("impl", IMPLS)
+def test_c3_chunked_prefill(impl):
+    wl = W.c3_chunked()
+    want, _, _ = helpers.oracle_prefill(wl)
+    out, _, _ = helpers.gpu_prefill(wl, impl=impl)
+    helpers.assert_parity(out.cpu().numpy(), want, f"C3 chunked prefill impl={impl}")
+
+
+@pytest.mark.parametrize("impl", IMPLS)
+@pytest.mark.parametrize("n_tok,pos0", [(1, 0), (2, 0), (7, 0), (43, 0), (85, 0), (86, 0), (100, 3), (129, 0), (300, 77), (64, 1000)])
+def test_prefill_ragged_shapes(impl, n_tok, pos0):
+    rng = np.random.default_rng(n_tok * 31 + pos0)
+    q = rng.standard_normal((n_tok, H, D), dtype=np.float32)
+    k = rng.standard_normal((n_tok, HKV, D), dtype=np.float32)
+    v = rng.standard_normal((n_tok, HKV, D), dtype=np.float32)
+    ck = cv = None
+    if pos0:
+        ck = rng.standard_normal((pos0, HKV, D), dtype=np.float32).astype(np.float16)
+        cv = rng.standard_normal((pos0, HKV, D), dtype=np.float32).astype(np.float16)
+    wl = W.Prefill(q, k, v, pos0, True, ck, cv)
+    want, _, _ = helpers.oracle_prefill(wl)
+    out, _, _ = helpers.gpu_prefill(wl, impl=impl)
+    helpers.assert_parity(out.cpu().numpy(), want, f"prefill n_tok={n_tok} pos0={pos0} impl={impl}")
+
+
+@pytest.mark.parametrize("impl", IMPLS)
+def test_prefill_first_row_is_v0(impl):
+    """Token 0 sees only key 0, so its output is v[0] rounded to f16, for every head of the group."""
+    wl = W.c1_prefill128(seed=9, n_tok=40)
+    out, _, _ = helpers.gpu_prefill(wl, impl=impl)
+    got = out.cpu().numpy()[0].reshape(HKV, H // HKV, D)
+    want = wl.v[0].astype(np.float16).astype(np.float32)
+    for g in range(H // HKV):
+        assert np.array_equal(got[:, g, :], want)
+
+
+@pytest.mark.parametrize("n_head,n_head_kv", [(8, 8), (16, 8), (32, 8), (4, 1)])
+def test_prefill_group_sizes(n_head, n_head_kv):
+    rng = np.random.default_rng(n_head)
+    n_tok = 150
+    wl = W.Prefill(rng.standard_normal((n_tok, n_head, D), dtype=np.float32),
+                   rng.standard_normal((n_tok, n_head_kv, D), dtype=np.float32),
+                   rng.standard_normal((n_tok, n_head_kv, D), dtype=np.float32), 0, True)
+    want, _, _ = helpers.oracle_prefill(wl)
+    out, _, _ = helpers.gpu_prefill(wl, impl=1)
+    helpers.assert_parity(out.cpu().numpy(), want, f"prefill H={n_head} Hkv={n_head_kv}")
+
+
+def test_prefill_paged_equals_contiguous():
+    import torch
+    wl = W.c1_prefill128(seed=21, n_tok=200)
+    out_c, _, _ = helpers.gpu_prefill(wl, impl=1)
+    out_p, _, _ = helpers.gpu_prefill(wl, impl=1, paged=True)
+    assert torch.equal(out_c, out_p)
+
+
+@pytest.mark.parametrize("impl", IMPLS)
+def test_chunked_equals_one_shot(impl):
+    """Prefilling 384 tokens in chunks of 128 matches one 384-token prefill row for row."""
+    import torch
+    import ingot_b200 as ib
+    wl = W.c1_prefill128(seed=22, n_tok=384)
+    out_full, _, _ = helpers.gpu_prefill(wl, impl=impl)
+    kv = ib.KVCache(ib.KV_CONTIGUOUS, 1, HKV, 384)
+    inv = helpers.to_dev(helpers.inv_freq())
+    outs = []
+    for c in range(3):
+        sl = slice(c * 128, (c + 1) * 128)
+        qr = ib.rope_kv_append(kv, 0, helpers.to_dev(wl.q[sl]), helpers.to_dev(wl.k[sl]), helpers.to_dev(wl.v[sl]), inv, c * 128)
+        outs.append(ib.attn_prefill(kv, 0, qr, c * 128, impl=impl))
+    torch.cuda.synchronize()
+    got = torch.cat(outs).cpu().numpy()
+    max_abs, rel = helpers.errors(got, out_full.cpu().numpy())
+    assert max_abs <= 1e-5 and rel <= 1e-6, (max_abs, rel)
+
+
+@pytest.mark.parametrize("impl", IMPLS)
+def test_c5_long_prefill_sampled_rows(impl):
+    """32768-token causal prefill (bf16 q, f16 k/v). The reference is evaluated on a stratified row
+    sample (first rows, last rows, random rows); every sampled row must meet the tolerance."""
+    import torch
+    wl = W.c5_prefill32k()
+    rng = np.random.default_rng(44)
+    rows = np.unique(np.concatenate([np.arange(16), np.arange(32768 - 16, 32768), rng.integers(0, 32768, 32)]))
+    want, _, _ = helpers.oracle_prefill(wl, rows=rows)
+    out, _, _ = helpers.gpu_prefill(wl, impl=impl, out_f16=True)
+    got = out[torch.from_numpy(rows).cuda()].float().cpu().numpy()
+    assert np.isfinite(got).all()
+    max_abs, rel = helpers.errors(got, want)
+    # f16 output adds half an f16 ulp of the value (|out| < 8 -> 2e-3 at most, typically 1e-4).
+    assert max_abs <= 2e-3 + 2e-3 and rel <= 1e-3, (max_abs, rel)
+    # size-independent property: no row of the full output is non-finite, row 0 equals v[0]
+    assert torch.isfinite(out).all().item()
+    assert np.array_equal(out[0].float().cpu().numpy().reshape(HKV, 3, D)[:, 0], wl.v[0].astype(np.float32))
+
+
+def test_prefill_rejects_bad_arguments():
+    import ingot_b200 as ib
+    kv = ib.KVCache(ib.KV_CONTIGUOUS, 1, HKV, 64)
+    q = helpers.to_dev(np.zeros((8, H, D), dtype=np.float16))
+    with pytest.raises(ib.IngotError, match="context window exceeded"):
+        ib.attn_prefill(kv, 0, q, 60)
+    with pytest.raises(ib.IngotError, match="multiple of n_head_kv"):
+        ib.attn_prefill(kv, 0, helpers.to_dev(np.zeros((8, 7, D), dtype=np.float16)), 0)
