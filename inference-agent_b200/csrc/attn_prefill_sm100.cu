@@ -1,6 +1,529 @@
+// K2 (tcgen05 form) — causal GQA flash-attention prefill / chunked prefill for sm_100a:
+// TMA-staged K/V tiles, tcgen05.mma with accumulators in tensor memory, online softmax.
+//
+// Replaces n_tok iterations of the CPU reference's attention lambda (src/backend.h:16-20 looping
+// src/cpu_backend.cpp:51-69) and Metal's attn_prefill (shaders/kernels.metal:518-633) for long
+// prefills on a contiguous cache. Query token i sits at position q_pos0 + i and sees keys
+// 0..q_pos0+i (kernels.metal:555,578).
+//
+// Work decomposition. One CTA = one KV head x 256 query ROWS (two 128-row tiles). A row is a
+// (token, query head of the GQA group) pair: row R -> token R / G, head R % G, so the G query heads
+// that share the KV head sit in the M dimension of the MMAs and every staged K/V tile serves all of
+// them. The CTA walks the keys in tiles of 128.
+//
+// Roles (12 warps, one CTA per SM):
+//   warp 0       TMA producer: K_j and V_j tiles ([128 keys][128 dims] f16 = 32 KB, as two
+//                128-byte-swizzled boxes of 64 dims) into a 4-slot shared-memory ring.
+//   warp 1       MMA issuer (one elected thread): S_q = Q_q K_j^T (SS MMA, 128x128x128) and
+//                O_q += P_q V_j (A operand = P from tensor memory, B = V tile, MN-major).
+//   warps 4-7    softmax for Q tile 0; warps 8-11 for Q tile 1: one thread per row. tcgen05.ld the
+//                128 scores of the row, running max / sum in the exp2 domain, P = exp2(..) rounded to
+//                f16 and stored over the first 64 columns of the same S region (tcgen05.st).
+//                The O accumulator is rescaled only when the running max grew by more than 2^8
+//                (P <= 256 stays exact enough in f16; l and O carry the same reference max).
+// Tensor memory (512 columns): S0 [0,128) S1 [128,256) O0 [256,384) O1 [384,512); P_q aliases S_q.
+// The tensor pipe executes one thread's MMAs in issue order, which is what makes the aliasing safe:
+//   QK(0,0) QK(1,0) | PV(0,j) QK(0,j+1) PV(1,j) QK(1,j+1) | ...
+// so while the softmax warps of one tile work, the tensor pipe runs the other tile's MMAs.
+//
+// Every mbarrier wait is bounded (wall-clock limit): on expiry the CTA raises a bit in the cache's
+// status word, every role leaves its loop, outstanding TMA copies are drained with a bounded wait
+// and tensor memory is released before the CTA exits.
+#include "attn_common.cuh"
 #include "ingot_internal.cuh"
-int launch_attn_prefill_sm100(ingot_kv*, int, const void*, int, void*, int, int, int, int, cudaStream_t) {
-    ingot_set_error("tcgen05 prefill not built yet");
-    return INGOT_ERR_UNSUPPORTED;
+
+#include <mutex>
+#include <vector>
+
+namespace {
+
+constexpr int kTileRows = 128;        // rows per Q tile (= TMEM lanes)
+constexpr int kTileKeys = 128;        // keys per K/V tile
+constexpr int kStages = 4;            // K/V ring slots
+constexpr int kStageBytes = kTileKeys * kHeadDim * 2;   // 32 KB
+constexpr int kHalfBytes = kStageBytes / 2;             // one 64-dim box
+constexpr int kQBytes = kTileRows * kHeadDim * 2;       // 32 KB per Q tile
+constexpr int kThreads = 384;
+constexpr uint32_t kTmemCols = 512;
+constexpr float kRescaleThreshold = 8.0f;  // log2 units
+
+// shared memory map (dynamic, 1024-byte aligned base)
+constexpr int kOffQ = 0;                                  // 2 Q tiles
+constexpr int kOffKV = 2 * kQBytes;                       // ring
+constexpr int kOffBar = kOffKV + kStages * kStageBytes;   // barriers
+constexpr int kSmemBytes = kOffBar + 256 + 1024;          // + alignment slack
+
+struct Bars {
+    uint64_t kv_full[kStages];
+    uint64_t kv_empty[kStages];
+    uint64_t q_ready;
+    uint64_t s_ready[2];
+    uint64_t p_ready[2];
+    uint64_t o_final[2];
+    uint32_t tmem_base;
+    uint32_t abort_flag;
+};
+
+struct Sm100Params {
+    const void* q;
+    void* out;
+    int* status;
+    int q_dtype, out_dtype;
+    int n_head, group;
+    int q_pos0, n_tok;
+    float scale_log2;
+};
+
+// ---- PTX wrappers ---------------------------------------------------------------------------
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
 }
-void free_prefill_sm100_state(ingot_kv*) {}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ uint64_t globaltimer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+
+// Bounded wait: returns false (and raises the CTA's abort flag) if the barrier does not complete
+// within ~2 s or another role already aborted.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t t0 = globaltimer_ns();
+    for (uint32_t spins = 1;; spins++) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((spins & 63u) == 0) {
+            if (*abort_flag) return false;
+            if (globaltimer_ns() - t0 > 2000000000ull) {
+                *abort_flag = 1;
+                return false;
+            }
+        }
+    }
+}
+
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int x, int y, int z, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+// D[tmem] (+)= A[smem desc] * B[smem desc]
+__device__ __forceinline__ void tc_mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t acc) {
+    asm volatile(
+        "{\n.reg .pred p;\nsetp.ne.u32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(acc) : "memory");
+}
+// D[tmem] (+)= A[tmem] * B[smem desc]
+__device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t acc) {
+    asm volatile(
+        "{\n.reg .pred p;\nsetp.ne.u32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(acc) : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
+    uint32_t* r = reinterpret_cast<uint32_t*>(v);
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+          "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
+          "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
+          "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// Shared-memory matrix descriptor, 128-byte swizzle, descriptor version 1 (sm_100).
+// lbo/sbo in bytes: K-major operands use sbo = 1024 (eight 128-byte rows) and ignore lbo;
+// MN-major operands use lbo = distance between 64-element column blocks, sbo = 1024.
+__device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr, uint32_t lbo, uint32_t sbo) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);
+    d |= (uint64_t)((lbo >> 4) & 0x3FFF) << 16;
+    d |= (uint64_t)((sbo >> 4) & 0x3FFF) << 32;
+    d |= (uint64_t)1 << 46;  // descriptor version
+    d |= (uint64_t)2 << 61;  // SWIZZLE_128B
+    return d;
+}
+
+// Instruction descriptor, kind::f16: f16 A and B, f32 accumulate, M = 128, N = 128.
+constexpr uint32_t kIdescBase = (1u << 4) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
+constexpr uint32_t kIdescQK = kIdescBase;               // A K-major, B K-major
+constexpr uint32_t kIdescPV = kIdescBase | (1u << 16);  // B (= V) MN-major
+
+__global__ void __launch_bounds__(kThreads, 1)
+attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                          const Sm100Params p) {
+    extern __shared__ unsigned char smem_dyn[];
+    const uint32_t smem_base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
+    unsigned char* smem_al = smem_dyn + (smem_base - smem_u32(smem_dyn));
+    Bars* bars = reinterpret_cast<Bars*>(smem_al + kOffBar);
+    volatile uint32_t* abort_flag = &bars->abort_flag;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int G = p.group;
+    const int kvh = blockIdx.y;
+    const int n_rows = p.n_tok * G;
+    const int tile256 = gridDim.x - 1 - blockIdx.x;  // heavier (later) tiles first
+    const int row_base = tile256 * 2 * kTileRows;
+    const int last_row = min(row_base + 2 * kTileRows, n_rows) - 1;
+    const int n_kv = (p.q_pos0 + last_row / G + 1 + kTileKeys - 1) / kTileKeys;  // K/V tiles this CTA walks
+
+    auto bar_addr = [&](const uint64_t* b) { return smem_u32(b); };
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; s++) { mbar_init(bar_addr(&bars->kv_full[s]), 1); mbar_init(bar_addr(&bars->kv_empty[s]), 1); }
+        mbar_init(bar_addr(&bars->q_ready), 256);
+        for (int q = 0; q < 2; q++) {
+            mbar_init(bar_addr(&bars->s_ready[q]), 1);
+            mbar_init(bar_addr(&bars->p_ready[q]), 128);
+            mbar_init(bar_addr(&bars->o_final[q]), 1);
+        }
+        bars->abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&bars->tmem_base)), "r"(kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = bars->tmem_base;
+
+    if (warp < 4) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+        if (warp == 0 && lane == 0) {
+            // ---------------- TMA producer ----------------
+            int armed = 0;  // ring slots handed to TMA so far
+            bool ok = true;
+            for (int it = 0; it < 2 * n_kv && ok; it++) {
+                const int s = it % kStages;
+                const uint32_t par = (uint32_t)((it / kStages) & 1);
+                ok = mbar_wait(bar_addr(&bars->kv_empty[s]), par ^ 1u, abort_flag);
+                if (!ok) break;
+                const uint32_t full = bar_addr(&bars->kv_full[s]);
+                const uint32_t dst = smem_base + kOffKV + s * kStageBytes;
+                const CUtensorMap* map = (it & 1) ? &map_v : &map_k;
+                const int key0 = (it >> 1) * kTileKeys;
+                mbar_expect_tx(full, kStageBytes);
+                tma_load_3d(dst, map, 0, key0, kvh, full);
+                tma_load_3d(dst + kHalfBytes, map, 64, key0, kvh, full);
+                armed = it + 1;
+            }
+            if (!ok) {
+                // Drain: copies already issued must land before the CTA's shared memory is released.
+                for (int it = max(0, armed - kStages); it < armed; it++) {
+                    const uint64_t t0 = globaltimer_ns();
+                    const uint32_t full = bar_addr(&bars->kv_full[it % kStages]);
+                    while (!mbar_try_wait(full, (uint32_t)((it / kStages) & 1)) && globaltimer_ns() - t0 < 100000000ull) {}
+                }
+            }
+        } else if (warp == 1 && lane == 0) {
+            // ---------------- MMA issuer ----------------
+            const uint32_t q_addr[2] = {smem_base + kOffQ, smem_base + kOffQ + kQBytes};
+            const uint32_t s_tmem[2] = {tmem + 0, tmem + 128};
+            const uint32_t o_tmem[2] = {tmem + 256, tmem + 384};
+            auto stage_addr = [&](int it) { return smem_base + kOffKV + (it % kStages) * kStageBytes; };
+            auto wait_full = [&](int it) {
+                return mbar_wait(bar_addr(&bars->kv_full[it % kStages]), (uint32_t)((it / kStages) & 1), abort_flag);
+            };
+            auto release = [&](int it) { tc_commit(bar_addr(&bars->kv_empty[it % kStages])); };
+            // S_q = Q_q K^T : 8 k-steps of 16 dims; dims 0-63 in the first 16 KB box, 64-127 in the second.
+            auto issue_qk = [&](int q, uint32_t k_addr) {
+#pragma unroll
+                for (int ks = 0; ks < 8; ks++) {
+                    const uint32_t off = (ks >> 2) * kHalfBytes + (ks & 3) * 32;
+                    tc_mma_ss(s_tmem[q], make_desc(q_addr[q] + off, 16, 1024), make_desc(k_addr + off, 16, 1024), kIdescQK, ks > 0);
+                }
+                tc_commit(bar_addr(&bars->s_ready[q]));
+            };
+            // O_q += P_q V : 8 k-steps of 16 keys; P packed f16 in TMEM (8 columns per step);
+            // V rows are 128-byte swizzled, 16 keys = 2048 B further per step, dims 64-127 one box further.
+            auto issue_pv = [&](int q, uint32_t v_addr, bool first) {
+#pragma unroll
+                for (int ks = 0; ks < 8; ks++)
+                    tc_mma_ts(o_tmem[q], s_tmem[q] + ks * 8, make_desc(v_addr + ks * 2048, kHalfBytes, 1024), kIdescPV,
+                              (!first || ks > 0) ? 1u : 0u);
+            };
+            bool ok = mbar_wait(bar_addr(&bars->q_ready), 0, abort_flag);
+            ok = ok && wait_full(0);
+            if (ok) {
+                tc_fence_after();
+                issue_qk(0, stage_addr(0));
+                issue_qk(1, stage_addr(0));
+                release(0);
+            }
+            for (int j = 0; j < n_kv && ok; j++) {
+                const int it_v = 2 * j + 1, it_k = 2 * j + 2;
+                const bool more = j + 1 < n_kv;
+                ok = wait_full(it_v) && (!more || wait_full(it_k));
+                for (int q = 0; q < 2 && ok; q++) {
+                    ok = mbar_wait(bar_addr(&bars->p_ready[q]), (uint32_t)(j & 1), abort_flag);
+                    if (!ok) break;
+                    tc_fence_after();
+                    issue_pv(q, stage_addr(it_v), j == 0);
+                    if (q == 1) release(it_v);
+                    if (more) {
+                        issue_qk(q, stage_addr(it_k));
+                        if (q == 1) release(it_k);
+                    } else {
+                        tc_commit(bar_addr(&bars->o_final[q]));
+                    }
+                }
+            }
+        }
+    } else {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
+        // ---------------- softmax warps: one thread per query row ----------------
+        const int q = (warp - 4) >> 2;              // Q tile 0 or 1
+        const int row_in_tile = ((warp & 3) << 5) | lane;
+        const int R = row_base + q * kTileRows + row_in_tile;
+        const bool valid = R < n_rows;
+        const int tok = valid ? R / G : 0;
+        const int head = kvh * G + (valid ? R % G : 0);
+        const int qpos = valid ? p.q_pos0 + tok : 0x3fffffff;  // rows past the end are never masked
+        const uint32_t lane_sel = (uint32_t)((warp & 3) << 5) << 16;
+        const uint32_t s_tmem = tmem + q * 128 + lane_sel;
+        const uint32_t o_tmem = tmem + 256 + q * 128 + lane_sel;
+
+        // Stage this row of Q into the 128-byte-swizzled K-major layout the MMA descriptor expects:
+        // 16-byte chunk c of row r lands at r*128 + ((c & 7) ^ (r & 7))*16 in the box of dims (c>>3)*64.
+        {
+            unsigned char* qdst = smem_al + kOffQ + q * kQBytes + row_in_tile * 128;
+            const size_t qbase = ((size_t)tok * p.n_head + head) * kHeadDim;
+#pragma unroll
+            for (int c = 0; c < 16; c++) {
+                const uint4 val = valid ? load_q8(p.q, p.q_dtype, qbase + c * 8) : make_uint4(0, 0, 0, 0);
+                *reinterpret_cast<uint4*>(qdst + (c >> 3) * kHalfBytes + (((c & 7) ^ (row_in_tile & 7)) << 4)) = val;
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy stores -> async proxy (MMA)
+            mbar_arrive(bar_addr(&bars->q_ready));
+        }
+
+        float m_ref = 0.f, l = 0.f;
+        bool ok = true;
+        const int qpos_warp_min = __shfl_sync(0xffffffffu, qpos, 0);  // rows ascend with the lane
+        for (int j = 0; j < n_kv; j++) {
+            ok = mbar_wait(bar_addr(&bars->s_ready[q]), (uint32_t)(j & 1), abort_flag);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after();
+            float s[128];
+#pragma unroll
+            for (int c = 0; c < 4; c++) tmem_ld32(s_tmem + c * 32, *reinterpret_cast<float(*)[32]>(&s[c * 32]));
+            tmem_wait_ld();
+
+            const int key0 = j * kTileKeys;
+            if (key0 + kTileKeys - 1 > qpos_warp_min) {  // warp-uniform: some row of this warp needs the mask
+                const int limit = qpos - key0;           // columns > limit are in the future
+#pragma unroll
+                for (int i = 0; i < 128; i++) s[i] = i <= limit ? s[i] : -INFINITY;
+            }
+            float mx = s[0];
+#pragma unroll
+            for (int i = 1; i < 128; i++) mx = fmaxf(mx, s[i]);
+            mx *= p.scale_log2;  // scale > 0: max commutes with the scaling
+
+            // Lazy rescale: keep the old reference max unless the new one is more than 2^8 above it.
+            bool grow = j == 0 || mx > m_ref + kRescaleThreshold;
+            if (j == 0) {
+                m_ref = mx;  // key 0 is visible to every row, so this is finite
+            } else if (__any_sync(0xffffffffu, grow)) {
+                const float alpha = grow ? ex2(m_ref - mx) : 1.0f;
+                if (grow) { m_ref = mx; l *= alpha; }
+#pragma unroll
+                for (int c = 0; c < 4; c++) {
+                    float o[32];
+                    tmem_ld32(o_tmem + c * 32, o);
+                    tmem_wait_ld();
+                    uint32_t ob[32];
+#pragma unroll
+                    for (int i = 0; i < 32; i++) ob[i] = __float_as_uint(o[i] * alpha);
+                    tmem_st32(o_tmem + c * 32, ob);
+                }
+            }
+            const float neg_m = -m_ref;
+            float sum = 0.f;
+#pragma unroll
+            for (int c = 0; c < 2; c++) {
+                uint32_t pk[32];
+#pragma unroll
+                for (int i = 0; i < 32; i++) {
+                    const float p0 = ex2(fmaf(s[c * 64 + 2 * i], p.scale_log2, neg_m));
+                    const float p1 = ex2(fmaf(s[c * 64 + 2 * i + 1], p.scale_log2, neg_m));
+                    sum += p0 + p1;
+                    pk[i] = pack_half2_rn(p0, p1);
+                }
+                tmem_st32(s_tmem + c * 32, pk);
+            }
+            l += sum;
+            tmem_wait_st();
+            tc_fence_before();
+            mbar_arrive(bar_addr(&bars->p_ready[q]));
+        }
+
+        // ---------------- epilogue: O / l -> global ----------------
+        if (ok) {
+            ok = mbar_wait(bar_addr(&bars->o_final[q]), 0, abort_flag);
+            ok = __all_sync(0xffffffffu, ok);
+        }
+        if (ok) {
+            tc_fence_after();
+            const float inv = 1.0f / l;
+            const size_t obase = ((size_t)tok * p.n_head + head) * kHeadDim;
+#pragma unroll
+            for (int c = 0; c < 4; c++) {
+                float o[32];
+                tmem_ld32(o_tmem + c * 32, o);
+                tmem_wait_ld();
+                if (valid) {
+                    if (p.out_dtype == INGOT_F32) {
+                        float4* dst = reinterpret_cast<float4*>(static_cast<float*>(p.out) + obase + c * 32);
+#pragma unroll
+                        for (int i = 0; i < 8; i++)
+                            dst[i] = make_float4(o[4 * i] * inv, o[4 * i + 1] * inv, o[4 * i + 2] * inv, o[4 * i + 3] * inv);
+                    } else {
+                        uint4* dst = reinterpret_cast<uint4*>(static_cast<__half*>(p.out) + obase + c * 32);
+#pragma unroll
+                        for (int i = 0; i < 4; i++)
+                            dst[i] = make_uint4(pack_half2_rn(o[8 * i] * inv, o[8 * i + 1] * inv),
+                                                pack_half2_rn(o[8 * i + 2] * inv, o[8 * i + 3] * inv),
+                                                pack_half2_rn(o[8 * i + 4] * inv, o[8 * i + 5] * inv),
+                                                pack_half2_rn(o[8 * i + 6] * inv, o[8 * i + 7] * inv));
+                    }
+                }
+            }
+        }
+    }
+
+    // ---------------- teardown ----------------
+    tc_fence_before();
+    __syncthreads();
+    if (threadIdx.x == 0 && *abort_flag) atomicOr(p.status, kDevErrBarrierTimeout);
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
+    }
+}
+
+// ---- host side: tensor maps -------------------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(sym);
+    });
+    return fn;
+}
+
+struct Sm100State {
+    std::vector<CUtensorMap> maps;  // [layer][K/V]
+    std::vector<char> built;
+};
+
+}  // namespace
+
+void free_prefill_sm100_state(ingot_kv* kv) {
+    delete static_cast<Sm100State*>(kv->tmaps);
+    kv->tmaps = nullptr;
+}
+
+int launch_attn_prefill_sm100(ingot_kv* kv, int layer, const void* q, int q_dtype, void* out, int out_dtype,
+                              int n_head, int q_pos0, int n_tok, cudaStream_t stream) {
+    if (kv->layout != INGOT_KV_CONTIGUOUS) {
+        ingot_set_error("tcgen05 prefill: contiguous cache required");
+        return INGOT_ERR_UNSUPPORTED;
+    }
+    EncodeTiledFn encode = get_encode_fn();
+    if (!encode) {
+        ingot_set_error("tcgen05 prefill: cuTensorMapEncodeTiled is not available from the driver");
+        return INGOT_ERR_CUDA;
+    }
+    if (!kv->tmaps) {
+        Sm100State* st = new Sm100State();
+        st->maps.resize(size_t(kv->n_layer) * 2);
+        st->built.assign(kv->n_layer, 0);
+        kv->tmaps = st;
+    }
+    Sm100State* st = static_cast<Sm100State*>(kv->tmaps);
+    if (!st->built[layer]) {
+        for (int which = 0; which < 2; which++) {
+            __half* base = (which ? kv->v : kv->k) + size_t(layer) * kv->layer_elems;
+            // [head][position][dim] f16, dim fastest; box = 64 dims x 128 positions x 1 head, 128-byte swizzle.
+            cuuint64_t dims[3] = {cuuint64_t(kHeadDim), cuuint64_t(kv->capacity), cuuint64_t(kv->n_head_kv)};
+            cuuint64_t strides[2] = {cuuint64_t(kHeadDim) * 2, cuuint64_t(kv->capacity) * kHeadDim * 2};
+            cuuint32_t box[3] = {64, cuuint32_t(kTileKeys), 1};
+            cuuint32_t estr[3] = {1, 1, 1};
+            CUresult r = encode(&st->maps[size_t(layer) * 2 + which], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, base, dims, strides,
+                                box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+            if (r != CUDA_SUCCESS) {
+                ingot_set_error("tcgen05 prefill: cuTensorMapEncodeTiled failed with CUresult " + std::to_string(int(r)));
+                return INGOT_ERR_CUDA;
+            }
+        }
+        st->built[layer] = 1;
+    }
+    Sm100Params p;
+    p.q = q; p.out = out; p.status = kv->status_dev;
+    p.q_dtype = q_dtype; p.out_dtype = out_dtype;
+    p.n_head = n_head; p.group = n_head / kv->n_head_kv;
+    p.q_pos0 = q_pos0; p.n_tok = n_tok;
+    p.scale_log2 = 1.4426950408889634f / sqrtf(float(kHeadDim));
+    INGOT_CUDA_TRY(cudaFuncSetAttribute(attn_prefill_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+    const long long n_rows = (long long)n_tok * p.group;
+    dim3 grid(unsigned((n_rows + 2 * kTileRows - 1) / (2 * kTileRows)), kv->n_head_kv);
+    attn_prefill_sm100_kernel<<<grid, kThreads, kSmemBytes, stream>>>(st->maps[size_t(layer) * 2], st->maps[size_t(layer) * 2 + 1], p);
+    INGOT_CUDA_TRY(cudaGetLastError());
+    return INGOT_OK;
+}
