@@ -110,6 +110,16 @@ int ingot_attn_decode(ingot_kv* kv, int layer, const void* q_dev, int q_dtype, v
                       int n_head, int n_seq, const int32_t* seq_lens_dev, int max_seq_len,
                       const int32_t* block_tables_dev, int max_blocks_per_seq, int chunk_keys, void* stream);
 
+/* The same for `layer_count` consecutive layers in one call, with the same lengths and block tables:
+ * q_dev [layer_count][n_seq][n_head][128], out_dev likewise. This is the shape of the reference's
+ * decode-attention microbenchmark, which encodes every layer's attention for one token into one
+ * command buffer (src/metal_backend.mm:594-649, src/main.cpp:441-449). The launches are chained with
+ * programmatic dependent launch: a layer's K/V loads overlap the previous layer's split merge. */
+int ingot_attn_decode_layers(ingot_kv* kv, int layer_begin, int layer_count, const void* q_dev, int q_dtype,
+                             void* out_dev, int out_dtype, int n_head, int n_seq, const int32_t* seq_lens_dev,
+                             int max_seq_len, const int32_t* block_tables_dev, int max_blocks_per_seq,
+                             int chunk_keys, void* stream);
+
 /* ---- K2: causal GQA flash-attention prefill / chunked prefill -----------------------------------
  * Replaces n_tok iterations of the attention lambda (src/backend.h:16-20 + src/cpu_backend.cpp:51-69)
  * and Metal's attn_prefill (shaders/kernels.metal:518-633; src/metal_backend.mm:361-372).
@@ -134,6 +144,12 @@ int ingot_attn_prefill(ingot_kv* kv, int layer, const void* q_dev, int q_dtype, 
 int ingot_attn_layer_host(ingot_kv* kv, int layer, const float* q_host, const float* k_host, const float* v_host,
                           float* out_host, const float* inv_freq_dev, int n_head, int pos0, int n_tok,
                           void* stream);
+/* The same for `layer_count` consecutive layers starting at `layer_begin` in one call, as the
+ * reference's attention microbenchmark drives its backend (every layer's attention for one step,
+ * src/metal_backend.mm:594-649): host arrays are [layer_count][n_tok][heads][128], one slice per layer. */
+int ingot_attn_layers_host(ingot_kv* kv, int layer_begin, int layer_count, const float* q_host, const float* k_host,
+                           const float* v_host, float* out_host, const float* inv_freq_dev, int n_head, int pos0,
+                           int n_tok, void* stream);
 int ingot_stream_sync(void* stream);
 
 #ifdef __cplusplus

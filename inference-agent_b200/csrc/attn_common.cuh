@@ -11,15 +11,6 @@ __device__ __forceinline__ uint4 ld_stream16(const void* p) {
     return r;
 }
 
-// D(rows 0-7 only) += A(rows 0-7 only) * B. Rows 8-15 of A are zero, so their outputs are scratch.
-__device__ __forceinline__ void mma_rows8(float& d0, float& d1, uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
-    float z0, z1;
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%10,%10};"
-        : "+f"(d0), "+f"(d1), "=f"(z0), "=f"(z1)
-        : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1), "f"(0.0f));
-}
-
 __device__ __forceinline__ uint32_t pack_half2_rn(float a, float b) {
     __half2 h = __floats2half2_rn(a, b);
     return *reinterpret_cast<uint32_t*>(&h);

@@ -2,15 +2,17 @@
 //
 // Replaces the attention lambda of the CPU reference for a single query token
 // (src/cpu_backend.cpp:51-69) and Metal's attn_decode_g3 + attn_combine pair
-// (shaders/kernels.metal:428-516, dispatch src/metal_backend.mm:340-360) with ONE launch.
+// (shaders/kernels.metal:428-516, dispatch src/metal_backend.mm:340-360).
 //
 // Work decomposition. grid = (splits, kv heads, sequences). A CTA owns one KV head of one sequence
 // over one split of `chunk_keys` keys and serves ALL query heads that share that KV head (GQA), so
 // every K/V byte is fetched from HBM exactly once. Inside the CTA each warp walks its own 16-key
 // units with a private online-softmax state (m, l, o); the warp states are merged through shared
-// memory, the split's partial (o[128], m, l per head) goes to a global scratch, and the last CTA
-// of a (sequence, kv head) to arrive — found with an atomic ticket, nobody waits — merges the
-// partials: out = sum_s o_s 2^(m_s-M) / sum_s l_s 2^(m_s-M), the attn_combine formula.
+// memory and the split's partial (o[128], m, l per head) goes to a global scratch. A small combine
+// kernel chained behind it with programmatic dependent launch merges the partials:
+// out = sum_s o_s 2^(m_s-M) / sum_s l_s 2^(m_s-M), the attn_combine formula. Split CTAs therefore
+// retire as soon as their partial is written (no fence, ticket or polling), and the combine of one
+// launch overlaps the K/V loads of the next.
 //
 // Data path. HBM-bound: 2 * len * 128 * 2 B per (sequence, kv head). Every lane issues 16-byte
 // loads straight from global memory into registers, 16 of them (one whole 16-key unit, 8 KB per
@@ -37,21 +39,156 @@ struct DecodeParams {
     void* out;
     const int32_t* seq_lens;
     const int32_t* block_tables;
-    float* part;
-    unsigned int* counters;
+    float* part;          // split role: partials written here
+    const float* c_part;  // combine role: partials of the launch being merged
+    void* c_out;          // combine role: its output
     int* status;
     int q_dtype, out_dtype;
     int n_head, n_head_kv, group;
     int capacity, paged, max_blocks_per_seq;
     int len0, chunk_keys, n_parts_max;
+    int early_loads;  // the K/V rows and q read here are not written by the preceding kernel in the stream
+    int split_parts;  // grid.x values below this are split CTAs; the one CTA above it (if any) merges
     float scale_log2;
 };
+
+// Merges the splits of one (sequence, kv head): out = sum_s o_s 2^(m_s-M) / sum_s l_s 2^(m_s-M)
+// (the attn_combine formula, shaders/kernels.metal:502-516). Runs in one extra CTA per (kv head,
+// sequence) of the launch that FOLLOWS the one that wrote the partials (or of a merge-only launch):
+// programmatic dependent launch orders it behind that launch, so no fences, tickets or polling are
+// involved, and the merge overlaps the K/V loads of the split CTAs it shares the grid with.
+__device__ __forceinline__ void combine_splits(const DecodeParams& p, float* smem, int kvh, int seq) {
+    const int n_keys = p.seq_lens ? p.seq_lens[seq] : p.len0;
+    if (n_keys < 1) return;
+    const int n_chunks = (n_keys + p.chunk_keys - 1) / p.chunk_keys;
+    if (n_chunks == 1) return;  // the split CTA wrote the final output itself
+    const int G = p.group;
+
+    // Parallel merge. A thread owns one (head, 4-dim column) pair for a strided subset of the splits
+    // ("slot"); all of its partial loads are independent and issued before anything waits on them, so
+    // the merge costs about one L2 round trip instead of one per split.
+    const int T = blockDim.x;
+    const int pairs = G * 32;                     // (head, float4 column) pairs
+    const int slots = max(1, T / pairs);          // threads per pair
+    const int pair = threadIdx.x % pairs, slot = threadIdx.x / pairs;
+    const bool active = slot < slots;
+    const int gi_t = pair >> 5, col = pair & 31;
+    const size_t step = (size_t)p.n_head * kPartStride;
+    const float* base = p.c_part + (((size_t)seq * p.n_parts_max) * p.n_head + (size_t)kvh * G) * kPartStride;
+    const float* my_rows = base + (size_t)gi_t * kPartStride + col * 4;
+
+    float* mg_m = smem;                       // [G][kMaxParts] split maxima, then weights
+    float* mg_l = mg_m + G * kMaxParts;       // [G][kMaxParts] split sums
+    float* mg_acc = mg_l + G * kMaxParts;     // [slots][pairs] float4 partial outputs
+
+    constexpr int kBatch = 16;
+    float4 v[kBatch];
+    if (active) {
+#pragma unroll
+        for (int u = 0; u < kBatch; u++) {
+            const int c = slot + u * slots;
+            if (c < n_chunks) v[u] = __ldcg(reinterpret_cast<const float4*>(my_rows + c * step));
+        }
+    }
+    for (int idx = threadIdx.x; idx < G * n_chunks; idx += T) {
+        const int gi = idx / n_chunks, c = idx - gi * n_chunks;
+        const float2 ml = __ldcg(reinterpret_cast<const float2*>(base + (size_t)gi * kPartStride + c * step + 128));
+        mg_m[gi * kMaxParts + c] = ml.x;
+        mg_l[gi * kMaxParts + c] = ml.y;
+    }
+    __syncthreads();
+    float w_mine[4];
+    {
+        // weight of split c for head gi: 2^(m_c - M), M = max over the head's splits
+        int k = 0;
+        for (int idx = threadIdx.x; idx < G * n_chunks; idx += T, k++) {
+            const int gi = idx / n_chunks;
+            float M = -INFINITY;
+            for (int c = 0; c < n_chunks; c++) M = fmaxf(M, mg_m[gi * kMaxParts + c]);
+            if (k < 4) w_mine[k] = exp2f(mg_m[gi * kMaxParts + (idx - gi * n_chunks)] - M);
+        }
+    }
+    __syncthreads();
+    {
+        int k = 0;
+        for (int idx = threadIdx.x; idx < G * n_chunks && k < 4; idx += T, k++) {
+            const int gi = idx / n_chunks;
+            mg_m[gi * kMaxParts + (idx - gi * n_chunks)] = w_mine[k];
+        }
+    }
+    __syncthreads();
+    if (active) {
+        const float* wrow = mg_m + gi_t * kMaxParts;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int u = 0; u < kBatch; u++) {
+            const int c = slot + u * slots;
+            if (c < n_chunks) {
+                const float w = wrow[c];
+                acc.x += v[u].x * w; acc.y += v[u].y * w; acc.z += v[u].z * w; acc.w += v[u].w * w;
+            }
+        }
+        for (int c = slot + kBatch * slots; c < n_chunks; c += slots) {  // only when n_chunks > 16 * slots
+            const float4 x = __ldcg(reinterpret_cast<const float4*>(my_rows + c * step));
+            const float w = wrow[c];
+            acc.x += x.x * w; acc.y += x.y * w; acc.z += x.z * w; acc.w += x.w * w;
+        }
+        reinterpret_cast<float4*>(mg_acc)[slot * pairs + pair] = acc;
+    }
+    // More (head, column) pairs than threads (large groups on a small CTA): remaining pairs, one slot.
+    for (int pr = T + threadIdx.x; pr < pairs; pr += T) {
+        const float* rows = base + (size_t)(pr >> 5) * kPartStride + (pr & 31) * 4;
+        const float* wrow = mg_m + (pr >> 5) * kMaxParts;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int c0 = 0; c0 < n_chunks; c0 += kBatch) {
+#pragma unroll
+            for (int u = 0; u < kBatch; u++)
+                if (c0 + u < n_chunks) v[u] = __ldcg(reinterpret_cast<const float4*>(rows + (c0 + u) * step));
+#pragma unroll
+            for (int u = 0; u < kBatch; u++)
+                if (c0 + u < n_chunks) {
+                    const float w = wrow[c0 + u];
+                    acc.x += v[u].x * w; acc.y += v[u].y * w; acc.z += v[u].z * w; acc.w += v[u].w * w;
+                }
+        }
+        reinterpret_cast<float4*>(mg_acc)[pr] = acc;  // slots == 1 here
+    }
+    __syncthreads();
+    for (int pr = threadIdx.x; pr < pairs; pr += T) {
+        const int gi = pr >> 5, cl = pr & 31;
+        float L = 0.f;
+        for (int c = 0; c < n_chunks; c++) L += mg_l[gi * kMaxParts + c] * mg_m[gi * kMaxParts + c];
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int sl_i = 0; sl_i < slots; sl_i++) {
+            const float4 x = reinterpret_cast<const float4*>(mg_acc)[sl_i * pairs + pr];
+            acc.x += x.x; acc.y += x.y; acc.z += x.z; acc.w += x.w;
+        }
+        const float inv = L > 0.f ? 1.0f / L : 0.f;
+        const size_t e = ((size_t)seq * p.n_head + (size_t)kvh * G + gi) * kHeadDim + cl * 4;
+        store_out(p.c_out, p.out_dtype, e + 0, acc.x * inv);
+        store_out(p.c_out, p.out_dtype, e + 1, acc.y * inv);
+        store_out(p.c_out, p.out_dtype, e + 2, acc.z * inv);
+        store_out(p.c_out, p.out_dtype, e + 3, acc.w * inv);
+    }
+}
 
 struct KRegs { uint4 k[8]; };  // [n-tile 0/1][i=0..3]: key (nt*8 + g), 16-byte chunk (4i + j)
 struct VRegs { uint4 v[8]; };  // [slot 0..3 -> keys 2j, 2j+1, 2j+8, 2j+9][chunk g / g+8]
 
 __global__ void __launch_bounds__(kMaxDecodeWarps * 32, 1) attn_decode_kernel(const DecodeParams p) {
     extern __shared__ float smem[];
+    // Programmatic dependent launch: let the next kernel in the stream start as soon as SM resources
+    // allow. Unless the caller vouches that nothing read here was written by the preceding kernel,
+    // wait for that kernel before the first global read; otherwise only before the first global write
+    // (the split scratch and the output are shared with it).
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    if ((int)blockIdx.x >= p.split_parts) {  // merge role: partials of the preceding launch
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        combine_splits(p, smem, blockIdx.y, blockIdx.z);
+        return;
+    }
+    if (!p.early_loads) asm volatile("griddepcontrol.wait;" ::: "memory");
+
     const int chunk = blockIdx.x, kvh = blockIdx.y, seq = blockIdx.z;
     const int n_keys = p.seq_lens ? p.seq_lens[seq] : p.len0;
     if (n_keys < 1) return;
@@ -65,17 +202,6 @@ __global__ void __launch_bounds__(kMaxDecodeWarps * 32, 1) attn_decode_kernel(co
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, j = lane & 3;
     const int G = p.group;
-
-    // Query fragments: head row g, chunks 4i + j.
-    uint4 qa[4];
-    if (g < G) {
-        const size_t qbase = ((size_t)seq * p.n_head + (size_t)kvh * G + g) * kHeadDim;
-#pragma unroll
-        for (int i = 0; i < 4; i++) qa[i] = load_q8(p.q, p.q_dtype, qbase + (size_t)(4 * i + j) * 8);
-    } else {
-#pragma unroll
-        for (int i = 0; i < 4; i++) qa[i] = make_uint4(0, 0, 0, 0);
-    }
 
     const int32_t* bt = p.paged ? p.block_tables + (size_t)seq * p.max_blocks_per_seq : nullptr;
 
@@ -112,6 +238,9 @@ __global__ void __launch_bounds__(kMaxDecodeWarps * 32, 1) attn_decode_kernel(co
         }
     };
 
+    uint4 qa[4];
+#pragma unroll
+    for (int i = 0; i < 4; i++) qa[i] = make_uint4(0, 0, 0, 0);
     float m = -INFINITY, l = 0.f;
     // O^T accumulators: o[t] = {O[2j][8g+t], O[2j+1][8g+t], O[2j][64+8g+t], O[2j+1][64+8g+t]} (head, dim).
     float o[8][4];
@@ -182,27 +311,35 @@ __global__ void __launch_bounds__(kMaxDecodeWarps * 32, 1) attn_decode_kernel(co
         }
     };
 
-    // Key loop, software-pipelined: while unit u is consumed the loads of the warp's next unit are
-    // in flight (K of the next unit is requested before QK^T of this one, V before PV), so a warp
-    // keeps 8-12 KB outstanding and at most three 4 KB register sets are live at a time.
+    // Key loop, software-pipelined two units deep: both the K and the V rows of the warp's next two
+    // 16-key units (16 KB) are requested before anything is consumed, and a unit's registers are
+    // refilled as soon as it has been used. For a 4096-key decode every warp owns at most two units, so
+    // all of its loads are in flight at once and the kernel pays the DRAM latency once.
     {
-        KRegs ka, kb;
-        VRegs va, vb;
-        int u = warp;
-        if (u < n_units) { load_k(ka, u); load_v(va, u); }
-        while (u < n_units) {
-            const int u1 = u + n_warps;
-            if (u1 < n_units) load_k(kb, u1);
-            compute_qk(ka, u);
-            if (u1 < n_units) load_v(vb, u1);
-            compute_pv(va);
-            if (u1 >= n_units) break;
+        KRegs k0, k1;
+        VRegs v0, v1;
+        int u0 = warp, u1 = warp + n_warps;
+        if (u0 < n_units) { load_k(k0, u0); load_v(v0, u0); }
+        if (u1 < n_units) { load_k(k1, u1); load_v(v1, u1); }
+        // Query fragments (head row g, chunks 4i + j), requested after the K/V units so that the wait
+        // for them overlaps the K/V latency instead of preceding it.
+        if (g < G) {
+            const size_t qbase = ((size_t)seq * p.n_head + (size_t)kvh * G + g) * kHeadDim;
+#pragma unroll
+            for (int i = 0; i < 4; i++) qa[i] = load_q8(p.q, p.q_dtype, qbase + (size_t)(4 * i + j) * 8);
+        }
+        while (u0 < n_units) {
+            compute_qk(k0, u0);
+            compute_pv(v0);
             const int u2 = u1 + n_warps;
-            if (u2 < n_units) load_k(ka, u2);
-            compute_qk(kb, u1);
-            if (u2 < n_units) load_v(va, u2);
-            compute_pv(vb);
-            u = u2;
+            if (u2 < n_units) { load_k(k0, u2); load_v(v0, u2); }
+            if (u1 >= n_units) break;
+            compute_qk(k1, u1);
+            compute_pv(v1);
+            const int u3 = u2 + n_warps;
+            if (u3 < n_units) { load_k(k1, u3); load_v(v1, u3); }
+            u0 = u2;
+            u1 = u3;
         }
     }
     l += __shfl_xor_sync(0xffffffffu, l, 1);
@@ -226,6 +363,7 @@ __global__ void __launch_bounds__(kMaxDecodeWarps * 32, 1) attn_decode_kernel(co
     }
     if (g < G && j == 0) { sm[warp * G + g] = m; sl[warp * G + g] = l; }
     __syncthreads();
+    if (p.early_loads) asm volatile("griddepcontrol.wait;" ::: "memory");
 
     const bool single = n_chunks == 1;
     const size_t part_row0 = ((size_t)seq * p.n_parts_max + chunk) * p.n_head + (size_t)kvh * G;
@@ -247,38 +385,10 @@ __global__ void __launch_bounds__(kMaxDecodeWarps * 32, 1) attn_decode_kernel(co
             if (dim == 0) { row[128] = M; row[129] = L; }
         }
     }
-    if (single) return;
-
-    // ---- last CTA of this (sequence, kv head) merges the splits ----
-    __shared__ int s_is_last;
-    __threadfence();
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        unsigned int* ctr = p.counters + (size_t)seq * p.n_head_kv + kvh;
-        const unsigned int prev = atomicAdd(ctr, 1u);
-        s_is_last = prev == (unsigned int)(n_chunks - 1);
-        if (s_is_last) *ctr = 0;  // ready for the next launch
-    }
-    __syncthreads();
-    if (!s_is_last) return;
-    __threadfence();
-    for (int idx = threadIdx.x; idx < G * kHeadDim; idx += blockDim.x) {
-        const int gi = idx >> 7, dim = idx & 127;
-        const float* rows = p.part + (((size_t)seq * p.n_parts_max) * p.n_head + (size_t)kvh * G + gi) * kPartStride;
-        const size_t step = (size_t)p.n_head * kPartStride;
-        float M = -INFINITY;
-        for (int c = 0; c < n_chunks; c++) M = fmaxf(M, __ldcg(rows + c * step + 128));
-        float L = 0.f, O = 0.f;
-        for (int c = 0; c < n_chunks; c++) {
-            const float wgt = exp2f(__ldcg(rows + c * step + 128) - M);
-            L += __ldcg(rows + c * step + 129) * wgt;
-            O += __ldcg(rows + c * step + dim) * wgt;
-        }
-        store_out(p.out, p.out_dtype, ((size_t)seq * p.n_head + (size_t)kvh * G + gi) * kHeadDim + dim, L > 0.f ? O / L : 0.f);
-    }
 }
 
 int g_num_sms = 0;
+bool g_use_pdl = true;
 
 }  // namespace
 
@@ -286,41 +396,69 @@ size_t decode_part_floats(int n_seq, int /*max_seq_len*/, int n_head) {
     return (size_t)n_seq * kMaxParts * n_head * kPartStride;
 }
 
+// One launch of the decode kernel: split CTAs for `layer` (when split.q != nullptr) and/or one merge CTA
+// per (kv head, sequence) for the partials a previous launch left in `merge_part` (when merge_out != nullptr).
 int launch_attn_decode(ingot_kv* kv, int layer, const void* q, int q_dtype, void* out, int out_dtype, int n_head,
                        int n_seq, const int32_t* seq_lens, int max_seq_len, const int32_t* block_tables,
-                       int max_blocks_per_seq, int chunk_keys, float* part, unsigned int* counters,
-                       cudaStream_t stream) {
+                       int max_blocks_per_seq, int chunk_keys, float* part, const float* merge_part, void* merge_out,
+                       int early_loads, int concurrency, int* chunk_keys_used, cudaStream_t stream) {
+    static int n_warps_cfg = 0;
     if (g_num_sms == 0) {
         int dev = 0;
         INGOT_CUDA_TRY(cudaGetDevice(&dev));
         INGOT_CUDA_TRY(cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev));
+        // Tuning knob (like the reference's LLM_ATTN_SPLITS): warps per CTA, 4 (two CTAs per SM) or 8.
+        const char* e = getenv("INGOT_DECODE_WARPS");
+        n_warps_cfg = (e && atoi(e) == 8) ? 8 : 4;
+        g_use_pdl = getenv("INGOT_NO_PDL") == nullptr;  // diagnostics: plain stream order between launches
     }
-    const int n_warps = 4;
+    const int n_warps = n_warps_cfg;
     if (chunk_keys == 0) {
-        // Aim for two resident CTAs per SM; never fewer than 64 keys per split on small jobs and
-        // never more than 512 on large ones (keeps variable-length batches balanced).
-        const int target = 2 * g_num_sms;
-        const int per_head = max(1, target / (n_seq * kv->n_head_kv));
-        chunk_keys = ((max_seq_len + per_head - 1) / per_head + 15) / 16 * 16;
-        chunk_keys = min(max(chunk_keys, 64), 512);
+        // Small jobs: fill every CTA slot of the GPU once (the kernel needs ~240 registers per thread,
+        // so an SM holds 8 warps) with whole 16-key units per warp. Large jobs: 512 keys per split,
+        // which keeps variable-length batches balanced across SMs.
+        // `concurrency` launches share the GPU (the multi-layer call keeps several layers in flight).
+        const int slots = g_num_sms * (8 / n_warps) / max(1, concurrency);
+        const int per_head = max(1, slots / (n_seq * kv->n_head_kv));
+        const int quantum = n_warps * 16;
+        chunk_keys = ((max_seq_len + per_head - 1) / per_head + quantum - 1) / quantum * quantum;
+        chunk_keys = min(max(chunk_keys, quantum), 512);
     }
     const int min_chunk = ((max_seq_len + kMaxParts - 1) / kMaxParts + 15) / 16 * 16;
     chunk_keys = max(chunk_keys, min_chunk);
     const int n_parts = (max_seq_len + chunk_keys - 1) / chunk_keys;
+    if (chunk_keys_used) *chunk_keys_used = chunk_keys;
+    const bool has_split = q != nullptr;
+    const bool has_merge = merge_out != nullptr && n_parts > 1;
+    if (!has_split && !has_merge) return INGOT_OK;
 
     DecodeParams p;
     p.kc = kv->k + size_t(layer) * kv->layer_elems;
     p.vc = kv->v + size_t(layer) * kv->layer_elems;
     p.q = q; p.out = out; p.seq_lens = seq_lens; p.block_tables = block_tables;
-    p.part = part; p.counters = counters; p.status = kv->status_dev;
+    p.part = part; p.c_part = merge_part; p.c_out = merge_out; p.status = kv->status_dev;
     p.q_dtype = q_dtype; p.out_dtype = out_dtype;
     p.n_head = n_head; p.n_head_kv = kv->n_head_kv; p.group = n_head / kv->n_head_kv;
     p.capacity = kv->capacity; p.paged = kv->layout == INGOT_KV_PAGED; p.max_blocks_per_seq = max_blocks_per_seq;
     p.len0 = max_seq_len; p.chunk_keys = chunk_keys; p.n_parts_max = n_parts;
+    p.early_loads = early_loads;
+    p.split_parts = has_split ? n_parts : 0;
     p.scale_log2 = 1.4426950408889634f / sqrtf(float(kHeadDim));
-    const size_t smem = (size_t)n_warps * p.group * (kHeadDim + 2) * sizeof(float);
-    dim3 grid(n_parts, kv->n_head_kv, n_seq);
-    attn_decode_kernel<<<grid, n_warps * 32, smem, stream>>>(p);
-    INGOT_CUDA_TRY(cudaGetLastError());
+    const int threads = n_warps * 32;
+    const size_t smem_split = (size_t)n_warps * p.group * (kHeadDim + 2);
+    const size_t smem_merge = (size_t)2 * p.group * kMaxParts + (size_t)4 * max(threads, p.group * 32);
+    const size_t smem = max(smem_split, smem_merge) * sizeof(float);
+
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(p.split_parts + (has_merge ? 1 : 0), kv->n_head_kv, n_seq);
+    cfg.blockDim = dim3(threads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_use_pdl ? 1 : 0;
+    INGOT_CUDA_TRY(cudaLaunchKernelEx(&cfg, attn_decode_kernel, p));
     return INGOT_OK;
 }

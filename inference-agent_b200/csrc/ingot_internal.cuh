@@ -20,6 +20,8 @@ constexpr int kPartStride = 132;
 // Most 16-key units a decode split may be asked to cover is unbounded; the smallest split the
 // library picks is one unit, which bounds the number of partials per (sequence, head).
 constexpr int kMinChunkKeys = 16;
+// Independent launch chains the multi-layer decode call spreads its layers over.
+constexpr int kDecodeStreams = 4;
 
 // Bits of the device status word (ingot_kv::status_dev).
 enum : int {
@@ -38,14 +40,17 @@ struct ingot_kv {
     __half* k = nullptr;
     __half* v = nullptr;
     int* status_dev = nullptr;
-    // split-KV decode scratch: partials [max_seqs][max_parts][n_head_max][kPartStride] and
-    // arrival counters [max_seqs][n_head_kv]
+    // split-KV decode scratch: two buffers of partials [n_seq][splits][n_head][kPartStride]; consecutive
+    // launches alternate between them so that one launch's merge can overlap the next launch's splits
     float* part = nullptr;
-    size_t part_floats = 0;
-    unsigned int* counters = nullptr;
-    // staging for the host-buffer entry point (grown on demand)
+    size_t part_floats = 0;  // floats per buffer
+    // staging for the host-buffer entry points (grown on demand)
     void* stage = nullptr;
     size_t stage_bytes = 0;
+    // side streams of the multi-layer decode call (created on first use) and their fork/join events
+    cudaStream_t side_stream[kDecodeStreams] = {};
+    cudaEvent_t side_done[kDecodeStreams] = {};
+    cudaEvent_t fork_event = nullptr;
     // tensor maps for the TMA prefill kernel, one per layer and per tile height, built on first use
     void* tmaps = nullptr;  // host array, see attn_prefill_sm100.cu
 };
@@ -80,13 +85,13 @@ __host__ __device__ inline size_t kv_row_offset_paged(int n_head_kv, int blk, in
 int launch_rope_kv_append(ingot_kv* kv, int layer, const float* q, __half* q_out, const float* k, const float* v,
                           const float* inv_freq, int n_head, int pos0, int n_tok, const int32_t* positions,
                           const int32_t* seq_ids, const int32_t* block_tables, int max_blocks_per_seq,
-                          cudaStream_t stream);
+                          int layer_count, cudaStream_t stream);
 int launch_kv_import_f16(ingot_kv* kv, int layer, const __half* k, const __half* v, int pos0, int n_tok,
                          const int32_t* block_table, cudaStream_t stream);
 int launch_attn_decode(ingot_kv* kv, int layer, const void* q, int q_dtype, void* out, int out_dtype, int n_head,
                        int n_seq, const int32_t* seq_lens, int max_seq_len, const int32_t* block_tables,
-                       int max_blocks_per_seq, int chunk_keys, float* part, unsigned int* counters,
-                       cudaStream_t stream);
+                       int max_blocks_per_seq, int chunk_keys, float* part, const float* merge_part, void* merge_out,
+                       int early_loads, int concurrency, int* chunk_keys_used, cudaStream_t stream);
 int launch_attn_prefill_mma(ingot_kv* kv, int layer, const void* q, int q_dtype, void* out, int out_dtype,
                             int n_head, int q_pos0, int n_tok, const int32_t* block_table, cudaStream_t stream);
 int launch_attn_prefill_sm100(ingot_kv* kv, int layer, const void* q, int q_dtype, void* out, int out_dtype,

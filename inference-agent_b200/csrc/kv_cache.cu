@@ -5,6 +5,7 @@
 // order on Metal (src/metal_backend.mm:197-198). Here it is f16 in HBM and head-major, so that one
 // KV head's keys are a dense [positions][128] matrix: a decode split reads one contiguous byte
 // range, a prefill tile is one 2-D TMA box, and a KV-head shard of the cache is one slab.
+#include <algorithm>
 #include <cstdio>
 #include <cstring>
 #include <new>
@@ -68,15 +69,11 @@ int ingot_kv_create(ingot_kv** out, int layout, int n_layer, int n_head_kv, int 
     if ((e = cudaMalloc(&kv->k, bytes)) != cudaSuccess) return fail(e, "cudaMalloc(K cache)");
     if ((e = cudaMalloc(&kv->v, bytes)) != cudaSuccess) return fail(e, "cudaMalloc(V cache)");
     if ((e = cudaMalloc(&kv->status_dev, sizeof(int))) != cudaSuccess) return fail(e, "cudaMalloc(status)");
-    if ((e = cudaMalloc(&kv->counters, sizeof(unsigned int) * size_t(max_seqs) * n_head_kv)) != cudaSuccess)
-        return fail(e, "cudaMalloc(counters)");
     // Zero-filled cache: rows that were never appended hold finite values, so a masked key can never
     // inject NaN through 0 * garbage.
     if ((e = cudaMemset(kv->k, 0, bytes)) != cudaSuccess) return fail(e, "cudaMemset(K)");
     if ((e = cudaMemset(kv->v, 0, bytes)) != cudaSuccess) return fail(e, "cudaMemset(V)");
     if ((e = cudaMemset(kv->status_dev, 0, sizeof(int))) != cudaSuccess) return fail(e, "cudaMemset(status)");
-    if ((e = cudaMemset(kv->counters, 0, sizeof(unsigned int) * size_t(max_seqs) * n_head_kv)) != cudaSuccess)
-        return fail(e, "cudaMemset(counters)");
     if ((e = cudaDeviceSynchronize()) != cudaSuccess) return fail(e, "cudaDeviceSynchronize");
     *out = kv;
     return INGOT_OK;
@@ -89,8 +86,12 @@ void ingot_kv_destroy(ingot_kv* kv) {
     cudaFree(kv->v);
     cudaFree(kv->status_dev);
     cudaFree(kv->part);
-    cudaFree(kv->counters);
     cudaFree(kv->stage);
+    for (int i = 0; i < kDecodeStreams; i++) {
+        if (kv->side_stream[i]) cudaStreamDestroy(kv->side_stream[i]);
+        if (kv->side_done[i]) cudaEventDestroy(kv->side_done[i]);
+    }
+    if (kv->fork_event) cudaEventDestroy(kv->fork_event);
     delete kv;
 }
 
@@ -140,7 +141,7 @@ int ingot_rope_kv_append(ingot_kv* kv, int layer, const float* q_dev, void* q_ou
                       "context window exceeded");
     }
     return launch_rope_kv_append(kv, layer, q_dev, static_cast<__half*>(q_out_dev), k_dev, v_dev, inv_freq_dev, n_head,
-                                 pos0, n_tok, positions_dev, seq_ids_dev, block_tables_dev, max_blocks_per_seq,
+                                 pos0, n_tok, positions_dev, seq_ids_dev, block_tables_dev, max_blocks_per_seq, 1,
                                  static_cast<cudaStream_t>(stream));
 }
 
@@ -166,14 +167,15 @@ static int ensure_decode_scratch(ingot_kv* kv, size_t floats) {
     cudaFree(kv->part);
     kv->part = nullptr;
     kv->part_floats = 0;
-    INGOT_CUDA_TRY(cudaMalloc(&kv->part, floats * sizeof(float)));
+    INGOT_CUDA_TRY(cudaMalloc(&kv->part, 2 * kDecodeStreams * floats * sizeof(float)));
     kv->part_floats = floats;
     return INGOT_OK;
 }
 
-int ingot_attn_decode(ingot_kv* kv, int layer, const void* q_dev, int q_dtype, void* out_dev, int out_dtype,
-                      int n_head, int n_seq, const int32_t* seq_lens_dev, int max_seq_len,
-                      const int32_t* block_tables_dev, int max_blocks_per_seq, int chunk_keys, void* stream) {
+// Argument checks shared by the decode entry points; also sizes the split scratch.
+static int decode_checked(ingot_kv* kv, int layer, const void* q_dev, int q_dtype, void* out_dev, int out_dtype,
+                          int n_head, int n_seq, const int32_t* seq_lens_dev, int max_seq_len,
+                          const int32_t* block_tables_dev, int max_blocks_per_seq, int chunk_keys) {
     INGOT_REQUIRE(kv != nullptr, "ingot_attn_decode: kv is null");
     INGOT_REQUIRE(layer >= 0 && layer < kv->n_layer, "ingot_attn_decode: layer out of range");
     INGOT_REQUIRE(q_dev && out_dev, "ingot_attn_decode: null q/out");
@@ -195,11 +197,83 @@ int ingot_attn_decode(ingot_kv* kv, int layer, const void* q_dev, int q_dtype, v
         INGOT_REQUIRE((max_seq_len + kBlockTokens - 1) / kBlockTokens <= max_blocks_per_seq, "ingot_attn_decode: max_seq_len exceeds the block table");
     }
     const size_t need = decode_part_floats(n_seq, max_seq_len, n_head);
-    int rc = ensure_decode_scratch(kv, need);
+    return ensure_decode_scratch(kv, need);
+}
+
+int ingot_attn_decode(ingot_kv* kv, int layer, const void* q_dev, int q_dtype, void* out_dev, int out_dtype,
+                      int n_head, int n_seq, const int32_t* seq_lens_dev, int max_seq_len,
+                      const int32_t* block_tables_dev, int max_blocks_per_seq, int chunk_keys, void* stream) {
+    int rc = decode_checked(kv, layer, q_dev, q_dtype, out_dev, out_dtype, n_head, n_seq, seq_lens_dev, max_seq_len,
+                            block_tables_dev, max_blocks_per_seq, chunk_keys);
     if (rc != INGOT_OK) return rc;
-    return launch_attn_decode(kv, layer, q_dev, q_dtype, out_dev, out_dtype, n_head, n_seq, seq_lens_dev, max_seq_len,
-                              block_tables_dev, max_blocks_per_seq, chunk_keys, kv->part, kv->counters,
-                              static_cast<cudaStream_t>(stream));
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    int used = 0;
+    // Splits into scratch buffer 0, then a merge-only launch (skipped when one split covers everything).
+    rc = launch_attn_decode(kv, layer, q_dev, q_dtype, out_dev, out_dtype, n_head, n_seq, seq_lens_dev, max_seq_len,
+                            block_tables_dev, max_blocks_per_seq, chunk_keys, kv->part, nullptr, nullptr, 0, 1, &used, s);
+    if (rc != INGOT_OK) return rc;
+    return launch_attn_decode(kv, layer, nullptr, q_dtype, nullptr, out_dtype, n_head, n_seq, seq_lens_dev, max_seq_len,
+                              block_tables_dev, max_blocks_per_seq, used, nullptr, kv->part, out_dev, 0, 1, nullptr, s);
+}
+
+int ingot_attn_decode_layers(ingot_kv* kv, int layer_begin, int layer_count, const void* q_dev, int q_dtype,
+                             void* out_dev, int out_dtype, int n_head, int n_seq, const int32_t* seq_lens_dev,
+                             int max_seq_len, const int32_t* block_tables_dev, int max_blocks_per_seq,
+                             int chunk_keys, void* stream) {
+    INGOT_REQUIRE(kv != nullptr, "ingot_attn_decode_layers: kv is null");
+    INGOT_REQUIRE(layer_begin >= 0 && layer_count >= 0 && layer_begin + layer_count <= kv->n_layer,
+                  "ingot_attn_decode_layers: layer range out of bounds");
+    if (layer_count == 0) return INGOT_OK;
+    int rc = decode_checked(kv, layer_begin, q_dev, q_dtype, out_dev, out_dtype, n_head, n_seq, seq_lens_dev, max_seq_len,
+                            block_tables_dev, max_blocks_per_seq, chunk_keys);
+    if (rc != INGOT_OK) return rc;
+    cudaStream_t user = static_cast<cudaStream_t>(stream);
+    const size_t q_bytes = size_t(n_seq) * n_head * kHeadDim * (q_dtype == INGOT_F32 ? 4 : 2);
+    const size_t o_bytes = size_t(n_seq) * n_head * kHeadDim * (out_dtype == INGOT_F32 ? 4 : 2);
+    // The layers are independent of one another, so they are dealt round-robin to a few side streams
+    // (forked from and joined back into the caller's stream with events; this is capturable in a CUDA
+    // graph). Inside a stream, launch i carries the splits of one layer (partials into one of the
+    // stream's two scratch buffers) and the merge of the stream's previous layer (from the other
+    // buffer); a last launch merges the final layer. From a stream's second launch on, the K/V loads
+    // start while the previous launch is still finishing (programmatic dependent launch); a split CTA
+    // waits for the preceding launch only before it writes its partial, which also makes reusing the
+    // two scratch buffers safe. Several chains keep the per-launch completion latency off the
+    // critical path.
+    const int n_streams = std::min(kDecodeStreams, layer_count);
+    if (!kv->fork_event) INGOT_CUDA_TRY(cudaEventCreateWithFlags(&kv->fork_event, cudaEventDisableTiming));
+    for (int t = 0; t < n_streams; t++) {
+        if (!kv->side_stream[t]) INGOT_CUDA_TRY(cudaStreamCreateWithFlags(&kv->side_stream[t], cudaStreamNonBlocking));
+        if (!kv->side_done[t]) INGOT_CUDA_TRY(cudaEventCreateWithFlags(&kv->side_done[t], cudaEventDisableTiming));
+    }
+    INGOT_CUDA_TRY(cudaEventRecord(kv->fork_event, user));
+    for (int t = 0; t < n_streams; t++) INGOT_CUDA_TRY(cudaStreamWaitEvent(kv->side_stream[t], kv->fork_event, 0));
+    int used = chunk_keys;
+    // rounds: round r launches, on stream t, the splits of layer r*n_streams + t and the merge of layer (r-1)*n_streams + t
+    const int rounds = (layer_count + n_streams - 1) / n_streams;
+    for (int r = 0; r <= rounds; r++) {
+        for (int t = 0; t < n_streams; t++) {
+            const int li = r * n_streams + t;          // layer whose splits this launch carries
+            const int lm = (r - 1) * n_streams + t;    // layer whose partials this launch merges
+            const bool split = li < layer_count;
+            const bool merge = r > 0 && lm < layer_count;
+            if (!split && !merge) continue;
+            float* bufs = kv->part + size_t(2 * t) * kv->part_floats;
+            const void* q_i = split ? static_cast<const char*>(q_dev) + size_t(li) * q_bytes : nullptr;
+            void* out_i = split ? static_cast<char*>(out_dev) + size_t(li) * o_bytes : nullptr;
+            const float* merge_part = merge ? bufs + size_t((r - 1) & 1) * kv->part_floats : nullptr;
+            void* merge_out = merge ? static_cast<char*>(out_dev) + size_t(lm) * o_bytes : nullptr;
+            rc = launch_attn_decode(kv, layer_begin + (split ? li : lm), q_i, q_dtype, out_i, out_dtype, n_head, n_seq,
+                                    seq_lens_dev, max_seq_len, block_tables_dev, max_blocks_per_seq, used,
+                                    bufs + size_t(r & 1) * kv->part_floats, merge_part, merge_out, r > 0 ? 1 : 0, n_streams,
+                                    &used, kv->side_stream[t]);
+            if (rc != INGOT_OK) return rc;
+        }
+    }
+    for (int t = 0; t < n_streams; t++) {
+        INGOT_CUDA_TRY(cudaEventRecord(kv->side_done[t], kv->side_stream[t]));
+        INGOT_CUDA_TRY(cudaStreamWaitEvent(user, kv->side_done[t], 0));
+    }
+    return INGOT_OK;
 }
 
 int ingot_attn_prefill(ingot_kv* kv, int layer, const void* q_dev, int q_dtype, void* out_dev, int out_dtype,
@@ -233,20 +307,24 @@ int ingot_attn_prefill(ingot_kv* kv, int layer, const void* q_dev, int q_dtype, 
     return launch_attn_prefill_mma(kv, layer, q_dev, q_dtype, out_dev, out_dtype, n_head, q_pos0, n_tok, block_table_dev, s);
 }
 
-int ingot_attn_layer_host(ingot_kv* kv, int layer, const float* q_host, const float* k_host, const float* v_host,
-                          float* out_host, const float* inv_freq_dev, int n_head, int pos0, int n_tok, void* stream) {
-    INGOT_REQUIRE(kv != nullptr, "ingot_attn_layer_host: kv is null");
-    INGOT_REQUIRE(kv->layout == INGOT_KV_CONTIGUOUS, "ingot_attn_layer_host: contiguous cache only");
-    INGOT_REQUIRE(q_host && k_host && v_host && out_host && inv_freq_dev, "ingot_attn_layer_host: null argument");
-    INGOT_REQUIRE(n_tok >= 1 && pos0 >= 0, "ingot_attn_layer_host: bad range");
-    INGOT_REQUIRE(n_head >= kv->n_head_kv && n_head % kv->n_head_kv == 0, "ingot_attn_layer_host: n_head must be a multiple of n_head_kv");
+int ingot_attn_layers_host(ingot_kv* kv, int layer_begin, int layer_count, const float* q_host, const float* k_host,
+                           const float* v_host, float* out_host, const float* inv_freq_dev, int n_head, int pos0,
+                           int n_tok, void* stream) {
+    INGOT_REQUIRE(kv != nullptr, "ingot_attn_layers_host: kv is null");
+    INGOT_REQUIRE(kv->layout == INGOT_KV_CONTIGUOUS, "ingot_attn_layers_host: contiguous cache only");
+    INGOT_REQUIRE(layer_begin >= 0 && layer_count >= 0 && layer_begin + layer_count <= kv->n_layer,
+                  "ingot_attn_layers_host: layer range out of bounds");
+    if (layer_count == 0) return INGOT_OK;
+    INGOT_REQUIRE(q_host && k_host && v_host && out_host && inv_freq_dev, "ingot_attn_layers_host: null argument");
+    INGOT_REQUIRE(n_tok >= 1 && pos0 >= 0, "ingot_attn_layers_host: bad range");
+    INGOT_REQUIRE(n_head >= kv->n_head_kv && n_head % kv->n_head_kv == 0, "ingot_attn_layers_host: n_head must be a multiple of n_head_kv");
     INGOT_REQUIRE(size_t(pos0) + n_tok <= size_t(kv->capacity), "context window exceeded");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const size_t L = size_t(layer_count);
     const size_t q_elems = size_t(n_tok) * n_head * kHeadDim, kv_elems = size_t(n_tok) * kv->n_head_kv * kHeadDim;
-    // Staging is per layer so that consecutive layers can be queued without waiting on each other.
-    const size_t per_layer = q_elems * 4 + kv_elems * 8 + q_elems * 2 + q_elems * 4;
-    const size_t per_layer_al = (per_layer + 255) / 256 * 256;
-    const size_t need = per_layer_al * kv->n_layer;
+    // Device staging: q, k, v (f32), out (f32), rotated q (f16), each stacked over the layers so that the
+    // whole call needs three host->device copies and one device->host copy.
+    const size_t need = L * (q_elems * 4 + kv_elems * 8 + q_elems * 4 + q_elems * 2);
     if (need > kv->stage_bytes) {
         INGOT_CUDA_TRY(cudaDeviceSynchronize());
         cudaFree(kv->stage);
@@ -255,25 +333,35 @@ int ingot_attn_layer_host(ingot_kv* kv, int layer, const float* q_host, const fl
         INGOT_CUDA_TRY(cudaMalloc(&kv->stage, need));
         kv->stage_bytes = need;
     }
-    char* base = static_cast<char*>(kv->stage) + per_layer_al * layer;
-    float* q_d = reinterpret_cast<float*>(base);
-    float* k_d = q_d + q_elems;
-    float* v_d = k_d + kv_elems;
-    float* o_d = v_d + kv_elems;
-    __half* qh_d = reinterpret_cast<__half*>(o_d + q_elems);
-    INGOT_CUDA_TRY(cudaMemcpyAsync(q_d, q_host, q_elems * 4, cudaMemcpyHostToDevice, s));
-    INGOT_CUDA_TRY(cudaMemcpyAsync(k_d, k_host, kv_elems * 4, cudaMemcpyHostToDevice, s));
-    INGOT_CUDA_TRY(cudaMemcpyAsync(v_d, v_host, kv_elems * 4, cudaMemcpyHostToDevice, s));
-    int rc = ingot_rope_kv_append(kv, layer, q_d, qh_d, k_d, v_d, inv_freq_dev, n_head, pos0, n_tok, nullptr, nullptr,
-                                  nullptr, 0, stream);
+    float* q_d = static_cast<float*>(kv->stage);
+    float* k_d = q_d + L * q_elems;
+    float* v_d = k_d + L * kv_elems;
+    float* o_d = v_d + L * kv_elems;
+    __half* qh_d = reinterpret_cast<__half*>(o_d + L * q_elems);
+    INGOT_CUDA_TRY(cudaMemcpyAsync(q_d, q_host, L * q_elems * 4, cudaMemcpyHostToDevice, s));
+    INGOT_CUDA_TRY(cudaMemcpyAsync(k_d, k_host, L * kv_elems * 4, cudaMemcpyHostToDevice, s));
+    INGOT_CUDA_TRY(cudaMemcpyAsync(v_d, v_host, L * kv_elems * 4, cudaMemcpyHostToDevice, s));
+    int rc = launch_rope_kv_append(kv, layer_begin, q_d, qh_d, k_d, v_d, inv_freq_dev, n_head, pos0, n_tok, nullptr, nullptr,
+                                   nullptr, 0, layer_count, s);
     if (rc != INGOT_OK) return rc;
-    if (n_tok == 1)
-        rc = ingot_attn_decode(kv, layer, qh_d, INGOT_F16, o_d, INGOT_F32, n_head, 1, nullptr, pos0 + 1, nullptr, 0, 0, stream);
-    else
-        rc = ingot_attn_prefill(kv, layer, qh_d, INGOT_F16, o_d, INGOT_F32, n_head, pos0, n_tok, nullptr, 0, stream);
-    if (rc != INGOT_OK) return rc;
-    INGOT_CUDA_TRY(cudaMemcpyAsync(out_host, o_d, q_elems * 4, cudaMemcpyDeviceToHost, s));
+    if (n_tok == 1) {
+        rc = ingot_attn_decode_layers(kv, layer_begin, layer_count, qh_d, INGOT_F16, o_d, INGOT_F32, n_head, 1, nullptr,
+                                      pos0 + 1, nullptr, 0, 0, stream);
+        if (rc != INGOT_OK) return rc;
+    } else {
+        for (int i = 0; i < layer_count; i++) {
+            rc = ingot_attn_prefill(kv, layer_begin + i, qh_d + i * q_elems, INGOT_F16, o_d + i * q_elems, INGOT_F32, n_head,
+                                    pos0, n_tok, nullptr, 0, stream);
+            if (rc != INGOT_OK) return rc;
+        }
+    }
+    INGOT_CUDA_TRY(cudaMemcpyAsync(out_host, o_d, L * q_elems * 4, cudaMemcpyDeviceToHost, s));
     return INGOT_OK;
+}
+
+int ingot_attn_layer_host(ingot_kv* kv, int layer, const float* q_host, const float* k_host, const float* v_host,
+                          float* out_host, const float* inv_freq_dev, int n_head, int pos0, int n_tok, void* stream) {
+    return ingot_attn_layers_host(kv, layer, 1, q_host, k_host, v_host, out_host, inv_freq_dev, n_head, pos0, n_tok, stream);
 }
 
 int ingot_stream_sync(void* stream) {

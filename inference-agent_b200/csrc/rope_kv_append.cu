@@ -32,6 +32,7 @@ struct AppendParams {
     int capacity;            // positions (contiguous) or blocks (paged)
     int max_blocks_per_seq;
     int paged;
+    size_t layer_elems;      // cache elements between consecutive layers (blockIdx.y = layer offset)
 };
 
 __device__ __forceinline__ uint32_t pack_half2(float a, float b) {
@@ -63,13 +64,17 @@ __global__ void __launch_bounds__(256) rope_kv_append_kernel(const AppendParams 
     const int tok = int(u / units_per_tok);
     int r = int(u % units_per_tok);
     const int pos = p.positions ? p.positions[tok] : p.pos0 + tok;
+    // blockIdx.y selects one of several consecutive layers whose inputs are stacked [layer][token][...].
+    const size_t lq = (size_t)blockIdx.y * p.n_tok * p.n_head * kHeadDim;
+    const size_t lkv = (size_t)blockIdx.y * p.n_tok * p.n_head_kv * kHeadDim;
+    const size_t lc = (size_t)blockIdx.y * p.layer_elems;
 
     const float* src;
     __half* dst;
     bool rotate = true;
     if (r < q_units) {
-        src = p.q + ((size_t)tok * p.n_head) * kHeadDim + (size_t)r * 8;
-        dst = p.q_out + ((size_t)tok * p.n_head) * kHeadDim + (size_t)r * 8;
+        src = p.q + lq + ((size_t)tok * p.n_head) * kHeadDim + (size_t)r * 8;
+        dst = p.q_out + lq + ((size_t)tok * p.n_head) * kHeadDim + (size_t)r * 8;
     } else {
         r -= q_units;
         const bool is_v = r >= kv_units;
@@ -80,8 +85,8 @@ __global__ void __launch_bounds__(256) rope_kv_append_kernel(const AppendParams 
             if ((r & 15) == 0) atomicOr(p.status, row == -1 ? kDevErrPosRange : kDevErrBlockRange);
             return;
         }
-        src = (is_v ? p.v : p.k) + ((size_t)tok * p.n_head_kv) * kHeadDim + (size_t)r * 8;
-        dst = (is_v ? p.vc : p.kc) + row + (size_t)(r & 15) * 8;
+        src = (is_v ? p.v : p.k) + lkv + ((size_t)tok * p.n_head_kv) * kHeadDim + (size_t)r * 8;
+        dst = (is_v ? p.vc : p.kc) + lc + row + (size_t)(r & 15) * 8;
         rotate = !is_v;
     }
     const float4 a = __ldg(reinterpret_cast<const float4*>(src));
@@ -148,7 +153,7 @@ __global__ void __launch_bounds__(256) kv_import_f16_kernel(const ImportParams p
 int launch_rope_kv_append(ingot_kv* kv, int layer, const float* q, __half* q_out, const float* k, const float* v,
                           const float* inv_freq, int n_head, int pos0, int n_tok, const int32_t* positions,
                           const int32_t* seq_ids, const int32_t* block_tables, int max_blocks_per_seq,
-                          cudaStream_t stream) {
+                          int layer_count, cudaStream_t stream) {
     AppendParams p;
     p.q = q; p.q_out = q_out; p.k = k; p.v = v; p.inv_freq = inv_freq;
     p.kc = kv->k + size_t(layer) * kv->layer_elems;
@@ -158,9 +163,10 @@ int launch_rope_kv_append(ingot_kv* kv, int layer, const float* q, __half* q_out
     p.n_head = n_head; p.n_head_kv = kv->n_head_kv; p.n_tok = n_tok; p.pos0 = pos0;
     p.capacity = kv->capacity; p.max_blocks_per_seq = max_blocks_per_seq;
     p.paged = kv->layout == INGOT_KV_PAGED;
+    p.layer_elems = kv->layer_elems;
     const long long units = (long long)((q ? n_head : 0) + 2 * kv->n_head_kv) * 16 * n_tok;
     const unsigned blocks = unsigned((units + 255) / 256);
-    rope_kv_append_kernel<<<blocks, 256, 0, stream>>>(p);
+    rope_kv_append_kernel<<<dim3(blocks, layer_count), 256, 0, stream>>>(p);
     INGOT_CUDA_TRY(cudaGetLastError());
     return INGOT_OK;
 }

@@ -30,8 +30,10 @@ ABI = {
     "ingot_rope_kv_append": (_I, [_P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _P, _P, _P, _I, _P]),
     "ingot_kv_import_f16": (_I, [_P, _I, _P, _P, _I, _I, _P, _P]),
     "ingot_attn_decode": (_I, [_P, _I, _P, _I, _P, _I, _I, _I, _P, _I, _P, _I, _I, _P]),
+    "ingot_attn_decode_layers": (_I, [_P, _I, _I, _P, _I, _P, _I, _I, _I, _P, _I, _P, _I, _I, _P]),
     "ingot_attn_prefill": (_I, [_P, _I, _P, _I, _P, _I, _I, _I, _I, _P, _I, _P]),
     "ingot_attn_layer_host": (_I, [_P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _P]),
+    "ingot_attn_layers_host": (_I, [_P, _I, _I, _P, _P, _P, _P, _P, _I, _I, _I, _P]),
     "ingot_stream_sync": (_I, [_P]),
 }
 
@@ -161,6 +163,17 @@ def attn_decode(kv, layer, q, out=None, out_dtype=None, seq_lens=None, max_seq_l
     return out
 
 
+def attn_decode_layers(kv, layer_begin, q, out, seq_lens=None, max_seq_len=None, block_tables=None, chunk_keys=0):
+    """q, out [n_layers, n_seq, H, 128]: decode attention of consecutive layers in one call."""
+    assert q.is_contiguous() and out.is_contiguous()
+    n_layers, n_seq, n_head = q.shape[0], q.shape[1], q.shape[2]
+    mb = 0 if block_tables is None else block_tables.shape[-1]
+    _check(lib().ingot_attn_decode_layers(kv.handle, layer_begin, n_layers, _ptr(q), _dtype_code(q), _ptr(out),
+                                          _dtype_code(out), n_head, n_seq, _ptr(seq_lens), int(max_seq_len),
+                                          _ptr(block_tables), mb, chunk_keys, _stream()))
+    return out
+
+
 def attn_prefill(kv, layer, q, q_pos0, out=None, out_dtype=None, block_table=None, impl=0):
     """q [n_tok,H,128]; returns out [n_tok,H,128]."""
     import torch
@@ -178,3 +191,10 @@ def attn_layer_host(kv, layer, q_host, k_host, v_host, out_host, inv_freq_dev, p
     n_tok, n_head = q_host.shape[0], q_host.shape[1]
     _check(lib().ingot_attn_layer_host(kv.handle, layer, _ptr(q_host), _ptr(k_host), _ptr(v_host), _ptr(out_host),
                                        _ptr(inv_freq_dev), n_head, pos0, n_tok, _stream()))
+
+
+def attn_layers_host(kv, layer_begin, q_host, k_host, v_host, out_host, inv_freq_dev, pos0):
+    """q_host [L,n_tok,H,128], k/v_host [L,n_tok,Hkv,128], out_host like q_host: pinned host tensors."""
+    n_layers, n_tok, n_head = q_host.shape[0], q_host.shape[1], q_host.shape[2]
+    _check(lib().ingot_attn_layers_host(kv.handle, layer_begin, n_layers, _ptr(q_host), _ptr(k_host), _ptr(v_host),
+                                        _ptr(out_host), _ptr(inv_freq_dev), n_head, pos0, n_tok, _stream()))

@@ -87,13 +87,13 @@ def to_dev(x, dtype=None):
     return t if dtype is None else t.to(dtype)
 
 
-def gpu_prefill(wl, impl=0, paged=False, out_f16=False, seed=0):
+def gpu_prefill(wl, impl=0, paged=False, out_f16=False, seed=0, extra_ctx=0):
     """Runs a workloads.Prefill through K1 (if rope) / import and K2. Returns (out, q_rot_f16, kv)."""
     import torch
     import ingot_b200 as ib
     n, Hq, d = wl.q.shape
     hkv = wl.k.shape[1]
-    n_ctx = wl.pos0 + n
+    n_ctx = wl.pos0 + n + extra_ctx
     bt = None
     if paged:
         nb = (n_ctx + 15) // 16
