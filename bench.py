@@ -170,10 +170,12 @@ def run_decode(args, rank, world):
         while time.perf_counter() < t_end:
             step()
         torch.cuda.synchronize()
-    launches = args.steps * N_LAYER
+    # A step is 28 launches that each carry one layer's splits (and the previous layer's merge) plus
+    # 4 merge-only launches that close the 4 launch chains.
+    launches = args.steps * (N_LAYER + min(4, N_LAYER))
     bytes_step = decode_bytes_per_step()
     value = world * bytes_step * args.steps / (ms * 1e-3) / 1e9
-    per_launch_s = ms * 1e-3 / launches
+    per_launch_s = ms * 1e-3 / (args.steps * N_LAYER)  # per data-carrying launch (one layer)
     peaks = measured_peaks()
     achieved = bytes_step / N_LAYER / per_launch_s / 1e9
     roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
@@ -196,7 +198,7 @@ def run_decode(args, rank, world):
     ms_e2e = timed(step_e2e, args.steps, args.warmup, world)
     e2e = {"value": round(world * bytes_step * args.steps / (ms_e2e * 1e-3) / 1e9, 1), "unit": "GB/s",
            "h2d_bytes_per_step": int(N_LAYER * (H + 2 * HKV) * D * 4), "d2h_bytes_per_step": int(N_LAYER * H * D * 4),
-           "ms_per_step": round(ms_e2e / args.steps, 4), "gpu_launches_per_step": 2 * N_LAYER}
+           "ms_per_step": round(ms_e2e / args.steps, 4), "gpu_launches_per_step": 1 + N_LAYER + min(4, N_LAYER)}
     assert kv.status() == 0
     return {"metric": "decode attention KV-cache HBM GB/s (4096 keys, 24q/8kv heads, d128, f16 KV, 28 layers)",
             "value": round(value, 1), "unit": "GB/s", "ms_per_step": round(ms / args.steps, 5), "scaling": "weak",
