@@ -120,6 +120,26 @@ int ingot_attn_decode_layers(ingot_kv* kv, int layer_begin, int layer_count, con
                              int max_seq_len, const int32_t* block_tables_dev, int max_blocks_per_seq,
                              int chunk_keys, void* stream);
 
+/* Decode for callers that cannot allocate device memory (no counterpart in the reference).
+ * Meant for code that lives inside somebody else's memory budget: a plugin that is only ever handed
+ * pre-allocated buffers, a component of a serving loop where cudaMalloc/cudaFree are banned because
+ * they synchronise the device, or a process whose allocator is a fixed pool. This entry point takes
+ * raw device pointers, needs no ingot_kv handle, and calls no cudaMalloc, cudaFree or allocating
+ * library routine: the split-KV partials go to a fixed 2.06 MiB array that is part of the library
+ * image (each GPU that loads the library holds it until the process exits).
+ *   k_dev, v_dev  one layer of a contiguous f16 cache, [n_head_kv][n_ctx][128] (the caller's memory)
+ *   q_dev   [n_head][128]  q_dtype in {F32, F16, BF16}, already rotated;  out_dev [n_head][128] F32 or F16
+ *   n_keys  keys 0..n_keys-1 are attended (1 <= n_keys <= n_ctx); one sequence per call
+ * Limits: n_head <= 64 and n_head / n_head_kv <= 8; larger calls are rejected with INGOT_ERR_INVALID
+ * (use ingot_attn_decode). The first call on each device resolves the array's device address; make
+ * that call before starting any stream capture. All calls on a device share the one array and it keeps
+ * the previous call's contents (nothing in it needs clearing: every partial a call reads was written by
+ * that same call), so two calls whose kernels can overlap on the GPU — different streams without an
+ * ordering between them — race; keep them in one stream or order them with events. */
+int ingot_attn_decode_noalloc(const void* k_dev, const void* v_dev, int n_ctx, int n_head_kv, const void* q_dev,
+                              int q_dtype, void* out_dev, int out_dtype, int n_head, int n_keys, int chunk_keys,
+                              void* stream);
+
 /* ---- K2: causal GQA flash-attention prefill / chunked prefill -----------------------------------
  * Replaces n_tok iterations of the attention lambda (src/backend.h:16-20 + src/cpu_backend.cpp:51-69)
  * and Metal's attn_prefill (shaders/kernels.metal:518-633; src/metal_backend.mm:361-372).

@@ -27,6 +27,8 @@
 #include "attn_common.cuh"
 #include "ingot_internal.cuh"
 
+#include <mutex>
+
 namespace {
 
 constexpr int kMaxDecodeWarps = 8;
@@ -460,5 +462,93 @@ int launch_attn_decode(ingot_kv* kv, int layer, const void* q, int q_dtype, void
     cfg.attrs = attr;
     cfg.numAttrs = g_use_pdl ? 1 : 0;
     INGOT_CUDA_TRY(cudaLaunchKernelEx(&cfg, attn_decode_kernel, p));
+    return INGOT_OK;
+}
+
+// ---- decode without any allocation ----------------------------------------------------------------
+// Some callers must not allocate device memory at all: code that runs inside a memory pool it does
+// not own, a plugin that is only handed pre-allocated buffers by its host application, or a
+// latency-critical serving loop where cudaMalloc/cudaFree (which synchronise the device) are
+// forbidden. For them the split partials live in a fixed array inside the library image instead of
+// the cache handle's heap scratch. Every GPU that loads the library holds these 2.06 MiB until exit.
+namespace {
+constexpr int kStaticMaxHeads = 64;  // most query heads one call may carry
+constexpr int kStaticMaxDevices = 64;
+static __device__ __align__(256) float g_static_part[(size_t)kMaxParts * kStaticMaxHeads * kPartStride];
+float* g_static_part_addr[kStaticMaxDevices] = {};
+int g_static_sms[kStaticMaxDevices] = {};
+std::mutex g_static_mu;
+}  // namespace
+
+extern "C" int ingot_attn_decode_noalloc(const void* k_dev, const void* v_dev, int n_ctx, int n_head_kv, const void* q_dev,
+                                         int q_dtype, void* out_dev, int out_dtype, int n_head, int n_keys, int chunk_keys,
+                                         void* stream) {
+    INGOT_REQUIRE(k_dev && v_dev && q_dev && out_dev, "ingot_attn_decode_noalloc: null pointer");
+    INGOT_REQUIRE(n_head_kv >= 1 && n_head >= n_head_kv && n_head % n_head_kv == 0,
+                  "ingot_attn_decode_noalloc: n_head must be a multiple of n_head_kv");
+    INGOT_REQUIRE(n_keys >= 1 && n_keys <= n_ctx, "context window exceeded");
+    INGOT_REQUIRE(chunk_keys >= 0 && chunk_keys % 16 == 0, "ingot_attn_decode_noalloc: chunk_keys must be a multiple of 16");
+    if (n_head > kStaticMaxHeads) {
+        ingot_set_error("ingot_attn_decode_noalloc: n_head exceeds the 64 heads the built-in scratch is sized for; "
+                        "use ingot_attn_decode");
+        return INGOT_ERR_INVALID;
+    }
+    if (n_head / n_head_kv > 8 || (q_dtype != INGOT_F32 && q_dtype != INGOT_F16 && q_dtype != INGOT_BF16) ||
+        (out_dtype != INGOT_F32 && out_dtype != INGOT_F16)) {
+        ingot_set_error("ingot_attn_decode_noalloc: group size > 8 or unsupported dtype");
+        return INGOT_ERR_UNSUPPORTED;
+    }
+    int dev = 0;
+    INGOT_CUDA_TRY(cudaGetDevice(&dev));
+    INGOT_REQUIRE(dev >= 0 && dev < kStaticMaxDevices, "ingot_attn_decode_noalloc: device index too large");
+    float* scratch = nullptr;
+    int sms = 0;
+    {
+        // First call on this device: resolve the device address of the array. The array's name is only
+        // a host-side handle; the kernel must be given the address cudaGetSymbolAddress reports, taken
+        // with this device current.
+        std::lock_guard<std::mutex> lk(g_static_mu);
+        if (!g_static_part_addr[dev]) {
+            void* addr = nullptr;
+            INGOT_CUDA_TRY(cudaGetSymbolAddress(&addr, g_static_part));
+            INGOT_CUDA_TRY(cudaDeviceGetAttribute(&g_static_sms[dev], cudaDevAttrMultiProcessorCount, dev));
+            g_static_part_addr[dev] = static_cast<float*>(addr);
+        }
+        scratch = g_static_part_addr[dev];
+        sms = g_static_sms[dev];
+    }
+    const int n_warps = 4;
+    if (chunk_keys == 0) {
+        const int per_head = max(1, sms * 2 / n_head_kv);
+        chunk_keys = ((n_keys + per_head - 1) / per_head + 63) / 64 * 64;
+        chunk_keys = min(max(chunk_keys, 64), 512);
+    }
+    chunk_keys = max(chunk_keys, ((n_keys + kMaxParts - 1) / kMaxParts + 15) / 16 * 16);
+    const int n_parts = (n_keys + chunk_keys - 1) / chunk_keys;  // <= kMaxParts, so the partials fit the array
+
+    DecodeParams p;
+    p.kc = static_cast<const __half*>(k_dev);
+    p.vc = static_cast<const __half*>(v_dev);
+    p.q = q_dev; p.out = out_dev; p.seq_lens = nullptr; p.block_tables = nullptr;
+    p.part = scratch; p.c_part = scratch; p.c_out = out_dev; p.status = nullptr;
+    p.q_dtype = q_dtype; p.out_dtype = out_dtype;
+    p.n_head = n_head; p.n_head_kv = n_head_kv; p.group = n_head / n_head_kv;
+    p.capacity = n_ctx; p.paged = 0; p.max_blocks_per_seq = 0;
+    p.len0 = n_keys; p.chunk_keys = chunk_keys; p.n_parts_max = n_parts;
+    p.early_loads = 0;
+    p.scale_log2 = 1.4426950408889634f / sqrtf(float(kHeadDim));
+    const int threads = n_warps * 32;
+    const size_t smem_split = (size_t)n_warps * p.group * (kHeadDim + 2);
+    const size_t smem_merge = (size_t)2 * p.group * kMaxParts + (size_t)4 * max(threads, p.group * 32);
+    const size_t smem = max(smem_split, smem_merge) * sizeof(float);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    p.split_parts = n_parts;
+    attn_decode_kernel<<<dim3(n_parts, n_head_kv, 1), threads, smem, s>>>(p);
+    INGOT_CUDA_TRY(cudaGetLastError());
+    if (n_parts > 1) {  // merge-only launch; stream order makes the partials visible
+        p.split_parts = 0;
+        attn_decode_kernel<<<dim3(1, n_head_kv, 1), threads, smem, s>>>(p);
+        INGOT_CUDA_TRY(cudaGetLastError());
+    }
     return INGOT_OK;
 }

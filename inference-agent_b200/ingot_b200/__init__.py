@@ -31,6 +31,7 @@ ABI = {
     "ingot_kv_import_f16": (_I, [_P, _I, _P, _P, _I, _I, _P, _P]),
     "ingot_attn_decode": (_I, [_P, _I, _P, _I, _P, _I, _I, _I, _P, _I, _P, _I, _I, _P]),
     "ingot_attn_decode_layers": (_I, [_P, _I, _I, _P, _I, _P, _I, _I, _I, _P, _I, _P, _I, _I, _P]),
+    "ingot_attn_decode_noalloc": (_I, [_P, _P, _I, _I, _P, _I, _P, _I, _I, _I, _I, _P]),
     "ingot_attn_prefill": (_I, [_P, _I, _P, _I, _P, _I, _I, _I, _I, _P, _I, _P]),
     "ingot_attn_layer_host": (_I, [_P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _P]),
     "ingot_attn_layers_host": (_I, [_P, _I, _I, _P, _P, _P, _P, _P, _I, _I, _I, _P]),
