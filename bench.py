@@ -246,7 +246,7 @@ def run_prefill(args, rank, world):
     q = q_all[:, rank * h_l:(rank + 1) * h_l].contiguous()
     del k_all, v_all, q_all
     out = torch.empty(S, h_l, D, device="cuda", dtype=torch.float16)
-    gathered = torch.empty(world, S, h_l, D, device="cuda", dtype=torch.float16) if world > 1 else None
+    gathered = torch.empty(world * S, h_l, D, device="cuda", dtype=torch.float16) if world > 1 else None  # rank-major
 
     def step():
         ib.attn_prefill(kv, 0, q, 0, out=out, impl=2)
