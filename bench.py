@@ -36,7 +36,10 @@ PREFILL_TOKENS = 32768
 
 # DRAM bytes per launch of the dominant kernel from an ncu capture of the same kernel
 # (dram__bytes_read.sum + dram__bytes_write.sum); see profiles/ for the command and the raw figures.
-NCU_TRAFFIC = {"attn_decode_kernel": None, "attn_prefill_sm100_kernel": None}
+# decode: captured at the benchmark shape (profiles/attn_decode_c2.md). prefill: captured at 8192 tokens
+# (84.1 MB read + 18.4 MB written; profiles/attn_prefill_sm100_8k.md) and scaled by the 4x token count,
+# compulsory q/K/V/out traffic growing in proportion.
+NCU_TRAFFIC = {"attn_decode_kernel": 16845824, "attn_prefill_sm100_kernel": 4 * (84126208 + 18397184)}
 
 
 def measured_peaks():
@@ -225,8 +228,9 @@ def inv_freq_table():
 # prefill: configs[4]
 # ------------------------------------------------------------------------------------------------
 
-def prefill_flops():
-    return 4 * PREFILL_TOKENS * PREFILL_TOKENS * H * D // 2
+def prefill_flops(n_tok=None):
+    n_tok = n_tok or PREFILL_TOKENS
+    return 4 * n_tok * n_tok * H * D // 2
 
 
 def run_prefill(args, rank, world):
@@ -235,7 +239,7 @@ def run_prefill(args, rank, world):
     assert HKV % world == 0
     hkv_l, h_l = HKV // world, H // world
     torch.manual_seed(4)  # same tensors on every rank; each rank keeps its KV-head slice
-    S = PREFILL_TOKENS
+    S = args.prefill_tokens
     kv = ib.KVCache(ib.KV_CONTIGUOUS, 1, hkv_l, S)
     g = torch.Generator(device="cuda").manual_seed(4)
     k_all = torch.randn(HKV, S, D, device="cuda", generator=g).half()
@@ -262,7 +266,7 @@ def run_prefill(args, rank, world):
         ms = timed(step, steps, args.warmup, world)
     ms_kernel = timed(step_kernel_only, steps, 1, world)
     assert kv.status() == 0
-    flops = prefill_flops()
+    flops = prefill_flops(S)
     value = flops * steps / (ms * 1e-3) / 1e12
     peaks = measured_peaks()
     per_gpu = flops / world * steps / (ms_kernel * 1e-3) / 1e12
@@ -286,11 +290,12 @@ def run_prefill(args, rank, world):
     e2e = {"value": round(flops * steps / (ms_e2e * 1e-3) / 1e12, 1), "unit": "TFLOP/s",
            "h2d_bytes_per_step": int(q.numel() * 2), "d2h_bytes_per_step": int(out.numel() * 2),
            "ms_per_step": round(ms_e2e / steps, 4)}
-    return {"metric": "causal GQA prefill attention TFLOP/s (32768 tokens, 24q/8kv heads, d128, bf16 q, f16 K/V)",
+    return {"metric": f"causal GQA prefill attention TFLOP/s ({S} tokens, 24q/8kv heads, d128, bf16 q, f16 K/V)",
             "value": round(value, 1), "unit": "TFLOP/s", "ms_per_step": round(ms / steps, 4), "steps": steps,
             "scaling": "strong", "dtype": "f16 MMA operands (bf16 q converted on load) / f32 accumulate+softmax",
             "roofline": roofline, "e2e": e2e, "gpu_launches": steps, "clocks": clk.summary(),
-            "config": {"workload": "configs[4]: 32768-token causal prefill, FLOPs = 4*S^2*H*d/2", "n_tok": S,
+            "config": {"workload": ("configs[4]: 32768-token causal prefill, FLOPs = 4*S^2*H*d/2" if S == PREFILL_TOKENS
+                                    else f"PROFILING CASE: {S}-token causal prefill (not the benchmark configuration)"), "n_tok": S,
                        "n_head": H, "n_head_kv": HKV, "head_dim": D,
                        "l2": "inputs larger than L2 (q+out 400 MB, K/V 134 MB)",
                        "parallelism": f"KV-head sharding x{world}" + (" + NCCL all-gather of head outputs (timed)" if world > 1 else "")}}
@@ -400,6 +405,8 @@ def main():
     ap.add_argument("--workload", default="decode_c2", choices=["decode_c2", "prefill_c5"])
     ap.add_argument("--chunk-keys", type=int, default=0, help="decode split size (0 = library default)")
     ap.add_argument("--prefill-steps", type=int, default=10, help="cap on timed prefill steps (each is ~10 ms)")
+    ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS,
+                    help="prefill length; anything but 32768 is a profiling case, not the benchmark configuration")
     ap.add_argument("--no-secondary", action="store_true", help="skip the non-headline workload")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-graph", action="store_true", help="decode: launch the 28 layers from Python instead of replaying a CUDA graph")
