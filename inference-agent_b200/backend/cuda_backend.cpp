@@ -1,0 +1,257 @@
+// CudaBackend — drop-in third implementation of Ingot's Backend (src/backend.h:9-23), beside the CPU
+// reference (src/cpu_backend.cpp) and the Metal backend (src/metal_backend.mm).
+//
+// Per layer it runs what MetalBackend::forward_batch encodes (src/metal_backend.mm:435-455): rmsnorm,
+// q/k/v projections, then the attention stage through the C ABI of libingot_cuda.so — fused RoPE + KV
+// append, then split-KV decode (n == 1) or causal prefill (n > 1) — then wo (+= x), rmsnorm, gate/up,
+// silu_mul, down (+= x); finally the last token's norm and the logits projection.
+//
+// Contracts kept from the reference backends:
+//  - positions are 0-based and may be revisited in any order (src/main.cpp:295, 374-375);
+//  - forward_batch returns the logits of the LAST token only (src/metal_backend.mm:456-458);
+//  - the returned pointer is writable host memory owned by the backend and valid until the next call
+//    (callers const_cast and edit it, src/main.cpp:238-239, src/sampler.cpp:20): a pinned buffer;
+//  - the same exceptions and messages for a bad position, token id or batch size
+//    (src/cpu_backend.cpp:24-25, src/metal_backend.mm:421-424);
+//  - Model and gguf::File are borrowed and must outlive the backend; weights are uploaded once.
+// This file also defines make_metal_backend and the four metal_* diagnostics, so that the reference's
+// engine.cpp / main.cpp link against this backend without a source edit.
+#include "cuda_backend.h"
+
+#include <cuda_runtime.h>
+
+#include <cmath>
+#include <cstring>
+#include <stdexcept>
+#include <string>
+#include <vector>
+
+#include "ingot_cuda.h"
+#include "metal_backend.h"
+#include "ops.h"
+
+extern "C" {
+cudaError_t ingot_support_rmsnorm(float* out, const float* x, const float* w, int n_rows, int n, float eps, cudaStream_t s);
+cudaError_t ingot_support_silu_mul(float* gate, const float* up, size_t n, cudaStream_t s);
+cudaError_t ingot_support_linear(float* out, const void* w, int w_is_f16, const float* x, int n_in, int n_out, int n_tok,
+                                 int accumulate, cudaStream_t s);
+}
+
+namespace {
+
+void cuda_check(cudaError_t e, const char* what) {
+    if (e != cudaSuccess) throw std::runtime_error(std::string("cuda: ") + what + ": " + cudaGetErrorString(e));
+}
+void ingot_check(int rc) {
+    if (rc != INGOT_OK) throw std::runtime_error(ingot_last_error()[0] ? ingot_last_error() : ingot_status_string(rc));
+}
+
+struct DevWeight {
+    void* data = nullptr;
+    int is_f16 = 0;
+    int n_in = 0, n_out = 0;
+};
+
+class CudaBackend : public Backend {
+public:
+    CudaBackend(const Model& m, int n_ctx, int n_batch) : m_(m), n_ctx_(n_ctx), n_batch_(n_batch) {
+        const Config& c = m.cfg;
+        if (n_batch < 1) throw std::runtime_error("cuda: --batch must be at least 1");
+        if (c.head_dim != INGOT_HEAD_DIM) throw std::runtime_error("cuda: head_dim must be 128");
+        if (c.n_head / c.n_head_kv > 8) throw std::runtime_error("cuda: more than 8 query heads per kv head not supported");
+        int n_dev = 0;
+        if (cudaGetDeviceCount(&n_dev) != cudaSuccess || n_dev < 1) throw std::runtime_error("cuda: no GPU device");
+        cuda_check(cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking), "cudaStreamCreate");
+        ingot_check(ingot_kv_create(&kv_, INGOT_KV_CONTIGUOUS, c.n_layer, c.n_head_kv, c.head_dim, n_ctx, 1));
+
+        layers_.resize(c.n_layer);
+        for (int l = 0; l < c.n_layer; l++) {
+            const Layer& L = m.layers[l];
+            DevLayer& D = layers_[l];
+            D.attn_norm = upload_f32(L.attn_norm);
+            D.ffn_norm = upload_f32(L.ffn_norm);
+            D.wq = upload(*L.wq); D.wk = upload(*L.wk); D.wv = upload(*L.wv); D.wo = upload(*L.wo);
+            D.w_gate = upload(*L.w_gate); D.w_up = upload(*L.w_up); D.w_down = upload(*L.w_down);
+        }
+        output_norm_ = upload_f32(m.output_norm);
+        output_ = upload(*m.output);
+        inv_freq_ = upload_f32(m.rope_inv_freq);
+
+        const size_t nb = size_t(n_batch);
+        const size_t q_dim = size_t(c.n_head) * c.head_dim, kv_dim = size_t(c.n_head_kv) * c.head_dim;
+        x_ = alloc_f32(nb * c.n_embd); h_ = alloc_f32(nb * c.n_embd);
+        q_ = alloc_f32(nb * q_dim); attn_ = alloc_f32(nb * q_dim);
+        k_ = alloc_f32(nb * kv_dim); v_ = alloc_f32(nb * kv_dim);
+        gate_ = alloc_f32(nb * c.n_ff); up_ = alloc_f32(nb * c.n_ff);
+        logits_dev_ = alloc_f32(size_t(c.n_vocab));
+        cuda_check(cudaMalloc(&q_rot_, nb * q_dim * 2), "cudaMalloc(q_rot)");
+        allocs_.push_back(q_rot_);
+        cuda_check(cudaMallocHost(&x_host_, nb * c.n_embd * sizeof(float)), "cudaMallocHost(x)");
+        cuda_check(cudaMallocHost(&logits_, size_t(c.n_vocab) * sizeof(float)), "cudaMallocHost(logits)");
+    }
+
+    ~CudaBackend() override {
+        cudaStreamSynchronize(stream_);
+        for (void* p : allocs_) cudaFree(p);
+        cudaFreeHost(x_host_);
+        cudaFreeHost(logits_);
+        ingot_kv_destroy(kv_);
+        cudaStreamDestroy(stream_);
+    }
+
+    const float* forward(int32_t token, int pos) override { return forward_batch(&token, 1, pos); }
+
+    const float* forward_batch(const int32_t* tokens, int n, int pos) override {
+        const Config& c = m_.cfg;
+        if (n < 1 || n > n_batch_) throw std::runtime_error("cuda: batch size out of range");
+        if (pos < 0 || pos + n > n_ctx_) throw std::runtime_error("context window exceeded");
+        for (int i = 0; i < n; i++)
+            if (tokens[i] < 0 || tokens[i] >= c.n_vocab) throw std::runtime_error("token id out of range");
+
+        // Embedding rows are dequantised on the host straight into pinned memory, as the Metal
+        // backend does (src/metal_backend.mm:426-428).
+        for (int i = 0; i < n; i++) ops::dequant_row(*m_.tok_embd, size_t(tokens[i]), x_host_ + size_t(i) * c.n_embd);
+        cuda_check(cudaMemcpyAsync(x_, x_host_, size_t(n) * c.n_embd * sizeof(float), cudaMemcpyHostToDevice, stream_), "H2D x");
+
+        const int q_dim = c.n_head * c.head_dim, kv_dim = c.n_head_kv * c.head_dim;
+        for (int l = 0; l < c.n_layer; l++) {
+            const DevLayer& D = layers_[l];
+            cuda_check(ingot_support_rmsnorm(h_, x_, D.attn_norm, n, c.n_embd, c.rms_eps, stream_), "rmsnorm");
+            linear(q_, D.wq, h_, n, false);
+            linear(k_, D.wk, h_, n, false);
+            linear(v_, D.wv, h_, n, false);
+            ingot_check(ingot_rope_kv_append(kv_, l, q_, q_rot_, k_, v_, inv_freq_, c.n_head, pos, n, nullptr, nullptr,
+                                             nullptr, 0, stream_));
+            if (n == 1)
+                ingot_check(ingot_attn_decode(kv_, l, q_rot_, INGOT_F16, attn_, INGOT_F32, c.n_head, 1, nullptr, pos + 1,
+                                              nullptr, 0, 0, stream_));
+            else
+                ingot_check(ingot_attn_prefill(kv_, l, q_rot_, INGOT_F16, attn_, INGOT_F32, c.n_head, pos, n, nullptr, 0,
+                                               stream_));
+            linear(x_, D.wo, attn_, n, true);
+            cuda_check(ingot_support_rmsnorm(h_, x_, D.ffn_norm, n, c.n_embd, c.rms_eps, stream_), "rmsnorm");
+            linear(gate_, D.w_gate, h_, n, false);
+            linear(up_, D.w_up, h_, n, false);
+            cuda_check(ingot_support_silu_mul(gate_, up_, size_t(n) * c.n_ff, stream_), "silu_mul");
+            linear(x_, D.w_down, gate_, n, true);
+        }
+        (void)q_dim; (void)kv_dim;
+        // Logits for the last token only.
+        cuda_check(ingot_support_rmsnorm(h_, x_ + size_t(n - 1) * c.n_embd, output_norm_, 1, c.n_embd, c.rms_eps, stream_), "rmsnorm");
+        linear(logits_dev_, output_, h_, 1, false);
+        cuda_check(cudaMemcpyAsync(logits_, logits_dev_, size_t(c.n_vocab) * sizeof(float), cudaMemcpyDeviceToHost, stream_), "D2H logits");
+        cuda_check(cudaStreamSynchronize(stream_), "forward");
+        int status = 0;
+        ingot_check(ingot_kv_status(kv_, stream_, &status));
+        if (status != 0) throw std::runtime_error("cuda: attention kernel reported status " + std::to_string(status));
+        return logits_;
+    }
+
+    int n_ctx() const override { return n_ctx_; }
+    const char* name() const override { return "cuda"; }
+
+private:
+    struct DevLayer {
+        float *attn_norm = nullptr, *ffn_norm = nullptr;
+        DevWeight wq, wk, wv, wo, w_gate, w_up, w_down;
+    };
+
+    float* alloc_f32(size_t n) {
+        void* p = nullptr;
+        cuda_check(cudaMalloc(&p, n * sizeof(float)), "cudaMalloc");
+        allocs_.push_back(p);
+        return static_cast<float*>(p);
+    }
+    float* upload_f32(const std::vector<float>& v) {
+        float* p = alloc_f32(v.size());
+        cuda_check(cudaMemcpy(p, v.data(), v.size() * sizeof(float), cudaMemcpyHostToDevice), "cudaMemcpy");
+        return p;
+    }
+    // Weights are read from the mmap (src/gguf.h:56) and kept in their stored float type.
+    DevWeight upload(const gguf::TensorInfo& t) {
+        DevWeight w;
+        if (t.type == gguf::TensorType::F16) w.is_f16 = 1;
+        else if (t.type == gguf::TensorType::F32) w.is_f16 = 0;
+        else throw std::runtime_error(std::string("cuda: tensor ") + t.name + " has type " + gguf::type_name(t.type) +
+                                      "; this backend reads F16 and F32 weights");
+        w.n_in = int(t.dim(0));
+        w.n_out = int(t.dim(1));
+        if (w.n_in % 8 != 0) throw std::runtime_error("cuda: tensor " + t.name + " row length must be a multiple of 8");
+        cuda_check(cudaMalloc(&w.data, t.nbytes()), "cudaMalloc(weight)");
+        allocs_.push_back(w.data);
+        cuda_check(cudaMemcpy(w.data, t.data, t.nbytes(), cudaMemcpyHostToDevice), "cudaMemcpy(weight)");
+        return w;
+    }
+    void linear(float* out, const DevWeight& w, const float* x, int n_tok, bool accumulate) {
+        cuda_check(ingot_support_linear(out, w.data, w.is_f16, x, w.n_in, w.n_out, n_tok, accumulate ? 1 : 0, stream_), "linear");
+    }
+
+    const Model& m_;
+    int n_ctx_, n_batch_;
+    cudaStream_t stream_ = nullptr;
+    ingot_kv* kv_ = nullptr;
+    std::vector<DevLayer> layers_;
+    std::vector<void*> allocs_;
+    float *output_norm_ = nullptr, *inv_freq_ = nullptr;
+    DevWeight output_;
+    float *x_ = nullptr, *h_ = nullptr, *q_ = nullptr, *k_ = nullptr, *v_ = nullptr, *attn_ = nullptr, *gate_ = nullptr,
+          *up_ = nullptr, *logits_dev_ = nullptr;
+    void* q_rot_ = nullptr;
+    float *x_host_ = nullptr, *logits_ = nullptr;
+};
+
+}  // namespace
+
+std::unique_ptr<Backend> make_cuda_backend(const gguf::File&, const Model& model, int n_ctx, int n_batch) {
+    return std::make_unique<CudaBackend>(model, n_ctx, n_batch);
+}
+
+// Link seam: engine.cpp (src/engine.cpp:9-13) knows the GPU backend as "metal".
+std::unique_ptr<Backend> make_metal_backend(const gguf::File& file, const Model& model, int n_ctx, int n_batch) {
+    return make_cuda_backend(file, model, n_ctx, n_batch);
+}
+
+// Diagnostics verbs of the CLI (src/metal_backend.h:17-25, src/main.cpp:417-453).
+double metal_linear_bench(const gguf::File&, const Model&, const std::string&, int, int) {
+    throw std::runtime_error("kbench is not available on the cuda backend");
+}
+void metal_linear_check(const gguf::File&, const Model&, const std::string&, int) {
+    throw std::runtime_error("kcheck is not available on the cuda backend");
+}
+void metal_bandwidth_test(const gguf::File&, const Model&, size_t) {
+    throw std::runtime_error("bwtest is not available on the cuda backend");
+}
+
+// Seconds per token spent in decode attention across all layers at position pos
+// (src/metal_backend.mm:594-649): all layers' decode attention, `iters` times, timed with CUDA events.
+double metal_attention_bench(const gguf::File&, const Model& model, int pos, int iters) {
+    const Config& c = model.cfg;
+    ingot_kv* kv = nullptr;
+    ingot_check(ingot_kv_create(&kv, INGOT_KV_CONTIGUOUS, c.n_layer, c.n_head_kv, c.head_dim, pos + 1, 1));
+    const size_t q_elems = size_t(c.n_layer) * c.n_head * c.head_dim;
+    void *q = nullptr, *out = nullptr;
+    cuda_check(cudaMalloc(&q, q_elems * 2), "cudaMalloc");
+    cuda_check(cudaMalloc(&out, q_elems * 4), "cudaMalloc");
+    cuda_check(cudaMemset(q, 0, q_elems * 2), "cudaMemset");
+    cudaEvent_t e0, e1;
+    cudaEventCreate(&e0);
+    cudaEventCreate(&e1);
+    auto run = [&](int reps) {
+        for (int i = 0; i < reps; i++)
+            ingot_check(ingot_attn_decode_layers(kv, 0, c.n_layer, q, INGOT_F16, out, INGOT_F32, c.n_head, 1, nullptr, pos + 1,
+                                                 nullptr, 0, 0, nullptr));
+    };
+    run(2);
+    cudaEventRecord(e0, nullptr);
+    run(iters);
+    cudaEventRecord(e1, nullptr);
+    cuda_check(cudaEventSynchronize(e1), "attention bench");
+    float ms = 0;
+    cudaEventElapsedTime(&ms, e0, e1);
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    cudaFree(q);
+    cudaFree(out);
+    ingot_kv_destroy(kv);
+    return double(ms) * 1e-3 / iters;
+}

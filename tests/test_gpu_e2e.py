@@ -1,0 +1,78 @@
+"""End to end: the CUDA backend behind the reference's own engine glue against the reference CpuBackend.
+
+A seeded random-init Llama-3.2-3B-shaped F16 GGUF is generated on the machine, 128 uniformly drawn
+token ids are prefilled and 32 tokens are decoded greedily through make_backend / prefill / Sampler
+(src/engine.cpp, src/sampler.cpp) on both backends; the token lists must be identical.
+Default: 2 layers and a 32064-token vocabulary (seconds). INGOT_E2E_FULL=1 runs the full 28-layer,
+128256-token model (6.4 GB file, minutes).
+"""
+import ctypes as C
+import os
+import sys
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+ENGINE = os.path.join(ROOT, "inference-agent_b200", "backend", "_build", "libingot_engine_cuda.so")
+
+
+def _engine():
+    if not os.path.exists(ENGINE):
+        pytest.skip("libingot_engine_cuda.so not built (needs a reference checkout at build time)")
+    lib = C.CDLL(ENGINE)
+    i32p = np.ctypeslib.ndpointer(dtype=np.int32, flags="C_CONTIGUOUS")
+    f32p = np.ctypeslib.ndpointer(dtype=np.float32, flags="C_CONTIGUOUS")
+    lib.ingot_e2e_greedy.argtypes = [C.c_char_p, C.c_char_p, i32p, C.c_int, C.c_int, C.c_int, i32p, f32p]
+    lib.ingot_e2e_greedy.restype = C.c_int
+    lib.ingot_e2e_last_error.restype = C.c_char_p
+    return lib
+
+
+def _model(tmp_dir):
+    sys.path.insert(0, os.path.join(ROOT, "tests", "golden"))
+    import make_random_gguf
+    full = os.environ.get("INGOT_E2E_FULL") == "1"
+    n_layer, n_vocab = (28, 128256) if full else (2, 32064)
+    path = os.path.join(tmp_dir, f"ingot_random_l{n_layer}_v{n_vocab}_s0.gguf")
+    if not os.path.exists(path):
+        make_random_gguf.write(path + ".tmp", n_layer, n_vocab, seed=0)
+        os.replace(path + ".tmp", path)
+    return path, n_vocab
+
+
+def _greedy(lib, path, backend, prompt, n_gen, n_batch):
+    ids = np.zeros(n_gen, dtype=np.int32)
+    margin = np.zeros(n_gen, dtype=np.float32)
+    rc = lib.ingot_e2e_greedy(path.encode(), backend, prompt, len(prompt), n_gen, n_batch, ids, margin)
+    assert rc == 0, lib.ingot_e2e_last_error().decode()
+    return ids, margin
+
+
+@pytest.mark.parametrize("n_batch", [512, 48])
+def test_greedy_tokens_match_cpu_reference(n_batch):
+    lib = _engine()
+    path, n_vocab = _model(os.environ.get("INGOT_E2E_DIR", "/tmp"))
+    prompt = np.random.default_rng(0).integers(0, n_vocab, size=128).astype(np.int32)
+    want, want_margin = _greedy(lib, path, b"cpu", prompt, 32, n_batch)
+    got, got_margin = _greedy(lib, path, b"metal", prompt, 32, n_batch)  # "metal" = the GPU backend of this build
+    first_bad = next((i for i in range(32) if want[i] != got[i]), None)
+    detail = "" if first_bad is None else (f"first mismatch at step {first_bad}: cpu {want[first_bad]} (top-2 margin "
+                                           f"{want_margin[first_bad]:.3e}) vs cuda {got[first_bad]} (margin {got_margin[first_bad]:.3e})")
+    assert first_bad is None, detail
+    print(f"\n32 greedy tokens identical (n_batch={n_batch}); smallest reference top-2 margin {want_margin.min():.3e}")
+
+
+def test_backend_errors_match_reference():
+    lib = _engine()
+    path, n_vocab = _model(os.environ.get("INGOT_E2E_DIR", "/tmp"))
+    ids = np.zeros(1, dtype=np.int32)
+    m = np.zeros(1, dtype=np.float32)
+    bad = np.array([n_vocab + 5], dtype=np.int32)
+    for backend in (b"cpu", b"metal"):
+        assert lib.ingot_e2e_greedy(path.encode(), backend, bad, 1, 1, 512, ids, m) == -1
+        assert lib.ingot_e2e_last_error() == b"token id out of range"
+    assert lib.ingot_e2e_greedy(path.encode(), b"nope", bad, 1, 1, 512, ids, m) == -1
+    assert b"unknown backend" in lib.ingot_e2e_last_error()
