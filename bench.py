@@ -251,20 +251,53 @@ def run_prefill(args, rank, world):
     del k_all, v_all, q_all
     out = torch.empty(S, h_l, D, device="cuda", dtype=torch.float16)
     gathered = torch.empty(world * S, h_l, D, device="cuda", dtype=torch.float16) if world > 1 else None  # rank-major
+    # N > 1: the gather of head outputs is fused into the kernel's epilogue — every rank stores its rows
+    # straight into all ranks' token-major [S][24][128] buffers (symmetric memory, plain peer stores over
+    # NVLink), followed by a one-element NCCL all-reduce as the cross-rank completion barrier. If symmetric
+    # memory cannot be set up the step falls back to kernel + NCCL all-gather and says so in `config`.
+    gather_mode, peer_ptrs, full, token = "none (single GPU)", None, None, None
+    if world > 1:
+        import torch.distributed as dist
+        gather_mode = "NCCL all_gather_into_tensor after the kernel"
+        if not args.no_fused_gather:
+            try:
+                import torch.distributed._symmetric_memory as symm
+                full = symm.empty((S, H, D), dtype=torch.float16, device="cuda")
+                hdl = symm.rendezvous(full, dist.group.WORLD)
+                peer_ptrs = [int(x) for x in hdl.buffer_ptrs]
+                token = torch.zeros(1, device="cuda")
+                gather_mode = "fused: peer stores from the kernel epilogue + 1-element all-reduce barrier"
+            except Exception as e:  # noqa: BLE001
+                peer_ptrs = None
+                gather_mode += f" (symmetric memory unavailable: {type(e).__name__})"
 
     def step():
-        ib.attn_prefill(kv, 0, q, 0, out=out, impl=2)
-        if world > 1:
-            import torch.distributed as dist
-            dist.all_gather_into_tensor(gathered, out)
+        if peer_ptrs is not None:
+            ib.attn_prefill_gather(kv, 0, q, 0, peer_ptrs, ib.F16, H, rank * h_l)
+            dist.all_reduce(token)
+        else:
+            ib.attn_prefill(kv, 0, q, 0, out=out, impl=2)
+            if world > 1:
+                dist.all_gather_into_tensor(gathered, out)
 
     def step_kernel_only():
         ib.attn_prefill(kv, 0, q, 0, out=out, impl=2)
 
+    gather_checked = None
+    if peer_ptrs is not None:  # one-time check of the fused gather against kernel + NCCL all-gather
+        step()
+        step_kernel_only()
+        dist.all_gather_into_tensor(gathered, out)
+        torch.cuda.synchronize()
+        ref = gathered.view(world, S, h_l, D).permute(1, 0, 2, 3).reshape(S, H, D)
+        gather_checked = bool(torch.equal(ref, full))
+        if not gather_checked:
+            raise SystemExit("fused gather differs from kernel + NCCL all-gather")
+
     steps = max(1, min(args.steps, args.prefill_steps))
     with ClockSampler(torch.cuda.current_device()) as clk:
         ms = timed(step, steps, args.warmup, world)
-    ms_kernel = timed(step_kernel_only, steps, 1, world)
+    ms_kernel = ms if world == 1 else timed(step_kernel_only, steps, 3, world)
     assert kv.status() == 0
     flops = prefill_flops(S)
     value = flops * steps / (ms * 1e-3) / 1e12
@@ -298,8 +331,102 @@ def run_prefill(args, rank, world):
                                     else f"PROFILING CASE: {S}-token causal prefill (not the benchmark configuration)"), "n_tok": S,
                        "n_head": H, "n_head_kv": HKV, "head_dim": D,
                        "l2": "inputs larger than L2 (q+out 400 MB, K/V 134 MB)",
-                       "parallelism": f"KV-head sharding x{world}" + (" + NCCL all-gather of head outputs (timed)" if world > 1 else "")}}
+                       "parallelism": f"KV-head sharding x{world}", "gather": gather_mode, "gather_verified": gather_checked}}
 
+
+
+# ------------------------------------------------------------------------------------------------
+# the other configurations (parity-test shapes; reported for completeness, not headline lines)
+# ------------------------------------------------------------------------------------------------
+
+def run_chunked(args, rank, world, n_tok, pos0, label):
+    """K1 + K2 of one layer: n_tok new tokens appended at pos0 (configs[0] / configs[2]), one GPU per rank (replicas)."""
+    import torch
+    import ingot_b200 as ib
+    torch.manual_seed(2)
+    kv = ib.KVCache(ib.KV_CONTIGUOUS, N_LAYER, HKV, pos0 + n_tok)
+    for l in range(N_LAYER):
+        kv.layer_view(l, "k").copy_(torch.randn(HKV, pos0 + n_tok, D, device="cuda").half())
+        kv.layer_view(l, "v").copy_(torch.randn(HKV, pos0 + n_tok, D, device="cuda").half())
+    q = torch.randn(N_LAYER, n_tok, H, D, device="cuda")
+    k = torch.randn(N_LAYER, n_tok, HKV, D, device="cuda")
+    v = torch.randn(N_LAYER, n_tok, HKV, D, device="cuda")
+    out = torch.empty(N_LAYER, n_tok, H, D, device="cuda")
+    inv = torch.from_numpy(inv_freq_table()).cuda()
+    res = {}
+    for impl in (0, 1, 2):
+        def step():
+            for l in range(N_LAYER):
+                qr = ib.rope_kv_append(kv, l, q[l], k[l], v[l], inv, pos0)
+                ib.attn_prefill(kv, l, qr, pos0, out=out[l], impl=impl)
+        steps = max(1, min(args.steps, 10))
+        ms = timed(step, steps, args.warmup, world)
+        res[impl] = ms / steps / N_LAYER
+    flops = 4 * H * D * (n_tok * pos0 + n_tok * n_tok // 2)
+    best = res[0]
+    peaks = measured_peaks()
+    tf = flops / (best * 1e-3) / 1e12
+    return {"metric": f"causal GQA chunked prefill TFLOP/s ({label})", "value": round(world * tf, 2), "unit": "TFLOP/s",
+            "ms_per_step": round(best * N_LAYER, 4), "scaling": "weak", "dtype": "f16 MMA operands / f32 accumulate+softmax",
+            "roofline": {"bound": "tensor", "achieved": round(tf, 2), "peak": peaks["tflops_burst"], "unit": "TFLOP/s",
+                         "frac": round(tf / peaks["tflops_burst"], 4), "traffic": None,
+                         "us_per_layer": {"auto": round(res[0] * 1e3, 2), "warp_mma": round(res[1] * 1e3, 2),
+                                          "tcgen05": round(res[2] * 1e3, 2)}},
+            "gpu_launches": 2 * N_LAYER * max(1, min(args.steps, 10)),
+            "config": {"workload": label, "n_tok": n_tok, "pos0": pos0, "n_layer": N_LAYER, "flops_per_layer": flops,
+                       "includes": "RoPE+append (K1) and attention (K2) per layer, launched from Python",
+                       "parallelism": f"replicas x{world}"}}
+
+
+def run_batched_decode(args, rank, world):
+    """configs[3]: 64 sequences, lengths U{256..8192}, paged f16 cache with permuted 16-token blocks, bf16 queries;
+    sequences sharded over the ranks by length-balanced (LPT) assignment, no collective on the data path."""
+    import torch
+    import ingot_b200 as ib
+    from ingot_b200 import workloads as W
+    lens_all = W.c4_lengths()
+    mine = W.lpt_assign(lens_all, world)[rank]
+    lens = lens_all[mine]
+    n_seq = len(lens)
+    nb = int(((lens + 15) // 16).sum())
+    perm = np.random.default_rng([3, 2, rank]).permutation(nb).astype(np.int32)
+    bt = torch.from_numpy(W.block_tables(lens, perm)).cuda()
+    n_layers = 4  # distinct per-layer pools so that a step streams more than L2 holds
+    kv = ib.KVCache(ib.KV_PAGED, n_layers, HKV, nb, max_seqs=n_seq)
+    torch.manual_seed(3 + rank)
+    for l in range(n_layers):
+        kv.layer_view(l, "k").copy_(torch.randn(nb, HKV, 16, D, device="cuda").half())
+        kv.layer_view(l, "v").copy_(torch.randn(nb, HKV, 16, D, device="cuda").half())
+    q = torch.randn(n_layers, n_seq, H, D, device="cuda").bfloat16()
+    out = torch.empty(n_layers, n_seq, H, D, device="cuda")
+    lens_d = torch.from_numpy(lens).cuda()
+
+    def step():
+        ib.attn_decode_layers(kv, 0, q, out, seq_lens=lens_d, max_seq_len=int(lens.max()), block_tables=bt,
+                              chunk_keys=args.chunk_keys)
+
+    ms = timed(step, args.steps, args.warmup, world)
+    assert kv.status() == 0
+    bytes_rank = int(lens.astype(np.int64).sum()) * HKV * D * 2 * 2 * n_layers
+    tot = torch.tensor([float(bytes_rank)], device="cuda", dtype=torch.float64)
+    mx = tot.clone()
+    if world > 1:
+        import torch.distributed as dist
+        dist.all_reduce(tot)
+        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+    value = float(tot.item()) * args.steps / (ms * 1e-3) / 1e9
+    peaks = measured_peaks()
+    per_gpu = bytes_rank * args.steps / (ms * 1e-3) / 1e9
+    return {"metric": "batched paged decode attention KV-cache HBM GB/s (64 sequences, lengths 256..8192)", "value": round(value, 1),
+            "unit": "GB/s", "ms_per_step": round(ms / args.steps, 5), "scaling": "strong",
+            "dtype": "f16 KV / f16 MMA operands (bf16 q converted on load) / f32 accumulate+softmax",
+            "roofline": {"bound": "hbm", "achieved": round(per_gpu, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                         "frac": round(per_gpu / peaks["hbm_gbs"], 4), "traffic": None},
+            "gpu_launches": args.steps * (n_layers + min(4, n_layers)),
+            "config": {"workload": "configs[3]: 64-sequence paged decode, 16-token blocks, random block permutation",
+                       "n_seq_this_rank": n_seq, "layers_per_step": n_layers, "kv_bytes_per_layer_this_rank": bytes_rank // n_layers,
+                       "load_imbalance_max_over_mean": round(float(mx.item()) * world / float(tot.item()), 4),
+                       "parallelism": f"sequence sharding x{world} (LPT length balancing, no collective)"}}
 
 # ------------------------------------------------------------------------------------------------
 # CPU reference legs
@@ -402,13 +529,15 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ingot", choices=["ingot", "reference"])
-    ap.add_argument("--workload", default="decode_c2", choices=["decode_c2", "prefill_c5"])
+    ap.add_argument("--workload", default="decode_c2", choices=["decode_c2", "prefill_c5", "c1_prefill128", "c3_chunked", "c4_batched"])
     ap.add_argument("--chunk-keys", type=int, default=0, help="decode split size (0 = library default)")
     ap.add_argument("--prefill-steps", type=int, default=10, help="cap on timed prefill steps (each is ~10 ms)")
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS,
                     help="prefill length; anything but 32768 is a profiling case, not the benchmark configuration")
     ap.add_argument("--no-secondary", action="store_true", help="skip the non-headline workload")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-fused-gather", action="store_true",
+                    help="prefill at N > 1: kernel + NCCL all-gather instead of the fused peer-store epilogue")
     ap.add_argument("--no-graph", action="store_true", help="decode: launch the 28 layers from Python instead of replaying a CUDA graph")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
@@ -420,7 +549,14 @@ def main():
         return
 
     rank, world, _ = dist_setup(args.gpus)
-    primary, secondary = (run_decode, run_prefill) if args.workload == "decode_c2" else (run_prefill, run_decode)
+    if args.workload in ("c1_prefill128", "c3_chunked", "c4_batched"):
+        args.no_secondary = args.no_cpu = True
+        primary = {"c1_prefill128": lambda a, r, w: run_chunked(a, r, w, 128, 0, "configs[0]: 128-token prefill at position 0"),
+                   "c3_chunked": lambda a, r, w: run_chunked(a, r, w, 512, 3584, "configs[2]: 512-token chunk onto 3584 cached positions"),
+                   "c4_batched": run_batched_decode}[args.workload]
+        secondary = None
+    else:
+        primary, secondary = (run_decode, run_prefill) if args.workload == "decode_c2" else (run_prefill, run_decode)
     line = primary(args, rank, world)
     other = None if args.no_secondary else secondary(args, rank, world)
     if rank == 0:
@@ -428,6 +564,8 @@ def main():
                "steps": line.pop("steps", args.steps), "warmup": args.warmup, "ms_per_step": line.pop("ms_per_step"),
                "higher_is_better": True, "scaling": line.pop("scaling"), "vs_baseline": None, "dtype": line.pop("dtype"),
                "data": "synthetic"}
+        line.setdefault("clocks", None)
+        line.setdefault("e2e", None)
         out.update(line)
         if other is not None:
             out["prefill" if args.workload == "decode_c2" else "decode"] = other

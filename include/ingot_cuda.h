@@ -154,6 +154,19 @@ int ingot_attn_prefill(ingot_kv* kv, int layer, const void* q_dev, int q_dtype, 
                        int n_head, int q_pos0, int n_tok, const int32_t* block_table_dev, int impl,
                        void* stream);
 
+/* K2 with the gather of head outputs fused into its epilogue, for a prefill sharded by KV head over
+ * the GPUs of one NVLink/NVSwitch box (no counterpart in the reference, which is single-device; it
+ * replaces "attn_prefill, then an all-gather of the head outputs"). This GPU's cache holds n_head_kv / N
+ * KV heads and q_dev its n_head query heads [n_tok][n_head][128]. Every output row is written, by
+ * plain stores from the kernel's epilogue, to each of the n_out (<= 8) buffers in out_ptrs — this GPU's
+ * own and its peers' (peer-mapped device pointers, e.g. from symmetric memory) — in the token-major
+ * layout [n_tok][out_n_head][128] at head index out_head0 + local head. When every rank has run it
+ * and the ranks have synchronised (a barrier on the stream), each buffer holds all heads. tcgen05
+ * kernel, contiguous caches only. out_ptrs is a host array read during the call. */
+int ingot_attn_prefill_gather(ingot_kv* kv, int layer, const void* q_dev, int q_dtype, void* const* out_ptrs, int n_out,
+                              int out_dtype, int n_head, int out_n_head, int out_head0, int q_pos0, int n_tok,
+                              void* stream);
+
 /* ---- Host-buffer convenience call ---------------------------------------------------------------
  * One layer of the reference's attention stage with HOST inputs/outputs, as a CPU-side caller sees
  * it (q,k,v from the projections in; attention output for the wo projection out):

@@ -64,9 +64,14 @@ struct Bars {
     uint32_t abort_flag;
 };
 
+constexpr int kMaxOutputs = 8;
+
 struct Sm100Params {
     const void* q;
-    void* out;
+    void* outs[kMaxOutputs];  // every output row is stored to each of these (this GPU's buffer and, for a
+    int n_outs;               // KV-head-sharded prefill, the peers' buffers: plain peer stores over NVLink)
+    int out_n_head;           // heads per token in the destination layout [token][out_n_head][128]
+    int out_head0;            // destination index of this call's first query head
     int* status;
     int q_dtype, out_dtype;
     int n_head, group;
@@ -410,27 +415,62 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_k, const __gri
         }
         if (ok) {
             tc_fence_after();
+            // O / l goes through shared memory (the tile's Q buffer, idle once its last MMA has retired) so
+            // that the global stores are row-contiguous: a warp instruction writes two whole 256-byte row
+            // slices instead of 32 scattered 16-byte pieces. That matters most when the rows also go to
+            // peer GPUs. One pass moves 256 bytes per row: all 128 dims as f16, or 64 dims as f32.
             const float inv = 1.0f / l;
-            const size_t obase = ((size_t)tok * p.n_head + head) * kHeadDim;
+            unsigned char* stage = smem_al + kOffQ + q * kQBytes;  // [128 rows][256 B], 16-byte pieces XOR-swizzled by row
+            const int n_pass = p.out_dtype == INGOT_F32 ? 2 : 1;
+            const int warp_row0 = (warp & 3) << 5;
+            for (int ps = 0; ps < n_pass; ps++) {
+                if (ps) __syncwarp();
+                unsigned char* my = stage + row_in_tile * 256;
+                if (p.out_dtype == INGOT_F32) {
 #pragma unroll
-            for (int c = 0; c < 4; c++) {
-                float o[32];
-                tmem_ld32(o_tmem + c * 32, o);
-                tmem_wait_ld();
-                if (valid) {
-                    if (p.out_dtype == INGOT_F32) {
-                        float4* dst = reinterpret_cast<float4*>(static_cast<float*>(p.out) + obase + c * 32);
+                    for (int c = 0; c < 2; c++) {
+                        float o[32];
+                        tmem_ld32(o_tmem + ps * 64 + c * 32, o);
+                        tmem_wait_ld();
 #pragma unroll
-                        for (int i = 0; i < 8; i++)
-                            dst[i] = make_float4(o[4 * i] * inv, o[4 * i + 1] * inv, o[4 * i + 2] * inv, o[4 * i + 3] * inv);
-                    } else {
-                        uint4* dst = reinterpret_cast<uint4*>(static_cast<__half*>(p.out) + obase + c * 32);
+                        for (int i = 0; i < 8; i++) {
+                            const int piece = c * 8 + i;
+                            *reinterpret_cast<float4*>(my + ((piece ^ (row_in_tile & 7)) << 4)) =
+                                make_float4(o[4 * i] * inv, o[4 * i + 1] * inv, o[4 * i + 2] * inv, o[4 * i + 3] * inv);
+                        }
+                    }
+                } else {
 #pragma unroll
-                        for (int i = 0; i < 4; i++)
-                            dst[i] = make_uint4(pack_half2_rn(o[8 * i] * inv, o[8 * i + 1] * inv),
-                                                pack_half2_rn(o[8 * i + 2] * inv, o[8 * i + 3] * inv),
-                                                pack_half2_rn(o[8 * i + 4] * inv, o[8 * i + 5] * inv),
-                                                pack_half2_rn(o[8 * i + 6] * inv, o[8 * i + 7] * inv));
+                    for (int c = 0; c < 4; c++) {
+                        float o[32];
+                        tmem_ld32(o_tmem + c * 32, o);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int i = 0; i < 4; i++) {
+                            const int piece = c * 4 + i;
+                            *reinterpret_cast<uint4*>(my + ((piece ^ (row_in_tile & 7)) << 4)) =
+                                make_uint4(pack_half2_rn(o[8 * i] * inv, o[8 * i + 1] * inv),
+                                           pack_half2_rn(o[8 * i + 2] * inv, o[8 * i + 3] * inv),
+                                           pack_half2_rn(o[8 * i + 4] * inv, o[8 * i + 5] * inv),
+                                           pack_half2_rn(o[8 * i + 6] * inv, o[8 * i + 7] * inv));
+                        }
+                    }
+                }
+                __syncwarp();
+                // Each warp copies out the 32 rows its own lanes staged: two rows per instruction.
+                const int piece = lane & 15;
+#pragma unroll 4
+                for (int it = 0; it < 16; it++) {
+                    const int r = warp_row0 + it * 2 + (lane >> 4);
+                    const int Rr = row_base + q * kTileRows + r;
+                    if (Rr < n_rows) {
+                        const uint4 val = *reinterpret_cast<const uint4*>(stage + r * 256 + ((piece ^ (r & 7)) << 4));
+                        const size_t row_elem = ((size_t)(Rr / G) * p.out_n_head + p.out_head0 + kvh * G + Rr % G) * kHeadDim;
+                        const size_t byte_off = p.out_dtype == INGOT_F32 ? (row_elem + ps * 64) * 4 + piece * 16
+                                                                         : row_elem * 2 + piece * 16;
+#pragma unroll
+                        for (int d = 0; d < kMaxOutputs; d++)  // unrolled: keeps the pointer table in the parameter bank
+                            if (d < p.n_outs) *reinterpret_cast<uint4*>(static_cast<unsigned char*>(p.outs[d]) + byte_off) = val;
                     }
                 }
             }
@@ -478,8 +518,13 @@ void free_prefill_sm100_state(ingot_kv* kv) {
     kv->tmaps = nullptr;
 }
 
-int launch_attn_prefill_sm100(ingot_kv* kv, int layer, const void* q, int q_dtype, void* out, int out_dtype,
-                              int n_head, int q_pos0, int n_tok, cudaStream_t stream) {
+int launch_attn_prefill_sm100(ingot_kv* kv, int layer, const void* q, int q_dtype, void* const* outs, int n_outs,
+                              int out_dtype, int n_head, int out_n_head, int out_head0, int q_pos0, int n_tok,
+                              cudaStream_t stream) {
+    if (n_outs < 1 || n_outs > kMaxOutputs) {
+        ingot_set_error("tcgen05 prefill: between 1 and 8 output buffers");
+        return INGOT_ERR_INVALID;
+    }
     if (kv->layout != INGOT_KV_CONTIGUOUS) {
         ingot_set_error("tcgen05 prefill: contiguous cache required");
         return INGOT_ERR_UNSUPPORTED;
@@ -515,7 +560,9 @@ int launch_attn_prefill_sm100(ingot_kv* kv, int layer, const void* q, int q_dtyp
         st->built[layer] = 1;
     }
     Sm100Params p;
-    p.q = q; p.out = out; p.status = kv->status_dev;
+    p.q = q; p.status = kv->status_dev;
+    for (int i = 0; i < kMaxOutputs; i++) p.outs[i] = i < n_outs ? outs[i] : nullptr;
+    p.n_outs = n_outs; p.out_n_head = out_n_head; p.out_head0 = out_head0;
     p.q_dtype = q_dtype; p.out_dtype = out_dtype;
     p.n_head = n_head; p.group = n_head / kv->n_head_kv;
     p.q_pos0 = q_pos0; p.n_tok = n_tok;

@@ -300,11 +300,34 @@ int ingot_attn_prefill(ingot_kv* kv, int layer, const void* q_dev, int q_dtype, 
         ingot_set_error("ingot_attn_prefill: the tcgen05 kernel needs a contiguous cache");
         return INGOT_ERR_UNSUPPORTED;
     }
-    // The tcgen05 kernel works on 256-row tiles; below a few tiles per SM the warp-MMA kernel's
-    // finer 64-row tiles fill the GPU better.
-    const bool use_sm100 = impl == 2 || (impl == 0 && tma_ok && size_t(n_tok) * n_head >= 16384);
-    if (use_sm100) return launch_attn_prefill_sm100(kv, layer, q_dev, q_dtype, out_dev, out_dtype, n_head, q_pos0, n_tok, s);
+    // The tcgen05 kernel works on 256-row tiles of one KV head. Measured on a B200: a 512-token chunk onto
+    // 3584 cached positions (48 CTAs) takes 81 us against 166 us for the warp-MMA kernel, and at 128 tokens
+    // the two are level; below that the warp-MMA kernel's finer 64-row tiles win.
+    const bool use_sm100 = impl == 2 || (impl == 0 && tma_ok && size_t(n_tok) * n_head >= 4096);
+    if (use_sm100)
+        return launch_attn_prefill_sm100(kv, layer, q_dev, q_dtype, &out_dev, 1, out_dtype, n_head, n_head, 0, q_pos0, n_tok, s);
     return launch_attn_prefill_mma(kv, layer, q_dev, q_dtype, out_dev, out_dtype, n_head, q_pos0, n_tok, block_table_dev, s);
+}
+
+int ingot_attn_prefill_gather(ingot_kv* kv, int layer, const void* q_dev, int q_dtype, void* const* out_ptrs, int n_out,
+                              int out_dtype, int n_head, int out_n_head, int out_head0, int q_pos0, int n_tok,
+                              void* stream) {
+    INGOT_REQUIRE(kv != nullptr, "ingot_attn_prefill_gather: kv is null");
+    INGOT_REQUIRE(layer >= 0 && layer < kv->n_layer, "ingot_attn_prefill_gather: layer out of range");
+    INGOT_REQUIRE(n_tok >= 0 && q_pos0 >= 0, "ingot_attn_prefill_gather: negative range");
+    if (n_tok == 0) return INGOT_OK;
+    INGOT_REQUIRE(q_dev && out_ptrs && n_out >= 1 && n_out <= 8, "ingot_attn_prefill_gather: 1 to 8 output buffers");
+    for (int i = 0; i < n_out; i++) INGOT_REQUIRE(out_ptrs[i] != nullptr, "ingot_attn_prefill_gather: null output buffer");
+    INGOT_REQUIRE(n_head >= kv->n_head_kv && n_head % kv->n_head_kv == 0, "ingot_attn_prefill_gather: n_head must be a multiple of n_head_kv");
+    INGOT_REQUIRE(out_head0 >= 0 && out_head0 + n_head <= out_n_head, "ingot_attn_prefill_gather: head range exceeds the destination layout");
+    if (kv->layout != INGOT_KV_CONTIGUOUS || (q_dtype != INGOT_F32 && q_dtype != INGOT_F16 && q_dtype != INGOT_BF16) ||
+        (out_dtype != INGOT_F32 && out_dtype != INGOT_F16)) {
+        ingot_set_error("ingot_attn_prefill_gather: needs a contiguous cache and f32/f16/bf16 q, f32/f16 out");
+        return INGOT_ERR_UNSUPPORTED;
+    }
+    INGOT_REQUIRE(size_t(q_pos0) + n_tok <= size_t(kv->capacity), "context window exceeded");
+    return launch_attn_prefill_sm100(kv, layer, q_dev, q_dtype, out_ptrs, n_out, out_dtype, n_head, out_n_head, out_head0,
+                                     q_pos0, n_tok, static_cast<cudaStream_t>(stream));
 }
 
 int ingot_attn_layers_host(ingot_kv* kv, int layer_begin, int layer_count, const float* q_host, const float* k_host,

@@ -33,6 +33,7 @@ ABI = {
     "ingot_attn_decode_layers": (_I, [_P, _I, _I, _P, _I, _P, _I, _I, _I, _P, _I, _P, _I, _I, _P]),
     "ingot_attn_decode_noalloc": (_I, [_P, _P, _I, _I, _P, _I, _P, _I, _I, _I, _I, _P]),
     "ingot_attn_prefill": (_I, [_P, _I, _P, _I, _P, _I, _I, _I, _I, _P, _I, _P]),
+    "ingot_attn_prefill_gather": (_I, [_P, _I, _P, _I, C.POINTER(_P), _I, _I, _I, _I, _I, _I, _I, _P]),
     "ingot_attn_layer_host": (_I, [_P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _P]),
     "ingot_attn_layers_host": (_I, [_P, _I, _I, _P, _P, _P, _P, _P, _I, _I, _I, _P]),
     "ingot_stream_sync": (_I, [_P]),
@@ -185,6 +186,14 @@ def attn_prefill(kv, layer, q, q_pos0, out=None, out_dtype=None, block_table=Non
     _check(lib().ingot_attn_prefill(kv.handle, layer, _ptr(q), _dtype_code(q), _ptr(out), _dtype_code(out), n_head,
                                     q_pos0, n_tok, _ptr(block_table), impl, _stream()))
     return out
+
+
+def attn_prefill_gather(kv, layer, q, q_pos0, out_ptrs, out_dtype_code, out_n_head, out_head0):
+    """q [n_tok,H_local,128]; out_ptrs: device addresses (ints) of the destination buffers [n_tok,out_n_head,128]."""
+    assert q.is_contiguous()
+    arr = (C.c_void_p * len(out_ptrs))(*[C.c_void_p(int(x)) for x in out_ptrs])
+    _check(lib().ingot_attn_prefill_gather(kv.handle, layer, _ptr(q), _dtype_code(q), arr, len(out_ptrs), out_dtype_code,
+                                           q.shape[1], out_n_head, out_head0, q_pos0, q.shape[0], _stream()))
 
 
 def attn_layer_host(kv, layer, q_host, k_host, v_host, out_host, inv_freq_dev, pos0):

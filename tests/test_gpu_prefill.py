@@ -123,3 +123,28 @@ def test_prefill_rejects_bad_arguments():
         ib.attn_prefill(kv, 0, q, 60)
     with pytest.raises(ib.IngotError, match="multiple of n_head_kv"):
         ib.attn_prefill(kv, 0, helpers.to_dev(np.zeros((8, 7, D), dtype=np.float16)), 0)
+
+
+@pytest.mark.parametrize("n_shards,out_f16", [(2, True), (4, False), (8, True)])
+def test_kv_head_shards_with_fused_gather_reproduce_unsharded_output(n_shards, out_f16):
+    """KV-head sharding: every shard runs the same kernel on its own heads and stores its rows into every
+    destination buffer (here: two buffers on one GPU standing in for this GPU's and a peer's). The
+    gathered token-major result must equal the unsharded prefill bit for bit."""
+    import torch
+    import ingot_b200 as ib
+    wl = W.c1_prefill128(seed=31, n_tok=300)
+    dt = torch.float16 if out_f16 else torch.float32
+    full, _, _ = helpers.gpu_prefill(wl, impl=2, out_f16=out_f16)
+    inv = helpers.to_dev(helpers.inv_freq())
+    dst = [torch.zeros(300, H, D, device="cuda", dtype=dt) for _ in range(2)]
+    hkv_l, h_l = HKV // n_shards, H // n_shards
+    for r in range(n_shards):
+        kv = ib.KVCache(ib.KV_CONTIGUOUS, 1, hkv_l, 300)
+        q = helpers.to_dev(wl.q[:, r * h_l:(r + 1) * h_l])
+        k = helpers.to_dev(wl.k[:, r * hkv_l:(r + 1) * hkv_l])
+        v = helpers.to_dev(wl.v[:, r * hkv_l:(r + 1) * hkv_l])
+        qr = ib.rope_kv_append(kv, 0, q, k, v, inv, 0)
+        ib.attn_prefill_gather(kv, 0, qr, 0, [d.data_ptr() for d in dst], ib.F16 if out_f16 else ib.F32, H, r * h_l)
+        torch.cuda.synchronize()
+        assert kv.status() == 0
+    assert torch.equal(dst[0], full) and torch.equal(dst[1], full)
