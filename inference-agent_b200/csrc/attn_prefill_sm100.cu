@@ -46,6 +46,13 @@ constexpr int kQBytes = kTileRows * kHeadDim * 2;       // 32 KB per Q tile
 constexpr int kThreads = 384;
 constexpr uint32_t kTmemCols = 512;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
+#ifndef INGOT_POLY_EVERY
+#define INGOT_POLY_EVERY 1000000
+#endif
+// One score pair in this many takes the FMA-pipe polynomial exp2 instead of MUFU ex2. Measured on a B200
+// at 32768 tokens: never 1233, every 6th 1129, every 4th 1103, every 2nd 1088 TFLOP/s — the softmax warps
+// are bound by instruction issue and latency, not by MUFU throughput, so the default is "never".
+constexpr int kPolyEvery = INGOT_POLY_EVERY;
 
 // shared memory map (dynamic, 1024-byte aligned base)
 constexpr int kOffQ = 0;                                  // 2 Q tiles
@@ -178,6 +185,40 @@ __device__ __forceinline__ float ex2(float x) {
     return y;
 }
 
+// Packed f32x2 arithmetic (sm_100): one instruction works on two floats.
+__device__ __forceinline__ void ffma2(float& d0, float& d1, float a0, float a1, float b0, float b1, float c0, float c1) {
+    asm("{\n.reg .b64 ra, rb, rc, rd;\n"
+        "mov.b64 ra, {%2, %3};\nmov.b64 rb, {%4, %5};\nmov.b64 rc, {%6, %7};\n"
+        "fma.rn.f32x2 rd, ra, rb, rc;\nmov.b64 {%0, %1}, rd;\n}\n"
+        : "=f"(d0), "=f"(d1) : "f"(a0), "f"(a1), "f"(b0), "f"(b1), "f"(c0), "f"(c1));
+}
+__device__ __forceinline__ void fadd2(float& d0, float& d1, float a0, float a1, float b0, float b1) {
+    asm("{\n.reg .b64 ra, rb, rd;\n"
+        "mov.b64 ra, {%2, %3};\nmov.b64 rb, {%4, %5};\n"
+        "add.rn.f32x2 rd, ra, rb;\nmov.b64 {%0, %1}, rd;\n}\n"
+        : "=f"(d0), "=f"(d1) : "f"(a0), "f"(a1), "f"(b0), "f"(b1));
+}
+
+// 2^x for a pair on the FMA pipe instead of the MUFU pipe: round x to an integer n with the
+// 1.5*2^23 trick, evaluate a degree-4 minimax polynomial of 2^f on f = x - n in [-0.5, 0.5]
+// (max relative error 2.7e-6, far below the f16 rounding of P) and add n to the exponent field.
+// Inputs are clamped at -126 (masked scores are -inf; anything that small rounds to 0 in f16 anyway).
+__device__ __forceinline__ void exp2_poly2(float& r0, float& r1, float x0, float x1) {
+    constexpr float kMagic = 12582912.f;  // 1.5 * 2^23
+    x0 = fmaxf(x0, -126.f);
+    x1 = fmaxf(x1, -126.f);
+    float t0, t1, n0, n1, f0, f1, p0, p1;
+    fadd2(t0, t1, x0, x1, kMagic, kMagic);
+    fadd2(n0, n1, t0, t1, -kMagic, -kMagic);
+    ffma2(f0, f1, n0, n1, -1.f, -1.f, x0, x1);
+    ffma2(p0, p1, f0, f1, 0.009570102207362652f, 0.009570102207362652f, 0.05591785907745361f, 0.05591785907745361f);
+    ffma2(p0, p1, p0, p1, f0, f1, 0.240247443318367f, 0.240247443318367f);
+    ffma2(p0, p1, p0, p1, f0, f1, 0.6931217908859253f, 0.6931217908859253f);
+    ffma2(p0, p1, p0, p1, f0, f1, 0.9999992847442627f, 0.9999992847442627f);
+    r0 = __int_as_float(__float_as_int(p0) + (__float_as_int(t0) << 23));
+    r1 = __int_as_float(__float_as_int(p1) + (__float_as_int(t1) << 23));
+}
+
 // Shared-memory matrix descriptor, 128-byte swizzle, descriptor version 1 (sm_100).
 // lbo/sbo in bytes: K-major operands use sbo = 1024 (eight 128-byte rows) and ignore lbo;
 // MN-major operands use lbo = distance between 64-element column blocks, sbo = 1024.
@@ -218,10 +259,10 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_k, const __gri
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; s++) { mbar_init(bar_addr(&bars->kv_full[s]), 1); mbar_init(bar_addr(&bars->kv_empty[s]), 1); }
-        mbar_init(bar_addr(&bars->q_ready), 256);
+        mbar_init(bar_addr(&bars->q_ready), 8);      // one arrival per softmax warp
         for (int q = 0; q < 2; q++) {
             mbar_init(bar_addr(&bars->s_ready[q]), 1);
-            mbar_init(bar_addr(&bars->p_ready[q]), 128);
+            mbar_init(bar_addr(&bars->p_ready[q]), 4);  // one arrival per warp of the tile
             mbar_init(bar_addr(&bars->o_final[q]), 1);
         }
         bars->abort_flag = 0;
@@ -343,7 +384,8 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_k, const __gri
                 *reinterpret_cast<uint4*>(qdst + (c >> 3) * kHalfBytes + (((c & 7) ^ (row_in_tile & 7)) << 4)) = val;
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy stores -> async proxy (MMA)
-            mbar_arrive(bar_addr(&bars->q_ready));
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_addr(&bars->q_ready));
         }
 
         float m_ref = 0.f, l = 0.f;
@@ -365,9 +407,16 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_k, const __gri
 #pragma unroll
                 for (int i = 0; i < 128; i++) s[i] = i <= limit ? s[i] : -INFINITY;
             }
-            float mx = s[0];
+            // Row maximum: four independent chains of nested max (maps onto 3-input max instructions).
+            float mxa = fmaxf(s[0], s[1]), mxb = fmaxf(s[2], s[3]), mxc = fmaxf(s[4], s[5]), mxd = fmaxf(s[6], s[7]);
 #pragma unroll
-            for (int i = 1; i < 128; i++) mx = fmaxf(mx, s[i]);
+            for (int i = 8; i < 128; i += 8) {
+                mxa = fmaxf(mxa, fmaxf(s[i], s[i + 1]));
+                mxb = fmaxf(mxb, fmaxf(s[i + 2], s[i + 3]));
+                mxc = fmaxf(mxc, fmaxf(s[i + 4], s[i + 5]));
+                mxd = fmaxf(mxd, fmaxf(s[i + 6], s[i + 7]));
+            }
+            float mx = fmaxf(fmaxf(mxa, mxb), fmaxf(mxc, mxd));
             mx *= p.scale_log2;  // scale > 0: max commutes with the scaling
 
             // Lazy rescale: keep the old reference max unless the new one is more than 2^8 above it.
@@ -388,24 +437,34 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_k, const __gri
                     tmem_st32(o_tmem + c * 32, ob);
                 }
             }
+            // P = 2^(s*scale - m_ref). A 128x128 tile costs as many MUFU (ex2) cycles as it costs tensor-core
+            // cycles, so one pair in kPolyEvery goes to the FMA pipe instead (exp2_poly2); scaling and the
+            // row sum use packed f32x2 instructions.
             const float neg_m = -m_ref;
-            float sum = 0.f;
+            float sum0 = 0.f, sum1 = 0.f;
 #pragma unroll
             for (int c = 0; c < 2; c++) {
                 uint32_t pk[32];
 #pragma unroll
                 for (int i = 0; i < 32; i++) {
-                    const float p0 = ex2(fmaf(s[c * 64 + 2 * i], p.scale_log2, neg_m));
-                    const float p1 = ex2(fmaf(s[c * 64 + 2 * i + 1], p.scale_log2, neg_m));
-                    sum += p0 + p1;
+                    float x0, x1, p0, p1;
+                    ffma2(x0, x1, s[c * 64 + 2 * i], s[c * 64 + 2 * i + 1], p.scale_log2, p.scale_log2, neg_m, neg_m);
+                    if (i % kPolyEvery == kPolyEvery - 1) {
+                        exp2_poly2(p0, p1, x0, x1);
+                    } else {
+                        p0 = ex2(x0);
+                        p1 = ex2(x1);
+                    }
+                    fadd2(sum0, sum1, sum0, sum1, p0, p1);
                     pk[i] = pack_half2_rn(p0, p1);
                 }
                 tmem_st32(s_tmem + c * 32, pk);
             }
-            l += sum;
+            l += sum0 + sum1;
             tmem_wait_st();
             tc_fence_before();
-            mbar_arrive(bar_addr(&bars->p_ready[q]));
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_addr(&bars->p_ready[q]));
         }
 
         // ---------------- epilogue: O / l -> global ----------------

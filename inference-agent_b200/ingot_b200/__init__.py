@@ -8,7 +8,8 @@ import ctypes as C
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(os.path.dirname(_HERE), "libingot_cuda.so")
+# INGOT_CUDA_LIB points at another build of the same library (e.g. one compiled with different tuning macros).
+LIB_PATH = os.environ.get("INGOT_CUDA_LIB") or os.path.join(os.path.dirname(_HERE), "libingot_cuda.so")
 
 F32, F16, BF16 = 0, 1, 2
 KV_CONTIGUOUS, KV_PAGED = 0, 1
