@@ -1,0 +1,112 @@
+"""The multi-layer and host-buffer entry points (the calls bench.py times) against the CPU reference."""
+import numpy as np
+import pytest
+
+import helpers
+from helpers import D, H, HKV
+from ingot_b200 import workloads as W
+
+pytestmark = pytest.mark.gpu
+
+
+def _fill_layers(kv, n_layers, n_keys, rng):
+    ks, vs = [], []
+    for l in range(n_layers):
+        k = rng.standard_normal((n_keys, HKV, D), dtype=np.float32).astype(np.float16)
+        v = rng.standard_normal((n_keys, HKV, D), dtype=np.float32).astype(np.float16)
+        kv.import_f16(l, helpers.to_dev(k), helpers.to_dev(v), 0)
+        ks.append(k)
+        vs.append(v)
+    return ks, vs
+
+
+@pytest.mark.parametrize("n_layers,n_keys", [(1, 300), (3, 1000), (6, 4096), (9, 77)])
+def test_decode_layers_matches_reference_per_layer(n_layers, n_keys):
+    """ingot_attn_decode_layers deals layers over side streams with chained launches; every layer's output
+    must still be the reference's, and a second call on the same handle must give identical bits."""
+    import torch
+    import ingot_b200 as ib
+    rng = np.random.default_rng(n_layers * 1000 + n_keys)
+    kv = ib.KVCache(ib.KV_CONTIGUOUS, n_layers, HKV, n_keys)
+    ks, vs = _fill_layers(kv, n_layers, n_keys, rng)
+    q = rng.standard_normal((n_layers, 1, H, D), dtype=np.float32)
+    qd = helpers.to_dev(q)
+    out = torch.empty(n_layers, 1, H, D, device="cuda")
+    ib.attn_decode_layers(kv, 0, qd, out, max_seq_len=n_keys)
+    torch.cuda.synchronize()
+    first = out.clone()
+    for l in range(n_layers):
+        wl = W.Decode(q[l], [ks[l]], [vs[l]], np.array([n_keys], dtype=np.int32))
+        helpers.assert_parity(out[l].cpu().numpy(), helpers.oracle_decode(wl), f"layers decode, layer {l}")
+    out.zero_()
+    ib.attn_decode_layers(kv, 0, qd, out, max_seq_len=n_keys)
+    torch.cuda.synchronize()
+    assert torch.equal(out, first) and kv.status() == 0
+
+
+def test_decode_layers_in_a_cuda_graph():
+    """The fork/join over side streams is capturable: replaying the graph reproduces the eager result."""
+    import torch
+    import ingot_b200 as ib
+    rng = np.random.default_rng(5)
+    kv = ib.KVCache(ib.KV_CONTIGUOUS, 5, HKV, 2048)
+    _fill_layers(kv, 5, 2048, rng)
+    q = helpers.to_dev(rng.standard_normal((5, 1, H, D), dtype=np.float32))
+    out = torch.empty(5, 1, H, D, device="cuda")
+    ib.attn_decode_layers(kv, 0, q, out, max_seq_len=2048)
+    torch.cuda.synchronize()
+    eager = out.clone()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        ib.attn_decode_layers(kv, 0, q, out, max_seq_len=2048)
+    for _ in range(3):
+        out.zero_()
+        g.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(out, eager)
+
+
+@pytest.mark.parametrize("n_tok,pos0", [(1, 511), (1, 0), (40, 100)])
+def test_layers_host_matches_reference(n_tok, pos0):
+    """Host buffers in and out (q/k/v projections -> attention rows), all layers in one call: RoPE + append
+    + attention must equal the reference's per-token loop on every layer."""
+    import torch
+    import ingot_b200 as ib
+    n_layers = 3
+    rng = np.random.default_rng(n_tok * 7 + pos0)
+    kv = ib.KVCache(ib.KV_CONTIGUOUS, n_layers, HKV, pos0 + n_tok)
+    ck = [rng.standard_normal((pos0, HKV, D), dtype=np.float32).astype(np.float16) for _ in range(n_layers)]
+    cv = [rng.standard_normal((pos0, HKV, D), dtype=np.float32).astype(np.float16) for _ in range(n_layers)]
+    if pos0:
+        for l in range(n_layers):
+            kv.import_f16(l, helpers.to_dev(ck[l]), helpers.to_dev(cv[l]), 0)
+    q = rng.standard_normal((n_layers, n_tok, H, D), dtype=np.float32)
+    k = rng.standard_normal((n_layers, n_tok, HKV, D), dtype=np.float32)
+    v = rng.standard_normal((n_layers, n_tok, HKV, D), dtype=np.float32)
+    qh, kh, vh = (torch.from_numpy(x).pin_memory() for x in (q, k, v))
+    oh = torch.empty(n_layers, n_tok, H, D).pin_memory()
+    inv = helpers.to_dev(helpers.inv_freq())
+    ib.attn_layers_host(kv, 0, qh, kh, vh, oh, inv, pos0)
+    torch.cuda.synchronize()
+    assert kv.status() == 0
+    for l in range(n_layers):
+        wl = W.Prefill(q[l], k[l], v[l], pos0, True, ck[l] if pos0 else None, cv[l] if pos0 else None)
+        want, _, _ = helpers.oracle_prefill(wl)
+        helpers.assert_parity(oh[l].numpy(), want, f"layers_host n_tok={n_tok} pos0={pos0} layer {l}")
+    # single-layer form writes the same rows
+    oh1 = torch.empty(n_tok, H, D).pin_memory()
+    ib.attn_layer_host(kv, 1, qh[1], kh[1], vh[1], oh1, inv, pos0)
+    torch.cuda.synchronize()
+    want1, _, _ = helpers.oracle_prefill(W.Prefill(q[1], k[1], v[1], pos0, True, ck[1] if pos0 else None, cv[1] if pos0 else None))
+    helpers.assert_parity(oh1.numpy(), want1, "layer_host")
+
+
+def test_layers_host_rejects_overflow():
+    import torch
+    import ingot_b200 as ib
+    kv = ib.KVCache(ib.KV_CONTIGUOUS, 2, HKV, 8)
+    z = torch.zeros(2, 1, H, D).pin_memory()
+    zk = torch.zeros(2, 1, HKV, D).pin_memory()
+    inv = helpers.to_dev(helpers.inv_freq())
+    with pytest.raises(ib.IngotError, match="context window exceeded"):
+        ib.attn_layers_host(kv, 0, z, zk, zk, z.clone().pin_memory(), inv, 8)
