@@ -32,6 +32,7 @@
 #include "attn_common.cuh"
 #include "ingot_internal.cuh"
 
+#include <algorithm>
 #include <mutex>
 #include <vector>
 
@@ -83,6 +84,8 @@ struct Sm100Params {
     int q_dtype, out_dtype;
     int n_head, group;
     int q_pos0, n_tok;
+    int n_split;              // > 1: grid.z CTAs share a row tile, each walks a slice of the key tiles and writes an
+    float* part;              //      unnormalised partial (o[128], m, l per row) here for prefill_merge_kernel
     float scale_log2;
 };
 
@@ -253,7 +256,12 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_k, const __gri
     const int tile256 = gridDim.x - 1 - blockIdx.x;  // heavier (later) tiles first
     const int row_base = tile256 * 2 * kTileRows;
     const int last_row = min(row_base + 2 * kTileRows, n_rows) - 1;
-    const int n_kv = (p.q_pos0 + last_row / G + 1 + kTileKeys - 1) / kTileKeys;  // K/V tiles this CTA walks
+    const int n_kv = (p.q_pos0 + last_row / G + 1 + kTileKeys - 1) / kTileKeys;  // K/V tiles these rows need
+    // Split-KV prefill (few row tiles, e.g. a 512-token chunk onto a long cache): grid.z CTAs share the rows
+    // and each walks key tiles [j0, j1). n_it may be 0 for early row tiles; such a CTA writes an empty partial.
+    const int split = blockIdx.z;
+    const int j0 = (int)((long long)n_kv * split / p.n_split), j1 = (int)((long long)n_kv * (split + 1) / p.n_split);
+    const int n_it = j1 - j0;
 
     auto bar_addr = [&](const uint64_t* b) { return smem_u32(b); };
 
@@ -283,7 +291,7 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_k, const __gri
             // ---------------- TMA producer ----------------
             int armed = 0;  // ring slots handed to TMA so far
             bool ok = true;
-            for (int it = 0; it < 2 * n_kv && ok; it++) {
+            for (int it = 0; it < 2 * n_it && ok; it++) {
                 const int s = it % kStages;
                 const uint32_t par = (uint32_t)((it / kStages) & 1);
                 ok = mbar_wait(bar_addr(&bars->kv_empty[s]), par ^ 1u, abort_flag);
@@ -291,7 +299,7 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_k, const __gri
                 const uint32_t full = bar_addr(&bars->kv_full[s]);
                 const uint32_t dst = smem_base + kOffKV + s * kStageBytes;
                 const CUtensorMap* map = (it & 1) ? &map_v : &map_k;
-                const int key0 = (it >> 1) * kTileKeys;
+                const int key0 = (j0 + (it >> 1)) * kTileKeys;
                 mbar_expect_tx(full, kStageBytes);
                 tma_load_3d(dst, map, 0, key0, kvh, full);
                 tma_load_3d(dst + kHalfBytes, map, 64, key0, kvh, full);
@@ -333,16 +341,16 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_k, const __gri
                               (!first || ks > 0) ? 1u : 0u);
             };
             bool ok = mbar_wait(bar_addr(&bars->q_ready), 0, abort_flag);
-            ok = ok && wait_full(0);
-            if (ok) {
+            ok = ok && (n_it == 0 || wait_full(0));
+            if (ok && n_it > 0) {
                 tc_fence_after();
                 issue_qk(0, stage_addr(0));
                 issue_qk(1, stage_addr(0));
                 release(0);
             }
-            for (int j = 0; j < n_kv && ok; j++) {
+            for (int j = 0; j < n_it && ok; j++) {  // j counts this CTA's key tiles from j0
                 const int it_v = 2 * j + 1, it_k = 2 * j + 2;
-                const bool more = j + 1 < n_kv;
+                const bool more = j + 1 < n_it;
                 ok = wait_full(it_v) && (!more || wait_full(it_k));
                 for (int q = 0; q < 2 && ok; q++) {
                     ok = mbar_wait(bar_addr(&bars->p_ready[q]), (uint32_t)(j & 1), abort_flag);
@@ -391,8 +399,9 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_k, const __gri
         float m_ref = 0.f, l = 0.f;
         bool ok = true;
         const int qpos_warp_min = __shfl_sync(0xffffffffu, qpos, 0);  // rows ascend with the lane
-        for (int j = 0; j < n_kv; j++) {
-            ok = mbar_wait(bar_addr(&bars->s_ready[q]), (uint32_t)(j & 1), abort_flag);
+        for (int jj = 0; jj < n_it; jj++) {
+            const int j = j0 + jj;
+            ok = mbar_wait(bar_addr(&bars->s_ready[q]), (uint32_t)(jj & 1), abort_flag);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after();
@@ -420,9 +429,11 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_k, const __gri
             mx *= p.scale_log2;  // scale > 0: max commutes with the scaling
 
             // Lazy rescale: keep the old reference max unless the new one is more than 2^8 above it.
-            bool grow = j == 0 || mx > m_ref + kRescaleThreshold;
-            if (j == 0) {
-                m_ref = mx;  // key 0 is visible to every row, so this is finite
+            // (With split keys a row may see nothing but masked columns at first: m_ref stays -inf, every P is
+            // 0, and the first finite maximum later "grows" from -inf with a rescale factor of exactly 0.)
+            bool grow = jj == 0 || mx > m_ref + kRescaleThreshold;
+            if (jj == 0) {
+                m_ref = mx;  // finite whenever key 0 is among this CTA's keys (it is visible to every row)
             } else if (__any_sync(0xffffffffu, grow)) {
                 const float alpha = grow ? ex2(m_ref - mx) : 1.0f;
                 if (grow) { m_ref = mx; l *= alpha; }
@@ -440,7 +451,7 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_k, const __gri
             // P = 2^(s*scale - m_ref). A 128x128 tile costs as many MUFU (ex2) cycles as it costs tensor-core
             // cycles, so one pair in kPolyEvery goes to the FMA pipe instead (exp2_poly2); scaling and the
             // row sum use packed f32x2 instructions.
-            const float neg_m = -m_ref;
+            const float neg_m = m_ref == -INFINITY ? 0.f : -m_ref;
             float sum0 = 0.f, sum1 = 0.f;
 #pragma unroll
             for (int c = 0; c < 2; c++) {
@@ -468,24 +479,37 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_k, const __gri
         }
 
         // ---------------- epilogue: O / l -> global ----------------
-        if (ok) {
+        if (ok && n_it > 0) {
             ok = mbar_wait(bar_addr(&bars->o_final[q]), 0, abort_flag);
             ok = __all_sync(0xffffffffu, ok);
         }
-        if (ok) {
+        const bool partial = p.n_split > 1;
+        float* part_row = nullptr;
+        if (partial && valid) {
+            part_row = p.part + (((size_t)split * gridDim.y + kvh) * n_rows + R) * kPartStride;
+            if (n_it == 0) { m_ref = -INFINITY; l = 0.f; }
+            part_row[128] = m_ref;
+            part_row[129] = l;
+        }
+        if (ok && n_it == 0 && partial && valid) {
+            // No key tile fell to this CTA: an empty partial (weight 0 in the merge).
+            for (int i = 0; i < 32; i++) reinterpret_cast<float4*>(part_row)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        if (ok && n_it > 0) {
             tc_fence_after();
             // O / l goes through shared memory (the tile's Q buffer, idle once its last MMA has retired) so
             // that the global stores are row-contiguous: a warp instruction writes two whole 256-byte row
             // slices instead of 32 scattered 16-byte pieces. That matters most when the rows also go to
             // peer GPUs. One pass moves 256 bytes per row: all 128 dims as f16, or 64 dims as f32.
-            const float inv = 1.0f / l;
+            const float inv = partial ? 1.0f : 1.0f / l;  // partials stay unnormalised
+            const bool f32_out = partial || p.out_dtype == INGOT_F32;
             unsigned char* stage = smem_al + kOffQ + q * kQBytes;  // [128 rows][256 B], 16-byte pieces XOR-swizzled by row
-            const int n_pass = p.out_dtype == INGOT_F32 ? 2 : 1;
+            const int n_pass = f32_out ? 2 : 1;
             const int warp_row0 = (warp & 3) << 5;
             for (int ps = 0; ps < n_pass; ps++) {
                 if (ps) __syncwarp();
                 unsigned char* my = stage + row_in_tile * 256;
-                if (p.out_dtype == INGOT_F32) {
+                if (f32_out) {
 #pragma unroll
                     for (int c = 0; c < 2; c++) {
                         float o[32];
@@ -524,12 +548,20 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_k, const __gri
                     const int Rr = row_base + q * kTileRows + r;
                     if (Rr < n_rows) {
                         const uint4 val = *reinterpret_cast<const uint4*>(stage + r * 256 + ((piece ^ (r & 7)) << 4));
-                        const size_t row_elem = ((size_t)(Rr / G) * p.out_n_head + p.out_head0 + kvh * G + Rr % G) * kHeadDim;
-                        const size_t byte_off = p.out_dtype == INGOT_F32 ? (row_elem + ps * 64) * 4 + piece * 16
-                                                                         : row_elem * 2 + piece * 16;
+                        size_t byte_off;
+                        if (partial) {
+                            byte_off = ((((size_t)split * gridDim.y + kvh) * n_rows + Rr) * kPartStride + ps * 64) * 4 + piece * 16;
+                        } else {
+                            const size_t row_elem = ((size_t)(Rr / G) * p.out_n_head + p.out_head0 + kvh * G + Rr % G) * kHeadDim;
+                            byte_off = f32_out ? (row_elem + ps * 64) * 4 + piece * 16 : row_elem * 2 + piece * 16;
+                        }
+                        if (partial) {
+                            *reinterpret_cast<uint4*>(reinterpret_cast<unsigned char*>(p.part) + byte_off) = val;
+                        } else {
 #pragma unroll
-                        for (int d = 0; d < kMaxOutputs; d++)  // unrolled: keeps the pointer table in the parameter bank
-                            if (d < p.n_outs) *reinterpret_cast<uint4*>(static_cast<unsigned char*>(p.outs[d]) + byte_off) = val;
+                            for (int d = 0; d < kMaxOutputs; d++)  // unrolled: keeps the pointer table in the parameter bank
+                                if (d < p.n_outs) *reinterpret_cast<uint4*>(static_cast<unsigned char*>(p.outs[d]) + byte_off) = val;
+                        }
                     }
                 }
             }
@@ -543,6 +575,36 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_k, const __gri
     if (warp == 1) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
+    }
+}
+
+// Merges the key-split partials of a prefill: one warp per (kv head, row), lane = 4 dims.
+// out = sum_s o_s 2^(m_s-M) / sum_s l_s 2^(m_s-M), the same formula the decode merge uses.
+__global__ void __launch_bounds__(256) prefill_merge_kernel(const float* __restrict__ part, void* out, int out_dtype, int n_split,
+                                                            int n_kvh, int n_rows, int G, int out_n_head, int out_head0) {
+    const long long w = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (w >= (long long)n_kvh * n_rows) return;
+    const int kvh = int(w / n_rows), R = int(w % n_rows);
+    const size_t split_stride = (size_t)n_kvh * n_rows * kPartStride;
+    const float* row = part + ((size_t)kvh * n_rows + R) * kPartStride;
+    float M = -INFINITY;
+    for (int s = 0; s < n_split; s++) M = fmaxf(M, row[s * split_stride + 128]);
+    float L = 0.f;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s = 0; s < n_split; s++) {
+        const float wgt = ex2(row[s * split_stride + 128] - M);  // an empty partial has m = -inf: weight 0
+        L += row[s * split_stride + 129] * wgt;
+        const float4 o = *reinterpret_cast<const float4*>(row + s * split_stride + lane * 4);
+        acc.x += o.x * wgt; acc.y += o.y * wgt; acc.z += o.z * wgt; acc.w += o.w * wgt;
+    }
+    const float inv = 1.0f / L;
+    const size_t e = ((size_t)(R / G) * out_n_head + out_head0 + kvh * G + R % G) * kHeadDim + lane * 4;
+    if (out_dtype == INGOT_F32) {
+        *reinterpret_cast<float4*>(static_cast<float*>(out) + e) = make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
+    } else {
+        *reinterpret_cast<uint2*>(static_cast<__half*>(out) + e) =
+            make_uint2(pack_half2_rn(acc.x * inv, acc.y * inv), pack_half2_rn(acc.z * inv, acc.w * inv));
     }
 }
 
@@ -568,12 +630,17 @@ EncodeTiledFn get_encode_fn() {
 struct Sm100State {
     std::vector<CUtensorMap> maps;  // [layer][K/V]
     std::vector<char> built;
+    float* part = nullptr;          // key-split partials, grown on demand
+    size_t part_floats = 0;
+    int num_sms = 0;
 };
 
 }  // namespace
 
 void free_prefill_sm100_state(ingot_kv* kv) {
-    delete static_cast<Sm100State*>(kv->tmaps);
+    Sm100State* st = static_cast<Sm100State*>(kv->tmaps);
+    if (st) cudaFree(st->part);
+    delete st;
     kv->tmaps = nullptr;
 }
 
@@ -628,8 +695,40 @@ int launch_attn_prefill_sm100(ingot_kv* kv, int layer, const void* q, int q_dtyp
     p.scale_log2 = 1.4426950408889634f / sqrtf(float(kHeadDim));
     INGOT_CUDA_TRY(cudaFuncSetAttribute(attn_prefill_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
     const long long n_rows = (long long)n_tok * p.group;
-    dim3 grid(unsigned((n_rows + 2 * kTileRows - 1) / (2 * kTileRows)), kv->n_head_kv);
+    const unsigned row_tiles = unsigned((n_rows + 2 * kTileRows - 1) / (2 * kTileRows));
+    if (st->num_sms == 0) {
+        int dev = 0;
+        INGOT_CUDA_TRY(cudaGetDevice(&dev));
+        INGOT_CUDA_TRY(cudaDeviceGetAttribute(&st->num_sms, cudaDevAttrMultiProcessorCount, dev));
+    }
+    // Too few row tiles to fill the GPU (one CTA per SM): split the keys over grid.z and merge afterwards.
+    // Only the last row tile is guaranteed to have many key tiles, so the split count is bounded by them.
+    const int row_ctas = int(row_tiles) * kv->n_head_kv;
+    const int kv_tiles_last = (q_pos0 + n_tok + kTileKeys - 1) / kTileKeys;
+    int n_split = 1;
+    if (n_outs == 1 && row_ctas * 2 <= st->num_sms) n_split = std::max(1, std::min({st->num_sms / row_ctas, 8, kv_tiles_last / 2}));
+    p.n_split = n_split;
+    p.part = nullptr;
+    if (n_split > 1) {
+        const size_t need = size_t(n_split) * kv->n_head_kv * n_rows * kPartStride;
+        if (need > st->part_floats) {
+            INGOT_CUDA_TRY(cudaDeviceSynchronize());
+            cudaFree(st->part);
+            st->part = nullptr;
+            st->part_floats = 0;
+            INGOT_CUDA_TRY(cudaMalloc(&st->part, need * sizeof(float)));
+            st->part_floats = need;
+        }
+        p.part = st->part;
+    }
+    dim3 grid(row_tiles, kv->n_head_kv, n_split);
     attn_prefill_sm100_kernel<<<grid, kThreads, kSmemBytes, stream>>>(st->maps[size_t(layer) * 2], st->maps[size_t(layer) * 2 + 1], p);
     INGOT_CUDA_TRY(cudaGetLastError());
+    if (n_split > 1) {
+        const long long warps = (long long)kv->n_head_kv * n_rows;
+        prefill_merge_kernel<<<unsigned((warps * 32 + 255) / 256), 256, 0, stream>>>(st->part, outs[0], out_dtype, n_split, kv->n_head_kv,
+                                                                                    int(n_rows), p.group, out_n_head, out_head0);
+        INGOT_CUDA_TRY(cudaGetLastError());
+    }
     return INGOT_OK;
 }

@@ -28,7 +28,8 @@ def test_c3_chunked_prefill(impl):
 
 
 @pytest.mark.parametrize("impl", IMPLS)
-@pytest.mark.parametrize("n_tok,pos0", [(1, 0), (2, 0), (7, 0), (43, 0), (85, 0), (86, 0), (100, 3), (129, 0), (300, 77), (64, 1000)])
+@pytest.mark.parametrize("n_tok,pos0", [(1, 0), (2, 0), (7, 0), (43, 0), (85, 0), (86, 0), (100, 3), (129, 0), (300, 77), (64, 1000),
+                                        (600, 0), (16, 5000), (200, 2000)])  # the last three split the keys over CTAs
 def test_prefill_ragged_shapes(impl, n_tok, pos0):
     rng = np.random.default_rng(n_tok * 31 + pos0)
     q = rng.standard_normal((n_tok, H, D), dtype=np.float32)
