@@ -148,8 +148,7 @@ int ingot_attn_decode_noalloc(const void* k_dev, const void* v_dev, int n_ctx, i
  *   q_dev   [n_tok][n_head][128]  q_dtype in {F32, F16, BF16}, already rotated
  *   out_dev [n_tok][n_head][128]  out_dtype in {F32, F16}
  *   block_table_dev: the sequence's block-table row (paged caches), else NULL.
- * impl: 0 = library's choice, 1 = force the warp-MMA kernel, 2 = force the tcgen05/TMEM/TMA kernel
- *       (contiguous caches only). */
+ * impl: 0 = library's choice, 1 = force the warp-MMA kernel, 2 = force the tcgen05/TMEM/TMA kernel. */
 int ingot_attn_prefill(ingot_kv* kv, int layer, const void* q_dev, int q_dtype, void* out_dev, int out_dtype,
                        int n_head, int q_pos0, int n_tok, const int32_t* block_table_dev, int impl,
                        void* stream);

@@ -84,6 +84,8 @@ struct Sm100Params {
     int q_dtype, out_dtype;
     int n_head, group;
     int q_pos0, n_tok;
+    const int32_t* block_table;  // paged cache: this sequence's block-table row (device), else null
+    int capacity;             // paged: blocks in the pool
     int n_split;              // > 1: grid.z CTAs share a row tile, each walks a slice of the key tiles and writes an
     float* part;              //      unnormalised partial (o[128], m, l per row) here for prefill_merge_kernel
     float scale_log2;
@@ -287,25 +289,48 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_k, const __gri
 
     if (warp < 4) {
         asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
-        if (warp == 0 && lane == 0) {
+        if (warp == 0) {
             // ---------------- TMA producer ----------------
+            // Contiguous cache: lane 0 issues two boxes of [128 keys][64 dims] per tile. Paged cache: a tile
+            // is eight 16-token blocks; lanes 0-7 look their block up in the block table and each issue the
+            // two [16 keys][64 dims] boxes of it, 2 KB apart in the same swizzled tile. Blocks past the last
+            // key (or invalid entries, which also raise the status word) are replaced by block 0: their
+            // columns are masked, they only have to be finite.
             int armed = 0;  // ring slots handed to TMA so far
             bool ok = true;
+            const int last_block = (p.q_pos0 + p.n_tok - 1) / kBlockTokens;
             for (int it = 0; it < 2 * n_it && ok; it++) {
                 const int s = it % kStages;
                 const uint32_t par = (uint32_t)((it / kStages) & 1);
-                ok = mbar_wait(bar_addr(&bars->kv_empty[s]), par ^ 1u, abort_flag);
-                if (!ok) break;
                 const uint32_t full = bar_addr(&bars->kv_full[s]);
+                if (lane == 0) {
+                    ok = mbar_wait(bar_addr(&bars->kv_empty[s]), par ^ 1u, abort_flag);
+                    if (ok) mbar_expect_tx(full, kStageBytes);
+                }
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                if (!ok) break;
                 const uint32_t dst = smem_base + kOffKV + s * kStageBytes;
                 const CUtensorMap* map = (it & 1) ? &map_v : &map_k;
                 const int key0 = (j0 + (it >> 1)) * kTileKeys;
-                mbar_expect_tx(full, kStageBytes);
-                tma_load_3d(dst, map, 0, key0, kvh, full);
-                tma_load_3d(dst + kHalfBytes, map, 64, key0, kvh, full);
+                if (p.block_table == nullptr) {
+                    if (lane == 0) {
+                        tma_load_3d(dst, map, 0, key0, kvh, full);
+                        tma_load_3d(dst + kHalfBytes, map, 64, key0, kvh, full);
+                    }
+                } else if (lane < kTileKeys / kBlockTokens) {
+                    const int lb = key0 / kBlockTokens + lane;
+                    int blk = lb <= last_block ? p.block_table[lb] : 0;
+                    if (blk < 0 || blk >= p.capacity) {
+                        atomicOr(p.status, kDevErrBlockRange);
+                        blk = 0;
+                    }
+                    const int z = blk * (int)gridDim.y + kvh;  // pool is [block][kv head][16][128]
+                    tma_load_3d(dst + lane * (kBlockTokens * 128), map, 0, 0, z, full);
+                    tma_load_3d(dst + kHalfBytes + lane * (kBlockTokens * 128), map, 64, 0, z, full);
+                }
                 armed = it + 1;
             }
-            if (!ok) {
+            if (!ok && lane == 0) {
                 // Drain: copies already issued must land before the CTA's shared memory is released.
                 for (int it = max(0, armed - kStages); it < armed; it++) {
                     const uint64_t t0 = globaltimer_ns();
@@ -646,14 +671,15 @@ void free_prefill_sm100_state(ingot_kv* kv) {
 
 int launch_attn_prefill_sm100(ingot_kv* kv, int layer, const void* q, int q_dtype, void* const* outs, int n_outs,
                               int out_dtype, int n_head, int out_n_head, int out_head0, int q_pos0, int n_tok,
-                              cudaStream_t stream) {
+                              const int32_t* block_table, cudaStream_t stream) {
     if (n_outs < 1 || n_outs > kMaxOutputs) {
         ingot_set_error("tcgen05 prefill: between 1 and 8 output buffers");
         return INGOT_ERR_INVALID;
     }
-    if (kv->layout != INGOT_KV_CONTIGUOUS) {
-        ingot_set_error("tcgen05 prefill: contiguous cache required");
-        return INGOT_ERR_UNSUPPORTED;
+    const bool paged = kv->layout == INGOT_KV_PAGED;
+    if (paged && block_table == nullptr) {
+        ingot_set_error("tcgen05 prefill: a paged cache needs a block table");
+        return INGOT_ERR_INVALID;
     }
     EncodeTiledFn encode = get_encode_fn();
     if (!encode) {
@@ -670,10 +696,12 @@ int launch_attn_prefill_sm100(ingot_kv* kv, int layer, const void* q, int q_dtyp
     if (!st->built[layer]) {
         for (int which = 0; which < 2; which++) {
             __half* base = (which ? kv->v : kv->k) + size_t(layer) * kv->layer_elems;
-            // [head][position][dim] f16, dim fastest; box = 64 dims x 128 positions x 1 head, 128-byte swizzle.
-            cuuint64_t dims[3] = {cuuint64_t(kHeadDim), cuuint64_t(kv->capacity), cuuint64_t(kv->n_head_kv)};
-            cuuint64_t strides[2] = {cuuint64_t(kHeadDim) * 2, cuuint64_t(kv->capacity) * kHeadDim * 2};
-            cuuint32_t box[3] = {64, cuuint32_t(kTileKeys), 1};
+            // Contiguous: [head][position][dim] f16, dim fastest; box = 64 dims x 128 positions x 1 head.
+            // Paged: [block * kv head][16 tokens][dim]; box = 64 dims x 16 tokens x 1. 128-byte swizzle.
+            cuuint64_t dims[3] = {cuuint64_t(kHeadDim), cuuint64_t(paged ? kBlockTokens : kv->capacity),
+                                  cuuint64_t(paged ? size_t(kv->capacity) * kv->n_head_kv : size_t(kv->n_head_kv))};
+            cuuint64_t strides[2] = {cuuint64_t(kHeadDim) * 2, cuuint64_t(paged ? kBlockTokens : kv->capacity) * kHeadDim * 2};
+            cuuint32_t box[3] = {64, cuuint32_t(paged ? kBlockTokens : kTileKeys), 1};
             cuuint32_t estr[3] = {1, 1, 1};
             CUresult r = encode(&st->maps[size_t(layer) * 2 + which], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, base, dims, strides,
                                 box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
@@ -692,6 +720,8 @@ int launch_attn_prefill_sm100(ingot_kv* kv, int layer, const void* q, int q_dtyp
     p.q_dtype = q_dtype; p.out_dtype = out_dtype;
     p.n_head = n_head; p.group = n_head / kv->n_head_kv;
     p.q_pos0 = q_pos0; p.n_tok = n_tok;
+    p.block_table = paged ? block_table : nullptr;
+    p.capacity = kv->capacity;
     p.scale_log2 = 1.4426950408889634f / sqrtf(float(kHeadDim));
     INGOT_CUDA_TRY(cudaFuncSetAttribute(attn_prefill_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
     const long long n_rows = (long long)n_tok * p.group;

@@ -96,6 +96,6 @@ int launch_attn_prefill_mma(ingot_kv* kv, int layer, const void* q, int q_dtype,
                             int n_head, int q_pos0, int n_tok, const int32_t* block_table, cudaStream_t stream);
 int launch_attn_prefill_sm100(ingot_kv* kv, int layer, const void* q, int q_dtype, void* const* outs, int n_outs,
                               int out_dtype, int n_head, int out_n_head, int out_head0, int q_pos0, int n_tok,
-                              cudaStream_t stream);
+                              const int32_t* block_table, cudaStream_t stream);
 void free_prefill_sm100_state(ingot_kv* kv);
 size_t decode_part_floats(int max_seqs, int capacity_keys, int n_head_kv);

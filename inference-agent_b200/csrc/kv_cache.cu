@@ -295,17 +295,14 @@ int ingot_attn_prefill(ingot_kv* kv, int layer, const void* q_dev, int q_dtype, 
     else
         INGOT_REQUIRE(block_table_dev != nullptr, "ingot_attn_prefill: paged cache needs a block table");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    const bool tma_ok = kv->layout == INGOT_KV_CONTIGUOUS;
-    if (impl == 2 && !tma_ok) {
-        ingot_set_error("ingot_attn_prefill: the tcgen05 kernel needs a contiguous cache");
-        return INGOT_ERR_UNSUPPORTED;
-    }
-    // The tcgen05 kernel works on 256-row tiles of one KV head. Measured on a B200: a 512-token chunk onto
-    // 3584 cached positions (48 CTAs) takes 81 us against 166 us for the warp-MMA kernel, and at 128 tokens
-    // the two are level; below that the warp-MMA kernel's finer 64-row tiles win.
-    const bool use_sm100 = impl == 2 || (impl == 0 && tma_ok && size_t(n_tok) * n_head >= 4096);
+    // The tcgen05 kernel works on 256-row tiles of one KV head (and splits the keys over CTAs when there
+    // are few row tiles). Measured on a B200: a 512-token chunk onto 3584 cached positions takes 47 us
+    // against 162 us for the warp-MMA kernel; at 128 tokens the warp-MMA kernel's finer 64-row tiles win
+    // (11.5 us against 20 us).
+    const bool use_sm100 = impl == 2 || (impl == 0 && size_t(n_tok) * n_head >= 4096);
     if (use_sm100)
-        return launch_attn_prefill_sm100(kv, layer, q_dev, q_dtype, &out_dev, 1, out_dtype, n_head, n_head, 0, q_pos0, n_tok, s);
+        return launch_attn_prefill_sm100(kv, layer, q_dev, q_dtype, &out_dev, 1, out_dtype, n_head, n_head, 0, q_pos0, n_tok,
+                                         block_table_dev, s);
     return launch_attn_prefill_mma(kv, layer, q_dev, q_dtype, out_dev, out_dtype, n_head, q_pos0, n_tok, block_table_dev, s);
 }
 
@@ -327,7 +324,7 @@ int ingot_attn_prefill_gather(ingot_kv* kv, int layer, const void* q_dev, int q_
     }
     INGOT_REQUIRE(size_t(q_pos0) + n_tok <= size_t(kv->capacity), "context window exceeded");
     return launch_attn_prefill_sm100(kv, layer, q_dev, q_dtype, out_ptrs, n_out, out_dtype, n_head, out_n_head, out_head0,
-                                     q_pos0, n_tok, static_cast<cudaStream_t>(stream));
+                                     q_pos0, n_tok, nullptr, static_cast<cudaStream_t>(stream));
 }
 
 int ingot_attn_layers_host(ingot_kv* kv, int layer_begin, int layer_count, const float* q_host, const float* k_host,

@@ -68,11 +68,21 @@ def test_prefill_group_sizes(n_head, n_head_kv):
     helpers.assert_parity(out.cpu().numpy(), want, f"prefill H={n_head} Hkv={n_head_kv}")
 
 
-def test_prefill_paged_equals_contiguous():
+@pytest.mark.parametrize("impl", IMPLS)
+@pytest.mark.parametrize("n_tok,pos0", [(200, 0), (64, 1000), (700, 300)])
+def test_prefill_paged_equals_contiguous(impl, n_tok, pos0):
+    """A paged cache with a random block permutation gives the same bits as the contiguous cache: the
+    kernels read the same values in the same order, only the addresses differ."""
     import torch
-    wl = W.c1_prefill128(seed=21, n_tok=200)
-    out_c, _, _ = helpers.gpu_prefill(wl, impl=1)
-    out_p, _, _ = helpers.gpu_prefill(wl, impl=1, paged=True)
+    rng = np.random.default_rng(n_tok + pos0)
+    ck = cv = None
+    if pos0:
+        ck = rng.standard_normal((pos0, HKV, D), dtype=np.float32).astype(np.float16)
+        cv = rng.standard_normal((pos0, HKV, D), dtype=np.float32).astype(np.float16)
+    wl = W.Prefill(rng.standard_normal((n_tok, H, D), dtype=np.float32), rng.standard_normal((n_tok, HKV, D), dtype=np.float32),
+                   rng.standard_normal((n_tok, HKV, D), dtype=np.float32), pos0, True, ck, cv)
+    out_c, _, _ = helpers.gpu_prefill(wl, impl=impl)
+    out_p, _, _ = helpers.gpu_prefill(wl, impl=impl, paged=True)
     assert torch.equal(out_c, out_p)
 
 
