@@ -37,9 +37,9 @@ PREFILL_TOKENS = 32768
 # DRAM bytes per launch of the dominant kernel from an ncu capture of the same kernel
 # (dram__bytes_read.sum + dram__bytes_write.sum); see profiles/ for the command and the raw figures.
 # decode: captured at the benchmark shape (profiles/attn_decode_c2.md). prefill: captured at 8192 tokens
-# (84.1 MB read + 18.4 MB written; profiles/attn_prefill_sm100_8k.md) and scaled by the 4x token count,
+# (84.1 MB read + 22.6 MB written; profiles/attn_prefill_sm100_8k.md) and scaled by the 4x token count,
 # compulsory q/K/V/out traffic growing in proportion.
-NCU_TRAFFIC = {"attn_decode_kernel": 16845824, "attn_prefill_sm100_kernel": 4 * (84126208 + 18397184)}
+NCU_TRAFFIC = {"attn_decode_kernel": 16947456, "attn_prefill_sm100_kernel": 4 * (84079872 + 22571264)}
 
 
 def measured_peaks():
@@ -169,7 +169,9 @@ def run_decode(args, rank, world):
 
     with ClockSampler(torch.cuda.current_device()) as clk:
         ms = timed(step, args.steps, args.warmup, world)
-        t_end = time.perf_counter() + 0.4  # keep the same load running so that the clock samples mean something
+        # keep the same load running so that the clock samples mean something (skipped with --no-graph,
+        # which is the profiling form of the command: a profiler should see the timed launches only)
+        t_end = time.perf_counter() + (0.0 if args.no_graph else 0.4)
         while time.perf_counter() < t_end:
             step()
         torch.cuda.synchronize()
