@@ -88,6 +88,8 @@ struct Sm100Params {
     int capacity;             // paged: blocks in the pool
     int n_split;              // > 1: grid.z CTAs share a row tile, each walks a slice of the key tiles and writes an
     float* part;              //      unnormalised partial (o[128], m, l per row) here for prefill_merge_kernel
+    unsigned long long wait_limit_ns;  // bound of every mbarrier wait
+    int test_stall_producer;  // test hook: the TMA producer issues nothing, so that the bounded waits expire
     float scale_log2;
 };
 
@@ -118,15 +120,16 @@ __device__ __forceinline__ uint64_t globaltimer_ns() {
 }
 
 // Bounded wait: returns false (and raises the CTA's abort flag) if the barrier does not complete
-// within ~2 s or another role already aborted.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag) {
+// within limit_ns (2 s in production) or another role already aborted.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag,
+                                          unsigned long long limit_ns) {
     if (mbar_try_wait(bar, parity)) return true;
     const uint64_t t0 = globaltimer_ns();
     for (uint32_t spins = 1;; spins++) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((spins & 63u) == 0) {
             if (*abort_flag) return false;
-            if (globaltimer_ns() - t0 > 2000000000ull) {
+            if (globaltimer_ns() - t0 > limit_ns) {
                 *abort_flag = 1;
                 return false;
             }
@@ -299,12 +302,12 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_k, const __gri
             int armed = 0;  // ring slots handed to TMA so far
             bool ok = true;
             const int last_block = (p.q_pos0 + p.n_tok - 1) / kBlockTokens;
-            for (int it = 0; it < 2 * n_it && ok; it++) {
+            for (int it = 0; it < (p.test_stall_producer ? 0 : 2 * n_it) && ok; it++) {
                 const int s = it % kStages;
                 const uint32_t par = (uint32_t)((it / kStages) & 1);
                 const uint32_t full = bar_addr(&bars->kv_full[s]);
                 if (lane == 0) {
-                    ok = mbar_wait(bar_addr(&bars->kv_empty[s]), par ^ 1u, abort_flag);
+                    ok = mbar_wait(bar_addr(&bars->kv_empty[s]), par ^ 1u, abort_flag, p.wait_limit_ns);
                     if (ok) mbar_expect_tx(full, kStageBytes);
                 }
                 ok = __shfl_sync(0xffffffffu, ok, 0);
@@ -345,7 +348,7 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_k, const __gri
             const uint32_t o_tmem[2] = {tmem + 256, tmem + 384};
             auto stage_addr = [&](int it) { return smem_base + kOffKV + (it % kStages) * kStageBytes; };
             auto wait_full = [&](int it) {
-                return mbar_wait(bar_addr(&bars->kv_full[it % kStages]), (uint32_t)((it / kStages) & 1), abort_flag);
+                return mbar_wait(bar_addr(&bars->kv_full[it % kStages]), (uint32_t)((it / kStages) & 1), abort_flag, p.wait_limit_ns);
             };
             auto release = [&](int it) { tc_commit(bar_addr(&bars->kv_empty[it % kStages])); };
             // S_q = Q_q K^T : 8 k-steps of 16 dims; dims 0-63 in the first 16 KB box, 64-127 in the second.
@@ -365,7 +368,7 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_k, const __gri
                     tc_mma_ts(o_tmem[q], s_tmem[q] + ks * 8, make_desc(v_addr + ks * 2048, kHalfBytes, 1024), kIdescPV,
                               (!first || ks > 0) ? 1u : 0u);
             };
-            bool ok = mbar_wait(bar_addr(&bars->q_ready), 0, abort_flag);
+            bool ok = mbar_wait(bar_addr(&bars->q_ready), 0, abort_flag, p.wait_limit_ns);
             ok = ok && (n_it == 0 || wait_full(0));
             if (ok && n_it > 0) {
                 tc_fence_after();
@@ -378,7 +381,7 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_k, const __gri
                 const bool more = j + 1 < n_it;
                 ok = wait_full(it_v) && (!more || wait_full(it_k));
                 for (int q = 0; q < 2 && ok; q++) {
-                    ok = mbar_wait(bar_addr(&bars->p_ready[q]), (uint32_t)(j & 1), abort_flag);
+                    ok = mbar_wait(bar_addr(&bars->p_ready[q]), (uint32_t)(j & 1), abort_flag, p.wait_limit_ns);
                     if (!ok) break;
                     tc_fence_after();
                     issue_pv(q, stage_addr(it_v), j == 0);
@@ -426,7 +429,7 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_k, const __gri
         const int qpos_warp_min = __shfl_sync(0xffffffffu, qpos, 0);  // rows ascend with the lane
         for (int jj = 0; jj < n_it; jj++) {
             const int j = j0 + jj;
-            ok = mbar_wait(bar_addr(&bars->s_ready[q]), (uint32_t)(jj & 1), abort_flag);
+            ok = mbar_wait(bar_addr(&bars->s_ready[q]), (uint32_t)(jj & 1), abort_flag, p.wait_limit_ns);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after();
@@ -505,7 +508,7 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_k, const __gri
 
         // ---------------- epilogue: O / l -> global ----------------
         if (ok && n_it > 0) {
-            ok = mbar_wait(bar_addr(&bars->o_final[q]), 0, abort_flag);
+            ok = mbar_wait(bar_addr(&bars->o_final[q]), 0, abort_flag, p.wait_limit_ns);
             ok = __all_sync(0xffffffffu, ok);
         }
         const bool partial = p.n_split > 1;
@@ -723,6 +726,12 @@ int launch_attn_prefill_sm100(ingot_kv* kv, int layer, const void* q, int q_dtyp
     p.block_table = paged ? block_table : nullptr;
     p.capacity = kv->capacity;
     p.scale_log2 = 1.4426950408889634f / sqrtf(float(kHeadDim));
+    // Test hook for the bounded-wait path: INGOT_TEST_STALL_TMA=<milliseconds> makes the producer warp issue
+    // no copies and shortens the wait limit, so every role times out, the status word gets its bit and the
+    // kernel returns normally. Production: 2 s limit, producer active.
+    const char* stall = getenv("INGOT_TEST_STALL_TMA");
+    p.test_stall_producer = stall ? 1 : 0;
+    p.wait_limit_ns = stall ? (unsigned long long)std::max(1, atoi(stall)) * 1000000ull : 2000000000ull;
     INGOT_CUDA_TRY(cudaFuncSetAttribute(attn_prefill_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
     const long long n_rows = (long long)n_tok * p.group;
     const unsigned row_tiles = unsigned((n_rows + 2 * kTileRows - 1) / (2 * kTileRows));

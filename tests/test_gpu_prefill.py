@@ -159,3 +159,25 @@ def test_kv_head_shards_with_fused_gather_reproduce_unsharded_output(n_shards, o
         torch.cuda.synchronize()
         assert kv.status() == 0
     assert torch.equal(dst[0], full) and torch.equal(dst[1], full)
+
+
+def test_bounded_waits_expire_cleanly(monkeypatch):
+    """Failure detection without a fault: with the TMA producer stalled by the test hook, every mbarrier wait
+    of the tcgen05 kernel runs into its (shortened) limit, the kernel returns normally with the timeout bit in
+    the status word, tensor memory is released, and the next launch on the same handle is correct again."""
+    import torch
+    import ingot_b200 as ib
+    wl = W.c1_prefill128(seed=41, n_tok=40)
+    want, _, _ = helpers.oracle_prefill(wl)
+    kv = ib.KVCache(ib.KV_CONTIGUOUS, 1, HKV, 40)
+    inv = helpers.to_dev(helpers.inv_freq())
+    qr = ib.rope_kv_append(kv, 0, helpers.to_dev(wl.q), helpers.to_dev(wl.k), helpers.to_dev(wl.v), inv, 0)
+    monkeypatch.setenv("INGOT_TEST_STALL_TMA", "50")  # milliseconds
+    ib.attn_prefill(kv, 0, qr, 0, impl=2)
+    torch.cuda.synchronize()
+    assert kv.status() == 4  # kDevErrBarrierTimeout
+    monkeypatch.delenv("INGOT_TEST_STALL_TMA")
+    out = ib.attn_prefill(kv, 0, qr, 0, impl=2)
+    torch.cuda.synchronize()
+    assert kv.status() == 0
+    helpers.assert_parity(out.cpu().numpy(), want, "prefill after an expired wait")
