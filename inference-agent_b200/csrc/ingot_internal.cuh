@@ -17,11 +17,8 @@ constexpr int kBlockTokens = INGOT_BLOCK_TOKENS;
 // padded to a 16-byte multiple. The Metal reference keeps the same triple with stride 130
 // (shaders/kernels.metal:291).
 constexpr int kPartStride = 132;
-// Most 16-key units a decode split may be asked to cover is unbounded; the smallest split the
-// library picks is one unit, which bounds the number of partials per (sequence, head).
-constexpr int kMinChunkKeys = 16;
 // Independent launch chains the multi-layer decode call spreads its layers over.
-constexpr int kDecodeStreams = 4;
+constexpr int kDecodeStreams = 8;  // upper bound; INGOT_DECODE_STREAMS picks how many are used (default 4)
 
 // Bits of the device status word (ingot_kv::status_dev).
 enum : int {

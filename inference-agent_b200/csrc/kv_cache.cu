@@ -239,7 +239,12 @@ int ingot_attn_decode_layers(ingot_kv* kv, int layer_begin, int layer_count, con
     // waits for the preceding launch only before it writes its partial, which also makes reusing the
     // two scratch buffers safe. Several chains keep the per-launch completion latency off the
     // critical path.
-    const int n_streams = std::min(kDecodeStreams, layer_count);
+    static const int streams_cfg = [] {
+        const char* e = getenv("INGOT_DECODE_STREAMS");  // tuning knob, read once
+        const int v = e ? atoi(e) : 4;
+        return std::min(std::max(v, 1), kDecodeStreams);
+    }();
+    const int n_streams = std::min(streams_cfg, layer_count);
     if (!kv->fork_event) INGOT_CUDA_TRY(cudaEventCreateWithFlags(&kv->fork_event, cudaEventDisableTiming));
     for (int t = 0; t < n_streams; t++) {
         if (!kv->side_stream[t]) INGOT_CUDA_TRY(cudaStreamCreateWithFlags(&kv->side_stream[t], cudaStreamNonBlocking));
