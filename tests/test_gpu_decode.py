@@ -112,3 +112,64 @@ def test_decode_rejects_bad_arguments():
         ib.attn_decode(kv, 1, q, max_seq_len=10)
     with pytest.raises(ib.IngotError, match="multiple of 16"):
         ib.attn_decode(kv, 0, q, max_seq_len=10, chunk_keys=24)
+
+
+def test_decode_very_long_context():
+    """100 000 keys: the split size grows so that at most 64 partials per head exist; parity still holds."""
+    wl = _decode_case(100_000, seed=21)
+    want = helpers.oracle_decode(wl)
+    out, _ = helpers.gpu_decode(wl)
+    helpers.assert_parity(out.cpu().numpy(), want, "decode n_keys=100000")
+    out16, _ = helpers.gpu_decode(wl, chunk_keys=16)  # a too-small request is raised to the same bound
+    helpers.assert_parity(out16.cpu().numpy(), want, "decode n_keys=100000, chunk request 16")
+
+
+def test_batched_append_then_decode_paged():
+    """Three sequences in one paged pool: one K1 launch appends a token to each (device positions and
+    sequence ids), one K3 launch decodes all three; each sequence must match its own reference."""
+    import torch
+    import ingot_b200 as ib
+    rng = np.random.default_rng(55)
+    lens = np.array([37, 260, 16], dtype=np.int32)  # lengths AFTER the append
+    nb = int(((lens + 15) // 16).sum())
+    perm = rng.permutation(nb + 4).astype(np.int32)[:nb]
+    bt_np = W.block_tables(lens, perm)
+    kv = ib.KVCache(ib.KV_PAGED, 1, HKV, nb + 4, max_seqs=3)
+    bt = helpers.to_dev(bt_np)
+    inv_np = helpers.inv_freq()
+    ks, vs = [], []
+    for s in range(3):
+        k = rng.standard_normal((lens[s] - 1, HKV, D), dtype=np.float32).astype(np.float16)
+        v = rng.standard_normal((lens[s] - 1, HKV, D), dtype=np.float32).astype(np.float16)
+        if lens[s] > 1:
+            kv.import_f16(0, helpers.to_dev(k), helpers.to_dev(v), 0, bt[s])
+        ks.append(k)
+        vs.append(v)
+    q = rng.standard_normal((3, H, D), dtype=np.float32)
+    k_new = rng.standard_normal((3, HKV, D), dtype=np.float32)
+    v_new = rng.standard_normal((3, HKV, D), dtype=np.float32)
+    q_rot = ib.rope_kv_append(kv, 0, helpers.to_dev(q), helpers.to_dev(k_new), helpers.to_dev(v_new), helpers.to_dev(inv_np),
+                              positions=helpers.to_dev(lens - 1), seq_ids=helpers.to_dev(np.arange(3, dtype=np.int32)),
+                              block_tables=bt)
+    out = ib.attn_decode(kv, 0, q_rot, seq_lens=helpers.to_dev(lens), max_seq_len=int(lens.max()), block_tables=bt)
+    torch.cuda.synchronize()
+    assert kv.status() == 0
+    for s in range(3):
+        pos0 = int(lens[s]) - 1
+        wl = W.Prefill(q[s:s + 1], k_new[s:s + 1], v_new[s:s + 1], pos0, True, ks[s] if pos0 else None, vs[s] if pos0 else None)
+        want, _, _ = helpers.oracle_prefill(wl)
+        helpers.assert_parity(out[s].cpu().numpy(), want[0], f"batched append+decode, sequence {s}")
+
+
+def test_empty_calls_are_no_ops():
+    import ingot_b200 as ib
+    lib = ib.lib()
+    kv = ib.KVCache(ib.KV_CONTIGUOUS, 1, HKV, 16)
+    z = helpers.to_dev(np.zeros((1, H, D), dtype=np.float16))
+    import ctypes as C
+    p = C.c_void_p(z.data_ptr())
+    assert lib.ingot_attn_prefill(kv.handle, 0, p, ib.F16, p, ib.F16, H, 0, 0, None, 0, None) == 0      # n_tok == 0
+    assert lib.ingot_rope_kv_append(kv.handle, 0, None, None, p, p, p, H, 0, 0, None, None, None, 0, None) == 0
+    assert lib.ingot_kv_import_f16(kv.handle, 0, p, p, 0, 0, None, None) == 0
+    assert lib.ingot_attn_decode_layers(kv.handle, 0, 0, p, ib.F16, p, ib.F16, H, 1, None, 1, None, 0, 0, None) == 0
+    assert kv.status() == 0
