@@ -437,6 +437,40 @@ def run_batched_decode(args, rank, world):
                        "load_imbalance_max_over_mean": round(float(mx.item()) * world / float(tot.item()), 4),
                        "parallelism": f"sequence sharding x{world} (LPT length balancing, no collective)"}}
 
+
+def run_e2e_model(args):
+    """`ingot bench -p 128 -n 32` through the reference's own engine glue on a seeded random-init
+    Llama-3.2-3B-shaped F16 GGUF: the CUDA backend of this repository against the reference's CpuBackend
+    (both inside backend/_build/libingot_engine_cuda.so). Whole-model tokens/s; the non-attention kernels of
+    the CUDA backend are correctness-first, so this is a functional end-to-end figure, not a tuned one."""
+    import ctypes as C
+    sys.path.insert(0, os.path.join(ROOT, "tests", "golden"))
+    import make_random_gguf
+    eng = os.path.join(ROOT, "inference-agent_b200", "backend", "_build", "libingot_engine_cuda.so")
+    lib = C.CDLL(eng)
+    i32p = np.ctypeslib.ndpointer(dtype=np.int32, flags="C_CONTIGUOUS")
+    f64p = np.ctypeslib.ndpointer(dtype=np.float64, flags="C_CONTIGUOUS")
+    lib.ingot_e2e_bench.argtypes = [C.c_char_p, C.c_char_p, i32p, C.c_int, C.c_int, C.c_int, C.c_int, f64p]
+    lib.ingot_e2e_last_error.restype = C.c_char_p
+    n_layer, n_vocab = (28, 128256) if not args.small_model else (2, 32064)
+    path = os.path.join(os.environ.get("INGOT_E2E_DIR", "/tmp"), f"ingot_random_l{n_layer}_v{n_vocab}_s0.gguf")
+    if not os.path.exists(path):
+        make_random_gguf.write(path + ".tmp", n_layer, n_vocab, seed=0)
+        os.replace(path + ".tmp", path)
+    prompt = np.random.default_rng(0).integers(0, n_vocab, size=128).astype(np.int32)
+    res = {}
+    for name, backend, reps in (("cuda", b"metal", 3), ("cpu", b"cpu", 1)):
+        out = np.zeros(2, dtype=np.float64)
+        if lib.ingot_e2e_bench(path.encode(), backend, prompt, 128, 32, 512, reps, out) != 0:
+            raise SystemExit(lib.ingot_e2e_last_error().decode())
+        res[name] = {"pp128_tok_s": round(float(out[0]), 2), "tg32_tok_s": round(float(out[1]), 2)}
+    return {"metric": "whole-model tokens/s, pp128 / tg32 (the reference's `ingot bench` measurement)", "value": res["cuda"]["tg32_tok_s"],
+            "unit": "tok/s (tg32)", "n_gpus": 1, "steps": 3, "warmup": 1, "ms_per_step": None, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f16 weights, f32 activations, f16 KV", "data": "synthetic",
+            "config": {"workload": f"random-init Llama-3.2-3B-shaped F16 GGUF, {n_layer} layers, vocab {n_vocab}; 128 prompt ids, 32 greedy steps"},
+            "cuda_backend": res["cuda"], "cpu_reference_backend": res["cpu"],
+            "note": "reference README (Apple M5, Metal, F16): pp128 864 tok/s, tg32 15.6 tok/s"}
+
 # ------------------------------------------------------------------------------------------------
 # CPU reference legs
 # ------------------------------------------------------------------------------------------------
@@ -538,7 +572,8 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ingot", choices=["ingot", "reference"])
-    ap.add_argument("--workload", default="decode_c2", choices=["decode_c2", "prefill_c5", "c1_prefill128", "c3_chunked", "c4_batched"])
+    ap.add_argument("--workload", default="decode_c2", choices=["decode_c2", "prefill_c5", "c1_prefill128", "c3_chunked", "c4_batched", "e2e_model"])
+    ap.add_argument("--small-model", action="store_true", help="e2e_model: 2 layers and a 32064-token vocabulary")
     ap.add_argument("--chunk-keys", type=int, default=0, help="decode split size (0 = library default)")
     ap.add_argument("--prefill-steps", type=int, default=10, help="cap on timed prefill steps (each is ~10 ms)")
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS,
@@ -555,6 +590,10 @@ def main():
         line = run_reference(args)
         if line is not None:
             print(json.dumps(line), flush=True)
+        return
+
+    if args.workload == "e2e_model":
+        print(json.dumps(run_e2e_model(args)), flush=True)
         return
 
     rank, world, _ = dist_setup(args.gpus)

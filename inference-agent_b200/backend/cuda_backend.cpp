@@ -86,13 +86,19 @@ public:
         logits_dev_ = alloc_f32(size_t(c.n_vocab));
         cuda_check(cudaMalloc(&q_rot_, nb * q_dim * 2), "cudaMalloc(q_rot)");
         allocs_.push_back(q_rot_);
+        cuda_check(cudaMalloc(&pos_dev_, 2 * sizeof(int32_t)), "cudaMalloc(pos)");
+        allocs_.push_back(pos_dev_);
+        cuda_check(cudaMallocHost(&pos_host_, 2 * sizeof(int32_t)), "cudaMallocHost(pos)");
         cuda_check(cudaMallocHost(&x_host_, nb * c.n_embd * sizeof(float)), "cudaMallocHost(x)");
         cuda_check(cudaMallocHost(&logits_, size_t(c.n_vocab) * sizeof(float)), "cudaMallocHost(logits)");
     }
 
     ~CudaBackend() override {
         cudaStreamSynchronize(stream_);
+        if (decode_exec_) cudaGraphExecDestroy(decode_exec_);
+        if (decode_graph_) cudaGraphDestroy(decode_graph_);
         for (void* p : allocs_) cudaFree(p);
+        cudaFreeHost(pos_host_);
         cudaFreeHost(x_host_);
         cudaFreeHost(logits_);
         ingot_kv_destroy(kv_);
@@ -113,18 +119,59 @@ public:
         for (int i = 0; i < n; i++) ops::dequant_row(*m_.tok_embd, size_t(tokens[i]), x_host_ + size_t(i) * c.n_embd);
         cuda_check(cudaMemcpyAsync(x_, x_host_, size_t(n) * c.n_embd * sizeof(float), cudaMemcpyHostToDevice, stream_), "H2D x");
 
-        const int q_dim = c.n_head * c.head_dim, kv_dim = c.n_head_kv * c.head_dim;
+        if (n == 1) {
+            // Single-token steps read their position and key count from device memory, so that the whole
+            // step (about 370 launches) can be captured once into a CUDA graph and replayed; the Metal
+            // backend likewise encodes a forward pass into one command buffer (src/metal_backend.mm:433-461).
+            // The first single-token call runs eagerly (it sizes the decode scratch), the second is captured.
+            pos_host_[0] = pos;
+            pos_host_[1] = pos + 1;
+            cuda_check(cudaMemcpyAsync(pos_dev_, pos_host_, 2 * sizeof(int32_t), cudaMemcpyHostToDevice, stream_), "H2D pos");
+            if (decode_exec_) {
+                cuda_check(cudaGraphLaunch(decode_exec_, stream_), "cudaGraphLaunch");
+            } else if (decode_calls_++ == 0) {
+                encode_layers(1, pos, true);
+            } else {
+                cuda_check(cudaStreamBeginCapture(stream_, cudaStreamCaptureModeThreadLocal), "cudaStreamBeginCapture");
+                try {
+                    encode_layers(1, pos, true);
+                } catch (...) {
+                    cudaGraph_t dead = nullptr;
+                    cudaStreamEndCapture(stream_, &dead);
+                    if (dead) cudaGraphDestroy(dead);
+                    throw;
+                }
+                cuda_check(cudaStreamEndCapture(stream_, &decode_graph_), "cudaStreamEndCapture");
+                cuda_check(cudaGraphInstantiate(&decode_exec_, decode_graph_, 0), "cudaGraphInstantiate");
+                cuda_check(cudaGraphLaunch(decode_exec_, stream_), "cudaGraphLaunch");
+            }
+        } else {
+            encode_layers(n, pos, false);
+        }
+        cuda_check(cudaMemcpyAsync(logits_, logits_dev_, size_t(c.n_vocab) * sizeof(float), cudaMemcpyDeviceToHost, stream_), "D2H logits");
+        cuda_check(cudaStreamSynchronize(stream_), "forward");
+        int status = 0;
+        ingot_check(ingot_kv_status(kv_, stream_, &status));
+        if (status != 0) throw std::runtime_error("cuda: attention kernel reported status " + std::to_string(status));
+        return logits_;
+    }
+
+    // Every layer plus the final norm and logits projection for n tokens at positions pos..pos+n-1, queued
+    // on stream_. device_pos: single-token form whose position / key count are read from pos_dev_.
+    void encode_layers(int n, int pos, bool device_pos) {
+        const Config& c = m_.cfg;
         for (int l = 0; l < c.n_layer; l++) {
             const DevLayer& D = layers_[l];
             cuda_check(ingot_support_rmsnorm(h_, x_, D.attn_norm, n, c.n_embd, c.rms_eps, stream_), "rmsnorm");
             linear(q_, D.wq, h_, n, false);
             linear(k_, D.wk, h_, n, false);
             linear(v_, D.wv, h_, n, false);
-            ingot_check(ingot_rope_kv_append(kv_, l, q_, q_rot_, k_, v_, inv_freq_, c.n_head, pos, n, nullptr, nullptr,
-                                             nullptr, 0, stream_));
+            ingot_check(ingot_rope_kv_append(kv_, l, q_, q_rot_, k_, v_, inv_freq_, c.n_head, pos, n,
+                                             device_pos ? pos_dev_ : nullptr, nullptr, nullptr, 0, stream_));
             if (n == 1)
-                ingot_check(ingot_attn_decode(kv_, l, q_rot_, INGOT_F16, attn_, INGOT_F32, c.n_head, 1, nullptr, pos + 1,
-                                              nullptr, 0, 0, stream_));
+                ingot_check(ingot_attn_decode(kv_, l, q_rot_, INGOT_F16, attn_, INGOT_F32, c.n_head, 1,
+                                              device_pos ? pos_dev_ + 1 : nullptr, device_pos ? n_ctx_ : pos + 1, nullptr, 0, 0,
+                                              stream_));
             else
                 ingot_check(ingot_attn_prefill(kv_, l, q_rot_, INGOT_F16, attn_, INGOT_F32, c.n_head, pos, n, nullptr, 0,
                                                stream_));
@@ -135,16 +182,9 @@ public:
             cuda_check(ingot_support_silu_mul(gate_, up_, size_t(n) * c.n_ff, stream_), "silu_mul");
             linear(x_, D.w_down, gate_, n, true);
         }
-        (void)q_dim; (void)kv_dim;
         // Logits for the last token only.
         cuda_check(ingot_support_rmsnorm(h_, x_ + size_t(n - 1) * c.n_embd, output_norm_, 1, c.n_embd, c.rms_eps, stream_), "rmsnorm");
         linear(logits_dev_, output_, h_, 1, false);
-        cuda_check(cudaMemcpyAsync(logits_, logits_dev_, size_t(c.n_vocab) * sizeof(float), cudaMemcpyDeviceToHost, stream_), "D2H logits");
-        cuda_check(cudaStreamSynchronize(stream_), "forward");
-        int status = 0;
-        ingot_check(ingot_kv_status(kv_, stream_, &status));
-        if (status != 0) throw std::runtime_error("cuda: attention kernel reported status " + std::to_string(status));
-        return logits_;
     }
 
     int n_ctx() const override { return n_ctx_; }
@@ -198,6 +238,11 @@ private:
           *up_ = nullptr, *logits_dev_ = nullptr;
     void* q_rot_ = nullptr;
     float *x_host_ = nullptr, *logits_ = nullptr;
+    int32_t* pos_dev_ = nullptr;   // [0] = position of the single-token step, [1] = its key count
+    int32_t* pos_host_ = nullptr;  // pinned
+    int decode_calls_ = 0;
+    cudaGraph_t decode_graph_ = nullptr;
+    cudaGraphExec_t decode_exec_ = nullptr;
 };
 
 }  // namespace

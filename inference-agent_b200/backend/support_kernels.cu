@@ -101,6 +101,114 @@ __global__ void linear_kernel(float* out, const W* w, const float* x, int n_in, 
     }
 }
 
+
+// Single-token form (decode): HBM-bound streaming of the weight matrix. x is staged once per block in
+// shared memory; every warp owns two output rows at a time and keeps four 16-byte weight loads per lane in
+// flight. out[r] (+)= dot(W[r][:], x).
+template <typename W>
+__global__ void __launch_bounds__(256) gemv_kernel(float* out, const W* w, const float* x, int n_in, int n_out, int accumulate) {
+    extern __shared__ float sx[];
+    for (int i = threadIdx.x * 4; i < n_in; i += blockDim.x * 4) *reinterpret_cast<float4*>(sx + i) = *reinterpret_cast<const float4*>(x + i);
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int row0 = (blockIdx.x * (blockDim.x >> 5) + warp) * 2;
+    if (row0 >= n_out) return;
+    const bool two = row0 + 1 < n_out;
+    const W* w0 = w + (size_t)row0 * n_in;
+    const W* w1 = w + (size_t)(two ? row0 + 1 : row0) * n_in;
+    float a0 = 0.f, a1 = 0.f;
+    auto fma8 = [&](float& acc, const float (&wv)[8], const float* xs) {
+        const float4 xa = *reinterpret_cast<const float4*>(xs), xb = *reinterpret_cast<const float4*>(xs + 4);
+        acc = fmaf(wv[0], xa.x, acc); acc = fmaf(wv[1], xa.y, acc); acc = fmaf(wv[2], xa.z, acc); acc = fmaf(wv[3], xa.w, acc);
+        acc = fmaf(wv[4], xb.x, acc); acc = fmaf(wv[5], xb.y, acc); acc = fmaf(wv[6], xb.z, acc); acc = fmaf(wv[7], xb.w, acc);
+    };
+    int i = lane * 8;
+    for (; i + 256 < n_in; i += 512) {
+        float p0[8], p1[8], q0[8], q1[8];
+        load8<W>(w0 + i, p0); load8<W>(w1 + i, p1); load8<W>(w0 + i + 256, q0); load8<W>(w1 + i + 256, q1);
+        fma8(a0, p0, sx + i); fma8(a1, p1, sx + i); fma8(a0, q0, sx + i + 256); fma8(a1, q1, sx + i + 256);
+    }
+    for (; i < n_in; i += 256) {
+        float p0[8], p1[8];
+        load8<W>(w0 + i, p0); load8<W>(w1 + i, p1);
+        fma8(a0, p0, sx + i); fma8(a1, p1, sx + i);
+    }
+    a0 = warp_sum(a0);
+    a1 = warp_sum(a1);
+    if (lane == 0) {
+        out[row0] = accumulate ? out[row0] + a0 : a0;
+        if (two) out[row0 + 1] = accumulate ? out[row0 + 1] + a1 : a1;
+    }
+}
+
+
+// Batched form (prefill): out[t][r] (+)= dot(W[r][:], x[t][:]) as a shared-memory tiled f32 GEMM on the FMA
+// pipes: 128 tokens x 64 outputs per CTA, k-steps of 16, 8x4 outputs per thread; weights are widened to
+// f32 when they are staged. The whole token batch of a prefill chunk up to 128 sits in one tile, so the
+// weight matrix is read once per 128 tokens.
+constexpr int kGM = 128, kGN = 64, kGK = 16;
+template <typename W>
+__global__ void __launch_bounds__(256) gemm_kernel(float* out, const W* w, const float* x, int n_in, int n_out, int n_tok, int accumulate) {
+    __shared__ __align__(16) float xs[kGK][kGM + 4];
+    __shared__ __align__(16) float ws[kGK][kGN + 4];
+    const int t0 = blockIdx.y * kGM, r0 = blockIdx.x * kGN;
+    const int tid = threadIdx.x;
+    const int tm = (tid >> 4) * 8, tn = (tid & 15) * 4;  // this thread's 8 tokens x 4 outputs
+    float acc[8][4];
+#pragma unroll
+    for (int i = 0; i < 8; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) acc[i][j] = 0.f;
+    // staging assignments: x tile 128 x 16 floats = 512 float4 (2 per thread); w tile 64 x 16 = 128 chunks of 8 (threads 0..127)
+    for (int k0 = 0; k0 < n_in; k0 += kGK) {
+#pragma unroll
+        for (int it = 0; it < 2; it++) {
+            const int idx = it * 256 + tid;
+            const int row = idx >> 2, c4 = (idx & 3) * 4;
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (t0 + row < n_tok) v = *reinterpret_cast<const float4*>(x + (size_t)(t0 + row) * n_in + k0 + c4);
+            xs[c4 + 0][row] = v.x; xs[c4 + 1][row] = v.y; xs[c4 + 2][row] = v.z; xs[c4 + 3][row] = v.w;
+        }
+        if (tid < 128) {
+            const int row = tid >> 1, c8 = (tid & 1) * 8;
+            float wv[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            if (r0 + row < n_out) load8<W>(w + (size_t)(r0 + row) * n_in + k0 + c8, wv);
+#pragma unroll
+            for (int i = 0; i < 8; i++) ws[c8 + i][row] = wv[i];
+        }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < kGK; k++) {
+            const float4 xa = *reinterpret_cast<const float4*>(&xs[k][tm]), xb = *reinterpret_cast<const float4*>(&xs[k][tm + 4]);
+            const float4 wv = *reinterpret_cast<const float4*>(&ws[k][tn]);
+            const float xv[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
+            const float wq[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+            for (int i = 0; i < 8; i++)
+#pragma unroll
+                for (int j = 0; j < 4; j++) acc[i][j] = fmaf(xv[i], wq[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        const int t = t0 + tm + i;
+        if (t >= n_tok) continue;
+        float* o = out + (size_t)t * n_out + r0 + tn;
+        if (r0 + tn + 3 < n_out) {
+            float4 v = make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
+            if (accumulate) {
+                const float4 old = *reinterpret_cast<const float4*>(o);
+                v.x += old.x; v.y += old.y; v.z += old.z; v.w += old.w;
+            }
+            *reinterpret_cast<float4*>(o) = v;
+        } else {
+            for (int j = 0; j < 4; j++)
+                if (r0 + tn + j < n_out) o[j] = accumulate ? o[j] + acc[i][j] : acc[i][j];
+        }
+    }
+}
+
 }  // namespace
 
 extern "C" {
@@ -119,10 +227,19 @@ cudaError_t ingot_support_silu_mul(float* gate, const float* up, size_t n, cudaS
 cudaError_t ingot_support_linear(float* out, const void* w, int w_is_f16, const float* x, int n_in, int n_out, int n_tok,
                                  int accumulate, cudaStream_t s) {
     const int warps = 8;
-    if (n_tok == 1) {
+    if (n_tok == 1 && size_t(n_in) * sizeof(float) <= 48 * 1024) {
+        const unsigned grid = (n_out + 2 * warps - 1) / (2 * warps);
+        const size_t smem = size_t(n_in) * sizeof(float);
+        if (w_is_f16) gemv_kernel<__half><<<grid, warps * 32, smem, s>>>(out, static_cast<const __half*>(w), x, n_in, n_out, accumulate);
+        else gemv_kernel<float><<<grid, warps * 32, smem, s>>>(out, static_cast<const float*>(w), x, n_in, n_out, accumulate);
+    } else if (n_tok == 1) {
         dim3 grid((n_out + warps - 1) / warps, 1);
         if (w_is_f16) linear_kernel<__half, 1><<<grid, warps * 32, 0, s>>>(out, static_cast<const __half*>(w), x, n_in, n_out, n_tok, accumulate);
         else linear_kernel<float, 1><<<grid, warps * 32, 0, s>>>(out, static_cast<const float*>(w), x, n_in, n_out, n_tok, accumulate);
+    } else if (n_tok >= 16 && n_in % kGK == 0 && n_out % 4 == 0) {
+        dim3 grid((n_out + kGN - 1) / kGN, (n_tok + kGM - 1) / kGM);
+        if (w_is_f16) gemm_kernel<__half><<<grid, 256, 0, s>>>(out, static_cast<const __half*>(w), x, n_in, n_out, n_tok, accumulate);
+        else gemm_kernel<float><<<grid, 256, 0, s>>>(out, static_cast<const float*>(w), x, n_in, n_out, n_tok, accumulate);
     } else {
         dim3 grid((n_out + warps - 1) / warps, (n_tok + 7) / 8);
         if (w_is_f16) linear_kernel<__half, 8><<<grid, warps * 32, 0, s>>>(out, static_cast<const __half*>(w), x, n_in, n_out, n_tok, accumulate);
