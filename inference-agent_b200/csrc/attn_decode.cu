@@ -54,13 +54,25 @@ struct DecodeParams {
     float scale_log2;
 };
 
+// Number of keys of sequence `seq`. Lengths that come from device memory cannot be checked on the host:
+// one that exceeds what the cache (or the block table) can hold is clamped and raises the status word.
+__device__ __forceinline__ int load_seq_len(const DecodeParams& p, int seq) {
+    int n = p.seq_lens ? p.seq_lens[seq] : p.len0;
+    const int bound = p.paged ? p.max_blocks_per_seq * kBlockTokens : p.capacity;
+    if (n > bound) {
+        if (threadIdx.x == 0 && p.status) atomicOr(p.status, kDevErrPosRange);
+        n = bound;
+    }
+    return n;
+}
+
 // Merges the splits of one (sequence, kv head): out = sum_s o_s 2^(m_s-M) / sum_s l_s 2^(m_s-M)
 // (the attn_combine formula, shaders/kernels.metal:502-516). Runs in one extra CTA per (kv head,
 // sequence) of the launch that FOLLOWS the one that wrote the partials (or of a merge-only launch):
 // programmatic dependent launch orders it behind that launch, so no fences, tickets or polling are
 // involved, and the merge overlaps the K/V loads of the split CTAs it shares the grid with.
 __device__ __forceinline__ void combine_splits(const DecodeParams& p, float* smem, int kvh, int seq) {
-    const int n_keys = p.seq_lens ? p.seq_lens[seq] : p.len0;
+    const int n_keys = load_seq_len(p, seq);
     if (n_keys < 1) return;
     const int n_chunks = (n_keys + p.chunk_keys - 1) / p.chunk_keys;
     if (n_chunks == 1) return;  // the split CTA wrote the final output itself
@@ -192,7 +204,7 @@ __global__ void __launch_bounds__(kMaxDecodeWarps * 32, 1) attn_decode_kernel(co
     if (!p.early_loads) asm volatile("griddepcontrol.wait;" ::: "memory");
 
     const int chunk = blockIdx.x, kvh = blockIdx.y, seq = blockIdx.z;
-    const int n_keys = p.seq_lens ? p.seq_lens[seq] : p.len0;
+    const int n_keys = load_seq_len(p, seq);
     if (n_keys < 1) return;
     const int n_chunks = (n_keys + p.chunk_keys - 1) / p.chunk_keys;
     if (chunk >= n_chunks) return;

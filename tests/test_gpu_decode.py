@@ -173,3 +173,19 @@ def test_empty_calls_are_no_ops():
     assert lib.ingot_kv_import_f16(kv.handle, 0, p, p, 0, 0, None, None) == 0
     assert lib.ingot_attn_decode_layers(kv.handle, 0, 0, p, ib.F16, p, ib.F16, H, 1, None, 1, None, 0, 0, None) == 0
     assert kv.status() == 0
+
+
+def test_device_length_beyond_the_cache_is_clamped_and_flagged():
+    """A sequence length read from device memory that exceeds the cache cannot be rejected on the host: the
+    kernel clamps it to the capacity and raises the status word instead of reading past the cache."""
+    import torch
+    import ingot_b200 as ib
+    wl = _decode_case(64, seed=31)
+    kv = ib.KVCache(ib.KV_CONTIGUOUS, 2, HKV, 64)  # layer 1 follows layer 0 in memory
+    kv.import_f16(0, helpers.to_dev(wl.k[0]), helpers.to_dev(wl.v[0]), 0)
+    q = helpers.to_dev(wl.q)
+    want = ib.attn_decode(kv, 0, q, max_seq_len=64)
+    got = ib.attn_decode(kv, 0, q, seq_lens=helpers.to_dev(np.array([70], dtype=np.int32)), max_seq_len=64)
+    torch.cuda.synchronize()
+    assert kv.status() == 1
+    assert torch.equal(got, want)
