@@ -144,6 +144,21 @@ def decode_bytes_per_step():
     return 2 * N_LAYER * DECODE_KEYS * HKV * D * 2
 
 
+def decode_config(world):
+    """The workload description both arms (this library and the reference's CPU code) report."""
+    return {"workload": "configs[1]: decode @4096 keys, batch 1 per GPU, 28 per-layer caches per step",
+            "n_layer": N_LAYER, "n_keys": DECODE_KEYS, "n_head": H, "n_head_kv": HKV, "head_dim": D,
+            "l2": "inputs larger than L2 (470 MB of KV per step, 28 distinct caches)",
+            "parallelism": f"sequence sharding x{world} (one sequence per GPU, no collective)"}
+
+
+def prefill_config(S, world):
+    return {"workload": ("configs[4]: 32768-token causal prefill, FLOPs = 4*S^2*H*d/2" if S == PREFILL_TOKENS
+                         else f"PROFILING CASE: {S}-token causal prefill (not the benchmark configuration)"), "n_tok": S,
+            "n_head": H, "n_head_kv": HKV, "head_dim": D, "l2": "inputs larger than L2 (q+out 400 MB, K/V 134 MB)",
+            "parallelism": f"KV-head sharding x{world}"}
+
+
 def run_decode(args, rank, world):
     import torch
     import ingot_b200 as ib
@@ -209,10 +224,7 @@ def run_decode(args, rank, world):
             "value": round(value, 1), "unit": "GB/s", "ms_per_step": round(ms / args.steps, 5), "scaling": "weak",
             "dtype": "f16 KV / f16 MMA operands / f32 accumulate+softmax", "roofline": roofline, "e2e": e2e,
             "gpu_launches": launches, "clocks": clk.summary(),
-            "config": {"workload": "configs[1]: decode @4096 keys, batch 1 per GPU, 28 per-layer caches per step",
-                       "n_layer": N_LAYER, "n_keys": DECODE_KEYS, "n_head": H, "n_head_kv": HKV, "head_dim": D,
-                       "l2": "inputs larger than L2 (470 MB of KV per step, 28 distinct caches)",
-                       "parallelism": f"sequence sharding x{world} (one sequence per GPU, no collective)"}}
+            "config": decode_config(world)}
 
 
 def inv_freq_table():
@@ -329,11 +341,7 @@ def run_prefill(args, rank, world):
             "value": round(value, 1), "unit": "TFLOP/s", "ms_per_step": round(ms / steps, 4), "steps": steps,
             "scaling": "strong", "dtype": "f16 MMA operands (bf16 q converted on load) / f32 accumulate+softmax",
             "roofline": roofline, "e2e": e2e, "gpu_launches": steps, "clocks": clk.summary(),
-            "config": {"workload": ("configs[4]: 32768-token causal prefill, FLOPs = 4*S^2*H*d/2" if S == PREFILL_TOKENS
-                                    else f"PROFILING CASE: {S}-token causal prefill (not the benchmark configuration)"), "n_tok": S,
-                       "n_head": H, "n_head_kv": HKV, "head_dim": D,
-                       "l2": "inputs larger than L2 (q+out 400 MB, K/V 134 MB)",
-                       "parallelism": f"KV-head sharding x{world}", "gather": gather_mode, "gather_verified": gather_checked}}
+            "config": dict(prefill_config(S, world), gather=gather_mode, gather_verified=gather_checked)}
 
 
 
@@ -542,7 +550,7 @@ def run_reference(args):
         sample = f"{n} query rows (first 8, last 8, random) x 24 heads of the 32768-token prefill, extrapolated by FLOPs"
         line = {"metric": "causal GQA prefill attention TFLOP/s (32768 tokens, 24q/8kv heads, d128, bf16 q, f16 K/V)",
                 "value": round(tf, 5), "unit": "TFLOP/s", "ms_per_step": None, "scaling": "strong",
-                "config": {"workload": "configs[4]: 32768-token causal prefill, FLOPs = 4*S^2*H*d/2"}}
+                "config": prefill_config(PREFILL_TOKENS, args.gpus)}
     else:
         t0 = time.perf_counter()
         for _ in range(args.warmup):
@@ -558,7 +566,7 @@ def run_reference(args):
         sample = f"{len(vals)} steps x 28 layers of the full decode workload (f32 cache as the reference keeps it)"
         line = {"metric": "decode attention KV-cache HBM GB/s (4096 keys, 24q/8kv heads, d128, f16 KV, 28 layers)",
                 "value": round(gbs, 3), "unit": "GB/s", "ms_per_step": round(per_layer * N_LAYER * 1e3, 3), "scaling": "weak",
-                "config": {"workload": "configs[1]: decode @4096 keys, batch 1 per GPU, 28 per-layer caches per step"}}
+                "config": decode_config(args.gpus)}
     line.update({"impl": "reference", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
                  "higher_is_better": True, "vs_baseline": None, "dtype": "f32", "data": "synthetic",
                  "cpu_baseline": {"value": line["value"], "unit": line["unit"], "cores": cores, "kind": kind, "sample": sample},
