@@ -120,16 +120,20 @@ __device__ __forceinline__ uint64_t globaltimer_ns() {
 }
 
 // Bounded wait: returns false (and raises the CTA's abort flag) if the barrier does not complete
-// within limit_ns (2 s in production) or another role already aborted.
+// within limit_ns (2 s in production) or another role already aborted. The wall clock (%globaltimer, a
+// slow read) and the abort flag are only looked at every 256 failed polls, so that a wait that is
+// satisfied within microseconds — every wait of a healthy run — never pays for them.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag,
                                           unsigned long long limit_ns) {
-    if (mbar_try_wait(bar, parity)) return true;
-    const uint64_t t0 = globaltimer_ns();
+    uint64_t t0 = 0;
     for (uint32_t spins = 1;; spins++) {
         if (mbar_try_wait(bar, parity)) return true;
-        if ((spins & 63u) == 0) {
+        if ((spins & 255u) == 0) {
             if (*abort_flag) return false;
-            if (globaltimer_ns() - t0 > limit_ns) {
+            const uint64_t now = globaltimer_ns();
+            if (t0 == 0) {
+                t0 = now;
+            } else if (now - t0 > limit_ns) {
                 *abort_flag = 1;
                 return false;
             }
