@@ -20,7 +20,10 @@
 
 #include <cuda_runtime.h>
 
+#include <chrono>
 #include <cmath>
+#include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <stdexcept>
 #include <string>
@@ -62,6 +65,10 @@ public:
         int n_dev = 0;
         if (cudaGetDeviceCount(&n_dev) != cudaSuccess || n_dev < 1) throw std::runtime_error("cuda: no GPU device");
         cuda_check(cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking), "cudaStreamCreate");
+        if (profile_) {
+            cuda_check(cudaEventCreate(&ev0_), "cudaEventCreate");
+            cuda_check(cudaEventCreate(&ev1_), "cudaEventCreate");
+        }
         ingot_check(ingot_kv_create(&kv_, INGOT_KV_CONTIGUOUS, c.n_layer, c.n_head_kv, c.head_dim, n_ctx, 1));
 
         layers_.resize(c.n_layer);
@@ -95,6 +102,15 @@ public:
 
     ~CudaBackend() override {
         cudaStreamSynchronize(stream_);
+        // INGOT_PROFILE=1: GPU time against wall time per forward, as the Metal backend reports under
+        // LLM_PROFILE (src/metal_backend.mm:88-93, 463-468).
+        if (profile_ && calls_ > 0) {
+            fprintf(stderr, "cuda: %d forwards: gpu %.3f ms, wall %.3f ms per call", calls_, gpu_ms_ / calls_, wall_ms_ / calls_);
+            if (calls1_ > 0) fprintf(stderr, "; single-token: %d calls, gpu %.3f ms per call", calls1_, gpu1_ms_ / calls1_);
+            fprintf(stderr, "\n");
+        }
+        if (ev0_) cudaEventDestroy(ev0_);
+        if (ev1_) cudaEventDestroy(ev1_);
         if (decode_exec_) cudaGraphExecDestroy(decode_exec_);
         if (decode_graph_) cudaGraphDestroy(decode_graph_);
         for (void* p : allocs_) cudaFree(p);
@@ -116,7 +132,9 @@ public:
 
         // Embedding rows are dequantised on the host straight into pinned memory, as the Metal
         // backend does (src/metal_backend.mm:426-428).
+        const auto wall0 = std::chrono::steady_clock::now();
         for (int i = 0; i < n; i++) ops::dequant_row(*m_.tok_embd, size_t(tokens[i]), x_host_ + size_t(i) * c.n_embd);
+        if (profile_) cuda_check(cudaEventRecord(ev0_, stream_), "cudaEventRecord");
         cuda_check(cudaMemcpyAsync(x_, x_host_, size_t(n) * c.n_embd * sizeof(float), cudaMemcpyHostToDevice, stream_), "H2D x");
 
         if (n == 1) {
@@ -149,7 +167,16 @@ public:
             encode_layers(n, pos, false);
         }
         cuda_check(cudaMemcpyAsync(logits_, logits_dev_, size_t(c.n_vocab) * sizeof(float), cudaMemcpyDeviceToHost, stream_), "D2H logits");
+        if (profile_) cuda_check(cudaEventRecord(ev1_, stream_), "cudaEventRecord");
         cuda_check(cudaStreamSynchronize(stream_), "forward");
+        if (profile_) {
+            float ms = 0.f;
+            cudaEventElapsedTime(&ms, ev0_, ev1_);
+            gpu_ms_ += ms;
+            wall_ms_ += std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - wall0).count();
+            calls_++;
+            if (n == 1) { gpu1_ms_ += ms; calls1_++; }
+        }
         int status = 0;
         ingot_check(ingot_kv_status(kv_, stream_, &status));
         if (status != 0) throw std::runtime_error("cuda: attention kernel reported status " + std::to_string(status));
@@ -241,6 +268,10 @@ private:
     int32_t* pos_dev_ = nullptr;   // [0] = position of the single-token step, [1] = its key count
     int32_t* pos_host_ = nullptr;  // pinned
     int decode_calls_ = 0;
+    const bool profile_ = getenv("INGOT_PROFILE") != nullptr;
+    cudaEvent_t ev0_ = nullptr, ev1_ = nullptr;
+    double gpu_ms_ = 0, wall_ms_ = 0, gpu1_ms_ = 0;
+    int calls_ = 0, calls1_ = 0;
     cudaGraph_t decode_graph_ = nullptr;
     cudaGraphExec_t decode_exec_ = nullptr;
 };

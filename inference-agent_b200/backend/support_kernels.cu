@@ -102,45 +102,35 @@ __global__ void linear_kernel(float* out, const W* w, const float* x, int n_in, 
 }
 
 
-// Single-token form (decode): HBM-bound streaming of the weight matrix. x is staged once per block in
-// shared memory; every warp owns two output rows at a time and keeps four 16-byte weight loads per lane in
-// flight. out[r] (+)= dot(W[r][:], x).
+// Single-token form (decode): HBM-bound streaming of the weight matrix. One warp per output row; each lane
+// keeps four 16-byte weight loads in flight (2 KB per warp, up to 128 KB per SM) and reads x through L1.
+// out[r] (+)= dot(W[r][:], x).
 template <typename W>
 __global__ void __launch_bounds__(256) gemv_kernel(float* out, const W* w, const float* x, int n_in, int n_out, int accumulate) {
-    extern __shared__ float sx[];
-    for (int i = threadIdx.x * 4; i < n_in; i += blockDim.x * 4) *reinterpret_cast<float4*>(sx + i) = *reinterpret_cast<const float4*>(x + i);
-    __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int row0 = (blockIdx.x * (blockDim.x >> 5) + warp) * 2;
-    if (row0 >= n_out) return;
-    const bool two = row0 + 1 < n_out;
-    const W* w0 = w + (size_t)row0 * n_in;
-    const W* w1 = w + (size_t)(two ? row0 + 1 : row0) * n_in;
-    float a0 = 0.f, a1 = 0.f;
+    const int row = blockIdx.x * (blockDim.x >> 5) + warp;
+    if (row >= n_out) return;
+    const W* wr = w + (size_t)row * n_in;
+    float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;
     auto fma8 = [&](float& acc, const float (&wv)[8], const float* xs) {
-        const float4 xa = *reinterpret_cast<const float4*>(xs), xb = *reinterpret_cast<const float4*>(xs + 4);
+        const float4 xa = __ldg(reinterpret_cast<const float4*>(xs)), xb = __ldg(reinterpret_cast<const float4*>(xs + 4));
         acc = fmaf(wv[0], xa.x, acc); acc = fmaf(wv[1], xa.y, acc); acc = fmaf(wv[2], xa.z, acc); acc = fmaf(wv[3], xa.w, acc);
         acc = fmaf(wv[4], xb.x, acc); acc = fmaf(wv[5], xb.y, acc); acc = fmaf(wv[6], xb.z, acc); acc = fmaf(wv[7], xb.w, acc);
     };
     int i = lane * 8;
-    for (; i + 256 < n_in; i += 512) {
-        float p0[8], p1[8], q0[8], q1[8];
-        load8<W>(w0 + i, p0); load8<W>(w1 + i, p1); load8<W>(w0 + i + 256, q0); load8<W>(w1 + i + 256, q1);
-        fma8(a0, p0, sx + i); fma8(a1, p1, sx + i); fma8(a0, q0, sx + i + 256); fma8(a1, q1, sx + i + 256);
+    for (; i + 768 < n_in; i += 1024) {
+        float p0[8], p1[8], p2[8], p3[8];
+        load8<W>(wr + i, p0); load8<W>(wr + i + 256, p1); load8<W>(wr + i + 512, p2); load8<W>(wr + i + 768, p3);
+        fma8(acc0, p0, x + i); fma8(acc1, p1, x + i + 256); fma8(acc2, p2, x + i + 512); fma8(acc3, p3, x + i + 768);
     }
     for (; i < n_in; i += 256) {
-        float p0[8], p1[8];
-        load8<W>(w0 + i, p0); load8<W>(w1 + i, p1);
-        fma8(a0, p0, sx + i); fma8(a1, p1, sx + i);
+        float p0[8];
+        load8<W>(wr + i, p0);
+        fma8(acc0, p0, x + i);
     }
-    a0 = warp_sum(a0);
-    a1 = warp_sum(a1);
-    if (lane == 0) {
-        out[row0] = accumulate ? out[row0] + a0 : a0;
-        if (two) out[row0 + 1] = accumulate ? out[row0 + 1] + a1 : a1;
-    }
+    const float v = warp_sum((acc0 + acc1) + (acc2 + acc3));
+    if (lane == 0) out[row] = accumulate ? out[row] + v : v;
 }
-
 
 // Batched form (prefill): out[t][r] (+)= dot(W[r][:], x[t][:]) as a shared-memory tiled f32 GEMM on the FMA
 // pipes: 128 tokens x 64 outputs per CTA, k-steps of 16, 8x4 outputs per thread; weights are widened to
@@ -227,15 +217,10 @@ cudaError_t ingot_support_silu_mul(float* gate, const float* up, size_t n, cudaS
 cudaError_t ingot_support_linear(float* out, const void* w, int w_is_f16, const float* x, int n_in, int n_out, int n_tok,
                                  int accumulate, cudaStream_t s) {
     const int warps = 8;
-    if (n_tok == 1 && size_t(n_in) * sizeof(float) <= 48 * 1024) {
-        const unsigned grid = (n_out + 2 * warps - 1) / (2 * warps);
-        const size_t smem = size_t(n_in) * sizeof(float);
-        if (w_is_f16) gemv_kernel<__half><<<grid, warps * 32, smem, s>>>(out, static_cast<const __half*>(w), x, n_in, n_out, accumulate);
-        else gemv_kernel<float><<<grid, warps * 32, smem, s>>>(out, static_cast<const float*>(w), x, n_in, n_out, accumulate);
-    } else if (n_tok == 1) {
-        dim3 grid((n_out + warps - 1) / warps, 1);
-        if (w_is_f16) linear_kernel<__half, 1><<<grid, warps * 32, 0, s>>>(out, static_cast<const __half*>(w), x, n_in, n_out, n_tok, accumulate);
-        else linear_kernel<float, 1><<<grid, warps * 32, 0, s>>>(out, static_cast<const float*>(w), x, n_in, n_out, n_tok, accumulate);
+    if (n_tok == 1) {
+        const unsigned grid = (n_out + warps - 1) / warps;
+        if (w_is_f16) gemv_kernel<__half><<<grid, warps * 32, 0, s>>>(out, static_cast<const __half*>(w), x, n_in, n_out, accumulate);
+        else gemv_kernel<float><<<grid, warps * 32, 0, s>>>(out, static_cast<const float*>(w), x, n_in, n_out, accumulate);
     } else if (n_tok >= 16 && n_in % kGK == 0 && n_out % 4 == 0) {
         dim3 grid((n_out + kGN - 1) / kGN, (n_tok + kGM - 1) / kGM);
         if (w_is_f16) gemm_kernel<__half><<<grid, 256, 0, s>>>(out, static_cast<const __half*>(w), x, n_in, n_out, n_tok, accumulate);
