@@ -149,6 +149,20 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map
 
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+// Build with -DINGOT_PREFILL_TIMING to make CTA (0,0,0) print, per key tile, the cycles its MMA warp and
+// its first softmax warps spend in each phase (diagnostics only; the printing build is not for production).
+#ifdef INGOT_PREFILL_TIMING
+#define TIMING(...) __VA_ARGS__
+#else
+#define TIMING(...)
+#endif
+
+// True in exactly one lane of a converged warp.
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile("{\n.reg .pred P;\nelect.sync _|P, 0xffffffff;\nselp.u32 %0, 1, 0, P;\n}\n" : "=r"(pred));
+    return pred != 0;
+}
 __device__ __forceinline__ void tc_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
@@ -259,6 +273,7 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_k, const __gri
     volatile uint32_t* abort_flag = &bars->abort_flag;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int warp_u = __shfl_sync(0xffffffffu, warp, 0);  // the same number, known to the compiler as warp-uniform
     const int G = p.group;
     const int kvh = blockIdx.y;
     const int n_rows = p.n_tok * G;
@@ -294,9 +309,9 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_k, const __gri
     tc_fence_after();
     const uint32_t tmem = bars->tmem_base;
 
-    if (warp < 4) {
+    if (warp_u < 4) {
         asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
-        if (warp == 0) {
+        if (warp_u == 0) {
             // ---------------- TMA producer ----------------
             // Contiguous cache: lane 0 issues two boxes of [128 keys][64 dims] per tile. Paged cache: a tile
             // is eight 16-token blocks; lanes 0-7 look their block up in the block table and each issue the
@@ -345,22 +360,26 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_k, const __gri
                     while (!mbar_try_wait(full, (uint32_t)((it / kStages) & 1)) && globaltimer_ns() - t0 < 100000000ull) {}
                 }
             }
-        } else if (warp == 1 && lane == 0) {
+        } else if (warp_u == 1) {
             // ---------------- MMA issuer ----------------
-            const uint32_t q_addr[2] = {smem_base + kOffQ, smem_base + kOffQ + kQBytes};
-            const uint32_t s_tmem[2] = {tmem + 0, tmem + 128};
-            const uint32_t o_tmem[2] = {tmem + 256, tmem + 384};
+            // The whole warp walks this loop and only the tcgen05 instructions sit under an elected lane.
+            // With warp-uniform control flow the compiler keeps descriptors and addresses in uniform
+            // registers, which is what tcgen05.mma reads; a loop run by one lane of a diverged warp has to
+            // move every descriptor from vector to uniform registers first and then issues an MMA every
+            // ~88 cycles instead of the tensor pipe's 64.
+            const uint32_t q_base = smem_base + kOffQ;
             auto stage_addr = [&](int it) { return smem_base + kOffKV + (it % kStages) * kStageBytes; };
             auto wait_full = [&](int it) {
-                return mbar_wait(bar_addr(&bars->kv_full[it % kStages]), (uint32_t)((it / kStages) & 1), abort_flag, p.wait_limit_ns);
+                return __all_sync(0xffffffffu, mbar_wait(bar_addr(&bars->kv_full[it % kStages]), (uint32_t)((it / kStages) & 1),
+                                                         abort_flag, p.wait_limit_ns));
             };
-            auto release = [&](int it) { tc_commit(bar_addr(&bars->kv_empty[it % kStages])); };
             // S_q = Q_q K^T : 8 k-steps of 16 dims; dims 0-63 in the first 16 KB box, 64-127 in the second.
             auto issue_qk = [&](int q, uint32_t k_addr) {
 #pragma unroll
                 for (int ks = 0; ks < 8; ks++) {
                     const uint32_t off = (ks >> 2) * kHalfBytes + (ks & 3) * 32;
-                    tc_mma_ss(s_tmem[q], make_desc(q_addr[q] + off, 16, 1024), make_desc(k_addr + off, 16, 1024), kIdescQK, ks > 0);
+                    tc_mma_ss(tmem + q * 128, make_desc(q_base + q * kQBytes + off, 16, 1024), make_desc(k_addr + off, 16, 1024),
+                              kIdescQK, ks > 0);
                 }
                 tc_commit(bar_addr(&bars->s_ready[q]));
             };
@@ -369,35 +388,53 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_k, const __gri
             auto issue_pv = [&](int q, uint32_t v_addr, bool first) {
 #pragma unroll
                 for (int ks = 0; ks < 8; ks++)
-                    tc_mma_ts(o_tmem[q], s_tmem[q] + ks * 8, make_desc(v_addr + ks * 2048, kHalfBytes, 1024), kIdescPV,
-                              (!first || ks > 0) ? 1u : 0u);
+                    tc_mma_ts(tmem + 256 + q * 128, tmem + q * 128 + ks * 8, make_desc(v_addr + ks * 2048, kHalfBytes, 1024),
+                              kIdescPV, (!first || ks > 0) ? 1u : 0u);
             };
-            bool ok = mbar_wait(bar_addr(&bars->q_ready), 0, abort_flag, p.wait_limit_ns);
+            bool ok = __all_sync(0xffffffffu, mbar_wait(bar_addr(&bars->q_ready), 0, abort_flag, p.wait_limit_ns));
             ok = ok && (n_it == 0 || wait_full(0));
+            TIMING(const long long t_begin = clock64(); long long w_full = 0, w_p = 0, t_iss = 0, c0, c1;)
             if (ok && n_it > 0) {
                 tc_fence_after();
-                issue_qk(0, stage_addr(0));
-                issue_qk(1, stage_addr(0));
-                release(0);
+                if (elect_one()) {
+                    issue_qk(0, stage_addr(0));
+                    issue_qk(1, stage_addr(0));
+                    tc_commit(bar_addr(&bars->kv_empty[0]));
+                }
+                __syncwarp();
             }
             for (int j = 0; j < n_it && ok; j++) {  // j counts this CTA's key tiles from j0
                 const int it_v = 2 * j + 1, it_k = 2 * j + 2;
                 const bool more = j + 1 < n_it;
+                TIMING(c0 = clock64();)
                 ok = wait_full(it_v) && (!more || wait_full(it_k));
-                for (int q = 0; q < 2 && ok; q++) {
-                    ok = mbar_wait(bar_addr(&bars->p_ready[q]), (uint32_t)(j & 1), abort_flag, p.wait_limit_ns);
+                TIMING(w_full += clock64() - c0;)
+                if (!ok) break;
+                const uint32_t v_addr = stage_addr(it_v), k_addr = stage_addr(it_k);
+#pragma unroll
+                for (int q = 0; q < 2; q++) {
+                    TIMING(c0 = clock64();)
+                    ok = __all_sync(0xffffffffu, mbar_wait(bar_addr(&bars->p_ready[q]), (uint32_t)(j & 1), abort_flag, p.wait_limit_ns));
                     if (!ok) break;
                     tc_fence_after();
-                    issue_pv(q, stage_addr(it_v), j == 0);
-                    if (q == 1) release(it_v);
-                    if (more) {
-                        issue_qk(q, stage_addr(it_k));
-                        if (q == 1) release(it_k);
-                    } else {
-                        tc_commit(bar_addr(&bars->o_final[q]));
+                    TIMING(c1 = clock64(); w_p += c1 - c0;)
+                    if (elect_one()) {
+                        issue_pv(q, v_addr, j == 0);
+                        if (q == 1) tc_commit(bar_addr(&bars->kv_empty[it_v % kStages]));
+                        if (more) {
+                            issue_qk(q, k_addr);
+                            if (q == 1) tc_commit(bar_addr(&bars->kv_empty[it_k % kStages]));
+                        } else {
+                            tc_commit(bar_addr(&bars->o_final[q]));
+                        }
                     }
+                    __syncwarp();
+                    TIMING(t_iss += clock64() - c1;)
                 }
             }
+            TIMING(if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0 && n_it > 0)
+                       printf("MMA warp: %d key tiles, cycles/tile %lld: wait K/V %lld, wait P (2 tiles) %lld, issue 32 MMAs %lld\n", n_it,
+                              (clock64() - t_begin) / n_it, w_full / n_it, w_p / n_it, t_iss / n_it);)
         }
     } else {
         asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
@@ -431,9 +468,12 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_k, const __gri
         float m_ref = 0.f, l = 0.f;
         bool ok = true;
         const int qpos_warp_min = __shfl_sync(0xffffffffu, qpos, 0);  // rows ascend with the lane
+        TIMING(long long t_w = 0, t_ld = 0, t_mx = 0, t_ex = 0, t_st = 0, c0, c1, c2, c3, c4; const long long t_begin = clock64();)
         for (int jj = 0; jj < n_it; jj++) {
             const int j = j0 + jj;
+            TIMING(c0 = clock64();)
             ok = mbar_wait(bar_addr(&bars->s_ready[q]), (uint32_t)(jj & 1), abort_flag, p.wait_limit_ns);
+            TIMING(c1 = clock64();)
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after();
@@ -441,6 +481,7 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_k, const __gri
 #pragma unroll
             for (int c = 0; c < 4; c++) tmem_ld32(s_tmem + c * 32, *reinterpret_cast<float(*)[32]>(&s[c * 32]));
             tmem_wait_ld();
+            TIMING(c2 = clock64();)
 
             const int key0 = j * kTileKeys;
             if (key0 + kTileKeys - 1 > qpos_warp_min) {  // warp-uniform: some row of this warp needs the mask
@@ -483,6 +524,7 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_k, const __gri
             // P = 2^(s*scale - m_ref). A 128x128 tile costs as many MUFU (ex2) cycles as it costs tensor-core
             // cycles, so one pair in kPolyEvery goes to the FMA pipe instead (exp2_poly2); scaling and the
             // row sum use packed f32x2 instructions.
+            TIMING(c3 = clock64();)
             const float neg_m = m_ref == -INFINITY ? 0.f : -m_ref;
             float sum0 = 0.f, sum1 = 0.f;
 #pragma unroll
@@ -504,11 +546,16 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_k, const __gri
                 tmem_st32(s_tmem + c * 32, pk);
             }
             l += sum0 + sum1;
+            TIMING(c4 = clock64();)
             tmem_wait_st();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_addr(&bars->p_ready[q]));
+            TIMING(t_w += c1 - c0; t_ld += c2 - c1; t_mx += c3 - c2; t_ex += c4 - c3; t_st += clock64() - c4;)
         }
+        TIMING(if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (warp & 3) == 0 && lane == 0 && n_it > 0)
+                   printf("softmax warp of Q tile %d, cycles/tile %lld: wait S %lld, tcgen05.ld %lld, max+rescale %lld, exp+pack %lld, st+arrive %lld\n", q,
+                          (clock64() - t_begin) / n_it, t_w / n_it, t_ld / n_it, t_mx / n_it, t_ex / n_it, t_st / n_it);)
 
         // ---------------- epilogue: O / l -> global ----------------
         if (ok && n_it > 0) {
