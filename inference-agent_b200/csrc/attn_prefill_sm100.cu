@@ -393,7 +393,7 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_k, const __gri
             };
             bool ok = __all_sync(0xffffffffu, mbar_wait(bar_addr(&bars->q_ready), 0, abort_flag, p.wait_limit_ns));
             ok = ok && (n_it == 0 || wait_full(0));
-            TIMING(const long long t_begin = clock64(); long long w_full = 0, w_p = 0, t_iss = 0, c0, c1;)
+            TIMING(const long long t_begin = clock64(); const uint64_t g_begin = globaltimer_ns(); long long w_full = 0, w_p = 0, t_iss = 0, c0, c1;)
             if (ok && n_it > 0) {
                 tc_fence_after();
                 if (elect_one()) {
@@ -433,8 +433,9 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_k, const __gri
                 }
             }
             TIMING(if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0 && n_it > 0)
-                       printf("MMA warp: %d key tiles, cycles/tile %lld: wait K/V %lld, wait P (2 tiles) %lld, issue 32 MMAs %lld\n", n_it,
-                              (clock64() - t_begin) / n_it, w_full / n_it, w_p / n_it, t_iss / n_it);)
+                       printf("MMA warp: %d key tiles, cycles/tile %lld: wait K/V %lld, wait P (2 tiles) %lld, issue 32 MMAs %lld; SM clock %.3f GHz\n", n_it,
+                              (clock64() - t_begin) / n_it, w_full / n_it, w_p / n_it, t_iss / n_it,
+                              (double)(clock64() - t_begin) / (double)(globaltimer_ns() - g_begin));)
         }
     } else {
         asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
