@@ -39,7 +39,7 @@ PREFILL_TOKENS = 32768
 # decode: captured at the benchmark shape (profiles/attn_decode_c2.md). prefill: captured at 8192 tokens
 # (84.1 MB read + 22.6 MB written; profiles/attn_prefill_sm100_8k.md) and scaled by the 4x token count,
 # compulsory q/K/V/out traffic growing in proportion.
-NCU_TRAFFIC = {"attn_decode_kernel": 16947456, "attn_prefill_sm100_kernel": 4 * (84079872 + 22571264)}
+NCU_TRAFFIC = {"attn_decode_kernel": 16947456, "attn_prefill_sm100_kernel": 4 * (83955712 + 20809472)}
 
 
 def measured_peaks():
