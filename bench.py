@@ -37,7 +37,7 @@ PREFILL_TOKENS = 32768
 # DRAM bytes per launch of the dominant kernel from an ncu capture of the same kernel
 # (dram__bytes_read.sum + dram__bytes_write.sum); see profiles/ for the command and the raw figures.
 # decode: captured at the benchmark shape (profiles/attn_decode_c2.md). prefill: captured at 8192 tokens
-# (84.1 MB read + 22.6 MB written; profiles/attn_prefill_sm100_8k.md) and scaled by the 4x token count,
+# (84.0 MB read + 20.8 MB written; profiles/attn_prefill_sm100_8k.md) and scaled by the 4x token count,
 # compulsory q/K/V/out traffic growing in proportion.
 NCU_TRAFFIC = {"attn_decode_kernel": 16947456, "attn_prefill_sm100_kernel": 4 * (83955712 + 20809472)}
 
