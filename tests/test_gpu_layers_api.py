@@ -110,3 +110,39 @@ def test_layers_host_rejects_overflow():
     inv = helpers.to_dev(helpers.inv_freq())
     with pytest.raises(ib.IngotError, match="context window exceeded"):
         ib.attn_layers_host(kv, 0, z, zk, zk, z.clone().pin_memory(), inv, 8)
+
+
+def test_decode_layers_paged_batch_of_uneven_lengths():
+    """Several layers of a paged cache, sequences from one key to many splits long, in one call: every
+    (layer, sequence) must match the reference and equal the single-layer entry point's parity; a
+    second call gives the same bits and leaves the status word clear (work counters are back at zero)."""
+    import torch
+    import ingot_b200 as ib
+    n_layers = 3
+    lens = np.array([1, 17, 255, 256, 1000, 2049], dtype=np.int32)
+    n_seq = len(lens)
+    rng = np.random.default_rng(99)
+    nb = int(((lens + 15) // 16).sum())
+    perm = rng.permutation(nb).astype(np.int32)
+    bt_np = W.block_tables(lens, perm)
+    kv = ib.KVCache(ib.KV_PAGED, n_layers, HKV, nb, max_seqs=n_seq)
+    bt = helpers.to_dev(bt_np)
+    ks = [[rng.standard_normal((int(n), HKV, D), dtype=np.float32).astype(np.float16) for n in lens] for _ in range(n_layers)]
+    vs = [[rng.standard_normal((int(n), HKV, D), dtype=np.float32).astype(np.float16) for n in lens] for _ in range(n_layers)]
+    for l in range(n_layers):
+        for s in range(n_seq):
+            kv.import_f16(l, helpers.to_dev(ks[l][s]), helpers.to_dev(vs[l][s]), 0, bt[s])
+    q = rng.standard_normal((n_layers, n_seq, H, D), dtype=np.float32)
+    qd = helpers.to_dev(q)
+    lens_d = helpers.to_dev(lens)
+    out = torch.zeros(n_layers, n_seq, H, D, device="cuda")
+    ib.attn_decode_layers(kv, 0, qd, out, seq_lens=lens_d, max_seq_len=int(lens.max()), block_tables=bt)
+    torch.cuda.synchronize()
+    first = out.clone()
+    for l in range(n_layers):
+        wl = W.Decode(q[l], ks[l], vs[l], lens)
+        helpers.assert_parity(out[l].cpu().numpy(), helpers.oracle_decode(wl), f"paged layers decode, layer {l}")
+    out.zero_()
+    ib.attn_decode_layers(kv, 0, qd, out, seq_lens=lens_d, max_seq_len=int(lens.max()), block_tables=bt)
+    torch.cuda.synchronize()
+    assert torch.equal(out, first) and kv.status() == 0
