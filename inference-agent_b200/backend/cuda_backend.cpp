@@ -27,6 +27,7 @@
 #include <cstring>
 #include <stdexcept>
 #include <string>
+#include <algorithm>
 #include <vector>
 
 #include "ingot_cuda.h"
@@ -38,6 +39,14 @@ cudaError_t ingot_support_rmsnorm(float* out, const float* x, const float* w, in
 cudaError_t ingot_support_silu_mul(float* gate, const float* up, size_t n, cudaStream_t s);
 cudaError_t ingot_support_linear(float* out, const void* w, int w_is_f16, const float* x, int n_in, int n_out, int n_tok,
                                  int accumulate, cudaStream_t s);
+// tensor-core form of the batched projections (linear_sm100.cu)
+struct ingot_linear_ws;
+cudaError_t ingot_linear_ws_create(ingot_linear_ws** out, int max_tok, int max_in);
+void ingot_linear_ws_destroy(ingot_linear_ws* ws);
+int ingot_linear_tc_supported(const ingot_linear_ws* ws, int w_is_f16, int n_in, int n_out, int n_tok);
+cudaError_t ingot_linear_tc_prepare(ingot_linear_ws* ws, const float* x, int n_in, int n_tok, cudaStream_t s);
+cudaError_t ingot_linear_tc_run(ingot_linear_ws* ws, float* out, const void* w, int n_in, int n_out, int accumulate, cudaStream_t s);
+int ingot_linear_ws_status(ingot_linear_ws* ws);
 }
 
 namespace {
@@ -98,6 +107,10 @@ public:
         cuda_check(cudaMallocHost(&pos_host_, 2 * sizeof(int32_t)), "cudaMallocHost(pos)");
         cuda_check(cudaMallocHost(&x_host_, nb * c.n_embd * sizeof(float)), "cudaMallocHost(x)");
         cuda_check(cudaMallocHost(&logits_, size_t(c.n_vocab) * sizeof(float)), "cudaMallocHost(logits)");
+        // INGOT_LINEAR_TC=0 keeps the batched projections on the f32 FMA kernels (diagnostics).
+        const char* tc = getenv("INGOT_LINEAR_TC");
+        if (n_batch >= 16 && !(tc && atoi(tc) == 0))
+            cuda_check(ingot_linear_ws_create(&lin_ws_, n_batch, std::max(c.n_embd, std::max(c.n_ff, int(q_dim)))), "linear workspace");
     }
 
     ~CudaBackend() override {
@@ -117,6 +130,7 @@ public:
         cudaFreeHost(pos_host_);
         cudaFreeHost(x_host_);
         cudaFreeHost(logits_);
+        ingot_linear_ws_destroy(lin_ws_);
         ingot_kv_destroy(kv_);
         cudaStreamDestroy(stream_);
     }
@@ -180,6 +194,7 @@ public:
         int status = 0;
         ingot_check(ingot_kv_status(kv_, stream_, &status));
         if (status != 0) throw std::runtime_error("cuda: attention kernel reported status " + std::to_string(status));
+        if (n > 1 && lin_ws_ && ingot_linear_ws_status(lin_ws_) != 0) throw std::runtime_error("cuda: a projection kernel gave up on a bounded wait");
         return logits_;
     }
 
@@ -190,9 +205,9 @@ public:
         for (int l = 0; l < c.n_layer; l++) {
             const DevLayer& D = layers_[l];
             cuda_check(ingot_support_rmsnorm(h_, x_, D.attn_norm, n, c.n_embd, c.rms_eps, stream_), "rmsnorm");
-            linear(q_, D.wq, h_, n, false);
-            linear(k_, D.wk, h_, n, false);
-            linear(v_, D.wv, h_, n, false);
+            const DevWeight* qkv[3] = {&D.wq, &D.wk, &D.wv};
+            float* qkv_out[3] = {q_, k_, v_};
+            linear_group(qkv_out, qkv, 3, h_, n, false);
             ingot_check(ingot_rope_kv_append(kv_, l, q_, q_rot_, k_, v_, inv_freq_, c.n_head, pos, n,
                                              device_pos ? pos_dev_ : nullptr, nullptr, nullptr, 0, stream_));
             if (n == 1)
@@ -202,12 +217,15 @@ public:
             else
                 ingot_check(ingot_attn_prefill(kv_, l, q_rot_, INGOT_F16, attn_, INGOT_F32, c.n_head, pos, n, nullptr, 0,
                                                stream_));
-            linear(x_, D.wo, attn_, n, true);
+            const DevWeight* wo[1] = {&D.wo};
+            linear_group(&x_, wo, 1, attn_, n, true);
             cuda_check(ingot_support_rmsnorm(h_, x_, D.ffn_norm, n, c.n_embd, c.rms_eps, stream_), "rmsnorm");
-            linear(gate_, D.w_gate, h_, n, false);
-            linear(up_, D.w_up, h_, n, false);
+            const DevWeight* gu[2] = {&D.w_gate, &D.w_up};
+            float* gu_out[2] = {gate_, up_};
+            linear_group(gu_out, gu, 2, h_, n, false);
             cuda_check(ingot_support_silu_mul(gate_, up_, size_t(n) * c.n_ff, stream_), "silu_mul");
-            linear(x_, D.w_down, gate_, n, true);
+            const DevWeight* wd[1] = {&D.w_down};
+            linear_group(&x_, wd, 1, gate_, n, true);
         }
         // Logits for the last token only.
         cuda_check(ingot_support_rmsnorm(h_, x_ + size_t(n - 1) * c.n_embd, output_norm_, 1, c.n_embd, c.rms_eps, stream_), "rmsnorm");
@@ -249,6 +267,20 @@ private:
         cuda_check(cudaMemcpy(w.data, t.data, t.nbytes(), cudaMemcpyHostToDevice), "cudaMemcpy(weight)");
         return w;
     }
+    // Projections that read the same activations. Batches go to the tensor-core kernel (the activations are split
+    // into f16 hi/lo parts once per group); single tokens and unsupported shapes to the f32 kernels.
+    void linear_group(float* const* outs, const DevWeight* const* ws, int count, const float* x, int n_tok, bool accumulate) {
+        bool tc = lin_ws_ != nullptr;
+        for (int i = 0; i < count && tc; i++)
+            tc = ws[i]->n_in == ws[0]->n_in && ingot_linear_tc_supported(lin_ws_, ws[i]->is_f16, ws[i]->n_in, ws[i]->n_out, n_tok);
+        if (!tc) {
+            for (int i = 0; i < count; i++) linear(outs[i], *ws[i], x, n_tok, accumulate);
+            return;
+        }
+        cuda_check(ingot_linear_tc_prepare(lin_ws_, x, ws[0]->n_in, n_tok, stream_), "linear (split)");
+        for (int i = 0; i < count; i++)
+            cuda_check(ingot_linear_tc_run(lin_ws_, outs[i], ws[i]->data, ws[i]->n_in, ws[i]->n_out, accumulate ? 1 : 0, stream_), "linear (tensor core)");
+    }
     void linear(float* out, const DevWeight& w, const float* x, int n_tok, bool accumulate) {
         cuda_check(ingot_support_linear(out, w.data, w.is_f16, x, w.n_in, w.n_out, n_tok, accumulate ? 1 : 0, stream_), "linear");
     }
@@ -257,6 +289,7 @@ private:
     int n_ctx_, n_batch_;
     cudaStream_t stream_ = nullptr;
     ingot_kv* kv_ = nullptr;
+    ingot_linear_ws* lin_ws_ = nullptr;
     std::vector<DevLayer> layers_;
     std::vector<void*> allocs_;
     float *output_norm_ = nullptr, *inv_freq_ = nullptr;

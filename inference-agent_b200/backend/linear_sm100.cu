@@ -1,0 +1,339 @@
+// Batched projections of CudaBackend::forward_batch on the sm_100a tensor cores:
+//   out[t][r] (+)= sum_i W[r][i] * x[t][i]      W f16 [n_out][n_in] (ggml ne = [n_in, n_out]), x and out f32
+// — the job of the matmul loops of the CPU reference (src/cpu_backend.cpp:39-42, 71-85 over
+// ops::dot_row, src/ops.cpp:127-141) and of Metal's matmul_f16 (src/metal_backend.mm:282-322) for a
+// prefill chunk of up to n_batch tokens.
+//
+// Precision. The reference multiplies f32 activations with widened f16 weights and accumulates in f32, and
+// greedy decoding on a random-init model has to reproduce its token choices, so activations are NOT
+// rounded to f16: x is split as x = hi + lo with hi = f16(x), lo = f16(x - hi) (22 significant bits
+// together), and every k-step issues two MMAs into the same f32 accumulator, hi*W and lo*W. The weights are
+// used as stored, the products are exact, the accumulation is f32: the result differs from the reference
+// only by summation order and the 2^-22 truncation of x.
+//
+// Kernel. One CTA = 128 tokens x 128 outputs over a slice of k (split-k fills the GPU when there are few
+// output tiles; slices go to a scratch and are summed in a fixed order afterwards, so results are
+// reproducible). 6 warps: warp 0 streams [128 rows][64 k] boxes of hi, lo and W (128-byte swizzle, 48 KB per
+// stage, 4 stages) with TMA; warp 1 issues tcgen05.mma (kind::f16, M = N = 128, K = 16; all lanes walk the
+// loop, one elected lane issues); warps 2-5 read the 128x128 f32 accumulator out of tensor memory, one
+// thread per token row. Rows past n_tok and outputs past n_out are zero-filled by TMA and not stored.
+// Every mbarrier wait is bounded; on expiry the CTA raises the workspace's status word and leaves.
+#include "../csrc/sm100_ptx.cuh"
+
+#include <cuda_fp16.h>
+
+#include <algorithm>
+#include <map>
+#include <mutex>
+#include <tuple>
+
+namespace {
+
+using namespace ingot_sm100;
+
+constexpr int kBM = 128, kBN = 128, kBK = 64;
+constexpr int kStages = 4;
+constexpr int kBoxBytes = 128 * kBK * 2;        // 16 KB: 128 rows x 64 f16
+constexpr int kStageBytes = 3 * kBoxBytes;      // hi, lo, W
+constexpr int kThreads = 192;
+constexpr int kOffBar = kStages * kStageBytes;
+constexpr int kSmemBytes = kOffBar + 128 + 1024;  // barriers + alignment slack
+constexpr uint32_t kTmemCols = 128;
+constexpr uint32_t kIdesc = (1u << 4) | ((uint32_t)(kBN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);  // f16 x f16 -> f32, both K-major
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+struct Bars {
+    uint64_t full[kStages];
+    uint64_t empty[kStages];
+    uint64_t done;
+    uint32_t tmem_base;
+    uint32_t abort_flag;
+};
+
+struct GemmParams {
+    float* out;        // [n_tok][n_out]
+    float* partial;    // [n_split][n_tok][n_out] when n_split > 1
+    int* status;
+    int n_tok, n_out, k_steps, n_split, accumulate;
+};
+
+__global__ void __launch_bounds__(kThreads, 1)
+linear_sm100_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_constant__ CUtensorMap map_lo,
+                    const __grid_constant__ CUtensorMap map_w, const GemmParams p) {
+    extern __shared__ unsigned char smem_dyn[];
+    const uint32_t smem_base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
+    unsigned char* smem_al = smem_dyn + (smem_base - smem_u32(smem_dyn));
+    Bars* bars = reinterpret_cast<Bars*>(smem_al + kOffBar);
+    volatile uint32_t* abort_flag = &bars->abort_flag;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int warp_u = __shfl_sync(0xffffffffu, warp, 0);
+    const int n0 = blockIdx.x * kBN, m0 = blockIdx.y * kBM, split = blockIdx.z;
+    const int ks_begin = (int)((long long)p.k_steps * split / p.n_split);
+    const int ks_end = (int)((long long)p.k_steps * (split + 1) / p.n_split);
+    const int n_it = ks_end - ks_begin;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; s++) { mbar_init(smem_u32(&bars->full[s]), 1); mbar_init(smem_u32(&bars->empty[s]), 1); }
+        mbar_init(smem_u32(&bars->done), 1);
+        bars->abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&bars->tmem_base)), "r"(kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = bars->tmem_base;
+
+    if (warp_u == 0) {
+        // ---------------- TMA producer ----------------
+        int armed = 0;
+        bool ok = true;
+        for (int it = 0; it < n_it && ok; it++) {
+            const int s = it % kStages;
+            const uint32_t full = smem_u32(&bars->full[s]);
+            if (lane == 0) {
+                ok = mbar_wait(smem_u32(&bars->empty[s]), (uint32_t)(((it / kStages) & 1) ^ 1), abort_flag, kWaitLimitNs);
+                if (ok) {
+                    mbar_expect_tx(full, kStageBytes);
+                    const uint32_t dst = smem_base + s * kStageBytes;
+                    const int k = (ks_begin + it) * kBK;
+                    tma_load_2d(dst, &map_hi, k, m0, full);
+                    tma_load_2d(dst + kBoxBytes, &map_lo, k, m0, full);
+                    tma_load_2d(dst + 2 * kBoxBytes, &map_w, k, n0, full);
+                }
+            }
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (ok) armed = it + 1;
+        }
+        if (!ok && lane == 0) {
+            // copies already issued must land before the CTA's shared memory is released
+            for (int it = max(0, armed - kStages); it < armed; it++) {
+                const uint64_t t0 = globaltimer_ns();
+                while (!mbar_try_wait(smem_u32(&bars->full[it % kStages]), (uint32_t)((it / kStages) & 1)) &&
+                       globaltimer_ns() - t0 < 100000000ull) {}
+            }
+        }
+    } else if (warp_u == 1) {
+        // ---------------- MMA issuer ----------------
+        bool ok = true;
+        for (int it = 0; it < n_it && ok; it++) {
+            const int s = it % kStages;
+            ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars->full[s]), (uint32_t)((it / kStages) & 1), abort_flag, kWaitLimitNs)) != 0;
+            if (!ok) break;
+            tc_fence_after();
+            if (elect_one()) {
+                const uint32_t a_hi = smem_base + s * kStageBytes, a_lo = a_hi + kBoxBytes, b = a_hi + 2 * kBoxBytes;
+#pragma unroll
+                for (int ks = 0; ks < kBK / 16; ks++)
+                    tc_mma_ss(tmem, make_desc(a_hi + ks * 32, 16, 1024), make_desc(b + ks * 32, 16, 1024), kIdesc, (it > 0 || ks > 0) ? 1u : 0u);
+#pragma unroll
+                for (int ks = 0; ks < kBK / 16; ks++)
+                    tc_mma_ss(tmem, make_desc(a_lo + ks * 32, 16, 1024), make_desc(b + ks * 32, 16, 1024), kIdesc, 1u);
+                tc_commit(smem_u32(&bars->empty[s]));
+                if (it == n_it - 1) tc_commit(smem_u32(&bars->done));
+            }
+            __syncwarp();
+        }
+    } else {
+        // ---------------- epilogue: accumulator -> global, one thread per token row ----------------
+        const int lg = warp & 3;  // the tensor-memory lane group this warp may read
+        const int row = m0 + lg * 32 + lane;
+        bool ok = n_it > 0 && mbar_wait(smem_u32(&bars->done), 0, abort_flag, kWaitLimitNs);
+        ok = __all_sync(0xffffffffu, ok) != 0;
+        if (ok) {
+            tc_fence_after();
+            float* dst = (p.n_split > 1 ? p.partial + (size_t)split * p.n_tok * p.n_out : p.out) + (size_t)row * p.n_out + n0;
+            const bool add = p.n_split == 1 && p.accumulate;
+#pragma unroll
+            for (int c = 0; c < kBN / 32; c++) {
+                float v[32];
+                tmem_ld32(tmem + ((uint32_t)(lg * 32) << 16) + c * 32, v);
+                tmem_wait_ld();
+                if (row < p.n_tok) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 4) {
+                        const int col = n0 + c * 32 + i;
+                        if (col + 3 < p.n_out) {
+                            float4* d4 = reinterpret_cast<float4*>(dst + c * 32 + i);
+                            float4 o = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+                            if (add) { const float4 old = *d4; o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w; }
+                            *d4 = o;
+                        } else {
+                            for (int e = 0; e < 4; e++)
+                                if (col + e < p.n_out) dst[c * 32 + i + e] = add ? dst[c * 32 + i + e] + v[i + e] : v[i + e];
+                        }
+                    }
+                }
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (threadIdx.x == 0 && *abort_flag) atomicOr(p.status, 1);
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
+    }
+}
+
+// out (+)= sum over the k slices, in slice order
+__global__ void splitk_reduce_kernel(float* out, const float* partial, int n_split, size_t n, int accumulate) {
+    const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (i >= n) return;
+    float4 acc = accumulate ? *reinterpret_cast<const float4*>(out + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s = 0; s < n_split; s++) {
+        const float4 v = *reinterpret_cast<const float4*>(partial + (size_t)s * n + i);
+        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    *reinterpret_cast<float4*>(out + i) = acc;
+}
+
+// hi = f16(x), lo = f16(x - hi)
+__global__ void split_f16_kernel(__half* hi, __half* lo, const float* x, size_t n) {
+    const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (i >= n) return;
+    const float4 v = *reinterpret_cast<const float4*>(x + i);
+    const float f[4] = {v.x, v.y, v.z, v.w};
+    __half h[4], l[4];
+#pragma unroll
+    for (int e = 0; e < 4; e++) {
+        h[e] = __float2half_rn(f[e]);
+        l[e] = __float2half_rn(f[e] - __half2float(h[e]));
+    }
+    *reinterpret_cast<uint2*>(hi + i) = *reinterpret_cast<const uint2*>(h);
+    *reinterpret_cast<uint2*>(lo + i) = *reinterpret_cast<const uint2*>(l);
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(sym);
+    });
+    return fn;
+}
+
+// f16 matrix [rows][cols] row-major, boxes of 128 rows x 64 columns, 128-byte swizzle, zero fill outside
+bool make_map(CUtensorMap* map, const void* base, int rows, int cols) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)kBK, 128};
+    const cuuint32_t elem[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace
+
+struct ingot_linear_ws {
+    __half* hi = nullptr;
+    __half* lo = nullptr;
+    float* partial = nullptr;
+    int* status = nullptr;
+    size_t act_elems = 0, partial_floats = 0;
+    int num_sms = 0;
+    int prepared_tok = 0, prepared_in = 0;
+    CUtensorMap map_hi, map_lo;
+    std::map<std::tuple<const void*, int, int>, CUtensorMap> w_maps;  // one per weight matrix
+};
+
+extern "C" {
+
+// max_tok x max_in: the largest activation matrix that will be prepared.
+cudaError_t ingot_linear_ws_create(ingot_linear_ws** out, int max_tok, int max_in) {
+    *out = nullptr;
+    ingot_linear_ws* ws = new ingot_linear_ws();
+    ws->act_elems = (size_t)max_tok * max_in;
+    ws->partial_floats = (size_t)8 << 20;  // 32 MB of k-slice partials
+    int dev = 0;
+    cudaError_t e;
+    if ((e = cudaGetDevice(&dev)) != cudaSuccess ||
+        (e = cudaDeviceGetAttribute(&ws->num_sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess ||
+        (e = cudaMalloc(&ws->hi, ws->act_elems * 2)) != cudaSuccess || (e = cudaMalloc(&ws->lo, ws->act_elems * 2)) != cudaSuccess ||
+        (e = cudaMalloc(&ws->partial, ws->partial_floats * 4)) != cudaSuccess || (e = cudaMalloc(&ws->status, sizeof(int))) != cudaSuccess ||
+        (e = cudaMemset(ws->status, 0, sizeof(int))) != cudaSuccess ||
+        (e = cudaFuncSetAttribute(linear_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes)) != cudaSuccess) {
+        cudaFree(ws->hi); cudaFree(ws->lo); cudaFree(ws->partial); cudaFree(ws->status);
+        delete ws;
+        return e;
+    }
+    *out = ws;
+    return cudaSuccess;
+}
+
+void ingot_linear_ws_destroy(ingot_linear_ws* ws) {
+    if (!ws) return;
+    cudaFree(ws->hi); cudaFree(ws->lo); cudaFree(ws->partial); cudaFree(ws->status);
+    delete ws;
+}
+
+// Whether a projection of this shape can take the tensor-core path.
+int ingot_linear_tc_supported(const ingot_linear_ws* ws, int w_is_f16, int n_in, int n_out, int n_tok) {
+    return ws && encode_fn() && w_is_f16 && n_tok >= 16 && n_in % kBK == 0 && n_out % 4 == 0 && (size_t)n_tok * n_in <= ws->act_elems;
+}
+
+// Splits x [n_tok][n_in] f32 into the workspace's hi/lo f16 matrices; the following ingot_linear_tc_run calls use them.
+cudaError_t ingot_linear_tc_prepare(ingot_linear_ws* ws, const float* x, int n_in, int n_tok, cudaStream_t s) {
+    const size_t n = (size_t)n_tok * n_in;
+    if (n > ws->act_elems || n_in % kBK != 0) return cudaErrorInvalidValue;
+    split_f16_kernel<<<(unsigned)((n / 4 + 255) / 256), 256, 0, s>>>(ws->hi, ws->lo, x, n);
+    if (ws->prepared_tok != n_tok || ws->prepared_in != n_in) {
+        if (!make_map(&ws->map_hi, ws->hi, n_tok, n_in) || !make_map(&ws->map_lo, ws->lo, n_tok, n_in)) return cudaErrorUnknown;
+        ws->prepared_tok = n_tok;
+        ws->prepared_in = n_in;
+    }
+    return cudaGetLastError();
+}
+
+// out [n_tok][n_out] (+)= prepared activations x W^T, W f16 [n_out][n_in] on the device.
+cudaError_t ingot_linear_tc_run(ingot_linear_ws* ws, float* out, const void* w, int n_in, int n_out, int accumulate, cudaStream_t s) {
+    const int n_tok = ws->prepared_tok;
+    if (n_in != ws->prepared_in || n_tok < 1) return cudaErrorInvalidValue;
+    const auto key = std::make_tuple(w, n_out, n_in);
+    auto it = ws->w_maps.find(key);
+    if (it == ws->w_maps.end()) {
+        CUtensorMap m;
+        if (!make_map(&m, w, n_out, n_in)) return cudaErrorUnknown;
+        it = ws->w_maps.emplace(key, m).first;
+    }
+    const int tiles = ((n_out + kBN - 1) / kBN) * ((n_tok + kBM - 1) / kBM);
+    const int k_steps = n_in / kBK;
+    // enough k slices to give every SM a CTA, at least 4 k-steps each, and no more than the scratch holds
+    int n_split = std::max(1, std::min({ws->num_sms / tiles, k_steps / 4, (int)(ws->partial_floats / ((size_t)n_tok * n_out))}));
+    GemmParams p;
+    p.out = out; p.partial = ws->partial; p.status = ws->status;
+    p.n_tok = n_tok; p.n_out = n_out; p.k_steps = k_steps; p.n_split = n_split; p.accumulate = accumulate;
+    dim3 grid((n_out + kBN - 1) / kBN, (n_tok + kBM - 1) / kBM, n_split);
+    linear_sm100_kernel<<<grid, kThreads, kSmemBytes, s>>>(ws->map_hi, ws->map_lo, it->second, p);
+    if (n_split > 1) {
+        const size_t n = (size_t)n_tok * n_out;
+        splitk_reduce_kernel<<<(unsigned)((n / 4 + 255) / 256), 256, 0, s>>>(out, ws->partial, n_split, n, accumulate);
+    }
+    return cudaGetLastError();
+}
+
+// The status word: non-zero after a bounded wait expired in some launch since the last call. Synchronises the device.
+int ingot_linear_ws_status(ingot_linear_ws* ws) {
+    int v = 0;
+    if (cudaMemcpy(&v, ws->status, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+    if (v) cudaMemset(ws->status, 0, sizeof(int));
+    return v;
+}
+
+}  // extern "C"

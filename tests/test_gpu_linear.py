@@ -1,0 +1,69 @@
+"""The tensor-core form of CudaBackend's batched projections (backend/linear_sm100.cu) against float64 matmul.
+
+out[t][r] (+)= sum_i W[r][i] x[t][i] with f16 weights and f32 activations split into f16 hi + lo parts: the
+result has to be an f32-accurate product (the reference multiplies f32 activations with widened f16 weights,
+src/ops.cpp:127-141), not an f16-activation one.
+"""
+import ctypes as C
+import os
+
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+ENGINE = os.path.join(ROOT, "inference-agent_b200", "backend", "_build", "libingot_engine_cuda.so")
+
+
+def _lib():
+    if not os.path.exists(ENGINE):
+        pytest.skip("libingot_engine_cuda.so not built (needs a reference checkout at build time)")
+    lib = C.CDLL(ENGINE)
+    lib.ingot_linear_ws_create.argtypes = [C.POINTER(C.c_void_p), C.c_int, C.c_int]
+    lib.ingot_linear_ws_destroy.argtypes = [C.c_void_p]
+    lib.ingot_linear_tc_supported.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int]
+    lib.ingot_linear_tc_prepare.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p]
+    lib.ingot_linear_tc_run.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p]
+    lib.ingot_linear_ws_status.argtypes = [C.c_void_p]
+    return lib
+
+
+@pytest.mark.parametrize("n_tok,n_in,n_out,accumulate", [
+    (128, 3072, 3072, 1),    # wo at the Llama-3.2-3B shape, one token tile, split-k
+    (128, 3072, 1024, 0),    # wk / wv: few output tiles, deep split-k
+    (130, 3072, 8192, 0),    # gate / up, a second, nearly empty token tile
+    (512, 8192, 3072, 1),    # down projection of a full 512-token chunk
+    (16, 64, 4, 0),          # smallest supported shape: one k-step, four outputs
+    (77, 256, 132, 1),       # output count that is not a multiple of the tile
+])
+def test_linear_tc_matches_float64(n_tok, n_in, n_out, accumulate):
+    import torch
+    lib = _lib()
+    ws = C.c_void_p()
+    assert lib.ingot_linear_ws_create(C.byref(ws), 512, 8192) == 0
+    try:
+        g = torch.Generator(device="cuda").manual_seed(n_tok * 31 + n_out)
+        x = torch.randn(n_tok, n_in, device="cuda", generator=g)
+        w = (torch.randn(n_out, n_in, device="cuda", generator=g) * 0.02).half()
+        out0 = torch.randn(n_tok, n_out, device="cuda", generator=g)
+        out = out0.clone()
+        assert lib.ingot_linear_tc_supported(ws, 1, n_in, n_out, n_tok) == 1
+        stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+        assert lib.ingot_linear_tc_prepare(ws, x.data_ptr(), n_in, n_tok, stream) == 0
+        assert lib.ingot_linear_tc_run(ws, out.data_ptr(), w.data_ptr(), n_in, n_out, accumulate, stream) == 0
+        torch.cuda.synchronize()
+        want = x.double() @ w.double().t()
+        if accumulate:
+            want += out0.double()
+        err = (out.double() - want).abs().max().item()
+        scale = want.abs().max().item()
+        # f32 accumulation over n_in terms plus the 2^-22 truncation of x; an f16-activation product would be ~1e-3
+        assert err <= 1e-5 * scale * max(1.0, (n_in / 1024) ** 0.5), (err, scale)
+        # a second run on the same workspace gives the same bits (fixed summation order over the k slices)
+        out2 = out0.clone()
+        assert lib.ingot_linear_tc_run(ws, out2.data_ptr(), w.data_ptr(), n_in, n_out, accumulate, stream) == 0
+        torch.cuda.synchronize()
+        assert torch.equal(out, out2)
+        assert lib.ingot_linear_ws_status(ws) == 0
+    finally:
+        lib.ingot_linear_ws_destroy(ws)
