@@ -39,6 +39,8 @@ cudaError_t ingot_support_rmsnorm(float* out, const float* x, const float* w, in
 cudaError_t ingot_support_silu_mul(float* gate, const float* up, size_t n, cudaStream_t s);
 cudaError_t ingot_support_linear(float* out, const void* w, int w_is_f16, const float* x, int n_in, int n_out, int n_tok,
                                  int accumulate, cudaStream_t s);
+cudaError_t ingot_support_gemv_norm_group(float* const* outs, const void* const* ws, const int* n_out, int n_mat, int swiglu,
+                                          const float* x, const float* norm_w, float eps, int n_in, cudaStream_t s);
 // tensor-core form of the batched projections (linear_sm100.cu)
 struct ingot_linear_ws;
 cudaError_t ingot_linear_ws_create(ingot_linear_ws** out, int max_tok, int max_in);
@@ -204,10 +206,16 @@ public:
         const Config& c = m_.cfg;
         for (int l = 0; l < c.n_layer; l++) {
             const DevLayer& D = layers_[l];
-            cuda_check(ingot_support_rmsnorm(h_, x_, D.attn_norm, n, c.n_embd, c.rms_eps, stream_), "rmsnorm");
             const DevWeight* qkv[3] = {&D.wq, &D.wk, &D.wv};
             float* qkv_out[3] = {q_, k_, v_};
-            linear_group(qkv_out, qkv, 3, h_, n, false);
+            // single token, f16 weights: the norm and the projections that share it are one launch
+            const bool fused = n == 1 && fuse_decode_ && D.wq.is_f16 && D.wk.is_f16 && D.wv.is_f16 && D.w_gate.is_f16 && D.w_up.is_f16;
+            if (fused) {
+                gemv_norm_group(qkv_out, qkv, 3, false, x_, D.attn_norm);
+            } else {
+                cuda_check(ingot_support_rmsnorm(h_, x_, D.attn_norm, n, c.n_embd, c.rms_eps, stream_), "rmsnorm");
+                linear_group(qkv_out, qkv, 3, h_, n, false);
+            }
             ingot_check(ingot_rope_kv_append(kv_, l, q_, q_rot_, k_, v_, inv_freq_, c.n_head, pos, n,
                                              device_pos ? pos_dev_ : nullptr, nullptr, nullptr, 0, stream_));
             if (n == 1)
@@ -219,11 +227,15 @@ public:
                                                stream_));
             const DevWeight* wo[1] = {&D.wo};
             linear_group(&x_, wo, 1, attn_, n, true);
-            cuda_check(ingot_support_rmsnorm(h_, x_, D.ffn_norm, n, c.n_embd, c.rms_eps, stream_), "rmsnorm");
             const DevWeight* gu[2] = {&D.w_gate, &D.w_up};
             float* gu_out[2] = {gate_, up_};
-            linear_group(gu_out, gu, 2, h_, n, false);
-            cuda_check(ingot_support_silu_mul(gate_, up_, size_t(n) * c.n_ff, stream_), "silu_mul");
+            if (fused) {
+                gemv_norm_group(gu_out, gu, 2, true, x_, D.ffn_norm);  // gate_ <- silu(gate) * up
+            } else {
+                cuda_check(ingot_support_rmsnorm(h_, x_, D.ffn_norm, n, c.n_embd, c.rms_eps, stream_), "rmsnorm");
+                linear_group(gu_out, gu, 2, h_, n, false);
+                cuda_check(ingot_support_silu_mul(gate_, up_, size_t(n) * c.n_ff, stream_), "silu_mul");
+            }
             const DevWeight* wd[1] = {&D.w_down};
             linear_group(&x_, wd, 1, gate_, n, true);
         }
@@ -281,6 +293,13 @@ private:
         for (int i = 0; i < count; i++)
             cuda_check(ingot_linear_tc_run(lin_ws_, outs[i], ws[i]->data, ws[i]->n_in, ws[i]->n_out, accumulate ? 1 : 0, stream_), "linear (tensor core)");
     }
+    void gemv_norm_group(float* const* outs, const DevWeight* const* ws, int count, bool swiglu, const float* x, const float* norm_w) {
+        const void* wp[3] = {};
+        int rows[3] = {};
+        for (int i = 0; i < count; i++) { wp[i] = ws[i]->data; rows[i] = ws[i]->n_out; }
+        cuda_check(ingot_support_gemv_norm_group(outs, wp, rows, count, swiglu ? 1 : 0, x, norm_w, m_.cfg.rms_eps, ws[0]->n_in, stream_),
+                   "gemv (norm + projections)");
+    }
     void linear(float* out, const DevWeight& w, const float* x, int n_tok, bool accumulate) {
         cuda_check(ingot_support_linear(out, w.data, w.is_f16, x, w.n_in, w.n_out, n_tok, accumulate ? 1 : 0, stream_), "linear");
     }
@@ -302,6 +321,8 @@ private:
     int32_t* pos_host_ = nullptr;  // pinned
     int decode_calls_ = 0;
     const bool profile_ = getenv("INGOT_PROFILE") != nullptr;
+    // INGOT_DECODE_FUSED=0: separate norm / projection / SwiGLU launches in single-token steps (diagnostics)
+    const bool fuse_decode_ = !(getenv("INGOT_DECODE_FUSED") && atoi(getenv("INGOT_DECODE_FUSED")) == 0);
     cudaEvent_t ev0_ = nullptr, ev1_ = nullptr;
     double gpu_ms_ = 0, wall_ms_ = 0, gpu1_ms_ = 0;
     int calls_ = 0, calls1_ = 0;

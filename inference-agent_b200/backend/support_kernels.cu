@@ -132,6 +132,77 @@ __global__ void __launch_bounds__(256) gemv_kernel(float* out, const W* w, const
     if (lane == 0) out[row] = accumulate ? out[row] + v : v;
 }
 
+// Single-token form with the RMS norm folded in, for up to three f16 matrices that read the same vector
+// (q/k/v; or gate/up with the SwiGLU product as the epilogue): out_m[r] = scale * dot(W_m[r][:], x .* norm_w),
+// scale = rsqrt(mean(x^2) + eps). Every warp sees the whole of x while it walks its row, so it gets the sum of
+// squares for free; the scale is applied to the finished dot product (ops::rmsnorm, src/ops.cpp:227-232, scales
+// the vector first: the same product up to rounding order). One launch replaces the norm and two or three
+// matrix-vector launches of a layer.
+struct GemvGroup {
+    const __half* w[3];
+    float* out[3];
+    int row_end[3];  // running totals of the matrices' row counts
+    int n_mat;
+};
+
+template <bool kSwiGLU>
+__global__ void __launch_bounds__(256) gemv_norm_group_kernel(const GemvGroup g, const float* x, const float* norm_w, float eps, int n_in) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    int row = blockIdx.x * (blockDim.x >> 5) + warp;
+    const int total = kSwiGLU ? g.row_end[0] : g.row_end[g.n_mat - 1];
+    if (row >= total) return;
+    int mat = 0;
+    if (!kSwiGLU) {
+        while (row >= g.row_end[mat]) mat++;
+        if (mat > 0) row -= g.row_end[mat - 1];
+    }
+    const __half* wa = g.w[mat] + (size_t)row * n_in;
+    const __half* wb = kSwiGLU ? g.w[1] + (size_t)row * n_in : nullptr;
+    float acc_a = 0.f, acc_b = 0.f, ss = 0.f;
+    // four 16-byte weight loads in flight per lane (4 chunks of one matrix, or 2 of each of gate and up), all
+    // issued before the first use
+    constexpr int kChunks = kSwiGLU ? 2 : 4;
+    for (int i = lane * 8; i < n_in; i += 256 * kChunks) {
+        float a[kChunks][8], b[kChunks][8];
+#pragma unroll
+        for (int h = 0; h < kChunks; h++) {
+            if (i + h * 256 < n_in) {
+                load8<__half>(wa + i + h * 256, a[h]);
+                if (kSwiGLU) load8<__half>(wb + i + h * 256, b[h]);
+            }
+        }
+#pragma unroll
+        for (int h = 0; h < kChunks; h++) {
+            const int o = i + h * 256;
+            if (o < n_in) {
+                const float4 xa = __ldg(reinterpret_cast<const float4*>(x + o)), xb = __ldg(reinterpret_cast<const float4*>(x + o + 4));
+                const float4 na = __ldg(reinterpret_cast<const float4*>(norm_w + o)), nb = __ldg(reinterpret_cast<const float4*>(norm_w + o + 4));
+                const float xv[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
+                const float nv[8] = {na.x, na.y, na.z, na.w, nb.x, nb.y, nb.z, nb.w};
+#pragma unroll
+                for (int e = 0; e < 8; e++) {
+                    ss = fmaf(xv[e], xv[e], ss);
+                    const float xn = xv[e] * nv[e];
+                    acc_a = fmaf(a[h][e], xn, acc_a);
+                    if (kSwiGLU) acc_b = fmaf(b[h][e], xn, acc_b);
+                }
+            }
+        }
+    }
+    ss = warp_sum(ss);
+    acc_a = warp_sum(acc_a);
+    if (kSwiGLU) acc_b = warp_sum(acc_b);
+    if (lane == 0) {
+        const float scale = 1.0f / sqrtf(ss / float(n_in) + eps);
+        if (kSwiGLU) {
+            const float gt = acc_a * scale, up = acc_b * scale;
+            g.out[0][row] = gt / (1.0f + expf(-gt)) * up;  // silu(gate) * up, src/cpu_backend.cpp:79
+        } else {
+            g.out[mat][row] = acc_a * scale;
+        }
+    }
+}
+
 // Batched form (prefill): out[t][r] (+)= dot(W[r][:], x[t][:]) as a shared-memory tiled f32 GEMM on the FMA
 // pipes: 128 tokens x 64 outputs per CTA, k-steps of 16, 8x4 outputs per thread; weights are widened to
 // f32 when they are staged. The whole token batch of a prefill chunk up to 128 sits in one tile, so the
@@ -210,6 +281,28 @@ cudaError_t ingot_support_rmsnorm(float* out, const float* x, const float* w, in
 
 cudaError_t ingot_support_silu_mul(float* gate, const float* up, size_t n, cudaStream_t s) {
     silu_mul_kernel<<<unsigned((n + 255) / 256), 256, 0, s>>>(gate, up, n);
+    return cudaGetLastError();
+}
+
+// One token: out_m = (W_m . rmsnorm(x; norm_w, eps)) for n_mat <= 3 f16 matrices [n_out[m]][n_in] that share x; with
+// swiglu != 0 there are exactly two matrices of equal height (gate, up) and outs[0] receives silu(gate) * up.
+cudaError_t ingot_support_gemv_norm_group(float* const* outs, const void* const* ws, const int* n_out, int n_mat, int swiglu,
+                                          const float* x, const float* norm_w, float eps, int n_in, cudaStream_t s) {
+    if (n_mat < 1 || n_mat > 3 || n_in % 8 != 0 || (swiglu && (n_mat != 2 || n_out[0] != n_out[1]))) return cudaErrorInvalidValue;
+    GemvGroup g = {};
+    int total = 0;
+    for (int m = 0; m < n_mat; m++) {
+        g.w[m] = static_cast<const __half*>(ws[m]);
+        g.out[m] = outs[m];
+        total += n_out[m];
+        g.row_end[m] = swiglu ? n_out[0] : total;
+    }
+    g.n_mat = n_mat;
+    const int warps = 8;
+    const int rows = swiglu ? n_out[0] : total;
+    const unsigned grid = (rows + warps - 1) / warps;
+    if (swiglu) gemv_norm_group_kernel<true><<<grid, warps * 32, 0, s>>>(g, x, norm_w, eps, n_in);
+    else gemv_norm_group_kernel<false><<<grid, warps * 32, 0, s>>>(g, x, norm_w, eps, n_in);
     return cudaGetLastError();
 }
 

@@ -18,7 +18,8 @@ constexpr int kBlockTokens = INGOT_BLOCK_TOKENS;
 // (shaders/kernels.metal:291).
 constexpr int kPartStride = 132;
 // Independent launch chains the multi-layer decode call spreads its layers over.
-constexpr int kDecodeStreams = 8;  // upper bound; INGOT_DECODE_STREAMS picks how many are used (default 4)
+constexpr int kDecodeStreams = 8;
+constexpr int kHostPosSlots = 256;  // host-buffer calls that may be queued before the caller synchronises  // upper bound; INGOT_DECODE_STREAMS picks how many are used (default 4)
 
 // Bits of the device status word (ingot_kv::status_dev).
 enum : int {
@@ -44,6 +45,17 @@ struct ingot_kv {
     // staging for the host-buffer entry points (grown on demand)
     void* stage = nullptr;
     size_t stage_bytes = 0;
+    // single-token form of the host-buffer multi-layer call: its kernels captured once into a graph that reads the
+    // position and key count from device memory (fed from a ring of pinned slots), replayed by later calls
+    cudaGraph_t host_graph = nullptr;
+    cudaGraphExec_t host_exec = nullptr;
+    cudaStream_t capture_stream = nullptr;
+    int host_key[3] = {-1, -1, -1};      // layer_begin, layer_count, n_head the graph was captured for
+    const float* host_inv_freq = nullptr;
+    int host_calls = 0;                  // calls seen with this key (the first runs eagerly and sizes the scratch)
+    int32_t* host_pos_dev = nullptr;     // {position, key count}
+    int32_t* host_pos_pinned = nullptr;  // kHostPosSlots pairs
+    unsigned host_pos_next = 0;
     // side streams of the multi-layer decode call (created on first use) and their fork/join events
     cudaStream_t side_stream[kDecodeStreams] = {};
     cudaEvent_t side_done[kDecodeStreams] = {};

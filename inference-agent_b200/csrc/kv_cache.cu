@@ -87,6 +87,11 @@ void ingot_kv_destroy(ingot_kv* kv) {
     cudaFree(kv->status_dev);
     cudaFree(kv->part);
     cudaFree(kv->stage);
+    if (kv->host_exec) cudaGraphExecDestroy(kv->host_exec);
+    if (kv->host_graph) cudaGraphDestroy(kv->host_graph);
+    cudaFree(kv->host_pos_dev);
+    cudaFreeHost(kv->host_pos_pinned);
+    if (kv->capture_stream) cudaStreamDestroy(kv->capture_stream);
     for (int i = 0; i < kDecodeStreams; i++) {
         if (kv->side_stream[i]) cudaStreamDestroy(kv->side_stream[i]);
         if (kv->side_done[i]) cudaEventDestroy(kv->side_done[i]);
@@ -357,6 +362,7 @@ int ingot_attn_layers_host(ingot_kv* kv, int layer_begin, int layer_count, const
         kv->stage_bytes = 0;
         INGOT_CUDA_TRY(cudaMalloc(&kv->stage, need));
         kv->stage_bytes = need;
+        kv->host_key[0] = -1;  // a captured graph points into the old staging area
     }
     float* q_d = static_cast<float*>(kv->stage);
     float* k_d = q_d + L * q_elems;
@@ -366,19 +372,68 @@ int ingot_attn_layers_host(ingot_kv* kv, int layer_begin, int layer_count, const
     INGOT_CUDA_TRY(cudaMemcpyAsync(q_d, q_host, L * q_elems * 4, cudaMemcpyHostToDevice, s));
     INGOT_CUDA_TRY(cudaMemcpyAsync(k_d, k_host, L * kv_elems * 4, cudaMemcpyHostToDevice, s));
     INGOT_CUDA_TRY(cudaMemcpyAsync(v_d, v_host, L * kv_elems * 4, cudaMemcpyHostToDevice, s));
-    int rc = launch_rope_kv_append(kv, layer_begin, q_d, qh_d, k_d, v_d, inv_freq_dev, n_head, pos0, n_tok, nullptr, nullptr,
-                                   nullptr, 0, layer_count, s);
-    if (rc != INGOT_OK) return rc;
+    int rc = INGOT_OK;
     if (n_tok == 1) {
-        rc = ingot_attn_decode_layers(kv, layer_begin, layer_count, qh_d, INGOT_F16, o_d, INGOT_F32, n_head, 1, nullptr,
-                                      pos0 + 1, nullptr, 0, 0, stream);
-        if (rc != INGOT_OK) return rc;
-    } else {
-        for (int i = 0; i < layer_count; i++) {
-            rc = ingot_attn_prefill(kv, layer_begin + i, qh_d + i * q_elems, INGOT_F16, o_d + i * q_elems, INGOT_F32, n_head,
-                                    pos0, n_tok, nullptr, 0, stream);
-            if (rc != INGOT_OK) return rc;
+        // Single token: about 35 launches over 4 side streams. They are captured once per (layer range, head
+        // count) into a graph whose kernels read the position and the key count from device memory; later
+        // calls copy the new pair in and replay it, which takes the launch cost off the host.
+        if (!kv->host_pos_dev) {
+            INGOT_CUDA_TRY(cudaMalloc(&kv->host_pos_dev, 2 * sizeof(int32_t)));
+            INGOT_CUDA_TRY(cudaMallocHost(&kv->host_pos_pinned, kHostPosSlots * 2 * sizeof(int32_t)));
         }
+        const bool same = kv->host_key[0] == layer_begin && kv->host_key[1] == layer_count && kv->host_key[2] == n_head &&
+                          kv->host_inv_freq == inv_freq_dev;
+        if (!same) {
+            if (kv->host_exec) { cudaGraphExecDestroy(kv->host_exec); kv->host_exec = nullptr; }
+            if (kv->host_graph) { cudaGraphDestroy(kv->host_graph); kv->host_graph = nullptr; }
+            kv->host_key[0] = layer_begin; kv->host_key[1] = layer_count; kv->host_key[2] = n_head;
+            kv->host_inv_freq = inv_freq_dev;
+            kv->host_calls = 0;
+        }
+        int32_t* slot = kv->host_pos_pinned + 2 * (kv->host_pos_next++ % kHostPosSlots);
+        slot[0] = pos0;
+        slot[1] = pos0 + 1;
+        INGOT_CUDA_TRY(cudaMemcpyAsync(kv->host_pos_dev, slot, 2 * sizeof(int32_t), cudaMemcpyHostToDevice, s));
+        auto encode = [&](cudaStream_t on) -> int {
+            int r = launch_rope_kv_append(kv, layer_begin, q_d, qh_d, k_d, v_d, inv_freq_dev, n_head, pos0, 1, kv->host_pos_dev,
+                                          nullptr, nullptr, 0, layer_count, on);
+            if (r != INGOT_OK) return r;
+            return ingot_attn_decode_layers(kv, layer_begin, layer_count, qh_d, INGOT_F16, o_d, INGOT_F32, n_head, 1,
+                                            kv->host_pos_dev + 1, kv->capacity, nullptr, 0, 0, on);
+        };
+        static const bool use_graph = getenv("INGOT_HOST_GRAPH") == nullptr || atoi(getenv("INGOT_HOST_GRAPH")) != 0;
+        if (kv->host_exec) {
+            INGOT_CUDA_TRY(cudaGraphLaunch(kv->host_exec, s));
+        } else if (kv->host_calls++ == 0 || !use_graph) {
+            rc = encode(s);  // first call with this shape: eager (it sizes the decode scratch, which cannot happen under capture)
+            if (rc != INGOT_OK) return rc;
+        } else {
+            // Captured on a stream of the handle's own (the caller's may be the legacy default stream, which cannot
+            // be captured); the graph is then launched into the caller's stream like any other work.
+            if (!kv->capture_stream) INGOT_CUDA_TRY(cudaStreamCreateWithFlags(&kv->capture_stream, cudaStreamNonBlocking));
+            INGOT_CUDA_TRY(cudaStreamBeginCapture(kv->capture_stream, cudaStreamCaptureModeThreadLocal));
+            rc = encode(kv->capture_stream);
+            cudaGraph_t g = nullptr;
+            const cudaError_t ce = cudaStreamEndCapture(kv->capture_stream, &g);
+            if (rc != INGOT_OK || ce != cudaSuccess) {
+                if (g) cudaGraphDestroy(g);
+                kv->host_key[0] = -1;
+                return rc != INGOT_OK ? rc : ingot_cuda_fail(ce, "cudaStreamEndCapture");
+            }
+            kv->host_graph = g;
+            INGOT_CUDA_TRY(cudaGraphInstantiate(&kv->host_exec, g, 0));
+            INGOT_CUDA_TRY(cudaGraphLaunch(kv->host_exec, s));
+        }
+        INGOT_CUDA_TRY(cudaMemcpyAsync(out_host, o_d, L * q_elems * 4, cudaMemcpyDeviceToHost, s));
+        return INGOT_OK;
+    }
+    rc = launch_rope_kv_append(kv, layer_begin, q_d, qh_d, k_d, v_d, inv_freq_dev, n_head, pos0, n_tok, nullptr, nullptr,
+                               nullptr, 0, layer_count, s);
+    if (rc != INGOT_OK) return rc;
+    for (int i = 0; i < layer_count; i++) {
+        rc = ingot_attn_prefill(kv, layer_begin + i, qh_d + i * q_elems, INGOT_F16, o_d + i * q_elems, INGOT_F32, n_head, pos0,
+                                n_tok, nullptr, 0, stream);
+        if (rc != INGOT_OK) return rc;
     }
     INGOT_CUDA_TRY(cudaMemcpyAsync(out_host, o_d, L * q_elems * 4, cudaMemcpyDeviceToHost, s));
     return INGOT_OK;

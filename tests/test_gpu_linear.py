@@ -67,3 +67,39 @@ def test_linear_tc_matches_float64(n_tok, n_in, n_out, accumulate):
         assert lib.ingot_linear_ws_status(ws) == 0
     finally:
         lib.ingot_linear_ws_destroy(ws)
+
+
+@pytest.mark.parametrize("swiglu", [0, 1])
+def test_gemv_norm_group_matches_float64(swiglu):
+    """Single-token launch that folds the RMS norm into two or three matrix-vector products (and the SwiGLU
+    product into gate/up): against rmsnorm (src/ops.cpp:227-232) followed by float64 products."""
+    import torch
+    lib = _lib()
+    lib.ingot_support_gemv_norm_group.argtypes = [C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.POINTER(C.c_int), C.c_int, C.c_int,
+                                                  C.c_void_p, C.c_void_p, C.c_float, C.c_int, C.c_void_p]
+    n_in = 3072
+    rows = [8192, 8192] if swiglu else [3072, 1024, 1016]
+    g = torch.Generator(device="cuda").manual_seed(7 + swiglu)
+    x = torch.randn(n_in, device="cuda", generator=g) * 3
+    nw = 1 + 0.1 * torch.randn(n_in, device="cuda", generator=g)
+    ws = [(torch.randn(r, n_in, device="cuda", generator=g) * 0.02).half() for r in rows]
+    outs = [torch.zeros(r, device="cuda") for r in rows]
+    eps = 1e-5
+    outs_p = (C.c_void_p * len(rows))(*[o.data_ptr() for o in outs])
+    ws_p = (C.c_void_p * len(rows))(*[w.data_ptr() for w in ws])
+    rows_p = (C.c_int * len(rows))(*rows)
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    assert lib.ingot_support_gemv_norm_group(outs_p, ws_p, rows_p, len(rows), swiglu, x.data_ptr(), nw.data_ptr(), eps, n_in, stream) == 0
+    torch.cuda.synchronize()
+    xd = x.double()
+    h = xd * torch.rsqrt((xd * xd).mean() + eps) * nw.double()
+    want = [w.double() @ h for w in ws]
+    if swiglu:
+        gate, up = want
+        ref = gate / (1 + torch.exp(-gate)) * up
+        err = (outs[0].double() - ref).abs().max().item()
+        assert err <= 1e-5 * max(1.0, ref.abs().max().item()), err
+    else:
+        for o, r in zip(outs, want):
+            err = (o.double() - r).abs().max().item()
+            assert err <= 1e-5 * max(1.0, r.abs().max().item()), err
