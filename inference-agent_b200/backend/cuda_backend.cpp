@@ -39,8 +39,8 @@ cudaError_t ingot_support_rmsnorm(float* out, const float* x, const float* w, in
 cudaError_t ingot_support_silu_mul(float* gate, const float* up, size_t n, cudaStream_t s);
 cudaError_t ingot_support_linear(float* out, const void* w, int w_is_f16, const float* x, int n_in, int n_out, int n_tok,
                                  int accumulate, cudaStream_t s);
-cudaError_t ingot_support_gemv_norm_group(float* const* outs, const void* const* ws, const int* n_out, int n_mat, int swiglu,
-                                          const float* x, const float* norm_w, float eps, int n_in, cudaStream_t s);
+cudaError_t ingot_support_gemv_group(float* const* outs, const void* const* ws, const int* n_out, int n_mat, int swiglu, const float* x,
+                                     const float* norm_w, float eps, int n_in, int accumulate, cudaStream_t s);
 // tensor-core form of the batched projections (linear_sm100.cu)
 struct ingot_linear_ws;
 cudaError_t ingot_linear_ws_create(ingot_linear_ws** out, int max_tok, int max_in);
@@ -208,10 +208,11 @@ public:
             const DevLayer& D = layers_[l];
             const DevWeight* qkv[3] = {&D.wq, &D.wk, &D.wv};
             float* qkv_out[3] = {q_, k_, v_};
-            // single token, f16 weights: the norm and the projections that share it are one launch
-            const bool fused = n == 1 && fuse_decode_ && D.wq.is_f16 && D.wk.is_f16 && D.wv.is_f16 && D.w_gate.is_f16 && D.w_up.is_f16;
+            // single token, f16 weights: the weight-streaming kernel; the norm and the projections that share it are one launch
+            const bool fused = n == 1 && fuse_decode_ && streamable(D.wq) && streamable(D.wk) && streamable(D.wv) && streamable(D.wo) &&
+                               streamable(D.w_gate) && streamable(D.w_up) && streamable(D.w_down);
             if (fused) {
-                gemv_norm_group(qkv_out, qkv, 3, false, x_, D.attn_norm);
+                gemv_group(qkv_out, qkv, 3, false, x_, D.attn_norm, false);
             } else {
                 cuda_check(ingot_support_rmsnorm(h_, x_, D.attn_norm, n, c.n_embd, c.rms_eps, stream_), "rmsnorm");
                 linear_group(qkv_out, qkv, 3, h_, n, false);
@@ -226,22 +227,29 @@ public:
                 ingot_check(ingot_attn_prefill(kv_, l, q_rot_, INGOT_F16, attn_, INGOT_F32, c.n_head, pos, n, nullptr, 0,
                                                stream_));
             const DevWeight* wo[1] = {&D.wo};
-            linear_group(&x_, wo, 1, attn_, n, true);
+            if (fused) gemv_group(&x_, wo, 1, false, attn_, nullptr, true);
+            else linear_group(&x_, wo, 1, attn_, n, true);
             const DevWeight* gu[2] = {&D.w_gate, &D.w_up};
             float* gu_out[2] = {gate_, up_};
             if (fused) {
-                gemv_norm_group(gu_out, gu, 2, true, x_, D.ffn_norm);  // gate_ <- silu(gate) * up
+                gemv_group(gu_out, gu, 2, true, x_, D.ffn_norm, false);  // gate_ <- silu(gate) * up
             } else {
                 cuda_check(ingot_support_rmsnorm(h_, x_, D.ffn_norm, n, c.n_embd, c.rms_eps, stream_), "rmsnorm");
                 linear_group(gu_out, gu, 2, h_, n, false);
                 cuda_check(ingot_support_silu_mul(gate_, up_, size_t(n) * c.n_ff, stream_), "silu_mul");
             }
             const DevWeight* wd[1] = {&D.w_down};
-            linear_group(&x_, wd, 1, gate_, n, true);
+            if (fused) gemv_group(&x_, wd, 1, false, gate_, nullptr, true);
+            else linear_group(&x_, wd, 1, gate_, n, true);
         }
         // Logits for the last token only.
-        cuda_check(ingot_support_rmsnorm(h_, x_ + size_t(n - 1) * c.n_embd, output_norm_, 1, c.n_embd, c.rms_eps, stream_), "rmsnorm");
-        linear(logits_dev_, output_, h_, 1, false);
+        if (fuse_decode_ && streamable(output_)) {
+            const DevWeight* wl[1] = {&output_};
+            gemv_group(&logits_dev_, wl, 1, false, x_ + size_t(n - 1) * c.n_embd, output_norm_, false);
+        } else {
+            cuda_check(ingot_support_rmsnorm(h_, x_ + size_t(n - 1) * c.n_embd, output_norm_, 1, c.n_embd, c.rms_eps, stream_), "rmsnorm");
+            linear(logits_dev_, output_, h_, 1, false);
+        }
     }
 
     int n_ctx() const override { return n_ctx_; }
@@ -293,12 +301,14 @@ private:
         for (int i = 0; i < count; i++)
             cuda_check(ingot_linear_tc_run(lin_ws_, outs[i], ws[i]->data, ws[i]->n_in, ws[i]->n_out, accumulate ? 1 : 0, stream_), "linear (tensor core)");
     }
-    void gemv_norm_group(float* const* outs, const DevWeight* const* ws, int count, bool swiglu, const float* x, const float* norm_w) {
+    static bool streamable(const DevWeight& w) { return w.is_f16 && w.n_in % 256 == 0 && w.n_in <= 12288; }
+    void gemv_group(float* const* outs, const DevWeight* const* ws, int count, bool swiglu, const float* x, const float* norm_w,
+                    bool accumulate) {
         const void* wp[3] = {};
         int rows[3] = {};
         for (int i = 0; i < count; i++) { wp[i] = ws[i]->data; rows[i] = ws[i]->n_out; }
-        cuda_check(ingot_support_gemv_norm_group(outs, wp, rows, count, swiglu ? 1 : 0, x, norm_w, m_.cfg.rms_eps, ws[0]->n_in, stream_),
-                   "gemv (norm + projections)");
+        cuda_check(ingot_support_gemv_group(outs, wp, rows, count, swiglu ? 1 : 0, x, norm_w, m_.cfg.rms_eps, ws[0]->n_in,
+                                            accumulate ? 1 : 0, stream_), "gemv");
     }
     void linear(float* out, const DevWeight& w, const float* x, int n_tok, bool accumulate) {
         cuda_check(ingot_support_linear(out, w.data, w.is_f16, x, w.n_in, w.n_out, n_tok, accumulate ? 1 : 0, stream_), "linear");

@@ -1,12 +1,14 @@
-// Correctness-first support kernels for CudaBackend: the non-attention stages of the forward pass
+// Support kernels for CudaBackend: the non-attention stages of the forward pass
 // (src/cpu_backend.cpp:39-42, 71-85; Metal: rmsnorm / matvec_f16 / silu_mul,
 // shaders/kernels.metal:129-252, 706-710). Activations stay f32 everywhere, weights are read in their
 // stored type (f16 or f32) and widened, products accumulate in f32 — the arithmetic of ops::dot_row
 // (src/ops.cpp:127-141) up to summation order — so that greedy decoding follows the CPU reference.
-// These are not the tuned part of this library; the attention path is.
+// Single-token steps with f16 weights use the weight-streaming kernel (gemv_stream_kernel); batches use the
+// tensor-core kernel of linear_sm100.cu; the plain kernels here cover f32 weights and odd shapes.
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 namespace {
 
@@ -132,12 +134,17 @@ __global__ void __launch_bounds__(256) gemv_kernel(float* out, const W* w, const
     if (lane == 0) out[row] = accumulate ? out[row] + v : v;
 }
 
-// Single-token form with the RMS norm folded in, for up to three f16 matrices that read the same vector
-// (q/k/v; or gate/up with the SwiGLU product as the epilogue): out_m[r] = scale * dot(W_m[r][:], x .* norm_w),
-// scale = rsqrt(mean(x^2) + eps). Every warp sees the whole of x while it walks its row, so it gets the sum of
-// squares for free; the scale is applied to the finished dot product (ops::rmsnorm, src/ops.cpp:227-232, scales
-// the vector first: the same product up to rounding order). One launch replaces the norm and two or three
-// matrix-vector launches of a layer.
+// Single-token products with f16 weights: a weight-streaming kernel, HBM-bound by design.
+//   out_m[r] (+)= dot(W_m[r][:], x')            x' = x, or x .* norm_w with the result scaled by
+//   rsqrt(mean(x^2) + eps) (the RMS norm of ops::rmsnorm, src/ops.cpp:227-232, folded in; the same product up to
+//   rounding order), for up to three matrices that read the same vector (q/k/v), or for the gate/up pair with
+//   out[r] = silu(gate[r]) * up[r] as the epilogue (src/cpu_backend.cpp:79).
+// One launch is one resident wave of CTAs; a warp owns whole rows (r, r + W, ...), W chosen so that all warps get
+// the same number of rows. A lane keeps four 16-byte weight loads in flight and requests the next four before
+// it consumes the current ones, across row boundaries too, so a warp streams without gaps. x' is staged in
+// shared memory once per CTA. Under programmatic dependent launch the first weight loads are issued before
+// the wait for the preceding kernel (weights never depend on it), which hides the ramp of every launch
+// behind the tail of the previous one.
 struct GemvGroup {
     const __half* w[3];
     float* out[3];
@@ -145,61 +152,121 @@ struct GemvGroup {
     int n_mat;
 };
 
-template <bool kSwiGLU>
-__global__ void __launch_bounds__(256) gemv_norm_group_kernel(const GemvGroup g, const float* x, const float* norm_w, float eps, int n_in) {
+__device__ __forceinline__ uint4 ld_stream_u4(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ float dot8(const uint4& raw, const float* xs) {
+    const __half2* h = reinterpret_cast<const __half2*>(&raw);
+    const float4 xa = *reinterpret_cast<const float4*>(xs), xb = *reinterpret_cast<const float4*>(xs + 4);
+    const float2 w0 = __half22float2(h[0]), w1 = __half22float2(h[1]), w2 = __half22float2(h[2]), w3 = __half22float2(h[3]);
+    float acc = w0.x * xa.x;
+    acc = fmaf(w0.y, xa.y, acc); acc = fmaf(w1.x, xa.z, acc); acc = fmaf(w1.y, xa.w, acc);
+    acc = fmaf(w2.x, xb.x, acc); acc = fmaf(w2.y, xb.y, acc); acc = fmaf(w3.x, xb.z, acc); acc = fmaf(w3.y, xb.w, acc);
+    return acc;
+}
+
+template <bool kNorm, bool kSwiGLU>
+__global__ void __launch_bounds__(256) gemv_stream_kernel(const GemvGroup g, const float* x, const float* norm_w, float eps, int n_in,
+                                                          int total_rows, int accumulate, int use_pdl) {
+    extern __shared__ float xs[];  // x', n_in floats
+    __shared__ float red[9];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    int row = blockIdx.x * (blockDim.x >> 5) + warp;
-    const int total = kSwiGLU ? g.row_end[0] : g.row_end[g.n_mat - 1];
-    if (row >= total) return;
-    int mat = 0;
-    if (!kSwiGLU) {
-        while (row >= g.row_end[mat]) mat++;
-        if (mat > 0) row -= g.row_end[mat - 1];
-    }
-    const __half* wa = g.w[mat] + (size_t)row * n_in;
-    const __half* wb = kSwiGLU ? g.w[1] + (size_t)row * n_in : nullptr;
-    float acc_a = 0.f, acc_b = 0.f, ss = 0.f;
-    // four 16-byte weight loads in flight per lane (4 chunks of one matrix, or 2 of each of gate and up), all
-    // issued before the first use
-    constexpr int kChunks = kSwiGLU ? 2 : 4;
-    for (int i = lane * 8; i < n_in; i += 256 * kChunks) {
-        float a[kChunks][8], b[kChunks][8];
+    const int W = gridDim.x * (blockDim.x >> 5), gw = blockIdx.x * (blockDim.x >> 5) + warp;
+    if (use_pdl) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    constexpr int kPer = kSwiGLU ? 2 : 4;  // 256-element chunks per matrix and step: four loads per lane either way
+    const int n_chunks = n_in >> 8;
+    const int steps = (n_chunks + kPer - 1) / kPer;
+
+    auto row_base = [&](int r, const __half*& wa, const __half*& wb) {
+        if (kSwiGLU) {
+            wa = g.w[0] + (size_t)r * n_in;
+            wb = g.w[1] + (size_t)r * n_in;
+        } else {
+            const int m = (r >= g.row_end[0]) + (r >= g.row_end[1] && g.n_mat > 2);
+            const int local = m == 0 ? r : r - (m == 1 ? g.row_end[0] : g.row_end[1]);
+            wa = (m == 0 ? g.w[0] : m == 1 ? g.w[1] : g.w[2]) + (size_t)local * n_in;
+            wb = nullptr;
+        }
+    };
+    auto issue = [&](uint4 (&A)[kPer], uint4 (&B)[kPer], int r, int st) {
+        const __half *wa, *wb;
+        row_base(r, wa, wb);
 #pragma unroll
-        for (int h = 0; h < kChunks; h++) {
-            if (i + h * 256 < n_in) {
-                load8<__half>(wa + i + h * 256, a[h]);
-                if (kSwiGLU) load8<__half>(wb + i + h * 256, b[h]);
+        for (int h = 0; h < kPer; h++) {
+            const int c = st * kPer + h;
+            if (c < n_chunks) {
+                A[h] = ld_stream_u4(wa + (c << 8) + lane * 8);
+                if (kSwiGLU) B[h] = ld_stream_u4(wb + (c << 8) + lane * 8);
             }
         }
+    };
+
+    uint4 cur_a[kPer], cur_b[kPer], nxt_a[kPer], nxt_b[kPer];
+    int r = gw, st = 0;
+    bool have = r < total_rows;
+    if (have) issue(cur_a, cur_b, r, 0);  // before the wait below: weights do not depend on the preceding kernel
+
+    if (use_pdl) asm volatile("griddepcontrol.wait;" ::: "memory");
+    float ss = 0.f;
+    for (int i = threadIdx.x * 4; i < n_in; i += blockDim.x * 4) {
+        float4 v = *reinterpret_cast<const float4*>(x + i);
+        if (kNorm) {
+            ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+            const float4 n = *reinterpret_cast<const float4*>(norm_w + i);
+            v.x *= n.x; v.y *= n.y; v.z *= n.z; v.w *= n.w;
+        }
+        *reinterpret_cast<float4*>(xs + i) = v;
+    }
+    if (kNorm) {
+        ss = warp_sum(ss);
+        if (lane == 0) red[warp] = ss;
+    }
+    __syncthreads();
+    float scale = 1.0f;
+    if (kNorm) {
+        float t = 0.f;
+        for (int w = 0; w < (int)(blockDim.x >> 5); w++) t += red[w];
+        scale = 1.0f / sqrtf(t / float(n_in) + eps);
+    }
+
+    float acc_a = 0.f, acc_b = 0.f;
+    while (have) {
+        int r2 = r, st2 = st + 1;
+        if (st2 == steps) { st2 = 0; r2 = r + W; }
+        const bool have2 = r2 < total_rows;
+        if (have2) issue(nxt_a, nxt_b, r2, st2);
 #pragma unroll
-        for (int h = 0; h < kChunks; h++) {
-            const int o = i + h * 256;
-            if (o < n_in) {
-                const float4 xa = __ldg(reinterpret_cast<const float4*>(x + o)), xb = __ldg(reinterpret_cast<const float4*>(x + o + 4));
-                const float4 na = __ldg(reinterpret_cast<const float4*>(norm_w + o)), nb = __ldg(reinterpret_cast<const float4*>(norm_w + o + 4));
-                const float xv[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
-                const float nv[8] = {na.x, na.y, na.z, na.w, nb.x, nb.y, nb.z, nb.w};
-#pragma unroll
-                for (int e = 0; e < 8; e++) {
-                    ss = fmaf(xv[e], xv[e], ss);
-                    const float xn = xv[e] * nv[e];
-                    acc_a = fmaf(a[h][e], xn, acc_a);
-                    if (kSwiGLU) acc_b = fmaf(b[h][e], xn, acc_b);
+        for (int h = 0; h < kPer; h++) {
+            const int c = st * kPer + h;
+            if (c < n_chunks) {
+                const float* xp = xs + (c << 8) + lane * 8;
+                acc_a += dot8(cur_a[h], xp);
+                if (kSwiGLU) acc_b += dot8(cur_b[h], xp);
+            }
+        }
+        if (st == steps - 1) {
+            acc_a = warp_sum(acc_a);
+            if (kSwiGLU) acc_b = warp_sum(acc_b);
+            if (lane == 0) {
+                if (kSwiGLU) {
+                    const float gt = acc_a * scale, up = acc_b * scale;
+                    g.out[0][r] = gt / (1.0f + expf(-gt)) * up;
+                } else {
+                    const int m = (r >= g.row_end[0]) + (r >= g.row_end[1] && g.n_mat > 2);
+                    const int local = m == 0 ? r : r - (m == 1 ? g.row_end[0] : g.row_end[1]);
+                    float* o = (m == 0 ? g.out[0] : m == 1 ? g.out[1] : g.out[2]) + local;
+                    const float v = acc_a * scale;
+                    *o = accumulate ? *o + v : v;
                 }
             }
+            acc_a = 0.f;
+            acc_b = 0.f;
         }
-    }
-    ss = warp_sum(ss);
-    acc_a = warp_sum(acc_a);
-    if (kSwiGLU) acc_b = warp_sum(acc_b);
-    if (lane == 0) {
-        const float scale = 1.0f / sqrtf(ss / float(n_in) + eps);
-        if (kSwiGLU) {
-            const float gt = acc_a * scale, up = acc_b * scale;
-            g.out[0][row] = gt / (1.0f + expf(-gt)) * up;  // silu(gate) * up, src/cpu_backend.cpp:79
-        } else {
-            g.out[mat][row] = acc_a * scale;
-        }
+#pragma unroll
+        for (int h = 0; h < kPer; h++) { cur_a[h] = nxt_a[h]; if (kSwiGLU) cur_b[h] = nxt_b[h]; }
+        r = r2; st = st2; have = have2;
     }
 }
 
@@ -284,26 +351,53 @@ cudaError_t ingot_support_silu_mul(float* gate, const float* up, size_t n, cudaS
     return cudaGetLastError();
 }
 
-// One token: out_m = (W_m . rmsnorm(x; norm_w, eps)) for n_mat <= 3 f16 matrices [n_out[m]][n_in] that share x; with
-// swiglu != 0 there are exactly two matrices of equal height (gate, up) and outs[0] receives silu(gate) * up.
-cudaError_t ingot_support_gemv_norm_group(float* const* outs, const void* const* ws, const int* n_out, int n_mat, int swiglu,
-                                          const float* x, const float* norm_w, float eps, int n_in, cudaStream_t s) {
-    if (n_mat < 1 || n_mat > 3 || n_in % 8 != 0 || (swiglu && (n_mat != 2 || n_out[0] != n_out[1]))) return cudaErrorInvalidValue;
+// One token, f16 weights: out_m (+)= W_m . x' for n_mat <= 3 matrices [n_out[m]][n_in] that share x (see
+// gemv_stream_kernel). norm_w != nullptr folds the RMS norm in; swiglu != 0 takes exactly two matrices of equal
+// height (gate, up) and outs[0] receives silu(gate) * up. n_in must be a multiple of 256.
+cudaError_t ingot_support_gemv_group(float* const* outs, const void* const* ws, const int* n_out, int n_mat, int swiglu, const float* x,
+                                     const float* norm_w, float eps, int n_in, int accumulate, cudaStream_t s) {
+    if (n_mat < 1 || n_mat > 3 || n_in % 256 != 0 || n_in > 12288 || (swiglu && (n_mat != 2 || n_out[0] != n_out[1] || !norm_w)))
+        return cudaErrorInvalidValue;
     GemvGroup g = {};
     int total = 0;
-    for (int m = 0; m < n_mat; m++) {
-        g.w[m] = static_cast<const __half*>(ws[m]);
-        g.out[m] = outs[m];
-        total += n_out[m];
+    for (int m = 0; m < 3; m++) {
+        const int mm = m < n_mat ? m : n_mat - 1;
+        g.w[m] = static_cast<const __half*>(ws[mm]);
+        g.out[m] = outs[mm];
+        if (m < n_mat) total += n_out[m];
         g.row_end[m] = swiglu ? n_out[0] : total;
     }
     g.n_mat = n_mat;
-    const int warps = 8;
     const int rows = swiglu ? n_out[0] : total;
-    const unsigned grid = (rows + warps - 1) / warps;
-    if (swiglu) gemv_norm_group_kernel<true><<<grid, warps * 32, 0, s>>>(g, x, norm_w, eps, n_in);
-    else gemv_norm_group_kernel<false><<<grid, warps * 32, 0, s>>>(g, x, norm_w, eps, n_in);
-    return cudaGetLastError();
+    const size_t smem = (size_t)n_in * sizeof(float);
+    void (*kernel)(GemvGroup, const float*, const float*, float, int, int, int, int) =
+        swiglu ? gemv_stream_kernel<true, true> : norm_w ? gemv_stream_kernel<true, false> : gemv_stream_kernel<false, false>;
+    // one resident wave, every warp the same number of rows
+    static int num_sms = 0;
+    static bool use_pdl = true;
+    if (num_sms == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
+        use_pdl = getenv("INGOT_NO_PDL") == nullptr;
+    }
+    int occ = 0;
+    cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kernel, 256, smem);
+    if (e != cudaSuccess) return e;
+    const int capacity = num_sms * (occ > 0 ? occ : 1) * 8;
+    const int rows_per_warp = (rows + capacity - 1) / capacity;
+    const int warps = (rows + rows_per_warp - 1) / rows_per_warp;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((warps + 7) / 8);
+    cfg.blockDim = dim3(256);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = use_pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, g, x, norm_w, eps, n_in, rows, accumulate, use_pdl ? 1 : 0);
 }
 
 // w_is_f16: 1 = __half weights, 0 = float weights.

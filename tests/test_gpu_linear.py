@@ -69,37 +69,46 @@ def test_linear_tc_matches_float64(n_tok, n_in, n_out, accumulate):
         lib.ingot_linear_ws_destroy(ws)
 
 
-@pytest.mark.parametrize("swiglu", [0, 1])
-def test_gemv_norm_group_matches_float64(swiglu):
-    """Single-token launch that folds the RMS norm into two or three matrix-vector products (and the SwiGLU
-    product into gate/up): against rmsnorm (src/ops.cpp:227-232) followed by float64 products."""
+@pytest.mark.parametrize("mode", ["qkv_norm", "swiglu", "plain_accumulate", "many_rows"])
+def test_gemv_group_matches_float64(mode):
+    """The single-token weight-streaming launch: RMS norm folded into up to three matrix-vector products,
+    SwiGLU as the epilogue of gate/up, plain accumulate (wo / down), and a row count far above one wave (logits):
+    against rmsnorm (src/ops.cpp:227-232) and float64 products."""
     import torch
     lib = _lib()
-    lib.ingot_support_gemv_norm_group.argtypes = [C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.POINTER(C.c_int), C.c_int, C.c_int,
-                                                  C.c_void_p, C.c_void_p, C.c_float, C.c_int, C.c_void_p]
-    n_in = 3072
-    rows = [8192, 8192] if swiglu else [3072, 1024, 1016]
-    g = torch.Generator(device="cuda").manual_seed(7 + swiglu)
+    lib.ingot_support_gemv_group.argtypes = [C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.POINTER(C.c_int), C.c_int, C.c_int,
+                                             C.c_void_p, C.c_void_p, C.c_float, C.c_int, C.c_int, C.c_void_p]
+    swiglu = int(mode == "swiglu")
+    norm = mode != "plain_accumulate"
+    accumulate = int(mode == "plain_accumulate")
+    n_in = 8192 if mode == "plain_accumulate" else 3072
+    rows = {"qkv_norm": [3072, 1024, 1016], "swiglu": [8192, 8192], "plain_accumulate": [3072], "many_rows": [50001]}[mode]
+    g = torch.Generator(device="cuda").manual_seed(len(mode))
     x = torch.randn(n_in, device="cuda", generator=g) * 3
     nw = 1 + 0.1 * torch.randn(n_in, device="cuda", generator=g)
     ws = [(torch.randn(r, n_in, device="cuda", generator=g) * 0.02).half() for r in rows]
-    outs = [torch.zeros(r, device="cuda") for r in rows]
+    outs0 = [torch.randn(r, device="cuda", generator=g) for r in rows]
+    outs = [o.clone() for o in outs0]
     eps = 1e-5
     outs_p = (C.c_void_p * len(rows))(*[o.data_ptr() for o in outs])
     ws_p = (C.c_void_p * len(rows))(*[w.data_ptr() for w in ws])
     rows_p = (C.c_int * len(rows))(*rows)
     stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
-    assert lib.ingot_support_gemv_norm_group(outs_p, ws_p, rows_p, len(rows), swiglu, x.data_ptr(), nw.data_ptr(), eps, n_in, stream) == 0
+    for _ in range(2 if not accumulate else 1):  # a second launch right behind the first (dependent launch) gives the same result
+        assert lib.ingot_support_gemv_group(outs_p, ws_p, rows_p, len(rows), swiglu, x.data_ptr(), nw.data_ptr() if norm else None, eps,
+                                            n_in, accumulate, stream) == 0
     torch.cuda.synchronize()
     xd = x.double()
-    h = xd * torch.rsqrt((xd * xd).mean() + eps) * nw.double()
+    h = xd * torch.rsqrt((xd * xd).mean() + eps) * nw.double() if norm else xd
     want = [w.double() @ h for w in ws]
     if swiglu:
         gate, up = want
         ref = gate / (1 + torch.exp(-gate)) * up
         err = (outs[0].double() - ref).abs().max().item()
         assert err <= 1e-5 * max(1.0, ref.abs().max().item()), err
+        assert torch.equal(outs[1], outs0[1])  # the second output buffer is not touched
     else:
-        for o, r in zip(outs, want):
-            err = (o.double() - r).abs().max().item()
-            assert err <= 1e-5 * max(1.0, r.abs().max().item()), err
+        for o, o0, r in zip(outs, outs0, want):
+            ref = r + o0.double() if accumulate else r
+            err = (o.double() - ref).abs().max().item()
+            assert err <= 1e-5 * max(1.0, ref.abs().max().item()), err
