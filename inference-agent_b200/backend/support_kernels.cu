@@ -140,7 +140,7 @@ __global__ void __launch_bounds__(256) gemv_kernel(float* out, const W* w, const
 //   rounding order), for up to three matrices that read the same vector (q/k/v), or for the gate/up pair with
 //   out[r] = silu(gate[r]) * up[r] as the epilogue (src/cpu_backend.cpp:79).
 // One launch is one resident wave of CTAs; a warp owns whole rows (r, r + W, ...), W chosen so that all warps get
-// the same number of rows. A lane keeps four 16-byte weight loads in flight and requests the next four before
+// the same number of rows. A lane keeps four (or six) 16-byte weight loads in flight and requests the next set before
 // it consumes the current ones, across row boundaries too, so a warp streams without gaps. x' is staged in
 // shared memory once per CTA. Under programmatic dependent launch the first weight loads are issued before
 // the wait for the preceding kernel (weights never depend on it), which hides the ramp of every launch
@@ -167,7 +167,9 @@ __device__ __forceinline__ float dot8(const uint4& raw, const float* xs) {
     return acc;
 }
 
-template <bool kNorm, bool kSwiGLU>
+// kLoads: 16-byte weight loads per lane and step (split between gate and up under kSwiGLU). Current and next step
+// are in flight together, so with kLoads = 6 a whole row of 3072 weights (12 chunks) is requested at once.
+template <bool kNorm, bool kSwiGLU, int kLoads>
 __global__ void __launch_bounds__(256) gemv_stream_kernel(const GemvGroup g, const float* x, const float* norm_w, float eps, int n_in,
                                                           int total_rows, int accumulate, int use_pdl) {
     extern __shared__ float xs[];  // x', n_in floats
@@ -175,7 +177,7 @@ __global__ void __launch_bounds__(256) gemv_stream_kernel(const GemvGroup g, con
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int W = gridDim.x * (blockDim.x >> 5), gw = blockIdx.x * (blockDim.x >> 5) + warp;
     if (use_pdl) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    constexpr int kPer = kSwiGLU ? 2 : 4;  // 256-element chunks per matrix and step: four loads per lane either way
+    constexpr int kPer = kSwiGLU ? kLoads / 2 : kLoads;  // 256-element chunks per matrix and step
     const int n_chunks = n_in >> 8;
     const int steps = (n_chunks + kPer - 1) / kPer;
 
@@ -370,8 +372,10 @@ cudaError_t ingot_support_gemv_group(float* const* outs, const void* const* ws, 
     g.n_mat = n_mat;
     const int rows = swiglu ? n_out[0] : total;
     const size_t smem = (size_t)n_in * sizeof(float);
+    const bool short_rows = n_in <= 3072;  // short rows: the whole row in flight at once
     void (*kernel)(GemvGroup, const float*, const float*, float, int, int, int, int) =
-        swiglu ? gemv_stream_kernel<true, true> : norm_w ? gemv_stream_kernel<true, false> : gemv_stream_kernel<false, false>;
+        short_rows ? (swiglu ? gemv_stream_kernel<true, true, 6> : norm_w ? gemv_stream_kernel<true, false, 6> : gemv_stream_kernel<false, false, 6>)
+                   : (swiglu ? gemv_stream_kernel<true, true, 4> : norm_w ? gemv_stream_kernel<true, false, 4> : gemv_stream_kernel<false, false, 4>);
     // one resident wave, every warp the same number of rows
     static int num_sms = 0;
     static bool use_pdl = true;
