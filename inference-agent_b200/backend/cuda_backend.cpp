@@ -47,6 +47,9 @@ cudaError_t ingot_linear_ws_create(ingot_linear_ws** out, int max_tok, int max_i
 void ingot_linear_ws_destroy(ingot_linear_ws* ws);
 int ingot_linear_tc_supported(const ingot_linear_ws* ws, int w_is_f16, int n_in, int n_out, int n_tok);
 cudaError_t ingot_linear_tc_prepare(ingot_linear_ws* ws, const float* x, int n_in, int n_tok, cudaStream_t s);
+cudaError_t ingot_linear_tc_prepare_norm(ingot_linear_ws* ws, const float* x, const float* norm_w, float eps, int n_in, int n_tok,
+                                         cudaStream_t s);
+cudaError_t ingot_linear_tc_prepare_swiglu(ingot_linear_ws* ws, const float* gate, const float* up, int n_in, int n_tok, cudaStream_t s);
 cudaError_t ingot_linear_tc_run(ingot_linear_ws* ws, float* out, const void* w, int n_in, int n_out, int accumulate, cudaStream_t s);
 int ingot_linear_ws_status(ingot_linear_ws* ws);
 }
@@ -211,8 +214,13 @@ public:
             // single token, f16 weights: the weight-streaming kernel; the norm and the projections that share it are one launch
             const bool fused = n == 1 && fuse_decode_ && streamable(D.wq) && streamable(D.wk) && streamable(D.wv) && streamable(D.wo) &&
                                streamable(D.w_gate) && streamable(D.w_up) && streamable(D.w_down);
+            // batches on the tensor-core path: the norm (and below the SwiGLU product) writes the f16 hi/lo activations directly
+            const bool tc_layer = n > 1 && lin_ws_ != nullptr && layer_tc_ok(D, n);
             if (fused) {
                 gemv_group(qkv_out, qkv, 3, false, x_, D.attn_norm, false);
+            } else if (tc_layer) {
+                cuda_check(ingot_linear_tc_prepare_norm(lin_ws_, x_, D.attn_norm, c.rms_eps, c.n_embd, n, stream_), "rmsnorm (split)");
+                tc_run(qkv_out, qkv, 3, false);
             } else {
                 cuda_check(ingot_support_rmsnorm(h_, x_, D.attn_norm, n, c.n_embd, c.rms_eps, stream_), "rmsnorm");
                 linear_group(qkv_out, qkv, 3, h_, n, false);
@@ -233,6 +241,10 @@ public:
             float* gu_out[2] = {gate_, up_};
             if (fused) {
                 gemv_group(gu_out, gu, 2, true, x_, D.ffn_norm, false);  // gate_ <- silu(gate) * up
+            } else if (tc_layer) {
+                cuda_check(ingot_linear_tc_prepare_norm(lin_ws_, x_, D.ffn_norm, c.rms_eps, c.n_embd, n, stream_), "rmsnorm (split)");
+                tc_run(gu_out, gu, 2, false);
+                cuda_check(ingot_linear_tc_prepare_swiglu(lin_ws_, gate_, up_, c.n_ff, n, stream_), "silu_mul (split)");
             } else {
                 cuda_check(ingot_support_rmsnorm(h_, x_, D.ffn_norm, n, c.n_embd, c.rms_eps, stream_), "rmsnorm");
                 linear_group(gu_out, gu, 2, h_, n, false);
@@ -240,6 +252,7 @@ public:
             }
             const DevWeight* wd[1] = {&D.w_down};
             if (fused) gemv_group(&x_, wd, 1, false, gate_, nullptr, true);
+            else if (tc_layer) tc_run(&x_, wd, 1, true);
             else linear_group(&x_, wd, 1, gate_, n, true);
         }
         // Logits for the last token only.
@@ -287,13 +300,27 @@ private:
         cuda_check(cudaMemcpy(w.data, t.data, t.nbytes(), cudaMemcpyHostToDevice), "cudaMemcpy(weight)");
         return w;
     }
-    // Projections that read the same activations. Batches go to the tensor-core kernel (the activations are split
-    // into f16 hi/lo parts once per group); single tokens and unsupported shapes to the f32 kernels.
-    void linear_group(float* const* outs, const DevWeight* const* ws, int count, const float* x, int n_tok, bool accumulate) {
+    bool tc_group(const DevWeight* const* ws, int count, int n_tok) const {
         bool tc = lin_ws_ != nullptr;
         for (int i = 0; i < count && tc; i++)
             tc = ws[i]->n_in == ws[0]->n_in && ingot_linear_tc_supported(lin_ws_, ws[i]->is_f16, ws[i]->n_in, ws[i]->n_out, n_tok);
-        if (!tc) {
+        return tc;
+    }
+    bool layer_tc_ok(const DevLayer& D, int n_tok) const {
+        const DevWeight* all[7] = {&D.wq, &D.wk, &D.wv, &D.wo, &D.w_gate, &D.w_up, &D.w_down};
+        for (const DevWeight* w : all)
+            if (!ingot_linear_tc_supported(lin_ws_, w->is_f16, w->n_in, w->n_out, n_tok)) return false;
+        return D.wq.n_in == m_.cfg.n_embd && D.w_gate.n_in == m_.cfg.n_embd && D.w_down.n_in == m_.cfg.n_ff;
+    }
+    // Runs projections on the activations prepared last.
+    void tc_run(float* const* outs, const DevWeight* const* ws, int count, bool accumulate) {
+        for (int i = 0; i < count; i++)
+            cuda_check(ingot_linear_tc_run(lin_ws_, outs[i], ws[i]->data, ws[i]->n_in, ws[i]->n_out, accumulate ? 1 : 0, stream_), "linear (tensor core)");
+    }
+    // Projections that read the same activations. Batches go to the tensor-core kernel (the activations are split
+    // into f16 hi/lo parts once per group); single tokens and unsupported shapes to the f32 kernels.
+    void linear_group(float* const* outs, const DevWeight* const* ws, int count, const float* x, int n_tok, bool accumulate) {
+        if (!tc_group(ws, count, n_tok)) {
             for (int i = 0; i < count; i++) linear(outs[i], *ws[i], x, n_tok, accumulate);
             return;
         }

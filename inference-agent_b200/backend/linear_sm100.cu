@@ -12,7 +12,7 @@
 // only by summation order and the 2^-22 truncation of x.
 //
 // Kernel. One CTA = 128 tokens x 128 outputs over a slice of k (split-k fills the GPU when there are few
-// output tiles; slices go to a scratch and are summed in a fixed order afterwards, so results are
+// output tiles; slices go to a scratch and a second kernel sums them in slice order, so results are
 // reproducible). 6 warps: warp 0 streams [128 rows][64 k] boxes of hi, lo and W (128-byte swizzle, 48 KB per
 // stage, 4 stages) with TMA; warp 1 issues tcgen05.mma (kind::f16, M = N = 128, K = 16; all lanes walk the
 // loop, one elected lane issues); warps 2-5 read the 128x128 f32 accumulator out of tensor memory, one
@@ -145,10 +145,11 @@ linear_sm100_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_con
         const int row = m0 + lg * 32 + lane;
         bool ok = n_it > 0 && mbar_wait(smem_u32(&bars->done), 0, abort_flag, kWaitLimitNs);
         ok = __all_sync(0xffffffffu, ok) != 0;
+        const bool split_k = p.n_split > 1;
         if (ok) {
             tc_fence_after();
-            float* dst = (p.n_split > 1 ? p.partial + (size_t)split * p.n_tok * p.n_out : p.out) + (size_t)row * p.n_out + n0;
-            const bool add = p.n_split == 1 && p.accumulate;
+            float* dst = (split_k ? p.partial + (size_t)split * p.n_tok * p.n_out : p.out) + (size_t)row * p.n_out + n0;
+            const bool add = !split_k && p.accumulate;
 #pragma unroll
             for (int c = 0; c < kBN / 32; c++) {
                 float v[32];
@@ -210,6 +211,53 @@ __global__ void split_f16_kernel(__half* hi, __half* lo, const float* x, size_t 
     *reinterpret_cast<uint2*>(lo + i) = *reinterpret_cast<const uint2*>(l);
 }
 
+__device__ __forceinline__ void store_split4(__half* hi, __half* lo, size_t i, const float (&f)[4]) {
+    __half h[4], l[4];
+#pragma unroll
+    for (int e = 0; e < 4; e++) {
+        h[e] = __float2half_rn(f[e]);
+        l[e] = __float2half_rn(f[e] - __half2float(h[e]));
+    }
+    *reinterpret_cast<uint2*>(hi + i) = *reinterpret_cast<const uint2*>(h);
+    *reinterpret_cast<uint2*>(lo + i) = *reinterpret_cast<const uint2*>(l);
+}
+
+// hi/lo of rmsnorm(x) = x * rsqrt(mean(x^2) + eps) * w, one CTA per token row (ops::rmsnorm, src/ops.cpp:227-232,
+// with the same expression order as the standalone norm kernel, so the split sees the same f32 values).
+__global__ void rmsnorm_split_kernel(__half* hi, __half* lo, const float* x, const float* w, int n, float eps) {
+    __shared__ float red[32];
+    const float* xr = x + (size_t)blockIdx.x * n;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) ss += xr[i] * xr[i];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        float v = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0.f;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+        if (threadIdx.x == 0) red[0] = 1.0f / sqrtf(v / float(n) + eps);
+    }
+    __syncthreads();
+    const float scale = red[0];
+    for (int i = threadIdx.x * 4; i < n; i += blockDim.x * 4) {
+        const float4 v = *reinterpret_cast<const float4*>(xr + i), g = *reinterpret_cast<const float4*>(w + i);
+        const float f[4] = {v.x * scale * g.x, v.y * scale * g.y, v.z * scale * g.z, v.w * scale * g.w};
+        store_split4(hi, lo, (size_t)blockIdx.x * n + i, f);
+    }
+}
+
+// hi/lo of silu(gate) * up (src/cpu_backend.cpp:79)
+__global__ void swiglu_split_kernel(__half* hi, __half* lo, const float* gate, const float* up, size_t n) {
+    const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (i >= n) return;
+    const float4 g = *reinterpret_cast<const float4*>(gate + i), u = *reinterpret_cast<const float4*>(up + i);
+    const float f[4] = {g.x / (1.0f + expf(-g.x)) * u.x, g.y / (1.0f + expf(-g.y)) * u.y, g.z / (1.0f + expf(-g.z)) * u.z,
+                        g.w / (1.0f + expf(-g.w)) * u.w};
+    store_split4(hi, lo, i, f);
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -253,6 +301,16 @@ struct ingot_linear_ws {
     std::map<std::tuple<const void*, int, int>, CUtensorMap> w_maps;  // one per weight matrix
 };
 
+// (Re)builds the activation tensor maps when the prepared shape changes.
+static cudaError_t set_prepared(ingot_linear_ws* ws, int n_in, int n_tok) {
+    if (ws->prepared_tok != n_tok || ws->prepared_in != n_in) {
+        if (!make_map(&ws->map_hi, ws->hi, n_tok, n_in) || !make_map(&ws->map_lo, ws->lo, n_tok, n_in)) return cudaErrorUnknown;
+        ws->prepared_tok = n_tok;
+        ws->prepared_in = n_in;
+    }
+    return cudaGetLastError();
+}
+
 extern "C" {
 
 // max_tok x max_in: the largest activation matrix that will be prepared.
@@ -293,12 +351,23 @@ cudaError_t ingot_linear_tc_prepare(ingot_linear_ws* ws, const float* x, int n_i
     const size_t n = (size_t)n_tok * n_in;
     if (n > ws->act_elems || n_in % kBK != 0) return cudaErrorInvalidValue;
     split_f16_kernel<<<(unsigned)((n / 4 + 255) / 256), 256, 0, s>>>(ws->hi, ws->lo, x, n);
-    if (ws->prepared_tok != n_tok || ws->prepared_in != n_in) {
-        if (!make_map(&ws->map_hi, ws->hi, n_tok, n_in) || !make_map(&ws->map_lo, ws->lo, n_tok, n_in)) return cudaErrorUnknown;
-        ws->prepared_tok = n_tok;
-        ws->prepared_in = n_in;
-    }
-    return cudaGetLastError();
+    return set_prepared(ws, n_in, n_tok);
+}
+
+// The same with the producer of the activations folded in: rmsnorm(x; norm_w, eps) ...
+cudaError_t ingot_linear_tc_prepare_norm(ingot_linear_ws* ws, const float* x, const float* norm_w, float eps, int n_in, int n_tok,
+                                         cudaStream_t s) {
+    if ((size_t)n_tok * n_in > ws->act_elems || n_in % kBK != 0) return cudaErrorInvalidValue;
+    rmsnorm_split_kernel<<<n_tok, 256, 0, s>>>(ws->hi, ws->lo, x, norm_w, n_in, eps);
+    return set_prepared(ws, n_in, n_tok);
+}
+
+// ... and silu(gate) .* up, both [n_tok][n_in].
+cudaError_t ingot_linear_tc_prepare_swiglu(ingot_linear_ws* ws, const float* gate, const float* up, int n_in, int n_tok, cudaStream_t s) {
+    const size_t n = (size_t)n_tok * n_in;
+    if (n > ws->act_elems || n_in % kBK != 0) return cudaErrorInvalidValue;
+    swiglu_split_kernel<<<(unsigned)((n / 4 + 255) / 256), 256, 0, s>>>(ws->hi, ws->lo, gate, up, n);
+    return set_prepared(ws, n_in, n_tok);
 }
 
 // out [n_tok][n_out] (+)= prepared activations x W^T, W f16 [n_out][n_in] on the device.
