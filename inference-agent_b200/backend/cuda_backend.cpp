@@ -49,7 +49,10 @@ int ingot_linear_tc_supported(const ingot_linear_ws* ws, int w_is_f16, int n_in,
 cudaError_t ingot_linear_tc_prepare(ingot_linear_ws* ws, const float* x, int n_in, int n_tok, cudaStream_t s);
 cudaError_t ingot_linear_tc_prepare_norm(ingot_linear_ws* ws, const float* x, const float* norm_w, float eps, int n_in, int n_tok,
                                          cudaStream_t s);
-cudaError_t ingot_linear_tc_prepare_swiglu(ingot_linear_ws* ws, const float* gate, const float* up, int n_in, int n_tok, cudaStream_t s);
+cudaError_t ingot_linear_tc_run_partial(ingot_linear_ws* ws, const void* w, int n_in, int n_out, int slot, cudaStream_t s);
+cudaError_t ingot_linear_tc_finish_group(ingot_linear_ws* ws, float* const* outs, int count, cudaStream_t s);
+cudaError_t ingot_linear_tc_finish_residual_norm(ingot_linear_ws* ws, float* x, const float* norm_w, float eps, int slot, cudaStream_t s);
+cudaError_t ingot_linear_tc_finish_swiglu(ingot_linear_ws* ws, int slot_gate, int slot_up, cudaStream_t s);
 cudaError_t ingot_linear_tc_run(ingot_linear_ws* ws, float* out, const void* w, int n_in, int n_out, int accumulate, cudaStream_t s);
 int ingot_linear_ws_status(ingot_linear_ws* ws);
 }
@@ -207,6 +210,7 @@ public:
     // on stream_. device_pos: single-token form whose position / key count are read from pos_dev_.
     void encode_layers(int n, int pos, bool device_pos) {
         const Config& c = m_.cfg;
+        bool norm_prepared = false;  // tensor-core path: the previous layer's last kernel already normalised and split x
         for (int l = 0; l < c.n_layer; l++) {
             const DevLayer& D = layers_[l];
             const DevWeight* qkv[3] = {&D.wq, &D.wk, &D.wv};
@@ -219,8 +223,11 @@ public:
             if (fused) {
                 gemv_group(qkv_out, qkv, 3, false, x_, D.attn_norm, false);
             } else if (tc_layer) {
-                cuda_check(ingot_linear_tc_prepare_norm(lin_ws_, x_, D.attn_norm, c.rms_eps, c.n_embd, n, stream_), "rmsnorm (split)");
-                tc_run(qkv_out, qkv, 3, false);
+                // Every split-k product stays in scratch as k slices; the kernel that consumes it sums them.
+                if (!norm_prepared)
+                    cuda_check(ingot_linear_tc_prepare_norm(lin_ws_, x_, D.attn_norm, c.rms_eps, c.n_embd, n, stream_), "rmsnorm (split)");
+                for (int i = 0; i < 3; i++) tc_partial(*qkv[i], i);
+                cuda_check(ingot_linear_tc_finish_group(lin_ws_, qkv_out, 3, stream_), "q/k/v (slice sum)");
             } else {
                 cuda_check(ingot_support_rmsnorm(h_, x_, D.attn_norm, n, c.n_embd, c.rms_eps, stream_), "rmsnorm");
                 linear_group(qkv_out, qkv, 3, h_, n, false);
@@ -235,16 +242,24 @@ public:
                 ingot_check(ingot_attn_prefill(kv_, l, q_rot_, INGOT_F16, attn_, INGOT_F32, c.n_head, pos, n, nullptr, 0,
                                                stream_));
             const DevWeight* wo[1] = {&D.wo};
-            if (fused) gemv_group(&x_, wo, 1, false, attn_, nullptr, true);
-            else linear_group(&x_, wo, 1, attn_, n, true);
+            if (fused) {
+                gemv_group(&x_, wo, 1, false, attn_, nullptr, true);
+            } else if (tc_layer) {
+                cuda_check(ingot_linear_tc_prepare(lin_ws_, attn_, D.wo.n_in, n, stream_), "linear (split)");
+                tc_partial(D.wo, 0);
+                // x += wo product; hi/lo of rmsnorm(x; ffn_norm) for gate/up
+                cuda_check(ingot_linear_tc_finish_residual_norm(lin_ws_, x_, D.ffn_norm, c.rms_eps, 0, stream_), "residual + rmsnorm (split)");
+            } else {
+                linear_group(&x_, wo, 1, attn_, n, true);
+            }
             const DevWeight* gu[2] = {&D.w_gate, &D.w_up};
             float* gu_out[2] = {gate_, up_};
             if (fused) {
                 gemv_group(gu_out, gu, 2, true, x_, D.ffn_norm, false);  // gate_ <- silu(gate) * up
             } else if (tc_layer) {
-                cuda_check(ingot_linear_tc_prepare_norm(lin_ws_, x_, D.ffn_norm, c.rms_eps, c.n_embd, n, stream_), "rmsnorm (split)");
-                tc_run(gu_out, gu, 2, false);
-                cuda_check(ingot_linear_tc_prepare_swiglu(lin_ws_, gate_, up_, c.n_ff, n, stream_), "silu_mul (split)");
+                tc_partial(D.w_gate, 0);
+                tc_partial(D.w_up, 1);
+                cuda_check(ingot_linear_tc_finish_swiglu(lin_ws_, 0, 1, stream_), "silu_mul (split)");
             } else {
                 cuda_check(ingot_support_rmsnorm(h_, x_, D.ffn_norm, n, c.n_embd, c.rms_eps, stream_), "rmsnorm");
                 linear_group(gu_out, gu, 2, h_, n, false);
@@ -252,8 +267,15 @@ public:
             }
             const DevWeight* wd[1] = {&D.w_down};
             if (fused) gemv_group(&x_, wd, 1, false, gate_, nullptr, true);
-            else if (tc_layer) tc_run(&x_, wd, 1, true);
-            else linear_group(&x_, wd, 1, gate_, n, true);
+            else if (tc_layer) {
+                tc_partial(D.w_down, 0);
+                // x += down product; if the next layer also takes this path, its attention norm rides along
+                const bool next_tc = l + 1 < c.n_layer && layer_tc_ok(layers_[l + 1], n);
+                cuda_check(ingot_linear_tc_finish_residual_norm(lin_ws_, x_, next_tc ? layers_[l + 1].attn_norm : nullptr, c.rms_eps, 0, stream_),
+                           "residual (+ rmsnorm, split)");
+                norm_prepared = next_tc;
+            } else linear_group(&x_, wd, 1, gate_, n, true);
+            if (!tc_layer) norm_prepared = false;
         }
         // Logits for the last token only.
         if (fuse_decode_ && streamable(output_)) {
@@ -312,10 +334,8 @@ private:
             if (!ingot_linear_tc_supported(lin_ws_, w->is_f16, w->n_in, w->n_out, n_tok)) return false;
         return D.wq.n_in == m_.cfg.n_embd && D.w_gate.n_in == m_.cfg.n_embd && D.w_down.n_in == m_.cfg.n_ff;
     }
-    // Runs projections on the activations prepared last.
-    void tc_run(float* const* outs, const DevWeight* const* ws, int count, bool accumulate) {
-        for (int i = 0; i < count; i++)
-            cuda_check(ingot_linear_tc_run(lin_ws_, outs[i], ws[i]->data, ws[i]->n_in, ws[i]->n_out, accumulate ? 1 : 0, stream_), "linear (tensor core)");
+    void tc_partial(const DevWeight& w, int slot) {
+        cuda_check(ingot_linear_tc_run_partial(lin_ws_, w.data, w.n_in, w.n_out, slot, stream_), "linear (tensor core)");
     }
     // Projections that read the same activations. Batches go to the tensor-core kernel (the activations are split
     // into f16 hi/lo parts once per group); single tokens and unsupported shapes to the f32 kernels.

@@ -31,14 +31,19 @@ namespace {
 
 using namespace ingot_sm100;
 
-constexpr int kBM = 128, kBN = 128, kBK = 64;
-constexpr int kStages = 4;
+#ifndef INGOT_GEMM_BN
+#define INGOT_GEMM_BN 128
+#endif
+constexpr int kBM = 128, kBN = INGOT_GEMM_BN, kBK = 64;  // outputs per CTA: 128, or 256 (a third less L2 traffic per output)
+static_assert(kBN == 128 || kBN == 256, "128 or 256 outputs per CTA");
+constexpr int kStages = kBN == 256 ? 3 : 4;
 constexpr int kBoxBytes = 128 * kBK * 2;        // 16 KB: 128 rows x 64 f16
-constexpr int kStageBytes = 3 * kBoxBytes;      // hi, lo, W
+constexpr int kWBytes = kBN * kBK * 2;          // the W box: kBN rows
+constexpr int kStageBytes = 2 * kBoxBytes + kWBytes;  // hi, lo, W
 constexpr int kThreads = 192;
 constexpr int kOffBar = kStages * kStageBytes;
 constexpr int kSmemBytes = kOffBar + 128 + 1024;  // barriers + alignment slack
-constexpr uint32_t kTmemCols = 128;
+constexpr uint32_t kTmemCols = kBN;
 constexpr uint32_t kIdesc = (1u << 4) | ((uint32_t)(kBN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);  // f16 x f16 -> f32, both K-major
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;
 
@@ -57,6 +62,7 @@ struct GemmParams {
     float* partial;    // [n_split][n_tok][n_out] when n_split > 1
     int* status;
     int n_tok, n_out, k_steps, n_split, accumulate;
+    int to_partial;  // write the slice(s) to `partial` even when there is only one (a consumer kernel sums them)
 };
 
 __global__ void __launch_bounds__(kThreads, 1)
@@ -145,7 +151,7 @@ linear_sm100_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_con
         const int row = m0 + lg * 32 + lane;
         bool ok = n_it > 0 && mbar_wait(smem_u32(&bars->done), 0, abort_flag, kWaitLimitNs);
         ok = __all_sync(0xffffffffu, ok) != 0;
-        const bool split_k = p.n_split > 1;
+        const bool split_k = p.n_split > 1 || p.to_partial;
         if (ok) {
             tc_fence_after();
             float* dst = (split_k ? p.partial + (size_t)split * p.n_tok * p.n_out : p.out) + (size_t)row * p.n_out + n0;
@@ -248,11 +254,75 @@ __global__ void rmsnorm_split_kernel(__half* hi, __half* lo, const float* x, con
     }
 }
 
-// hi/lo of silu(gate) * up (src/cpu_backend.cpp:79)
-__global__ void swiglu_split_kernel(__half* hi, __half* lo, const float* gate, const float* up, size_t n) {
+// Consumers of k-slice partials [n_split][n_tok][n_out]: the sum over slices (always in slice order) is folded into
+// the kernel that needs the result, so a split-k GEMM costs no reduction launch of its own.
+struct Slices {
+    const float* base;
+    int n_split;
+};
+__device__ __forceinline__ float4 sum_slices(const Slices& p, size_t idx, size_t slice_elems, float4 acc) {
+    for (int sl = 0; sl < p.n_split; sl++) {
+        const float4 v = *reinterpret_cast<const float4*>(p.base + sl * slice_elems + idx);
+        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    return acc;
+}
+
+// Up to three plain outputs (q, k, v): out_m = sum of its slices. grid.y selects the output.
+struct FinishGroup {
+    Slices in[3];
+    float* out[3];
+    int n_out[3];
+};
+__global__ void finish_group_kernel(const FinishGroup g, int n_tok) {
+    const int m = blockIdx.y;
+    const Slices in = m == 0 ? g.in[0] : m == 1 ? g.in[1] : g.in[2];
+    float* out = m == 0 ? g.out[0] : m == 1 ? g.out[1] : g.out[2];
+    const size_t n = (size_t)n_tok * (m == 0 ? g.n_out[0] : m == 1 ? g.n_out[1] : g.n_out[2]);
     const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
     if (i >= n) return;
-    const float4 g = *reinterpret_cast<const float4*>(gate + i), u = *reinterpret_cast<const float4*>(up + i);
+    *reinterpret_cast<float4*>(out + i) = sum_slices(in, i, n, make_float4(0.f, 0.f, 0.f, 0.f));
+}
+
+// x[t][:] += sum of slices (the residual add of wo / down), then, if norm_w is given, hi/lo of rmsnorm(x[t]) for the
+// next projections. One CTA per token.
+__global__ void finish_residual_norm_kernel(float* x, const Slices in, __half* hi, __half* lo, const float* norm_w, int n, int n_tok,
+                                            float eps) {
+    __shared__ float red[32];
+    const size_t row = (size_t)blockIdx.x * n;
+    const size_t slice = (size_t)n_tok * n;
+    float ss = 0.f;
+    for (int i = threadIdx.x * 4; i < n; i += blockDim.x * 4) {
+        const float4 v = sum_slices(in, row + i, slice, *reinterpret_cast<const float4*>(x + row + i));
+        *reinterpret_cast<float4*>(x + row + i) = v;
+        ss += v.x * v.x; ss += v.y * v.y; ss += v.z * v.z; ss += v.w * v.w;
+    }
+    if (norm_w == nullptr) return;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        float v = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0.f;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+        if (threadIdx.x == 0) red[0] = 1.0f / sqrtf(v / float(n) + eps);
+    }
+    __syncthreads();
+    const float scale = red[0];
+    for (int i = threadIdx.x * 4; i < n; i += blockDim.x * 4) {
+        const float4 v = *reinterpret_cast<const float4*>(x + row + i), g = *reinterpret_cast<const float4*>(norm_w + i);
+        const float f[4] = {v.x * scale * g.x, v.y * scale * g.y, v.z * scale * g.z, v.w * scale * g.w};
+        store_split4(hi, lo, row + i, f);
+    }
+}
+
+// hi/lo of silu(sum of gate slices) * (sum of up slices)
+__global__ void finish_swiglu_kernel(__half* hi, __half* lo, const Slices gate, const Slices up, size_t n) {
+    const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (i >= n) return;
+    const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+    const float4 g = sum_slices(gate, i, n, z), u = sum_slices(up, i, n, z);
     const float f[4] = {g.x / (1.0f + expf(-g.x)) * u.x, g.y / (1.0f + expf(-g.y)) * u.y, g.z / (1.0f + expf(-g.z)) * u.z,
                         g.w / (1.0f + expf(-g.w)) * u.w};
     store_split4(hi, lo, i, f);
@@ -275,13 +345,13 @@ EncodeTiledFn encode_fn() {
     return fn;
 }
 
-// f16 matrix [rows][cols] row-major, boxes of 128 rows x 64 columns, 128-byte swizzle, zero fill outside
-bool make_map(CUtensorMap* map, const void* base, int rows, int cols) {
+// f16 matrix [rows][cols] row-major, boxes of box_rows rows x 64 columns, 128-byte swizzle, zero fill outside
+bool make_map(CUtensorMap* map, const void* base, int rows, int cols, int box_rows = 128) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return false;
     const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
     const cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
-    const cuuint32_t box[2] = {(cuuint32_t)kBK, 128};
+    const cuuint32_t box[2] = {(cuuint32_t)kBK, (cuuint32_t)box_rows};
     const cuuint32_t elem[2] = {1, 1};
     return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
@@ -294,7 +364,9 @@ struct ingot_linear_ws {
     __half* lo = nullptr;
     float* partial = nullptr;
     int* status = nullptr;
-    size_t act_elems = 0, partial_floats = 0;
+    size_t act_elems = 0, partial_floats = 0;  // partial_floats: per slot; kSlots slots
+    int slot_split[3] = {0, 0, 0};             // slices the last GEMM into each slot produced
+    int slot_out[3] = {0, 0, 0};               // and its output width
     int num_sms = 0;
     int prepared_tok = 0, prepared_in = 0;
     CUtensorMap map_hi, map_lo;
@@ -313,18 +385,19 @@ static cudaError_t set_prepared(ingot_linear_ws* ws, int n_in, int n_tok) {
 
 extern "C" {
 
-// max_tok x max_in: the largest activation matrix that will be prepared.
+// max_tok x max_in: the largest activation matrix that will be prepared; also the largest output (tokens x width).
 cudaError_t ingot_linear_ws_create(ingot_linear_ws** out, int max_tok, int max_in) {
     *out = nullptr;
     ingot_linear_ws* ws = new ingot_linear_ws();
     ws->act_elems = (size_t)max_tok * max_in;
-    ws->partial_floats = (size_t)8 << 20;  // 32 MB of k-slice partials
+    // k-slice partials: three slots, each at least one full-width slice of the largest batch (24 MB or more)
+    ws->partial_floats = std::max((size_t)6 << 20, ws->act_elems);
     int dev = 0;
     cudaError_t e;
     if ((e = cudaGetDevice(&dev)) != cudaSuccess ||
         (e = cudaDeviceGetAttribute(&ws->num_sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess ||
         (e = cudaMalloc(&ws->hi, ws->act_elems * 2)) != cudaSuccess || (e = cudaMalloc(&ws->lo, ws->act_elems * 2)) != cudaSuccess ||
-        (e = cudaMalloc(&ws->partial, ws->partial_floats * 4)) != cudaSuccess || (e = cudaMalloc(&ws->status, sizeof(int))) != cudaSuccess ||
+        (e = cudaMalloc(&ws->partial, 3 * ws->partial_floats * 4)) != cudaSuccess || (e = cudaMalloc(&ws->status, sizeof(int))) != cudaSuccess ||
         (e = cudaMemset(ws->status, 0, sizeof(int))) != cudaSuccess ||
         (e = cudaFuncSetAttribute(linear_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes)) != cudaSuccess) {
         cudaFree(ws->hi); cudaFree(ws->lo); cudaFree(ws->partial); cudaFree(ws->status);
@@ -354,7 +427,7 @@ cudaError_t ingot_linear_tc_prepare(ingot_linear_ws* ws, const float* x, int n_i
     return set_prepared(ws, n_in, n_tok);
 }
 
-// The same with the producer of the activations folded in: rmsnorm(x; norm_w, eps) ...
+// The same with the producer of the activations folded in: rmsnorm(x; norm_w, eps).
 cudaError_t ingot_linear_tc_prepare_norm(ingot_linear_ws* ws, const float* x, const float* norm_w, float eps, int n_in, int n_tok,
                                          cudaStream_t s) {
     if ((size_t)n_tok * n_in > ws->act_elems || n_in % kBK != 0) return cudaErrorInvalidValue;
@@ -362,39 +435,84 @@ cudaError_t ingot_linear_tc_prepare_norm(ingot_linear_ws* ws, const float* x, co
     return set_prepared(ws, n_in, n_tok);
 }
 
-// ... and silu(gate) .* up, both [n_tok][n_in].
-cudaError_t ingot_linear_tc_prepare_swiglu(ingot_linear_ws* ws, const float* gate, const float* up, int n_in, int n_tok, cudaStream_t s) {
-    const size_t n = (size_t)n_tok * n_in;
-    if (n > ws->act_elems || n_in % kBK != 0) return cudaErrorInvalidValue;
-    swiglu_split_kernel<<<(unsigned)((n / 4 + 255) / 256), 256, 0, s>>>(ws->hi, ws->lo, gate, up, n);
-    return set_prepared(ws, n_in, n_tok);
-}
-
-// out [n_tok][n_out] (+)= prepared activations x W^T, W f16 [n_out][n_in] on the device.
-cudaError_t ingot_linear_tc_run(ingot_linear_ws* ws, float* out, const void* w, int n_in, int n_out, int accumulate, cudaStream_t s) {
+static cudaError_t launch_gemm(ingot_linear_ws* ws, float* out, const void* w, int n_in, int n_out, int accumulate, int slot,
+                               bool to_partial, cudaStream_t s) {
     const int n_tok = ws->prepared_tok;
-    if (n_in != ws->prepared_in || n_tok < 1) return cudaErrorInvalidValue;
+    if (n_in != ws->prepared_in || n_tok < 1 || slot < 0 || slot > 2) return cudaErrorInvalidValue;
     const auto key = std::make_tuple(w, n_out, n_in);
     auto it = ws->w_maps.find(key);
     if (it == ws->w_maps.end()) {
         CUtensorMap m;
-        if (!make_map(&m, w, n_out, n_in)) return cudaErrorUnknown;
+        if (!make_map(&m, w, n_out, n_in, kBN)) return cudaErrorUnknown;
         it = ws->w_maps.emplace(key, m).first;
     }
     const int tiles = ((n_out + kBN - 1) / kBN) * ((n_tok + kBM - 1) / kBM);
     const int k_steps = n_in / kBK;
-    // enough k slices to give every SM a CTA, at least 4 k-steps each, and no more than the scratch holds
-    int n_split = std::max(1, std::min({ws->num_sms / tiles, k_steps / 4, (int)(ws->partial_floats / ((size_t)n_tok * n_out))}));
+    // enough k slices to give every SM a CTA, at least 4 k-steps each, and no more than the slot holds
+    const int fit = (int)(ws->partial_floats / ((size_t)n_tok * n_out));
+    if (to_partial && fit < 1) return cudaErrorInvalidValue;
+    const int n_split = std::max(1, std::min({ws->num_sms / tiles, k_steps / 4, fit}));
     GemmParams p;
-    p.out = out; p.partial = ws->partial; p.status = ws->status;
+    p.out = out; p.partial = ws->partial + (size_t)slot * ws->partial_floats; p.status = ws->status;
     p.n_tok = n_tok; p.n_out = n_out; p.k_steps = k_steps; p.n_split = n_split; p.accumulate = accumulate;
+    p.to_partial = to_partial ? 1 : 0;
     dim3 grid((n_out + kBN - 1) / kBN, (n_tok + kBM - 1) / kBM, n_split);
     linear_sm100_kernel<<<grid, kThreads, kSmemBytes, s>>>(ws->map_hi, ws->map_lo, it->second, p);
-    if (n_split > 1) {
+    ws->slot_split[slot] = n_split;
+    ws->slot_out[slot] = n_out;
+    if (!to_partial && n_split > 1) {
         const size_t n = (size_t)n_tok * n_out;
-        splitk_reduce_kernel<<<(unsigned)((n / 4 + 255) / 256), 256, 0, s>>>(out, ws->partial, n_split, n, accumulate);
+        splitk_reduce_kernel<<<(unsigned)((n / 4 + 255) / 256), 256, 0, s>>>(out, p.partial, n_split, n, accumulate);
     }
     return cudaGetLastError();
+}
+
+// out [n_tok][n_out] (+)= prepared activations x W^T, W f16 [n_out][n_in] on the device.
+cudaError_t ingot_linear_tc_run(ingot_linear_ws* ws, float* out, const void* w, int n_in, int n_out, int accumulate, cudaStream_t s) {
+    return launch_gemm(ws, out, w, n_in, n_out, accumulate, 0, false, s);
+}
+
+// The same product left as k slices in scratch slot 0..2 for one of the ingot_linear_tc_finish_* calls below.
+cudaError_t ingot_linear_tc_run_partial(ingot_linear_ws* ws, const void* w, int n_in, int n_out, int slot, cudaStream_t s) {
+    return launch_gemm(ws, nullptr, w, n_in, n_out, 0, slot, true, s);
+}
+
+static Slices slices_of(const ingot_linear_ws* ws, int slot) {
+    return Slices{ws->partial + (size_t)slot * ws->partial_floats, ws->slot_split[slot]};
+}
+
+// outs[m] = product left in slot m, for count <= 3 outputs (q, k, v) in one launch.
+cudaError_t ingot_linear_tc_finish_group(ingot_linear_ws* ws, float* const* outs, int count, cudaStream_t s) {
+    if (count < 1 || count > 3) return cudaErrorInvalidValue;
+    FinishGroup g = {};
+    int widest = 0;
+    for (int m = 0; m < count; m++) {
+        g.in[m] = slices_of(ws, m);
+        g.out[m] = outs[m];
+        g.n_out[m] = ws->slot_out[m];
+        widest = std::max(widest, ws->slot_out[m]);
+    }
+    const size_t n = (size_t)ws->prepared_tok * widest;
+    finish_group_kernel<<<dim3((unsigned)((n / 4 + 255) / 256), count), 256, 0, s>>>(g, ws->prepared_tok);
+    return cudaGetLastError();
+}
+
+// x += product left in `slot` (the residual add), then, with norm_w, the hi/lo activations of rmsnorm(x; norm_w, eps)
+// become the prepared input of the next projections (n_in = the product's width).
+cudaError_t ingot_linear_tc_finish_residual_norm(ingot_linear_ws* ws, float* x, const float* norm_w, float eps, int slot, cudaStream_t s) {
+    const int n = ws->slot_out[slot], n_tok = ws->prepared_tok;
+    if (n % 4 != 0 || (norm_w && ((size_t)n_tok * n > ws->act_elems || n % kBK != 0))) return cudaErrorInvalidValue;
+    finish_residual_norm_kernel<<<n_tok, 256, 0, s>>>(x, slices_of(ws, slot), ws->hi, ws->lo, norm_w, n, n_tok, eps);
+    return norm_w ? set_prepared(ws, n, n_tok) : cudaGetLastError();
+}
+
+// hi/lo of silu(slot_gate) .* slot_up become the prepared input of the next projection.
+cudaError_t ingot_linear_tc_finish_swiglu(ingot_linear_ws* ws, int slot_gate, int slot_up, cudaStream_t s) {
+    const int n_in = ws->slot_out[slot_gate], n_tok = ws->prepared_tok;
+    const size_t n = (size_t)n_tok * n_in;
+    if (ws->slot_out[slot_up] != n_in || n > ws->act_elems || n_in % kBK != 0) return cudaErrorInvalidValue;
+    finish_swiglu_kernel<<<(unsigned)((n / 4 + 255) / 256), 256, 0, s>>>(ws->hi, ws->lo, slices_of(ws, slot_gate), slices_of(ws, slot_up), n);
+    return set_prepared(ws, n_in, n_tok);
 }
 
 // The status word: non-zero after a bounded wait expired in some launch since the last call. Synchronises the device.

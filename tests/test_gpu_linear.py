@@ -112,3 +112,67 @@ def test_gemv_group_matches_float64(mode):
             ref = r + o0.double() if accumulate else r
             err = (o.double() - ref).abs().max().item()
             assert err <= 1e-5 * max(1.0, ref.abs().max().item()), err
+
+
+def test_slice_consumers_match_float64():
+    """Split-k products left as k slices and summed by their consumers: the grouped q/k/v sum, the residual add
+    with the next RMS norm folded in, and the SwiGLU product, each checked through the projection that follows."""
+    import torch
+    lib = _lib()
+    vp, ci, cf = C.c_void_p, C.c_int, C.c_float
+    lib.ingot_linear_tc_run_partial.argtypes = [vp, vp, ci, ci, ci, vp]
+    lib.ingot_linear_tc_finish_group.argtypes = [vp, C.POINTER(vp), ci, vp]
+    lib.ingot_linear_tc_finish_residual_norm.argtypes = [vp, vp, vp, cf, ci, vp]
+    lib.ingot_linear_tc_finish_swiglu.argtypes = [vp, ci, ci, vp]
+    lib.ingot_linear_tc_prepare_norm.argtypes = [vp, vp, vp, cf, ci, ci, vp]
+    ws = vp()
+    assert lib.ingot_linear_ws_create(C.byref(ws), 256, 2048) == 0
+    try:
+        n_tok, d, ff, eps = 130, 512, 2048, 1e-5
+        g = torch.Generator(device="cuda").manual_seed(11)
+        rnd = lambda *shape: torch.randn(*shape, device="cuda", generator=g)
+        x = rnd(n_tok, d)
+        nw1, nw2 = 1 + 0.1 * rnd(d), 1 + 0.1 * rnd(d)
+        wq, wk, wv = [(rnd(r, d) * 0.05).half() for r in (512, 128, 256)]
+        wo = (rnd(d, 512) * 0.05).half()
+        wg, wu = [(rnd(ff, d) * 0.05).half() for _ in range(2)]
+        wd = (rnd(d, ff) * 0.05).half()
+        st = vp(torch.cuda.current_stream().cuda_stream)
+        rms = lambda t, w: t * torch.rsqrt((t * t).mean(dim=1, keepdim=True) + eps) * w.double()
+        close = lambda got, want: (got.double() - want).abs().max().item() <= 2e-5 * max(1.0, want.abs().max().item())
+
+        # norm -> q/k/v as slices -> one summing launch
+        assert lib.ingot_linear_tc_prepare_norm(ws, x.data_ptr(), nw1.data_ptr(), eps, d, n_tok, st) == 0
+        for slot, w in enumerate((wq, wk, wv)):
+            assert lib.ingot_linear_tc_run_partial(ws, w.data_ptr(), d, w.shape[0], slot, st) == 0
+        outs = [torch.zeros(n_tok, w.shape[0], device="cuda") for w in (wq, wk, wv)]
+        assert lib.ingot_linear_tc_finish_group(ws, (vp * 3)(*[o.data_ptr() for o in outs]), 3, st) == 0
+        torch.cuda.synchronize()
+        h = rms(x.double(), nw1)
+        for o, w in zip(outs, (wq, wk, wv)):
+            assert close(o, h @ w.double().t())
+
+        # wo product added to the residual, next norm folded in, checked through gate/up + SwiGLU + down
+        a = rnd(n_tok, 512)
+        lib.ingot_linear_tc_prepare.argtypes = [vp, vp, ci, ci, vp]
+        assert lib.ingot_linear_tc_prepare(ws, a.data_ptr(), 512, n_tok, st) == 0
+        assert lib.ingot_linear_tc_run_partial(ws, wo.data_ptr(), 512, d, 0, st) == 0
+        xr = x.clone()
+        assert lib.ingot_linear_tc_finish_residual_norm(ws, xr.data_ptr(), nw2.data_ptr(), eps, 0, st) == 0
+        assert lib.ingot_linear_tc_run_partial(ws, wg.data_ptr(), d, ff, 0, st) == 0
+        assert lib.ingot_linear_tc_run_partial(ws, wu.data_ptr(), d, ff, 1, st) == 0
+        assert lib.ingot_linear_tc_finish_swiglu(ws, 0, 1, st) == 0
+        assert lib.ingot_linear_tc_run_partial(ws, wd.data_ptr(), ff, d, 0, st) == 0
+        xr2 = xr.clone()
+        torch.cuda.synchronize()
+        want_x = x.double() + a.double() @ wo.double().t()
+        assert close(xr, want_x)
+        assert lib.ingot_linear_tc_finish_residual_norm(ws, xr2.data_ptr(), None, eps, 0, st) == 0
+        torch.cuda.synchronize()
+        h2 = rms(want_x, nw2)
+        gate, up = h2 @ wg.double().t(), h2 @ wu.double().t()
+        want_x2 = want_x + (gate / (1 + torch.exp(-gate)) * up) @ wd.double().t()
+        assert close(xr2, want_x2)
+        assert lib.ingot_linear_ws_status(ws) == 0
+    finally:
+        lib.ingot_linear_ws_destroy(ws)
