@@ -449,8 +449,7 @@ def run_batched_decode(args, rank, world):
 def run_e2e_model(args):
     """`ingot bench -p 128 -n 32` through the reference's own engine glue on a seeded random-init
     Llama-3.2-3B-shaped F16 GGUF: the CUDA backend of this repository against the reference's CpuBackend
-    (both inside backend/_build/libingot_engine_cuda.so). Whole-model tokens/s; the non-attention kernels of
-    the CUDA backend are correctness-first, so this is a functional end-to-end figure, not a tuned one."""
+    (both inside backend/_build/libingot_engine_cuda.so). Whole-model tokens/s. --no-cpu skips the CpuBackend leg."""
     import ctypes as C
     sys.path.insert(0, os.path.join(ROOT, "tests", "golden"))
     import make_random_gguf
@@ -467,7 +466,10 @@ def run_e2e_model(args):
         os.replace(path + ".tmp", path)
     prompt = np.random.default_rng(0).integers(0, n_vocab, size=128).astype(np.int32)
     res = {}
+    res["cpu"] = None
     for name, backend, reps in (("cuda", b"metal", 3), ("cpu", b"cpu", 1)):
+        if name == "cpu" and args.no_cpu:
+            continue
         out = np.zeros(2, dtype=np.float64)
         if lib.ingot_e2e_bench(path.encode(), backend, prompt, 128, 32, 512, reps, out) != 0:
             raise SystemExit(lib.ingot_e2e_last_error().decode())

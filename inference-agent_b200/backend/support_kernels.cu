@@ -377,18 +377,24 @@ cudaError_t ingot_support_gemv_group(float* const* outs, const void* const* ws, 
         short_rows ? (swiglu ? gemv_stream_kernel<true, true, 6> : norm_w ? gemv_stream_kernel<true, false, 6> : gemv_stream_kernel<false, false, 6>)
                    : (swiglu ? gemv_stream_kernel<true, true, 4> : norm_w ? gemv_stream_kernel<true, false, 4> : gemv_stream_kernel<false, false, 4>);
     // one resident wave, every warp the same number of rows
-    static int num_sms = 0;
+    static int num_sms = 0, ctas_per_sm_cap = 0;
     static bool use_pdl = true;
     if (num_sms == 0) {
         int dev = 0;
         cudaGetDevice(&dev);
         cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
         use_pdl = getenv("INGOT_NO_PDL") == nullptr;
+        // CTAs of one launch per SM. Fewer than fit leaves room for the next launch's CTAs, which then request
+        // their first weights while this launch is still streaming (programmatic dependent launch).
+        const char* c = getenv("INGOT_GEMV_CTAS_PER_SM");
+        ctas_per_sm_cap = c ? atoi(c) : 0;
     }
     int occ = 0;
     cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kernel, 256, smem);
     if (e != cudaSuccess) return e;
-    const int capacity = num_sms * (occ > 0 ? occ : 1) * 8;
+    if (occ < 1) occ = 1;
+    if (ctas_per_sm_cap > 0) occ = occ < ctas_per_sm_cap ? occ : ctas_per_sm_cap;
+    const int capacity = num_sms * occ * 8;
     const int rows_per_warp = (rows + capacity - 1) / capacity;
     const int warps = (rows + rows_per_warp - 1) / rows_per_warp;
     cudaLaunchConfig_t cfg = {};
