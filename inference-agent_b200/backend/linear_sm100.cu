@@ -12,8 +12,8 @@
 // only by summation order and the 2^-22 truncation of x.
 //
 // Kernel. One CTA = 128 tokens x 128 outputs over a slice of k (split-k fills the GPU when there are few
-// output tiles; slices go to a scratch and a second kernel sums them in slice order, so results are
-// reproducible). 6 warps: warp 0 streams [128 rows][64 k] boxes of hi, lo and W (128-byte swizzle, 48 KB per
+// output tiles; slices go to a scratch and are summed in slice order, by a small kernel or by the kernel
+// that consumes the product, so results are reproducible). 6 warps: warp 0 streams [128 rows][64 k] boxes of hi, lo and W (128-byte swizzle, 48 KB per
 // stage, 4 stages) with TMA; warp 1 issues tcgen05.mma (kind::f16, M = N = 128, K = 16; all lanes walk the
 // loop, one elected lane issues); warps 2-5 read the 128x128 f32 accumulator out of tensor memory, one
 // thread per token row. Rows past n_tok and outputs past n_out are zero-filled by TMA and not stored.
