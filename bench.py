@@ -159,6 +159,14 @@ def prefill_config(S, world):
             "parallelism": f"KV-head sharding x{world}"}
 
 
+def decode_chains(n_layers):
+    """Launch chains ingot_attn_decode_layers uses for n_layers (csrc/kv_cache.cu: up to INGOT_DECODE_STREAMS, default 8,
+    then as few as give the same number of rounds)."""
+    cap = min(max(int(os.environ.get("INGOT_DECODE_STREAMS", "8")), 1), 8, n_layers)
+    rounds = -(-n_layers // cap)
+    return -(-n_layers // rounds)
+
+
 def run_decode(args, rank, world):
     import torch
     import ingot_b200 as ib
@@ -191,8 +199,8 @@ def run_decode(args, rank, world):
             step()
         torch.cuda.synchronize()
     # A step is 28 launches that each carry one layer's splits (and the previous layer's merge) plus
-    # 4 merge-only launches that close the 4 launch chains.
-    launches = args.steps * (N_LAYER + min(4, N_LAYER))
+    # one merge-only launch per launch chain that closes it.
+    launches = args.steps * (N_LAYER + decode_chains(N_LAYER))
     bytes_step = decode_bytes_per_step()
     value = world * bytes_step * args.steps / (ms * 1e-3) / 1e9
     per_launch_s = ms * 1e-3 / (args.steps * N_LAYER)  # per data-carrying launch (one layer)
@@ -218,7 +226,7 @@ def run_decode(args, rank, world):
     ms_e2e = timed(step_e2e, args.steps, args.warmup, world)
     e2e = {"value": round(world * bytes_step * args.steps / (ms_e2e * 1e-3) / 1e9, 1), "unit": "GB/s",
            "h2d_bytes_per_step": int(N_LAYER * (H + 2 * HKV) * D * 4), "d2h_bytes_per_step": int(N_LAYER * H * D * 4),
-           "ms_per_step": round(ms_e2e / args.steps, 4), "gpu_launches_per_step": 1 + N_LAYER + min(4, N_LAYER)}
+           "ms_per_step": round(ms_e2e / args.steps, 4), "gpu_launches_per_step": 1 + N_LAYER + decode_chains(N_LAYER)}
     assert kv.status() == 0
     return {"metric": "decode attention KV-cache HBM GB/s (4096 keys, 24q/8kv heads, d128, f16 KV, 28 layers)",
             "value": round(value, 1), "unit": "GB/s", "ms_per_step": round(ms / args.steps, 5), "scaling": "weak",
@@ -439,7 +447,7 @@ def run_batched_decode(args, rank, world):
             "dtype": "f16 KV / f16 MMA operands (bf16 q converted on load) / f32 accumulate+softmax",
             "roofline": {"bound": "hbm", "achieved": round(per_gpu, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
                          "frac": round(per_gpu / peaks["hbm_gbs"], 4), "traffic": None},
-            "gpu_launches": args.steps * (n_layers + min(4, n_layers)),
+            "gpu_launches": args.steps * (n_layers + decode_chains(n_layers)),
             "config": {"workload": "configs[3]: 64-sequence paged decode, 16-token blocks, random block permutation",
                        "n_seq_this_rank": n_seq, "layers_per_step": n_layers, "kv_bytes_per_layer_this_rank": bytes_rank // n_layers,
                        "load_imbalance_max_over_mean": round(float(mx.item()) * world / float(tot.item()), 4),

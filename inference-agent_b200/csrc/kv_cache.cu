@@ -246,10 +246,14 @@ int ingot_attn_decode_layers(ingot_kv* kv, int layer_begin, int layer_count, con
     // critical path.
     static const int streams_cfg = [] {
         const char* e = getenv("INGOT_DECODE_STREAMS");  // tuning knob, read once
-        const int v = e ? atoi(e) : 4;
+        const int v = e ? atoi(e) : kDecodeStreams;
         return std::min(std::max(v, 1), kDecodeStreams);
     }();
-    const int n_streams = std::min(streams_cfg, layer_count);
+    // as many chains as allowed, then as few as give the same number of rounds: 28 layers on up to 8 chains are
+    // 4 rounds, which 7 chains do evenly
+    const int max_streams = std::min(streams_cfg, layer_count);
+    const int want_rounds = (layer_count + max_streams - 1) / max_streams;
+    const int n_streams = (layer_count + want_rounds - 1) / want_rounds;
     if (!kv->fork_event) INGOT_CUDA_TRY(cudaEventCreateWithFlags(&kv->fork_event, cudaEventDisableTiming));
     for (int t = 0; t < n_streams; t++) {
         if (!kv->side_stream[t]) INGOT_CUDA_TRY(cudaStreamCreateWithFlags(&kv->side_stream[t], cudaStreamNonBlocking));
@@ -374,7 +378,7 @@ int ingot_attn_layers_host(ingot_kv* kv, int layer_begin, int layer_count, const
     INGOT_CUDA_TRY(cudaMemcpyAsync(v_d, v_host, L * kv_elems * 4, cudaMemcpyHostToDevice, s));
     int rc = INGOT_OK;
     if (n_tok == 1) {
-        // Single token: about 35 launches over 4 side streams. They are captured once per (layer range, head
+        // Single token: about 35 launches over several side streams. They are captured once per (layer range, head
         // count) into a graph whose kernels read the position and the key count from device memory; later
         // calls copy the new pair in and replay it, which takes the launch cost off the host.
         if (!kv->host_pos_dev) {
