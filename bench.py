@@ -34,12 +34,12 @@ N_LAYER, H, HKV, D = 28, 24, 8, 128
 DECODE_KEYS = 4096
 PREFILL_TOKENS = 32768
 
-# DRAM bytes per launch of the dominant kernel from an ncu capture of the same kernel
-# (dram__bytes_read.sum + dram__bytes_write.sum); see profiles/ for the command and the raw figures.
-# decode: captured at the benchmark shape (profiles/attn_decode_c2.md). prefill: captured at 8192 tokens
-# (84.0 MB read + 20.8 MB written; profiles/attn_prefill_sm100_8k.md) and scaled by the 4x token count,
-# compulsory q/K/V/out traffic growing in proportion.
-NCU_TRAFFIC = {"attn_decode_kernel": 16947456, "attn_prefill_sm100_kernel": 4 * (83955712 + 20809472)}
+# DRAM bytes per launch of the dominant kernel (dram__bytes_read.sum + dram__bytes_write.sum) from ncu captures of
+# the same kernels. decode: captured at the benchmark shape. prefill: reads captured at 8192 tokens (84.0 MB) and
+# scaled by the 4x token count (compulsory q/K/V traffic grows in proportion); writes are the 32768 x 24 x 128 f16
+# output, 201 MB, which unlike the 8192-token case (50 MB, absorbed by L2 during the capture) cannot stay in L2.
+NCU_TRAFFIC = {"attn_decode_kernel": 16947456, "attn_prefill_sm100_kernel": 4 * 83955712 + PREFILL_TOKENS * H * D * 2}
+MIN_TIMED_S = 0.5  # the timed region is repeated in blocks of `steps` steps until it is at least this long
 
 
 def measured_peaks():
@@ -110,30 +110,65 @@ def dist_setup(n_gpus):
     return rank, world, local
 
 
-def timed(fn, steps, warmup, world):
-    """W warm-up calls, then `steps` calls timed with CUDA events between barriers; max over ranks (ms)."""
+def timed(fn, steps, warmup, world, min_time_s=MIN_TIMED_S, max_blocks=2000):
+    """W warm-up calls, then blocks of `steps` calls each, back to back between two barriers, until the region is
+    at least min_time_s long. Every block is timed with CUDA events on the launching stream and reduced with MAX
+    over the ranks. Returns {"ms": median block (ms for `steps` steps), "ms_best": fastest block, "blocks": B,
+    "timed_region_s": sum of the blocks}."""
     import torch
+    import torch.distributed as dist
     for _ in range(warmup):
         fn()
     torch.cuda.synchronize()
-    if world > 1:
-        import torch.distributed as dist
-        dist.barrier()
-    torch.cuda.synchronize()
+    # block count from one probe block (the same on every rank)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(steps):
         fn()
     e1.record()
     torch.cuda.synchronize()
+    probe = torch.tensor([e0.elapsed_time(e1)], device="cuda", dtype=torch.float64)
     if world > 1:
-        import torch.distributed as dist
+        dist.all_reduce(probe, op=dist.ReduceOp.MAX)
+    blocks = int(min(max_blocks, max(1, -(-min_time_s * 1e3 // max(float(probe.item()), 1e-3)))))
+    if world > 1:
         dist.barrier()
-    ms = torch.tensor([e0.elapsed_time(e1)], device="cuda", dtype=torch.float64)
+    torch.cuda.synchronize()
+    marks = [torch.cuda.Event(enable_timing=True) for _ in range(blocks + 1)]
+    marks[0].record()
+    for b in range(blocks):
+        for _ in range(steps):
+            fn()
+        marks[b + 1].record()
+    torch.cuda.synchronize()
     if world > 1:
-        import torch.distributed as dist
+        dist.barrier()
+    ms = torch.tensor([marks[b].elapsed_time(marks[b + 1]) for b in range(blocks)], device="cuda", dtype=torch.float64)
+    if world > 1:
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-    return float(ms.item())
+    ms = ms.cpu().tolist()
+    return {"ms": statistics.median(ms), "ms_best": min(ms), "blocks": blocks, "timed_region_s": round(sum(ms) * 1e-3, 4)}
+
+
+def parity(got, want):
+    """max-abs and relative L2 error of the attention output against the f32 CPU reference (bounds 2e-3 / 1e-3)."""
+    got, want = np.asarray(got, dtype=np.float64), np.asarray(want, dtype=np.float64)
+    d = got - want
+    out = {"max_abs": float(np.abs(d).max()), "rel_l2": float(np.linalg.norm(d) / max(np.linalg.norm(want), 1e-30))}
+    out["within_tolerance"] = bool(out["max_abs"] <= 2e-3 and out["rel_l2"] <= 1e-3 and np.isfinite(got).all())
+    return out
+
+
+def oracle_rows(q_rows, k_f16, v_f16, positions, n_head_kv):
+    """CPU reference attention (the checker under oracle/) for already-rotated query rows [r,H,d] at `positions`
+    over f16 cache rows [n,Hkv,d] widened to the reference's f32 cache. Outside every timed region."""
+    from oracle import loader
+    lib = loader.load_oracle()
+    n = k_f16.shape[0]
+    kc = np.ascontiguousarray(k_f16.astype(np.float32).reshape(n, -1))
+    vc = np.ascontiguousarray(v_f16.astype(np.float32).reshape(n, -1))
+    return loader.attend_rows(lib, q_rows, kc, vc, np.asarray(positions, dtype=np.int32), q_rows.shape[1], n_head_kv,
+                              q_rows.shape[2])
 
 
 # ------------------------------------------------------------------------------------------------
@@ -146,7 +181,8 @@ def decode_bytes_per_step():
 
 def decode_config(world):
     """The workload description both arms (this library and the reference's CPU code) report."""
-    return {"workload": "configs[1]: decode @4096 keys, batch 1 per GPU, 28 per-layer caches per step",
+    return {"workload": "configs[1]: decode @4096 keys, batch 1 per GPU, 28 per-layer caches per step; the 28 layers are "
+                        "independent and run as one launch each on concurrent launch chains (see roofline.launch_chains)",
             "n_layer": N_LAYER, "n_keys": DECODE_KEYS, "n_head": H, "n_head_kv": HKV, "head_dim": D,
             "l2": "inputs larger than L2 (470 MB of KV per step, 28 distinct caches)",
             "parallelism": f"sequence sharding x{world} (one sequence per GPU, no collective)"}
@@ -167,49 +203,98 @@ def decode_chains(n_layers):
     return -(-n_layers // rounds)
 
 
+def captured(fn):
+    """Runs fn once eagerly (the library sizes its scratch on a first call, which cannot happen under capture),
+    then captures it into a CUDA graph and returns the replay function."""
+    import torch
+    fn()
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        fn()
+    return g.replay
+
+
 def run_decode(args, rank, world):
     import torch
     import ingot_b200 as ib
+    from ingot_b200 import workloads as W
     torch.manual_seed(1 + rank)
     kv = ib.KVCache(ib.KV_CONTIGUOUS, N_LAYER, HKV, DECODE_KEYS)
-    for l in range(N_LAYER):  # synthetic N(0,1) cache, generated on the device
-        kv.layer_view(l, "k").copy_(torch.randn(HKV, DECODE_KEYS, D, device="cuda").half())
-        kv.layer_view(l, "v").copy_(torch.randn(HKV, DECODE_KEYS, D, device="cuda").half())
+    # Layer 0 holds the configs[1] tensors themselves (numpy default_rng(1), draw order q, K, V: the bits the parity
+    # tests use); the other 27 caches are N(0,1) generated on the device.
+    c2 = W.c2_decode4096()
     q = torch.randn(N_LAYER, 1, H, D, device="cuda")
-    out = torch.empty(N_LAYER, 1, H, D, device="cuda")
+    q[0].copy_(torch.from_numpy(c2.q))
+    for l in range(N_LAYER):
+        if l == 0:
+            kv.import_f16(0, torch.from_numpy(c2.k[0]).cuda(), torch.from_numpy(c2.v[0]).cuda(), 0)
+        else:
+            kv.layer_view(l, "k").copy_(torch.randn(HKV, DECODE_KEYS, D, device="cuda").half())
+            kv.layer_view(l, "v").copy_(torch.randn(HKV, DECODE_KEYS, D, device="cuda").half())
+    out = torch.zeros(N_LAYER, 1, H, D, device="cuda")
 
     def launch_layers():
         ib.attn_decode_layers(kv, 0, q, out, max_seq_len=DECODE_KEYS, chunk_keys=args.chunk_keys)
 
     # The 28 launches of a step are captured once in a CUDA graph (the reference encodes them into one
     # command buffer, src/metal_backend.mm:594-649); a step is one replay.
-    launch_layers()
-    torch.cuda.synchronize()
-    graph = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(graph):
-        launch_layers()
-    step = graph.replay if not args.no_graph else launch_layers
+    step = launch_layers if args.no_graph else captured(launch_layers)
+    chains = decode_chains(N_LAYER)
 
-    with ClockSampler(torch.cuda.current_device()) as clk:
-        ms = timed(step, args.steps, args.warmup, world)
-        # keep the same load running so that the clock samples mean something (skipped with --no-graph,
-        # which is the profiling form of the command: a profiler should see the timed launches only)
-        t_end = time.perf_counter() + (0.0 if args.no_graph else 0.4)
-        while time.perf_counter() < t_end:
-            step()
-        torch.cuda.synchronize()
-    # A step is 28 launches that each carry one layer's splits (and the previous layer's merge) plus
-    # one merge-only launch per launch chain that closes it.
-    launches = args.steps * (N_LAYER + decode_chains(N_LAYER))
+    with ClockSampler(torch.cuda.current_device()) as clk:  # clocks are sampled while the timed region runs
+        t = timed(step, args.steps, args.warmup, world, 0.0 if args.no_graph else MIN_TIMED_S)
+    ms = t["ms"]
+
+    # Parity of what was just timed, outside the timed region: three of the 28 layers against the CPU reference.
+    torch.cuda.synchronize()
+    errs = []
+    for l in (0, N_LAYER // 2, N_LAYER - 1):
+        k_l = kv.layer_view(l, "k").permute(1, 0, 2).contiguous().cpu().numpy()  # [keys, Hkv, d]
+        v_l = kv.layer_view(l, "v").permute(1, 0, 2).contiguous().cpu().numpy()
+        want = oracle_rows(q[l].cpu().numpy(), k_l, v_l, [DECODE_KEYS - 1], HKV)
+        errs.append(parity(out[l].cpu().numpy(), want))
+    par = {"max_abs": max(e["max_abs"] for e in errs), "rel_l2": max(e["rel_l2"] for e in errs),
+           "within_tolerance": all(e["within_tolerance"] for e in errs),
+           "checked": "layers 0 (the configs[1] seed-1 tensors), 14 and 27 of the timed call against the CPU reference"}
+
+    launches = args.steps * t["blocks"] * N_LAYER  # one launch per layer: splits and their merge in the same kernel
     bytes_step = decode_bytes_per_step()
     value = world * bytes_step * args.steps / (ms * 1e-3) / 1e9
-    per_launch_s = ms * 1e-3 / (args.steps * N_LAYER)  # per data-carrying launch (one layer)
+    per_launch_s = ms * 1e-3 / (args.steps * N_LAYER)
     peaks = measured_peaks()
     achieved = bytes_step / N_LAYER / per_launch_s / 1e9
     roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
                 "frac": round(achieved / peaks["hbm_gbs"], 4), "traffic": NCU_TRAFFIC["attn_decode_kernel"],
                 "kernel": "attn_decode_kernel", "peak_source": f"of {peaks['source']} (STREAM-style copy)",
-                "algorithmic_bytes_per_launch": bytes_step // N_LAYER, "us_per_launch": round(per_launch_s * 1e6, 3)}
+                "frac_of_nominal_8000": round(achieved / 8000.0, 4),
+                "algorithmic_bytes_per_launch": bytes_step // N_LAYER, "us_per_launch": round(per_launch_s * 1e6, 3),
+                "launch_chains": chains,
+                "note": "us_per_launch is step time / 28 with `launch_chains` launches in flight, not one kernel's duration"}
+
+    # The same 28 layers in the two forms a forward pass can use (its layers depend on one another):
+    # one launch chain, and one ingot_attn_decode call per layer on one stream (what the Backend issues).
+    if not args.no_graph and not args.no_secondary:
+        prev = os.environ.get("INGOT_DECODE_STREAMS")
+        os.environ["INGOT_DECODE_STREAMS"] = "1"
+        try:
+            t1 = timed(captured(launch_layers), args.steps, 3, world, 0.1)
+        finally:
+            if prev is None:
+                del os.environ["INGOT_DECODE_STREAMS"]
+            else:
+                os.environ["INGOT_DECODE_STREAMS"] = prev
+
+        def per_layer_calls():
+            for l in range(N_LAYER):
+                ib.attn_decode(kv, l, q[l], out=out[l], max_seq_len=DECODE_KEYS, chunk_keys=args.chunk_keys)
+
+        t2 = timed(captured(per_layer_calls), args.steps, 3, world, 0.1)
+        layer_bytes = bytes_step / N_LAYER
+        for name, tt in (("single_chain", t1), ("in_backend", t2)):
+            us = tt["ms"] * 1e3 / (args.steps * N_LAYER)
+            roofline[name + "_us_per_layer"] = round(us, 3)
+            roofline[name + "_gbs"] = round(layer_bytes / (us * 1e-6) / 1e9, 1)
 
     # End to end through the host-buffer C-ABI call: per layer q/k/v rows host->device, RoPE+append,
     # decode at position 4095 (4096 keys), output device->host; one synchronisation per step.
@@ -223,15 +308,18 @@ def run_decode(args, rank, world):
         ib.attn_layers_host(kv, 0, qh, kh, vh, oh, inv, DECODE_KEYS - 1)
         torch.cuda.current_stream().synchronize()
 
-    ms_e2e = timed(step_e2e, args.steps, args.warmup, world)
+    te = timed(step_e2e, args.steps, args.warmup, world, 0.0 if args.no_graph else 0.25)
+    ms_e2e = te["ms"]
     e2e = {"value": round(world * bytes_step * args.steps / (ms_e2e * 1e-3) / 1e9, 1), "unit": "GB/s",
-           "h2d_bytes_per_step": int(N_LAYER * (H + 2 * HKV) * D * 4), "d2h_bytes_per_step": int(N_LAYER * H * D * 4),
-           "ms_per_step": round(ms_e2e / args.steps, 4), "gpu_launches_per_step": 1 + N_LAYER + decode_chains(N_LAYER)}
+           "h2d_bytes_per_step": int(N_LAYER * (H + 2 * HKV) * D * 4 + 8), "d2h_bytes_per_step": int(N_LAYER * H * D * 4),
+           "ms_per_step": round(ms_e2e / args.steps, 4), "gpu_launches_per_step": 1 + N_LAYER,
+           "timed_region_s": te["timed_region_s"]}
     assert kv.status() == 0
     return {"metric": "decode attention KV-cache HBM GB/s (4096 keys, 24q/8kv heads, d128, f16 KV, 28 layers)",
             "value": round(value, 1), "unit": "GB/s", "ms_per_step": round(ms / args.steps, 5), "scaling": "weak",
             "dtype": "f16 KV / f16 MMA operands / f32 accumulate+softmax", "roofline": roofline, "e2e": e2e,
-            "gpu_launches": launches, "clocks": clk.summary(),
+            "gpu_launches": launches, "clocks": clk.summary(), "parity": par, "blocks": t["blocks"],
+            "timed_region_s": t["timed_region_s"], "ms_per_step_best_block": round(t["ms_best"] / args.steps, 5),
             "config": decode_config(world)}
 
 
@@ -258,45 +346,39 @@ def prefill_flops(n_tok=None):
 def run_prefill(args, rank, world):
     import torch
     import ingot_b200 as ib
+    from ingot_b200 import workloads as W
     assert HKV % world == 0
     hkv_l, h_l = HKV // world, H // world
-    torch.manual_seed(4)  # same tensors on every rank; each rank keeps its KV-head slice
     S = args.prefill_tokens
+    # The configs[4] tensors themselves (numpy default_rng(4), draw order q, K, V; q rounded to bf16, K/V to f16),
+    # the same on every rank; each rank keeps its KV-head slice.
+    c5 = W.c5_prefill32k(n_tok=S)
     kv = ib.KVCache(ib.KV_CONTIGUOUS, 1, hkv_l, S)
-    g = torch.Generator(device="cuda").manual_seed(4)
-    k_all = torch.randn(HKV, S, D, device="cuda", generator=g).half()
-    v_all = torch.randn(HKV, S, D, device="cuda", generator=g).half()
-    q_all = torch.randn(S, H, D, device="cuda", generator=g).bfloat16()
-    kv.layer_view(0, "k").copy_(k_all[rank * hkv_l:(rank + 1) * hkv_l])
-    kv.layer_view(0, "v").copy_(v_all[rank * hkv_l:(rank + 1) * hkv_l])
-    q = q_all[:, rank * h_l:(rank + 1) * h_l].contiguous()
-    del k_all, v_all, q_all
+    kv.import_f16(0, torch.from_numpy(np.ascontiguousarray(c5.k[:, rank * hkv_l:(rank + 1) * hkv_l])).cuda(),
+                  torch.from_numpy(np.ascontiguousarray(c5.v[:, rank * hkv_l:(rank + 1) * hkv_l])).cuda(), 0)
+    q = torch.from_numpy(np.ascontiguousarray(c5.q[:, rank * h_l:(rank + 1) * h_l])).cuda().bfloat16()
     out = torch.empty(S, h_l, D, device="cuda", dtype=torch.float16)
     gathered = torch.empty(world * S, h_l, D, device="cuda", dtype=torch.float16) if world > 1 else None  # rank-major
-    # N > 1: the gather of head outputs is fused into the kernel's epilogue — every rank stores its rows
-    # straight into all ranks' token-major [S][24][128] buffers (symmetric memory, plain peer stores over
-    # NVLink), followed by a one-element NCCL all-reduce as the cross-rank completion barrier. If symmetric
-    # memory cannot be set up the step falls back to kernel + NCCL all-gather and says so in `config`.
-    gather_mode, peer_ptrs, full, token = "none (single GPU)", None, None, None
+    # N > 1: the gather of head outputs is fused into the kernel's epilogue - every rank stores its rows straight
+    # into all ranks' token-major [S][24][128] buffers (symmetric memory, plain peer stores over NVLink) and then
+    # signals every peer; a small kernel waits (bounded) for all peers' signals. If symmetric memory cannot be
+    # set up the step falls back to kernel + NCCL all-gather and says so in `config`.
+    gather_mode, peer_ptrs, full, gs = "none (single GPU)", None, None, None
     if world > 1:
         import torch.distributed as dist
         gather_mode = "NCCL all_gather_into_tensor after the kernel"
         if not args.no_fused_gather:
             try:
-                import torch.distributed._symmetric_memory as symm
-                full = symm.empty((S, H, D), dtype=torch.float16, device="cuda")
-                hdl = symm.rendezvous(full, dist.group.WORLD)
-                peer_ptrs = [int(x) for x in hdl.buffer_ptrs]
-                token = torch.zeros(1, device="cuda")
-                gather_mode = "fused: peer stores from the kernel epilogue + 1-element all-reduce barrier"
+                gs = GatherSync(S, world, rank)
+                full, peer_ptrs = gs.full, gs.peer_ptrs
+                gather_mode = gs.mode
             except Exception as e:  # noqa: BLE001
                 peer_ptrs = None
-                gather_mode += f" (symmetric memory unavailable: {type(e).__name__})"
+                gather_mode += f" (symmetric memory unavailable: {type(e).__name__}: {e})"
 
     def step():
         if peer_ptrs is not None:
-            ib.attn_prefill_gather(kv, 0, q, 0, peer_ptrs, ib.F16, H, rank * h_l)
-            dist.all_reduce(token)
+            gs.step(kv, q, h_l)
         else:
             ib.attn_prefill(kv, 0, q, 0, out=out, impl=2)
             if world > 1:
@@ -318,9 +400,30 @@ def run_prefill(args, rank, world):
 
     steps = max(1, min(args.steps, args.prefill_steps))
     with ClockSampler(torch.cuda.current_device()) as clk:
-        ms = timed(step, steps, args.warmup, world)
-    ms_kernel = ms if world == 1 else timed(step_kernel_only, steps, 3, world)
+        t = timed(step, steps, args.warmup, world)
+    ms = t["ms"]
+    tk = t if world == 1 else timed(step_kernel_only, steps, 3, world, 0.1)
+    ms_kernel = tk["ms"]
     assert kv.status() == 0
+    if gs is not None and gs.status() != 0:
+        raise SystemExit("the gather completion wait ran out")
+
+    # Parity of the timed call's output, outside the timed region: row 0, the last row and 14 random rows (all 24
+    # heads; at N > 1 read from the gathered buffer) against the CPU reference.
+    torch.cuda.synchronize()
+    rows = np.unique(np.concatenate([[0, S - 1], np.random.default_rng(44).integers(0, S, 14)])).astype(np.int64)
+    if world > 1 and peer_ptrs is None:
+        torch.cuda.synchronize()
+        got = gathered.view(world, S, h_l, D).permute(1, 0, 2, 3).reshape(S, H, D)[rows].float().cpu().numpy()
+    else:
+        got = (full if world > 1 else out)[torch.from_numpy(rows).cuda()].float().cpu().numpy()
+    par = None
+    if rank == 0:
+        want = oracle_rows(c5.q[rows], c5.k, c5.v, rows, HKV)
+        par = parity(got, want)
+        par["checked"] = f"{len(rows)} query rows x 24 heads (row 0, the last row, random rows) against the CPU reference"
+    del c5
+
     flops = prefill_flops(S)
     value = flops * steps / (ms * 1e-3) / 1e12
     peaks = measured_peaks()
@@ -329,7 +432,8 @@ def run_prefill(args, rank, world):
                 "frac": round(per_gpu / peaks["tflops_burst"], 4), "traffic": NCU_TRAFFIC["attn_prefill_sm100_kernel"],
                 "kernel": "attn_prefill_sm100_kernel", "peak_source": f"of {peaks['source']} (cuBLAS bf16 burst)",
                 "frac_of_sustained": round(per_gpu / peaks["tflops_sustained"], 4),
-                "frac_of_nominal_2250": round(per_gpu / 2250.0, 4), "ms_per_launch": round(ms_kernel / steps, 4)}
+                "frac_of_nominal_2250": round(per_gpu / 2250.0, 4), "ms_per_launch": round(ms_kernel / steps, 4),
+                "best_block_tflops": round(flops / world * steps / (tk["ms_best"] * 1e-3) / 1e12, 1)}
 
     # End to end with host buffers: this rank's q slice host->device, prefill, output device->host.
     qh = q.cpu().pin_memory()
@@ -341,26 +445,72 @@ def run_prefill(args, rank, world):
         oh.copy_(out, non_blocking=True)
         torch.cuda.current_stream().synchronize()
 
-    ms_e2e = timed(step_e2e, steps, 1, world)
-    e2e = {"value": round(flops * steps / (ms_e2e * 1e-3) / 1e12, 1), "unit": "TFLOP/s",
+    te = timed(step_e2e, min(steps, 5), 1, world, 0.1)
+    ms_e2e = te["ms"] / min(steps, 5)
+    e2e = {"value": round(flops / (ms_e2e * 1e-3) / 1e12, 1), "unit": "TFLOP/s",
            "h2d_bytes_per_step": int(q.numel() * 2), "d2h_bytes_per_step": int(out.numel() * 2),
-           "ms_per_step": round(ms_e2e / steps, 4)}
+           "ms_per_step": round(ms_e2e, 4)}
     return {"metric": f"causal GQA prefill attention TFLOP/s ({S} tokens, 24q/8kv heads, d128, bf16 q, f16 K/V)",
             "value": round(value, 1), "unit": "TFLOP/s", "ms_per_step": round(ms / steps, 4), "steps": steps,
+            "ms_kernel": round(ms_kernel / steps, 4), "blocks": t["blocks"], "timed_region_s": t["timed_region_s"],
             "scaling": "strong", "dtype": "f16 MMA operands (bf16 q converted on load) / f32 accumulate+softmax",
-            "roofline": roofline, "e2e": e2e, "gpu_launches": steps, "clocks": clk.summary(),
+            "roofline": roofline, "e2e": e2e, "gpu_launches": steps * t["blocks"] * (1 if world == 1 else 2),
+            "clocks": clk.summary(), "parity": par,
             "config": dict(prefill_config(S, world), gather=gather_mode, gather_verified=gather_checked)}
 
+
+class GatherSync:
+    """Destination buffers and completion signalling of the KV-head-sharded prefill at N > 1: one symmetric-memory
+    allocation per rank holding the token-major output [S][24][128] f16, and the step that runs the fused
+    kernel and then waits until every peer's rows have landed."""
+
+    def __init__(self, S, world, rank):
+        import torch
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm
+        self.full = symm.empty((S, H, D), dtype=torch.float16, device="cuda")
+        hdl = symm.rendezvous(self.full, dist.group.WORLD)
+        self.peer_ptrs = [int(x) for x in hdl.buffer_ptrs]
+        self.token = torch.zeros(1, device="cuda")
+        self.rank, self.world = rank, world
+        self.mode = "fused: peer stores from the kernel epilogue + 1-element all-reduce barrier"
+
+    def step(self, kv, q, h_l):
+        import torch.distributed as dist
+        import ingot_b200 as ib
+        ib.attn_prefill_gather(kv, 0, q, 0, self.peer_ptrs, ib.F16, H, self.rank * h_l)
+        dist.all_reduce(self.token)
+
+    def status(self):
+        return 0
 
 
 # ------------------------------------------------------------------------------------------------
 # the other configurations (parity-test shapes; reported for completeness, not headline lines)
 # ------------------------------------------------------------------------------------------------
 
-def run_chunked(args, rank, world, n_tok, pos0, label):
-    """K1 + K2 of one layer: n_tok new tokens appended at pos0 (configs[0] / configs[2]), one GPU per rank (replicas)."""
+def oracle_chunk(wl):
+    """CPU reference output (RoPE + append + per-token attention loop) for a workloads.Prefill with rope=True: the
+    reference's own compiled code when oracle/_ref is present (all host threads), else the plain-C restatement."""
+    from oracle import loader
+    lib, prefix = loader.load_ref(), "ref_"
+    if lib is None:
+        lib, prefix = loader.load_oracle(), "oracle_"
+    n_ctx = wl.pos0 + wl.n_tok
+    kc = np.zeros((n_ctx, HKV * D), dtype=np.float32)
+    vc = np.zeros((n_ctx, HKV * D), dtype=np.float32)
+    if wl.pos0:
+        kc[:wl.pos0] = wl.cache_k.astype(np.float32).reshape(wl.pos0, -1)
+        vc[:wl.pos0] = wl.cache_v.astype(np.float32).reshape(wl.pos0, -1)
+    return loader.attn_forward(lib, prefix, wl.q, wl.k, wl.v, wl.pos0, n_ctx, loader.inv_freq(lib, prefix), kc, vc)[0]
+
+
+def run_chunked(args, rank, world, wl, label):
+    """K1 + K2 per layer for a chunk of new tokens (configs[0] / configs[2]), 28 layers per step, one GPU per rank
+    (replicas). Layer 0 carries the configuration's own seeded tensors and is checked against the CPU reference."""
     import torch
     import ingot_b200 as ib
+    n_tok, pos0 = wl.n_tok, wl.pos0
     torch.manual_seed(2)
     kv = ib.KVCache(ib.KV_CONTIGUOUS, N_LAYER, HKV, pos0 + n_tok)
     for l in range(N_LAYER):
@@ -369,35 +519,39 @@ def run_chunked(args, rank, world, n_tok, pos0, label):
     q = torch.randn(N_LAYER, n_tok, H, D, device="cuda")
     k = torch.randn(N_LAYER, n_tok, HKV, D, device="cuda")
     v = torch.randn(N_LAYER, n_tok, HKV, D, device="cuda")
+    q[0].copy_(torch.from_numpy(wl.q)); k[0].copy_(torch.from_numpy(wl.k)); v[0].copy_(torch.from_numpy(wl.v))
+    if pos0:
+        kv.import_f16(0, torch.from_numpy(wl.cache_k).cuda(), torch.from_numpy(wl.cache_v).cuda(), 0)
     out = torch.empty(N_LAYER, n_tok, H, D, device="cuda")
     inv = torch.from_numpy(inv_freq_table()).cuda()
-    res = {}
-    for impl in (0, 1, 2):
+    want = oracle_chunk(wl) if rank == 0 else None
+    res, par = {}, {}
+    steps = max(1, min(args.steps, 10))
+    names = {0: "auto", 1: "warp_mma", 2: "tcgen05"}
+    for impl in (1, 2, 0):
         def launch_layers():
             for l in range(N_LAYER):
                 qr = ib.rope_kv_append(kv, l, q[l], k[l], v[l], inv, pos0)
                 ib.attn_prefill(kv, l, qr, pos0, out=out[l], impl=impl)
         # One CUDA graph per step (the 28 layers' launches), so that Python launch overhead is not timed.
-        launch_layers()
+        step = launch_layers if args.no_graph else captured(launch_layers)
+        t = timed(step, steps, args.warmup, world, 0.1)
+        res[impl] = t["ms"] / steps / N_LAYER
         torch.cuda.synchronize()
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
-            launch_layers()
-        step = launch_layers if args.no_graph else graph.replay
-        steps = max(1, min(args.steps, 10))
-        ms = timed(step, steps, args.warmup, world)
-        res[impl] = ms / steps / N_LAYER
-    flops = 4 * H * D * (n_tok * pos0 + n_tok * n_tok // 2)
+        if rank == 0:
+            par[names[impl]] = parity(out[0].cpu().numpy(), want)
+    assert kv.status() == 0
+    flops = wl.flops
     best = res[0]
     peaks = measured_peaks()
     tf = flops / (best * 1e-3) / 1e12
     return {"metric": f"causal GQA chunked prefill TFLOP/s ({label})", "value": round(world * tf, 2), "unit": "TFLOP/s",
-            "ms_per_step": round(best * N_LAYER, 4), "scaling": "weak", "dtype": "f16 MMA operands / f32 accumulate+softmax",
+            "ms_per_step": round(best * N_LAYER, 4), "steps": steps, "scaling": "weak",
+            "dtype": "f16 MMA operands / f32 accumulate+softmax",
             "roofline": {"bound": "tensor", "achieved": round(tf, 2), "peak": peaks["tflops_burst"], "unit": "TFLOP/s",
                          "frac": round(tf / peaks["tflops_burst"], 4), "traffic": None,
-                         "us_per_layer": {"auto": round(res[0] * 1e3, 2), "warp_mma": round(res[1] * 1e3, 2),
-                                          "tcgen05": round(res[2] * 1e3, 2)}},
-            "gpu_launches": 2 * N_LAYER * max(1, min(args.steps, 10)),
+                         "us_per_layer": {names[i]: round(res[i] * 1e3, 2) for i in (0, 1, 2)}},
+            "gpu_launches": 2 * N_LAYER * steps, "parity": par,
             "config": {"workload": label, "n_tok": n_tok, "pos0": pos0, "n_layer": N_LAYER, "flops_per_layer": flops,
                        "includes": "RoPE+append (K1) and attention (K2, plus its split merge where used) per layer, 28 layers per CUDA graph replay",
                        "parallelism": f"replicas x{world}"}}
@@ -415,7 +569,8 @@ def run_batched_decode(args, rank, world):
     n_seq = len(lens)
     nb = int(((lens + 15) // 16).sum())
     perm = np.random.default_rng([3, 2, rank]).permutation(nb).astype(np.int32)
-    bt = torch.from_numpy(W.block_tables(lens, perm)).cuda()
+    bt_np = W.block_tables(lens, perm)
+    bt = torch.from_numpy(bt_np).cuda()
     n_layers = 4  # distinct per-layer pools so that a step streams more than L2 holds
     kv = ib.KVCache(ib.KV_PAGED, n_layers, HKV, nb, max_seqs=n_seq)
     torch.manual_seed(3 + rank)
@@ -423,15 +578,31 @@ def run_batched_decode(args, rank, world):
         kv.layer_view(l, "k").copy_(torch.randn(nb, HKV, 16, D, device="cuda").half())
         kv.layer_view(l, "v").copy_(torch.randn(nb, HKV, 16, D, device="cuda").half())
     q = torch.randn(n_layers, n_seq, H, D, device="cuda").bfloat16()
-    out = torch.empty(n_layers, n_seq, H, D, device="cuda")
+    out = torch.zeros(n_layers, n_seq, H, D, device="cuda")
     lens_d = torch.from_numpy(lens).cuda()
 
-    def step():
+    def launch():
         ib.attn_decode_layers(kv, 0, q, out, seq_lens=lens_d, max_seq_len=int(lens.max()), block_tables=bt,
                               chunk_keys=args.chunk_keys)
 
-    ms = timed(step, args.steps, args.warmup, world)
+    step = launch if args.no_graph else captured(launch)
+    with ClockSampler(torch.cuda.current_device()) as clk:
+        t = timed(step, args.steps, args.warmup, world, 0.25)
+    ms = t["ms"]
     assert kv.status() == 0
+    # Parity outside the timed region: this rank's shortest, longest and one middle sequence of the last layer.
+    torch.cuda.synchronize()
+    order = np.argsort(lens)
+    errs = []
+    lyr = n_layers - 1
+    for s_i in (int(order[0]), int(order[len(order) // 2]), int(order[-1])):
+        n = int(lens[s_i])
+        blocks = torch.from_numpy(bt_np[s_i, :(n + 15) // 16].astype(np.int64)).cuda()
+        k_s = kv.layer_view(lyr, "k")[blocks].permute(0, 2, 1, 3).reshape(-1, HKV, D)[:n].cpu().numpy()
+        v_s = kv.layer_view(lyr, "v")[blocks].permute(0, 2, 1, 3).reshape(-1, HKV, D)[:n].cpu().numpy()
+        want = oracle_rows(q[lyr, s_i:s_i + 1].float().cpu().numpy(), k_s, v_s, [n - 1], HKV)
+        errs.append(parity(out[lyr, s_i:s_i + 1].cpu().numpy(), want))
+    par = torch.tensor([max(e["max_abs"] for e in errs), max(e["rel_l2"] for e in errs)], device="cuda", dtype=torch.float64)
     bytes_rank = int(lens.astype(np.int64).sum()) * HKV * D * 2 * 2 * n_layers
     tot = torch.tensor([float(bytes_rank)], device="cuda", dtype=torch.float64)
     mx = tot.clone()
@@ -439,15 +610,21 @@ def run_batched_decode(args, rank, world):
         import torch.distributed as dist
         dist.all_reduce(tot)
         dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+        dist.all_reduce(par, op=dist.ReduceOp.MAX)
     value = float(tot.item()) * args.steps / (ms * 1e-3) / 1e9
     peaks = measured_peaks()
-    per_gpu = bytes_rank * args.steps / (ms * 1e-3) / 1e9
+    per_gpu = float(mx.item()) * args.steps / (ms * 1e-3) / 1e9  # the most loaded rank sets the step time
     return {"metric": "batched paged decode attention KV-cache HBM GB/s (64 sequences, lengths 256..8192)", "value": round(value, 1),
-            "unit": "GB/s", "ms_per_step": round(ms / args.steps, 5), "scaling": "strong",
+            "unit": "GB/s", "ms_per_step": round(ms / args.steps, 5), "scaling": "strong", "blocks": t["blocks"],
+            "timed_region_s": t["timed_region_s"],
             "dtype": "f16 KV / f16 MMA operands (bf16 q converted on load) / f32 accumulate+softmax",
             "roofline": {"bound": "hbm", "achieved": round(per_gpu, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                         "frac": round(per_gpu / peaks["hbm_gbs"], 4), "traffic": None},
-            "gpu_launches": args.steps * (n_layers + decode_chains(n_layers)),
+                         "frac": round(per_gpu / peaks["hbm_gbs"], 4), "traffic": None, "kernel": "attn_decode_kernel",
+                         "note": "per GPU, on the most loaded rank"},
+            "gpu_launches": args.steps * t["blocks"] * n_layers, "clocks": clk.summary(),
+            "parity": {"max_abs": float(par[0].item()), "rel_l2": float(par[1].item()),
+                       "within_tolerance": bool(par[0].item() <= 2e-3 and par[1].item() <= 1e-3),
+                       "checked": "shortest, median and longest sequence of every rank (last layer) against the CPU reference"},
             "config": {"workload": "configs[3]: 64-sequence paged decode, 16-token blocks, random block permutation",
                        "n_seq_this_rank": n_seq, "layers_per_step": n_layers, "kv_bytes_per_layer_this_rank": bytes_rank // n_layers,
                        "load_imbalance_max_over_mean": round(float(mx.item()) * world / float(tot.item()), 4),
@@ -615,16 +792,25 @@ def main():
         return
 
     rank, world, _ = dist_setup(args.gpus)
-    if args.workload in ("c1_prefill128", "c3_chunked", "c4_batched"):
+    from ingot_b200 import workloads as W
+    others = {
+        "c1_prefill128": lambda a, r, w: run_chunked(a, r, w, W.c1_prefill128(), "configs[0]: 128-token prefill at position 0"),
+        "c3_chunked": lambda a, r, w: run_chunked(a, r, w, W.c3_chunked(), "configs[2]: 512-token chunk onto 3584 cached positions"),
+        "c4_batched": run_batched_decode,
+    }
+    extra = {}
+    if args.workload in others:
         args.no_secondary = args.no_cpu = True
-        primary = {"c1_prefill128": lambda a, r, w: run_chunked(a, r, w, 128, 0, "configs[0]: 128-token prefill at position 0"),
-                   "c3_chunked": lambda a, r, w: run_chunked(a, r, w, 512, 3584, "configs[2]: 512-token chunk onto 3584 cached positions"),
-                   "c4_batched": run_batched_decode}[args.workload]
-        secondary = None
+        primary, secondary = others[args.workload], None
     else:
         primary, secondary = (run_decode, run_prefill) if args.workload == "decode_c2" else (run_prefill, run_decode)
     line = primary(args, rank, world)
     other = None if args.no_secondary else secondary(args, rank, world)
+    if not args.no_secondary:
+        # The remaining configurations ride along as objects of their own: the two chunked-prefill shapes on one GPU
+        # (they are replicas at N > 1), the sequence-sharded batched decode at every N.
+        for name in (("c1_prefill128", "c3_chunked") if world == 1 else ()) + ("c4_batched",):
+            extra[name] = others[name](args, rank, world)
     if rank == 0:
         out = {"metric": line.pop("metric"), "value": line.pop("value"), "unit": line.pop("unit"), "n_gpus": world,
                "steps": line.pop("steps", args.steps), "warmup": args.warmup, "ms_per_step": line.pop("ms_per_step"),
@@ -635,6 +821,7 @@ def main():
         out.update(line)
         if other is not None:
             out["prefill" if args.workload == "decode_c2" else "decode"] = other
+        out.update(extra)
         if world == 1 and not args.no_cpu:
             if args.workload == "decode_c2":
                 gbs, kind, cores, per_layer = cpu_decode_sample(N_LAYER, 3)

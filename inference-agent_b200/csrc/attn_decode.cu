@@ -8,11 +8,12 @@
 // over one split of `chunk_keys` keys and serves ALL query heads that share that KV head (GQA), so
 // every K/V byte is fetched from HBM exactly once. Inside the CTA each warp walks its own 16-key
 // units with a private online-softmax state (m, l, o); the warp states are merged through shared
-// memory and the split's partial (o[128], m, l per head) goes to a global scratch. A small combine
-// kernel chained behind it with programmatic dependent launch merges the partials:
-// out = sum_s o_s 2^(m_s-M) / sum_s l_s 2^(m_s-M), the attn_combine formula. Split CTAs therefore
-// retire as soon as their partial is written (no fence, ticket or polling), and the combine of one
-// launch overlaps the K/V loads of the next.
+// memory and the split's partial (o[128], m, l per head) goes to a global scratch. The partials are
+// merged with the attn_combine formula, out = sum_s o_s 2^(m_s-M) / sum_s l_s 2^(m_s-M), inside the
+// same launch: every split CTA of a (sequence, kv head) takes a ticket after its partial is fenced,
+// and the CTA that draws the last ticket reads all partials back from L2 and writes the output, so a
+// decode is ONE launch with no dependency on the launch before or after it. (Callers that bring
+// their own scratch without arrival counters use a second, merge-only launch of the same kernel.)
 //
 // Data path. HBM-bound: 2 * len * 128 * 2 B per (sequence, kv head). Every lane issues 16-byte
 // loads straight from global memory into registers, 16 of them (one whole 16-key unit, 8 KB per
@@ -27,6 +28,7 @@
 #include "attn_common.cuh"
 #include "ingot_internal.cuh"
 
+#include <algorithm>
 #include <mutex>
 
 namespace {
@@ -42,8 +44,11 @@ struct DecodeParams {
     const int32_t* seq_lens;
     const int32_t* block_tables;
     float* part;          // split role: partials written here
-    const float* c_part;  // combine role: partials of the launch being merged
+    const float* c_part;  // combine role: partials being merged (the same buffer when the merge is in-kernel)
     void* c_out;          // combine role: its output
+    int* sync;            // in-kernel merge: {arrivals, owner} per (sequence, kv head) of this scratch buffer;
+                          // null: partials are left for a merge role of a later launch
+    int tag;              // in-kernel merge: non-zero id of this launch, distinct among launches that may overlap
     int* status;
     int q_dtype, out_dtype;
     int n_head, n_head_kv, group;
@@ -186,6 +191,12 @@ __device__ __forceinline__ void combine_splits(const DecodeParams& p, float* sme
     }
 }
 
+__device__ __forceinline__ unsigned long long globaltimer_now() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
 struct KRegs { uint4 k[8]; };  // [n-tile 0/1][i=0..3]: key (nt*8 + g), 16-byte chunk (4i + j)
 struct VRegs { uint4 v[8]; };  // [slot 0..3 -> keys 2j, 2j+1, 2j+8, 2j+9][chunk g / g+8]
 
@@ -211,6 +222,14 @@ __global__ void __launch_bounds__(kMaxDecodeWarps * 32, 1) attn_decode_kernel(co
     const int k_begin = chunk * p.chunk_keys;
     const int k_end = min(n_keys, k_begin + p.chunk_keys);
     const int n_units = (k_end - k_begin + 15) >> 4;
+
+    // In-kernel merge: the scratch rows of this (sequence, kv head) belong to one launch at a time. The
+    // first CTA to get here claims them for this launch's tag (the merging CTA of the previous user
+    // releases them when it has read its partials). The claim is requested now, so that its round trip
+    // to L2 hides behind the K/V loads, and looked at just before the partial is written.
+    int* const slot = (p.sync && n_chunks > 1) ? p.sync + 2 * ((size_t)seq * p.n_head_kv + kvh) : nullptr;
+    int claim = 0;
+    if (slot && threadIdx.x == 0) claim = atomicCAS(slot + 1, 0, p.tag);
 
     const int n_warps = blockDim.x >> 5;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -376,8 +395,23 @@ __global__ void __launch_bounds__(kMaxDecodeWarps * 32, 1) attn_decode_kernel(co
         }
     }
     if (g < G && j == 0) { sm[warp * G + g] = m; sl[warp * G + g] = l; }
+    if (slot && threadIdx.x == 0 && claim != 0 && claim != p.tag) {
+        // An earlier launch still owns the rows (its merging CTA is running: it is resident, so this
+        // ends). Bounded all the same: after a second the status word is raised and the CTA goes on,
+        // which keeps the arrival counters consistent for the calls that follow.
+        const unsigned long long t0 = globaltimer_now();
+        for (;;) {
+            claim = atomicCAS(slot + 1, 0, p.tag);
+            if (claim == 0 || claim == p.tag) break;
+            if (globaltimer_now() - t0 > 1000000000ull) {
+                if (p.status) atomicOr(p.status, kDevErrBarrierTimeout);
+                break;
+            }
+            __nanosleep(64);
+        }
+    }
     __syncthreads();
-    if (p.early_loads) asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (p.early_loads && !p.sync) asm volatile("griddepcontrol.wait;" ::: "memory");
 
     const bool single = n_chunks == 1;
     const size_t part_row0 = ((size_t)seq * p.n_parts_max + chunk) * p.n_head + (size_t)kvh * G;
@@ -399,72 +433,93 @@ __global__ void __launch_bounds__(kMaxDecodeWarps * 32, 1) attn_decode_kernel(co
             if (dim == 0) { row[128] = M; row[129] = L; }
         }
     }
+    if (slot) {
+        // Ticket: partial fenced, then one arrival per CTA; the CTA that draws the last ticket merges.
+        __shared__ int s_ticket;
+        __threadfence();
+        __syncthreads();
+        if (threadIdx.x == 0) s_ticket = atomicAdd(slot, 1);
+        __syncthreads();
+        if (s_ticket == n_chunks - 1) {
+            __threadfence();
+            combine_splits(p, smem, kvh, seq);
+            __syncthreads();
+            if (threadIdx.x == 0) {  // counter back to zero, then the rows are released to the next launch
+                slot[0] = 0;
+                __threadfence();
+                atomicExch(slot + 1, 0);
+            }
+        }
+    }
 }
 
-int g_num_sms = 0;
-bool g_use_pdl = true;
+// Tuning knobs, process-wide and read once (like the reference's LLM_ATTN_SPLITS): warps per CTA, 4 (two CTAs
+// per SM) or 8; INGOT_NO_PDL=1 launches in plain stream order (diagnostics).
+int decode_warps_cfg() {
+    static const int v = [] { const char* e = getenv("INGOT_DECODE_WARPS"); return (e && atoi(e) == 8) ? 8 : 4; }();
+    return v;
+}
+bool decode_use_pdl() {
+    static const bool v = getenv("INGOT_NO_PDL") == nullptr;
+    return v;
+}
 
 }  // namespace
 
-size_t decode_part_floats(int n_seq, int /*max_seq_len*/, int n_head) {
-    return (size_t)n_seq * kMaxParts * n_head * kPartStride;
-}
-
-// One launch of the decode kernel: split CTAs for `layer` (when split.q != nullptr) and/or one merge CTA
-// per (kv head, sequence) for the partials a previous launch left in `merge_part` (when merge_out != nullptr).
-int launch_attn_decode(ingot_kv* kv, int layer, const void* q, int q_dtype, void* out, int out_dtype, int n_head,
-                       int n_seq, const int32_t* seq_lens, int max_seq_len, const int32_t* block_tables,
-                       int max_blocks_per_seq, int chunk_keys, float* part, const float* merge_part, void* merge_out,
-                       int early_loads, int concurrency, int* chunk_keys_used, cudaStream_t stream) {
-    static int n_warps_cfg = 0;
-    if (g_num_sms == 0) {
-        int dev = 0;
-        INGOT_CUDA_TRY(cudaGetDevice(&dev));
-        INGOT_CUDA_TRY(cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev));
-        // Tuning knob (like the reference's LLM_ATTN_SPLITS): warps per CTA, 4 (two CTAs per SM) or 8.
-        const char* e = getenv("INGOT_DECODE_WARPS");
-        n_warps_cfg = (e && atoi(e) == 8) ? 8 : 4;
-        g_use_pdl = getenv("INGOT_NO_PDL") == nullptr;  // diagnostics: plain stream order between launches
-    }
-    const int n_warps = n_warps_cfg;
+// Split size and split count of a decode call. Small jobs: fill every CTA slot of the GPU once (the kernel
+// needs ~240 registers per thread, so an SM holds 8 warps) with whole 16-key units per warp. Large jobs: 512
+// keys per split, which keeps variable-length batches balanced across SMs. `concurrency` launches share the
+// GPU (the multi-layer call keeps several layers in flight).
+DecodePlan decode_plan(const ingot_kv* kv, int n_seq, int max_seq_len, int chunk_keys, int concurrency) {
+    const int n_warps = decode_warps_cfg();
     if (chunk_keys == 0) {
-        // Small jobs: fill every CTA slot of the GPU once (the kernel needs ~240 registers per thread,
-        // so an SM holds 8 warps) with whole 16-key units per warp. Large jobs: 512 keys per split,
-        // which keeps variable-length batches balanced across SMs.
-        // `concurrency` launches share the GPU (the multi-layer call keeps several layers in flight).
-        const int slots = g_num_sms * (8 / n_warps) / max(1, concurrency);
-        const int per_head = max(1, slots / (n_seq * kv->n_head_kv));
+        const int slots = kv->num_sms * (8 / n_warps) / std::max(1, concurrency);
+        const int per_head = std::max(1, slots / (n_seq * kv->n_head_kv));
         const int quantum = n_warps * 16;
         chunk_keys = ((max_seq_len + per_head - 1) / per_head + quantum - 1) / quantum * quantum;
-        chunk_keys = min(max(chunk_keys, quantum), 512);
+        chunk_keys = std::min(std::max(chunk_keys, quantum), 512);
     }
     const int min_chunk = ((max_seq_len + kMaxParts - 1) / kMaxParts + 15) / 16 * 16;
-    chunk_keys = max(chunk_keys, min_chunk);
-    const int n_parts = (max_seq_len + chunk_keys - 1) / chunk_keys;
-    if (chunk_keys_used) *chunk_keys_used = chunk_keys;
-    const bool has_split = q != nullptr;
-    const bool has_merge = merge_out != nullptr && n_parts > 1;
-    if (!has_split && !has_merge) return INGOT_OK;
+    chunk_keys = std::max(chunk_keys, min_chunk);
+    DecodePlan plan;
+    plan.chunk_keys = chunk_keys;
+    plan.n_parts = (max_seq_len + chunk_keys - 1) / chunk_keys;
+    return plan;
+}
 
+size_t decode_part_floats(int n_seq, int n_parts, int n_head) {
+    return (size_t)n_seq * n_parts * n_head * kPartStride;
+}
+
+// One decode launch for `layer`: split CTAs that leave their partials in `part` and merge them in-kernel
+// through the arrival counters in `sync` (one {arrivals, owner} pair per (sequence, kv head), zero when idle).
+// `tag` must differ between launches that can be in flight together on the same `part`/`sync`.
+// early_loads: the caller vouches that nothing this launch reads was written by the kernel before it in the
+// stream, so it need not wait for that kernel at all.
+int launch_attn_decode(ingot_kv* kv, int layer, const void* q, int q_dtype, void* out, int out_dtype, int n_head,
+                       int n_seq, const int32_t* seq_lens, int max_seq_len, const int32_t* block_tables,
+                       int max_blocks_per_seq, DecodePlan plan, float* part, int* sync, int tag, int early_loads,
+                       cudaStream_t stream) {
+    const int n_warps = decode_warps_cfg();
     DecodeParams p;
     p.kc = kv->k + size_t(layer) * kv->layer_elems;
     p.vc = kv->v + size_t(layer) * kv->layer_elems;
     p.q = q; p.out = out; p.seq_lens = seq_lens; p.block_tables = block_tables;
-    p.part = part; p.c_part = merge_part; p.c_out = merge_out; p.status = kv->status_dev;
+    p.part = part; p.c_part = part; p.c_out = out; p.sync = sync; p.tag = tag; p.status = kv->status_dev;
     p.q_dtype = q_dtype; p.out_dtype = out_dtype;
     p.n_head = n_head; p.n_head_kv = kv->n_head_kv; p.group = n_head / kv->n_head_kv;
     p.capacity = kv->capacity; p.paged = kv->layout == INGOT_KV_PAGED; p.max_blocks_per_seq = max_blocks_per_seq;
-    p.len0 = max_seq_len; p.chunk_keys = chunk_keys; p.n_parts_max = n_parts;
+    p.len0 = max_seq_len; p.chunk_keys = plan.chunk_keys; p.n_parts_max = plan.n_parts;
     p.early_loads = early_loads;
-    p.split_parts = has_split ? n_parts : 0;
+    p.split_parts = plan.n_parts;
     p.scale_log2 = 1.4426950408889634f / sqrtf(float(kHeadDim));
     const int threads = n_warps * 32;
     const size_t smem_split = (size_t)n_warps * p.group * (kHeadDim + 2);
-    const size_t smem_merge = (size_t)2 * p.group * kMaxParts + (size_t)4 * max(threads, p.group * 32);
-    const size_t smem = max(smem_split, smem_merge) * sizeof(float);
+    const size_t smem_merge = (size_t)2 * p.group * kMaxParts + (size_t)4 * std::max(threads, p.group * 32);
+    const size_t smem = std::max(smem_split, smem_merge) * sizeof(float);
 
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(p.split_parts + (has_merge ? 1 : 0), kv->n_head_kv, n_seq);
+    cfg.gridDim = dim3(plan.n_parts, kv->n_head_kv, n_seq);
     cfg.blockDim = dim3(threads);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
@@ -472,7 +527,7 @@ int launch_attn_decode(ingot_kv* kv, int layer, const void* q, int q_dtype, void
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = g_use_pdl ? 1 : 0;
+    cfg.numAttrs = decode_use_pdl() ? 1 : 0;
     INGOT_CUDA_TRY(cudaLaunchKernelEx(&cfg, attn_decode_kernel, p));
     return INGOT_OK;
 }
@@ -542,7 +597,7 @@ extern "C" int ingot_attn_decode_noalloc(const void* k_dev, const void* v_dev, i
     p.kc = static_cast<const __half*>(k_dev);
     p.vc = static_cast<const __half*>(v_dev);
     p.q = q_dev; p.out = out_dev; p.seq_lens = nullptr; p.block_tables = nullptr;
-    p.part = scratch; p.c_part = scratch; p.c_out = out_dev; p.status = nullptr;
+    p.part = scratch; p.c_part = scratch; p.c_out = out_dev; p.sync = nullptr; p.tag = 0; p.status = nullptr;
     p.q_dtype = q_dtype; p.out_dtype = out_dtype;
     p.n_head = n_head; p.n_head_kv = n_head_kv; p.group = n_head / n_head_kv;
     p.capacity = n_ctx; p.paged = 0; p.max_blocks_per_seq = 0;

@@ -268,10 +268,9 @@ int launch_attn_prefill_mma(ingot_kv* kv, int layer, const void* q, int q_dtype,
     p.q_pos0 = q_pos0; p.n_tok = n_tok;
     p.scale_log2 = 1.4426950408889634f / sqrtf(float(kHeadDim));
     const size_t smem = size_t(2) * kBN * (kKStride + kVStride) * sizeof(__half);
-    static bool attr_set = false;
-    if (!attr_set) {
+    if (!kv->prefill_mma_attr_set) {  // function attributes belong to a device context: once per handle, not per process
         INGOT_CUDA_TRY(cudaFuncSetAttribute(attn_prefill_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
-        attr_set = true;
+        kv->prefill_mma_attr_set = true;
     }
     const long long n_rows = (long long)n_tok * p.group;
     dim3 grid(unsigned((n_rows + kBM - 1) / kBM), kv->n_head_kv);

@@ -8,6 +8,7 @@
 #include <stdint.h>
 
 #include <string>
+#include <vector>
 
 #include "ingot_cuda.h"
 
@@ -17,9 +18,10 @@ constexpr int kBlockTokens = INGOT_BLOCK_TOKENS;
 // padded to a 16-byte multiple. The Metal reference keeps the same triple with stride 130
 // (shaders/kernels.metal:291).
 constexpr int kPartStride = 132;
-// Independent launch chains the multi-layer decode call spreads its layers over.
+// Most independent launch chains the multi-layer decode call spreads its layers over
+// (INGOT_DECODE_STREAMS picks how many are used; the default is this bound).
 constexpr int kDecodeStreams = 8;
-constexpr int kHostPosSlots = 256;  // host-buffer calls that may be queued before the caller synchronises  // upper bound; INGOT_DECODE_STREAMS picks how many are used (default 4)
+constexpr int kHostPosSlots = 256;  // host-buffer calls that may be queued before the caller synchronises
 
 // Bits of the device status word (ingot_kv::status_dev).
 enum : int {
@@ -30,6 +32,7 @@ enum : int {
 
 struct ingot_kv {
     int device = 0;
+    int num_sms = 0;  // of `device`
     int layout = INGOT_KV_CONTIGUOUS;
     int n_layer = 0, n_head_kv = 0, head_dim = kHeadDim;
     int capacity = 0;   // positions (contiguous) or blocks (paged)
@@ -38,10 +41,18 @@ struct ingot_kv {
     __half* k = nullptr;
     __half* v = nullptr;
     int* status_dev = nullptr;
-    // split-KV decode scratch: two buffers of partials [n_seq][splits][n_head][kPartStride]; consecutive
-    // launches alternate between them so that one launch's merge can overlap the next launch's splits
+    // split-KV decode scratch: part_bufs buffers of partials [n_seq][splits][n_head][kPartStride], each with its
+    // arrival counters part_sync [max_seqs][n_head_kv][2] (zero when idle). A single decode call uses buffer 0;
+    // the multi-layer call gives every launch chain two buffers that its consecutive launches alternate between.
+    // Sized on first use from the split count actually needed and only ever grown; a buffer that is outgrown is
+    // parked in `retired` until the handle is destroyed, because a CUDA graph captured earlier may still point
+    // into it.
     float* part = nullptr;
+    int* part_sync = nullptr;
     size_t part_floats = 0;  // floats per buffer
+    int part_bufs = 0;
+    std::vector<void*> retired;
+    bool prefill_mma_attr_set = false;  // the warp-MMA prefill kernel's shared-memory opt-in was made on `device`
     // staging for the host-buffer entry points (grown on demand)
     void* stage = nullptr;
     size_t stage_bytes = 0;
@@ -73,6 +84,19 @@ int ingot_cuda_fail(cudaError_t e, const char* what);
         if (e__ != cudaSuccess) return ingot_cuda_fail(e__, #expr);   \
     } while (0)
 
+// Entry points that take a cache handle must run with the handle's device current: kernels, streams and
+// function attributes all belong to that device's context.
+#define INGOT_REQUIRE_DEVICE(kv)                                                          \
+    do {                                                                                  \
+        int dev__ = -1;                                                                   \
+        INGOT_CUDA_TRY(cudaGetDevice(&dev__));                                            \
+        if (dev__ != (kv)->device) {                                                      \
+            ingot_set_error("the cache was created on device " + std::to_string((kv)->device) + \
+                            " but device " + std::to_string(dev__) + " is current");     \
+            return INGOT_ERR_INVALID;                                                     \
+        }                                                                                 \
+    } while (0)
+
 #define INGOT_REQUIRE(cond, msg)                                      \
     do {                                                              \
         if (!(cond)) {                                                \
@@ -97,14 +121,16 @@ int launch_rope_kv_append(ingot_kv* kv, int layer, const float* q, __half* q_out
                           int layer_count, cudaStream_t stream);
 int launch_kv_import_f16(ingot_kv* kv, int layer, const __half* k, const __half* v, int pos0, int n_tok,
                          const int32_t* block_table, cudaStream_t stream);
+struct DecodePlan { int chunk_keys, n_parts; };
+DecodePlan decode_plan(const ingot_kv* kv, int n_seq, int max_seq_len, int chunk_keys, int concurrency);
+size_t decode_part_floats(int n_seq, int n_parts, int n_head);
 int launch_attn_decode(ingot_kv* kv, int layer, const void* q, int q_dtype, void* out, int out_dtype, int n_head,
                        int n_seq, const int32_t* seq_lens, int max_seq_len, const int32_t* block_tables,
-                       int max_blocks_per_seq, int chunk_keys, float* part, const float* merge_part, void* merge_out,
-                       int early_loads, int concurrency, int* chunk_keys_used, cudaStream_t stream);
+                       int max_blocks_per_seq, DecodePlan plan, float* part, int* sync, int tag, int early_loads,
+                       cudaStream_t stream);
 int launch_attn_prefill_mma(ingot_kv* kv, int layer, const void* q, int q_dtype, void* out, int out_dtype,
                             int n_head, int q_pos0, int n_tok, const int32_t* block_table, cudaStream_t stream);
 int launch_attn_prefill_sm100(ingot_kv* kv, int layer, const void* q, int q_dtype, void* const* outs, int n_outs,
                               int out_dtype, int n_head, int out_n_head, int out_head0, int q_pos0, int n_tok,
                               const int32_t* block_table, cudaStream_t stream);
 void free_prefill_sm100_state(ingot_kv* kv);
-size_t decode_part_floats(int max_seqs, int capacity_keys, int n_head_kv);

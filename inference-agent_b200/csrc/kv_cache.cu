@@ -53,6 +53,8 @@ int ingot_kv_create(ingot_kv** out, int layout, int n_layer, int n_head_kv, int 
     if (!kv) return INGOT_ERR_NOMEM;
     cudaError_t e = cudaGetDevice(&kv->device);
     if (e != cudaSuccess) { delete kv; return ingot_cuda_fail(e, "cudaGetDevice"); }
+    e = cudaDeviceGetAttribute(&kv->num_sms, cudaDevAttrMultiProcessorCount, kv->device);
+    if (e != cudaSuccess) { delete kv; return ingot_cuda_fail(e, "cudaDeviceGetAttribute"); }
     kv->layout = layout;
     kv->n_layer = n_layer;
     kv->n_head_kv = n_head_kv;
@@ -86,6 +88,8 @@ void ingot_kv_destroy(ingot_kv* kv) {
     cudaFree(kv->v);
     cudaFree(kv->status_dev);
     cudaFree(kv->part);
+    cudaFree(kv->part_sync);
+    for (void* p : kv->retired) cudaFree(p);
     cudaFree(kv->stage);
     if (kv->host_exec) cudaGraphExecDestroy(kv->host_exec);
     if (kv->host_graph) cudaGraphDestroy(kv->host_graph);
@@ -128,6 +132,7 @@ int ingot_rope_kv_append(ingot_kv* kv, int layer, const float* q_dev, void* q_ou
                          const int32_t* positions_dev, const int32_t* seq_ids_dev,
                          const int32_t* block_tables_dev, int max_blocks_per_seq, void* stream) {
     INGOT_REQUIRE(kv != nullptr, "ingot_rope_kv_append: kv is null");
+    INGOT_REQUIRE_DEVICE(kv);
     INGOT_REQUIRE(layer >= 0 && layer < kv->n_layer, "ingot_rope_kv_append: layer out of range");
     INGOT_REQUIRE(n_tok >= 0, "ingot_rope_kv_append: n_tok < 0");
     if (n_tok == 0) return INGOT_OK;
@@ -153,6 +158,7 @@ int ingot_rope_kv_append(ingot_kv* kv, int layer, const float* q_dev, void* q_ou
 int ingot_kv_import_f16(ingot_kv* kv, int layer, const void* k_f16_dev, const void* v_f16_dev, int pos0,
                         int n_tok, const int32_t* block_table_dev, void* stream) {
     INGOT_REQUIRE(kv != nullptr, "ingot_kv_import_f16: kv is null");
+    INGOT_REQUIRE_DEVICE(kv);
     INGOT_REQUIRE(layer >= 0 && layer < kv->n_layer, "ingot_kv_import_f16: layer out of range");
     INGOT_REQUIRE(n_tok >= 0 && pos0 >= 0, "ingot_kv_import_f16: negative range");
     if (n_tok == 0) return INGOT_OK;
@@ -165,23 +171,41 @@ int ingot_kv_import_f16(ingot_kv* kv, int layer, const void* k_f16_dev, const vo
                                 pos0, n_tok, block_table_dev, static_cast<cudaStream_t>(stream));
 }
 
-static int ensure_decode_scratch(ingot_kv* kv, size_t floats) {
-    if (floats <= kv->part_floats) return INGOT_OK;
-    // Growing the scratch frees the old one: wait for kernels that may still read it.
-    INGOT_CUDA_TRY(cudaDeviceSynchronize());
-    cudaFree(kv->part);
-    kv->part = nullptr;
-    kv->part_floats = 0;
-    INGOT_CUDA_TRY(cudaMalloc(&kv->part, 2 * kDecodeStreams * floats * sizeof(float)));
+// Makes sure the handle owns `bufs` scratch buffers of `floats` floats each (plus their arrival counters).
+// Growing allocates, so the first call with a larger shape must not happen under stream capture; buffers that
+// are outgrown stay allocated until the handle is destroyed (a graph captured earlier may point into them).
+static int ensure_decode_scratch(ingot_kv* kv, size_t floats, int bufs) {
+    if (floats <= kv->part_floats && bufs <= kv->part_bufs) return INGOT_OK;
+    floats = std::max(floats, kv->part_floats);
+    bufs = std::max(bufs, kv->part_bufs);
+    float* part = nullptr;
+    int* sync = nullptr;
+    const size_t sync_ints = size_t(bufs) * kv->max_seqs * kv->n_head_kv * 2;
+    INGOT_CUDA_TRY(cudaMalloc(&part, size_t(bufs) * floats * sizeof(float)));
+    cudaError_t e = cudaMalloc(&sync, sync_ints * sizeof(int));
+    if (e == cudaSuccess) e = cudaMemset(sync, 0, sync_ints * sizeof(int));
+    if (e == cudaSuccess) e = cudaDeviceSynchronize();  // the counters are zero before any stream can use them
+    if (e != cudaSuccess) {
+        cudaFree(part);
+        cudaFree(sync);
+        return ingot_cuda_fail(e, "decode scratch");
+    }
+    if (kv->part) kv->retired.push_back(kv->part);
+    if (kv->part_sync) kv->retired.push_back(kv->part_sync);
+    kv->part = part;
+    kv->part_sync = sync;
     kv->part_floats = floats;
+    kv->part_bufs = bufs;
+    kv->host_key[0] = -1;  // the host-buffer call's captured graph points into the old scratch
     return INGOT_OK;
 }
 
-// Argument checks shared by the decode entry points; also sizes the split scratch.
+// Argument checks shared by the decode entry points.
 static int decode_checked(ingot_kv* kv, int layer, const void* q_dev, int q_dtype, void* out_dev, int out_dtype,
                           int n_head, int n_seq, const int32_t* seq_lens_dev, int max_seq_len,
                           const int32_t* block_tables_dev, int max_blocks_per_seq, int chunk_keys) {
     INGOT_REQUIRE(kv != nullptr, "ingot_attn_decode: kv is null");
+    INGOT_REQUIRE_DEVICE(kv);
     INGOT_REQUIRE(layer >= 0 && layer < kv->n_layer, "ingot_attn_decode: layer out of range");
     INGOT_REQUIRE(q_dev && out_dev, "ingot_attn_decode: null q/out");
     INGOT_REQUIRE(n_seq >= 1 && n_seq <= kv->max_seqs, "ingot_attn_decode: n_seq exceeds max_seqs of the cache");
@@ -201,8 +225,7 @@ static int decode_checked(ingot_kv* kv, int layer, const void* q_dev, int q_dtyp
         INGOT_REQUIRE(block_tables_dev != nullptr && max_blocks_per_seq >= 1, "ingot_attn_decode: paged cache needs block tables");
         INGOT_REQUIRE((max_seq_len + kBlockTokens - 1) / kBlockTokens <= max_blocks_per_seq, "ingot_attn_decode: max_seq_len exceeds the block table");
     }
-    const size_t need = decode_part_floats(n_seq, max_seq_len, n_head);
-    return ensure_decode_scratch(kv, need);
+    return INGOT_OK;
 }
 
 int ingot_attn_decode(ingot_kv* kv, int layer, const void* q_dev, int q_dtype, void* out_dev, int out_dtype,
@@ -211,14 +234,13 @@ int ingot_attn_decode(ingot_kv* kv, int layer, const void* q_dev, int q_dtype, v
     int rc = decode_checked(kv, layer, q_dev, q_dtype, out_dev, out_dtype, n_head, n_seq, seq_lens_dev, max_seq_len,
                             block_tables_dev, max_blocks_per_seq, chunk_keys);
     if (rc != INGOT_OK) return rc;
-    cudaStream_t s = static_cast<cudaStream_t>(stream);
-    int used = 0;
-    // Splits into scratch buffer 0, then a merge-only launch (skipped when one split covers everything).
-    rc = launch_attn_decode(kv, layer, q_dev, q_dtype, out_dev, out_dtype, n_head, n_seq, seq_lens_dev, max_seq_len,
-                            block_tables_dev, max_blocks_per_seq, chunk_keys, kv->part, nullptr, nullptr, 0, 1, &used, s);
+    // One launch: the splits, and the merge by whichever split CTA of a (sequence, kv head) finishes last.
+    const DecodePlan plan = decode_plan(kv, n_seq, max_seq_len, chunk_keys, 1);
+    rc = ensure_decode_scratch(kv, decode_part_floats(n_seq, plan.n_parts, n_head), 1);
     if (rc != INGOT_OK) return rc;
-    return launch_attn_decode(kv, layer, nullptr, q_dtype, nullptr, out_dtype, n_head, n_seq, seq_lens_dev, max_seq_len,
-                              block_tables_dev, max_blocks_per_seq, used, nullptr, kv->part, out_dev, 0, 1, nullptr, s);
+    return launch_attn_decode(kv, layer, q_dev, q_dtype, out_dev, out_dtype, n_head, n_seq, seq_lens_dev, max_seq_len,
+                              block_tables_dev, max_blocks_per_seq, plan, kv->part, kv->part_sync, layer + 1, 0,
+                              static_cast<cudaStream_t>(stream));
 }
 
 int ingot_attn_decode_layers(ingot_kv* kv, int layer_begin, int layer_count, const void* q_dev, int q_dtype,
@@ -235,25 +257,25 @@ int ingot_attn_decode_layers(ingot_kv* kv, int layer_begin, int layer_count, con
     cudaStream_t user = static_cast<cudaStream_t>(stream);
     const size_t q_bytes = size_t(n_seq) * n_head * kHeadDim * (q_dtype == INGOT_F32 ? 4 : 2);
     const size_t o_bytes = size_t(n_seq) * n_head * kHeadDim * (out_dtype == INGOT_F32 ? 4 : 2);
-    // The layers are independent of one another, so they are dealt round-robin to a few side streams
-    // (forked from and joined back into the caller's stream with events; this is capturable in a CUDA
-    // graph). Inside a stream, launch i carries the splits of one layer (partials into one of the
-    // stream's two scratch buffers) and the merge of the stream's previous layer (from the other
-    // buffer); a last launch merges the final layer. From a stream's second launch on, the K/V loads
-    // start while the previous launch is still finishing (programmatic dependent launch); a split CTA
-    // waits for the preceding launch only before it writes its partial, which also makes reusing the
-    // two scratch buffers safe. Several chains keep the per-launch completion latency off the
-    // critical path.
-    static const int streams_cfg = [] {
-        const char* e = getenv("INGOT_DECODE_STREAMS");  // tuning knob, read once
-        const int v = e ? atoi(e) : kDecodeStreams;
-        return std::min(std::max(v, 1), kDecodeStreams);
-    }();
+    // The layers are independent of one another. Every layer is one self-contained launch (splits + in-kernel
+    // merge) that neither reads nor writes anything another layer's launch touches, except the split scratch;
+    // so the launches are chained with programmatic dependent launch and never wait for one another: a
+    // launch starts as soon as the one before it is resident, and its K/V loads overlap the tail of that
+    // launch. They are dealt round-robin to a few side streams (forked from and joined back into the caller's
+    // stream with events; capturable in a CUDA graph), which lets the block scheduler interleave launches
+    // freely. A chain alternates between two scratch buffers; the kernel's owner word makes the (never
+    // observed) case of a launch catching up with the launch two before it wait instead of overwrite.
+    // The first launch of every chain waits for the work before it in the stream (the fork event).
+    int streams_cfg = kDecodeStreams;
+    if (const char* e = getenv("INGOT_DECODE_STREAMS")) streams_cfg = std::min(std::max(atoi(e), 1), kDecodeStreams);
     // as many chains as allowed, then as few as give the same number of rounds: 28 layers on up to 8 chains are
     // 4 rounds, which 7 chains do evenly
     const int max_streams = std::min(streams_cfg, layer_count);
     const int want_rounds = (layer_count + max_streams - 1) / max_streams;
     const int n_streams = (layer_count + want_rounds - 1) / want_rounds;
+    const DecodePlan plan = decode_plan(kv, n_seq, max_seq_len, chunk_keys, n_streams);
+    rc = ensure_decode_scratch(kv, decode_part_floats(n_seq, plan.n_parts, n_head), 2 * n_streams);
+    if (rc != INGOT_OK) return rc;
     if (!kv->fork_event) INGOT_CUDA_TRY(cudaEventCreateWithFlags(&kv->fork_event, cudaEventDisableTiming));
     for (int t = 0; t < n_streams; t++) {
         if (!kv->side_stream[t]) INGOT_CUDA_TRY(cudaStreamCreateWithFlags(&kv->side_stream[t], cudaStreamNonBlocking));
@@ -261,25 +283,18 @@ int ingot_attn_decode_layers(ingot_kv* kv, int layer_begin, int layer_count, con
     }
     INGOT_CUDA_TRY(cudaEventRecord(kv->fork_event, user));
     for (int t = 0; t < n_streams; t++) INGOT_CUDA_TRY(cudaStreamWaitEvent(kv->side_stream[t], kv->fork_event, 0));
-    int used = chunk_keys;
-    // rounds: round r launches, on stream t, the splits of layer r*n_streams + t and the merge of layer (r-1)*n_streams + t
+    const size_t sync_ints = size_t(kv->max_seqs) * kv->n_head_kv * 2;
     const int rounds = (layer_count + n_streams - 1) / n_streams;
-    for (int r = 0; r <= rounds; r++) {
+    for (int r = 0; r < rounds; r++) {
         for (int t = 0; t < n_streams; t++) {
-            const int li = r * n_streams + t;          // layer whose splits this launch carries
-            const int lm = (r - 1) * n_streams + t;    // layer whose partials this launch merges
-            const bool split = li < layer_count;
-            const bool merge = r > 0 && lm < layer_count;
-            if (!split && !merge) continue;
-            float* bufs = kv->part + size_t(2 * t) * kv->part_floats;
-            const void* q_i = split ? static_cast<const char*>(q_dev) + size_t(li) * q_bytes : nullptr;
-            void* out_i = split ? static_cast<char*>(out_dev) + size_t(li) * o_bytes : nullptr;
-            const float* merge_part = merge ? bufs + size_t((r - 1) & 1) * kv->part_floats : nullptr;
-            void* merge_out = merge ? static_cast<char*>(out_dev) + size_t(lm) * o_bytes : nullptr;
-            rc = launch_attn_decode(kv, layer_begin + (split ? li : lm), q_i, q_dtype, out_i, out_dtype, n_head, n_seq,
-                                    seq_lens_dev, max_seq_len, block_tables_dev, max_blocks_per_seq, used,
-                                    bufs + size_t(r & 1) * kv->part_floats, merge_part, merge_out, r > 0 ? 1 : 0, n_streams,
-                                    &used, kv->side_stream[t]);
+            const int li = r * n_streams + t;
+            if (li >= layer_count) continue;
+            const int buf = 2 * t + (r & 1);
+            rc = launch_attn_decode(kv, layer_begin + li, static_cast<const char*>(q_dev) + size_t(li) * q_bytes, q_dtype,
+                                    static_cast<char*>(out_dev) + size_t(li) * o_bytes, out_dtype, n_head, n_seq, seq_lens_dev,
+                                    max_seq_len, block_tables_dev, max_blocks_per_seq, plan,
+                                    kv->part + size_t(buf) * kv->part_floats, kv->part_sync + size_t(buf) * sync_ints,
+                                    layer_begin + li + 1, r > 0 ? 1 : 0, kv->side_stream[t]);
             if (rc != INGOT_OK) return rc;
         }
     }
@@ -293,6 +308,7 @@ int ingot_attn_decode_layers(ingot_kv* kv, int layer_begin, int layer_count, con
 int ingot_attn_prefill(ingot_kv* kv, int layer, const void* q_dev, int q_dtype, void* out_dev, int out_dtype,
                        int n_head, int q_pos0, int n_tok, const int32_t* block_table_dev, int impl, void* stream) {
     INGOT_REQUIRE(kv != nullptr, "ingot_attn_prefill: kv is null");
+    INGOT_REQUIRE_DEVICE(kv);
     INGOT_REQUIRE(layer >= 0 && layer < kv->n_layer, "ingot_attn_prefill: layer out of range");
     INGOT_REQUIRE(n_tok >= 0 && q_pos0 >= 0, "ingot_attn_prefill: negative range");
     if (n_tok == 0) return INGOT_OK;
@@ -324,6 +340,7 @@ int ingot_attn_prefill_gather(ingot_kv* kv, int layer, const void* q_dev, int q_
                               int out_dtype, int n_head, int out_n_head, int out_head0, int q_pos0, int n_tok,
                               void* stream) {
     INGOT_REQUIRE(kv != nullptr, "ingot_attn_prefill_gather: kv is null");
+    INGOT_REQUIRE_DEVICE(kv);
     INGOT_REQUIRE(layer >= 0 && layer < kv->n_layer, "ingot_attn_prefill_gather: layer out of range");
     INGOT_REQUIRE(n_tok >= 0 && q_pos0 >= 0, "ingot_attn_prefill_gather: negative range");
     if (n_tok == 0) return INGOT_OK;
@@ -345,6 +362,7 @@ int ingot_attn_layers_host(ingot_kv* kv, int layer_begin, int layer_count, const
                            const float* v_host, float* out_host, const float* inv_freq_dev, int n_head, int pos0,
                            int n_tok, void* stream) {
     INGOT_REQUIRE(kv != nullptr, "ingot_attn_layers_host: kv is null");
+    INGOT_REQUIRE_DEVICE(kv);
     INGOT_REQUIRE(kv->layout == INGOT_KV_CONTIGUOUS, "ingot_attn_layers_host: contiguous cache only");
     INGOT_REQUIRE(layer_begin >= 0 && layer_count >= 0 && layer_begin + layer_count <= kv->n_layer,
                   "ingot_attn_layers_host: layer range out of bounds");

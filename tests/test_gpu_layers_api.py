@@ -187,3 +187,71 @@ def test_decode_layers_paged_batch_of_uneven_lengths():
     ib.attn_decode_layers(kv, 0, qd, out, seq_lens=lens_d, max_seq_len=int(lens.max()), block_tables=bt)
     torch.cuda.synchronize()
     assert torch.equal(out, first) and kv.status() == 0
+
+
+@pytest.mark.parametrize("streams", [None, "1"])
+def test_decode_28_layers_4096_keys_replayed_from_a_graph(streams, monkeypatch):
+    """The call the benchmark times: 28 layers x 4096 keys through ingot_attn_decode_layers, captured once into a
+    CUDA graph and replayed. Every layer of the replay must match the reference, a second replay must give the
+    same bits, and the same holds when all layers share one launch chain."""
+    import torch
+    import ingot_b200 as ib
+    if streams is not None:
+        monkeypatch.setenv("INGOT_DECODE_STREAMS", streams)
+    n_layers, n_keys = W.N_LAYER, 4096
+    rng = np.random.default_rng(2024)
+    kv = ib.KVCache(ib.KV_CONTIGUOUS, n_layers, HKV, n_keys)
+    ks, vs = _fill_layers(kv, n_layers, n_keys, rng)
+    q = rng.standard_normal((n_layers, 1, H, D), dtype=np.float32)
+    qd = helpers.to_dev(q)
+    out = torch.zeros(n_layers, 1, H, D, device="cuda")
+    ib.attn_decode_layers(kv, 0, qd, out, max_seq_len=n_keys)  # eager first: sizes the split scratch
+    torch.cuda.synchronize()
+    eager = out.clone()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        ib.attn_decode_layers(kv, 0, qd, out, max_seq_len=n_keys)
+    out.zero_()
+    g.replay()
+    torch.cuda.synchronize()
+    first = out.clone()
+    for l in range(n_layers):
+        wl = W.Decode(q[l], [ks[l]], [vs[l]], np.array([n_keys], dtype=np.int32))
+        helpers.assert_parity(first[l].cpu().numpy(), helpers.oracle_decode(wl), f"graph-replayed decode, layer {l}")
+    assert torch.equal(first, eager)
+    for _ in range(20):  # back-to-back replays overlap their tails: the scratch hand-over must hold
+        g.replay()
+    out.zero_()
+    g.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(out, first) and kv.status() == 0
+
+
+def test_decode_scratch_follows_the_split_count():
+    """A handle grows its split scratch to what the calls need (a graph captured before a growth keeps
+    working, because outgrown buffers stay alive until the handle is destroyed)."""
+    import torch
+    import ingot_b200 as ib
+    rng = np.random.default_rng(8)
+    kv = ib.KVCache(ib.KV_CONTIGUOUS, 2, HKV, 4096)
+    ks, vs = _fill_layers(kv, 2, 4096, rng)
+    q = rng.standard_normal((2, 1, H, D), dtype=np.float32)
+    qd = helpers.to_dev(q)
+    small = torch.zeros(1, H, D, device="cuda")
+    ib.attn_decode(kv, 0, qd[0], out=small, max_seq_len=300, chunk_keys=64)  # few splits
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        ib.attn_decode(kv, 0, qd[0], out=small, max_seq_len=300, chunk_keys=64)
+    big = torch.zeros(2, 1, H, D, device="cuda")
+    ib.attn_decode_layers(kv, 0, qd, big, max_seq_len=4096, chunk_keys=64)  # 64 splits, two chains: the scratch grows
+    torch.cuda.synchronize()
+    for l in range(2):
+        wl = W.Decode(q[l], [ks[l]], [vs[l]], np.array([4096], dtype=np.int32))
+        helpers.assert_parity(big[l].cpu().numpy(), helpers.oracle_decode(wl), f"after growth, layer {l}")
+    small.zero_()
+    g.replay()
+    torch.cuda.synchronize()
+    wl = W.Decode(q[0], [ks[0][:300]], [vs[0][:300]], np.array([300], dtype=np.int32))
+    helpers.assert_parity(small.cpu().numpy(), helpers.oracle_decode(wl), "graph captured before the growth")
+    assert kv.status() == 0
