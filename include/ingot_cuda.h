@@ -69,6 +69,11 @@ void* ingot_kv_v_dev(ingot_kv* kv, int layer);
 size_t ingot_kv_layer_bytes(const ingot_kv* kv);
 /* Reads and clears the device status word (0 = no kernel reported a problem). Synchronises `stream`. */
 int ingot_kv_status(ingot_kv* kv, void* stream, int* status_out);
+/* TEST HOOK (no reference counterpart): with stall_ms > 0 the tcgen05 prefill kernel launched for this handle
+ * issues no K/V copies and bounds its waits at stall_ms milliseconds, so that every wait runs out, the kernel
+ * returns normally and status bit 4 is raised; 0 restores normal operation. Lets a test exercise the
+ * bounded-wait exit without hanging or faulting anything. */
+int ingot_kv_test_stall_prefill(ingot_kv* kv, int stall_ms);
 
 /* ---- K1: fused RoPE + K/V append -------------------------------------------------------------
  * Replaces ops::rope on q and k plus the cache memcpy (src/ops.cpp:243-255,
@@ -166,6 +171,23 @@ int ingot_attn_prefill_gather(ingot_kv* kv, int layer, const void* q_dev, int q_
                               int out_dtype, int n_head, int out_n_head, int out_head0, int q_pos0, int n_tok,
                               void* stream);
 
+/* The same with completion signalling, so that no collective is needed as the cross-GPU barrier. Each GPU owns an
+ * array of 32-bit counters, zero-initialised, one per source GPU, mapped into every peer (symmetric memory).
+ * signal_ptrs[i] is the counter array that lives beside out_ptrs[i]; src_index is this GPU's slot in those arrays.
+ * When the last CTA of this call's grid has finished - all stores to all destinations issued and fenced at
+ * system scope - it adds 1 to counter src_index of every destination (red.release.sys). The consumer side is
+ * ingot_gather_wait on the destination GPU: a one-CTA kernel on `stream` that waits until each of its n_src
+ * counters is non-zero, takes the signal back off (so the counters need no reset between calls) and returns;
+ * work queued behind it on the stream then sees every source's rows. The wait is bounded by timeout_ms: a source
+ * that never signals raises status bit 4 (read it with ingot_kv_status) instead of hanging the GPU.
+ * The destination buffers of call n+1 must not be reused before the consumers of call n are done with them
+ * (alternate two buffers, or order the calls otherwise): the signal only says "written", not "read".
+ * No counterpart in the reference. tcgen05 kernel, contiguous caches only. */
+int ingot_attn_prefill_gather_signal(ingot_kv* kv, int layer, const void* q_dev, int q_dtype, void* const* out_ptrs,
+                                     void* const* signal_ptrs, int n_out, int src_index, int out_dtype, int n_head,
+                                     int out_n_head, int out_head0, int q_pos0, int n_tok, void* stream);
+int ingot_gather_wait(ingot_kv* kv, void* counters_dev, int n_src, int timeout_ms, void* stream);
+
 /* ---- Host-buffer convenience call ---------------------------------------------------------------
  * One layer of the reference's attention stage with HOST inputs/outputs, as a CPU-side caller sees
  * it (q,k,v from the projections in; attention output for the wo projection out):
@@ -183,6 +205,14 @@ int ingot_attn_layers_host(ingot_kv* kv, int layer_begin, int layer_count, const
                            const float* v_host, float* out_host, const float* inv_freq_dev, int n_head, int pos0,
                            int n_tok, void* stream);
 int ingot_stream_sync(void* stream);
+
+/* ---- Diagnostics ----------------------------------------------------------------------------------
+ * HBM read-bandwidth probe: what the reference's `bwtest` verb measures (src/main.cpp:450-455,
+ * MetalBackend::bandwidth_test src/metal_backend.mm:533-592 with the bw_fill / bw_sum kernels,
+ * shaders/kernels.metal:949-991). Allocates `bytes` on the current device, fills them, then times a kernel
+ * that only reads them with 16-byte streaming loads, `reps` times; *best_seconds receives the fastest pass
+ * (bandwidth = bytes / *best_seconds). Synchronous. Sizes beyond the L2 (126 MB) measure HBM. */
+int ingot_hbm_read_probe(size_t bytes, int reps, double* best_seconds, void* stream);
 
 #ifdef __cplusplus
 }

@@ -17,7 +17,9 @@
 // This file also defines make_metal_backend and the four metal_* diagnostics, so that the reference's
 // engine.cpp / main.cpp link against this backend without a source edit.
 #include "cuda_backend.h"
+#include "batched_backend.h"
 
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
 #include <chrono>
@@ -41,6 +43,17 @@ cudaError_t ingot_support_linear(float* out, const void* w, int w_is_f16, const 
                                  int accumulate, cudaStream_t s);
 cudaError_t ingot_support_gemv_group(float* const* outs, const void* const* ws, const int* n_out, int n_mat, int swiglu, const float* x,
                                      const float* norm_w, float eps, int n_in, int accumulate, cudaStream_t s);
+cudaError_t ingot_support_embed_rows(float* out, const void* table, int is_f16, int n_in, int n_rows_table, const int32_t* rows_dev,
+                                     int n_rows, int* status_dev, cudaStream_t s);
+// GGUF block-quantised weights (quant_kernels.cu); `type` is the ggml type code (gguf::TensorType)
+int ingot_quant_supported(int type, int n_in);
+size_t ingot_quant_planar_bytes(int type, int n_in, int n_out);
+cudaError_t ingot_quant_repack(void* planar_dev, const void* raw_dev, int type, int n_in, int n_out, cudaStream_t s);
+cudaError_t ingot_quant_dequant_rows(float* out, const void* planar_dev, int type, int n_in, int n_out, const int32_t* rows_dev, int n_rows,
+                                     int* status_dev, cudaStream_t s);
+cudaError_t ingot_quant_dequant_hilo(void* hi_f16, void* lo_f16, const void* planar_dev, int type, int n_in, int n_out, cudaStream_t s);
+cudaError_t ingot_quant_bf16_to_f32(float* out, const void* in_bf16, size_t n, cudaStream_t s);
+cudaError_t ingot_quant_gemv(float* out, const void* planar_dev, int type, const float* x, int n_in, int n_out, int accumulate, cudaStream_t s);
 // tensor-core form of the batched projections (linear_sm100.cu)
 struct ingot_linear_ws;
 cudaError_t ingot_linear_ws_create(ingot_linear_ws** out, int max_tok, int max_in);
@@ -67,14 +80,62 @@ void ingot_check(int rc) {
 }
 
 struct DevWeight {
-    void* data = nullptr;
+    void* data = nullptr;  // f32 / f16 rows, or the repacked planes of a block-quantised matrix (quant_kernels.cu)
     int is_f16 = 0;
+    int qtype = -1;        // ggml type code of a block-quantised matrix (Q8_0, Q4_0, Q4_1, Q6_K), else -1
     int n_in = 0, n_out = 0;
 };
 
-class CudaBackend : public Backend {
+// Streams weights from the memory-mapped model file to the device through a small ring of pinned staging buffers:
+// the CPU copy of chunk i+1 out of the page cache (where the page faults and disk reads happen) overlaps the DMA
+// of chunk i, and no call blocks on a pageable copy. The Metal backend wraps the mmap without copying
+// (src/metal_backend.mm:213-246); a discrete GPU has to move the bytes once, so they move as a stream.
+class WeightStreamer {
 public:
-    CudaBackend(const Model& m, int n_ctx, int n_batch) : m_(m), n_ctx_(n_ctx), n_batch_(n_batch) {
+    WeightStreamer() {
+        cuda_check(cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking), "cudaStreamCreate(load)");
+        for (int i = 0; i < kBufs; i++) {
+            cuda_check(cudaMallocHost(&buf_[i], kChunk), "cudaMallocHost(load staging)");
+            cuda_check(cudaEventCreateWithFlags(&done_[i], cudaEventDisableTiming), "cudaEventCreate");
+        }
+    }
+    ~WeightStreamer() {
+        cudaStreamSynchronize(stream_);
+        for (int i = 0; i < kBufs; i++) { cudaFreeHost(buf_[i]); cudaEventDestroy(done_[i]); }
+        cudaStreamDestroy(stream_);
+    }
+    void copy(void* dst_dev, const void* src_host, size_t bytes) {
+        const char* src = static_cast<const char*>(src_host);
+        char* dst = static_cast<char*>(dst_dev);
+        for (size_t off = 0; off < bytes; off += kChunk) {
+            const size_t n = std::min(kChunk, bytes - off);
+            const int b = next_++ % kBufs;
+            cuda_check(cudaEventSynchronize(done_[b]), "load staging");  // the DMA that last read this buffer is over
+            memcpy(buf_[b], src + off, n);
+            cuda_check(cudaMemcpyAsync(dst + off, buf_[b], n, cudaMemcpyHostToDevice, stream_), "cudaMemcpyAsync(weight)");
+            cuda_check(cudaEventRecord(done_[b], stream_), "cudaEventRecord");
+            bytes_ += n;
+        }
+    }
+    cudaStream_t stream() const { return stream_; }
+    void finish() { cuda_check(cudaStreamSynchronize(stream_), "weight upload"); }
+    size_t bytes() const { return bytes_; }
+
+private:
+    static constexpr int kBufs = 4;
+    static constexpr size_t kChunk = size_t(32) << 20;
+    cudaStream_t stream_ = nullptr;
+    void* buf_[kBufs] = {};
+    cudaEvent_t done_[kBufs] = {};
+    unsigned next_ = 0;
+    size_t bytes_ = 0;
+};
+
+class CudaBackend : public Backend, public BatchedBackend {
+public:
+    // max_seqs > 0 builds the batched form: a paged cache for max_seqs sequences of n_ctx positions each, and n_batch
+    // (the most tokens per call) equal to max_seqs.
+    CudaBackend(const Model& m, int n_ctx, int n_batch, int max_seqs = 0) : m_(m), n_ctx_(n_ctx), n_batch_(n_batch), max_seqs_(max_seqs) {
         const Config& c = m.cfg;
         if (n_batch < 1) throw std::runtime_error("cuda: --batch must be at least 1");
         if (c.head_dim != INGOT_HEAD_DIM) throw std::runtime_error("cuda: head_dim must be 128");
@@ -86,8 +147,21 @@ public:
             cuda_check(cudaEventCreate(&ev0_), "cudaEventCreate");
             cuda_check(cudaEventCreate(&ev1_), "cudaEventCreate");
         }
-        ingot_check(ingot_kv_create(&kv_, INGOT_KV_CONTIGUOUS, c.n_layer, c.n_head_kv, c.head_dim, n_ctx, 1));
+        if (max_seqs_ > 0) {
+            blocks_per_seq_ = (n_ctx + INGOT_BLOCK_TOKENS - 1) / INGOT_BLOCK_TOKENS;
+            const int n_blocks = blocks_per_seq_ * max_seqs_;
+            ingot_check(ingot_kv_create(&kv_, INGOT_KV_PAGED, c.n_layer, c.n_head_kv, c.head_dim, n_blocks, max_seqs_));
+            block_table_.assign(size_t(max_seqs_) * blocks_per_seq_, -1);
+            // Blocks are handed out in arrival order, so the sequences' blocks interleave in the pool.
+            for (int b = n_blocks - 1; b >= 0; b--) free_blocks_.push_back(b);
+        } else {
+            ingot_check(ingot_kv_create(&kv_, INGOT_KV_CONTIGUOUS, c.n_layer, c.n_head_kv, c.head_dim, n_ctx, 1));
+        }
 
+        // Weights: streamed to the device once (see WeightStreamer); block-quantised matrices are repacked there.
+        const auto load0 = std::chrono::steady_clock::now();
+        WeightStreamer loader;
+        loader_ = &loader;
         layers_.resize(c.n_layer);
         for (int l = 0; l < c.n_layer; l++) {
             const Layer& L = m.layers[l];
@@ -99,22 +173,49 @@ public:
         }
         output_norm_ = upload_f32(m.output_norm);
         output_ = upload(*m.output);
+        // The embedding table lives on the device too (rows are gathered / dequantised by a kernel); a model with
+        // tied embeddings shares the output matrix.
+        embd_ = m.tok_embd == m.output ? output_ : upload(*m.tok_embd);
         inv_freq_ = upload_f32(m.rope_inv_freq);
+        loader.finish();
+        loader_ = nullptr;
+        if (raw_tmp_) { cudaFree(raw_tmp_); raw_tmp_ = nullptr; raw_tmp_bytes_ = 0; }
+        if (profile_)
+            fprintf(stderr, "cuda: %.2f GB of weights on the device in %.2f s\n", loader.bytes() / 1e9,
+                    std::chrono::duration<double>(std::chrono::steady_clock::now() - load0).count());
 
+        if (max_quant_elems_ > 0 && n_batch > 1) {
+            quant_scratch_elems_ = max_quant_elems_;
+            cuda_check(cudaMalloc(&quant_scratch_, 2 * quant_scratch_elems_ * sizeof(__half)), "cudaMalloc(dequantisation scratch)");
+            allocs_.push_back(quant_scratch_);
+        }
         const size_t nb = size_t(n_batch);
         const size_t q_dim = size_t(c.n_head) * c.head_dim, kv_dim = size_t(c.n_head_kv) * c.head_dim;
         x_ = alloc_f32(nb * c.n_embd); h_ = alloc_f32(nb * c.n_embd);
         q_ = alloc_f32(nb * q_dim); attn_ = alloc_f32(nb * q_dim);
         k_ = alloc_f32(nb * kv_dim); v_ = alloc_f32(nb * kv_dim);
         gate_ = alloc_f32(nb * c.n_ff); up_ = alloc_f32(nb * c.n_ff);
-        logits_dev_ = alloc_f32(size_t(c.n_vocab));
+        if (max_seqs_ == 0) logits_dev_ = alloc_f32(size_t(c.n_vocab));
         cuda_check(cudaMalloc(&q_rot_, nb * q_dim * 2), "cudaMalloc(q_rot)");
         allocs_.push_back(q_rot_);
         cuda_check(cudaMalloc(&pos_dev_, 2 * sizeof(int32_t)), "cudaMalloc(pos)");
         allocs_.push_back(pos_dev_);
         cuda_check(cudaMallocHost(&pos_host_, 2 * sizeof(int32_t)), "cudaMallocHost(pos)");
-        cuda_check(cudaMallocHost(&x_host_, nb * c.n_embd * sizeof(float)), "cudaMallocHost(x)");
-        cuda_check(cudaMallocHost(&logits_, size_t(c.n_vocab) * sizeof(float)), "cudaMallocHost(logits)");
+        cuda_check(cudaMalloc(&tok_dev_, nb * sizeof(int32_t)), "cudaMalloc(tokens)");
+        allocs_.push_back(tok_dev_);
+        cuda_check(cudaMalloc(&embd_status_, sizeof(int)), "cudaMalloc(status)");
+        allocs_.push_back(embd_status_);
+        cuda_check(cudaMemset(embd_status_, 0, sizeof(int)), "cudaMemset");
+        cuda_check(cudaMallocHost(&tok_host_, nb * sizeof(int32_t)), "cudaMallocHost(tokens)");
+        const size_t logit_rows = max_seqs_ > 0 ? size_t(max_seqs_) : 1;
+        if (max_seqs_ > 0) {
+            logits_dev_ = alloc_f32(logit_rows * c.n_vocab);  // one row per sequence of a step
+            const size_t meta = size_t(max_seqs_) * (3 + blocks_per_seq_);  // positions, key counts, row ids, block-table rows
+            cuda_check(cudaMalloc(&multi_dev_, meta * sizeof(int32_t)), "cudaMalloc(step tables)");
+            allocs_.push_back(multi_dev_);
+            cuda_check(cudaMallocHost(&multi_host_, meta * sizeof(int32_t)), "cudaMallocHost(step tables)");
+        }
+        cuda_check(cudaMallocHost(&logits_, logit_rows * c.n_vocab * sizeof(float)), "cudaMallocHost(logits)");
         // INGOT_LINEAR_TC=0 keeps the batched projections on the f32 FMA kernels (diagnostics).
         const char* tc = getenv("INGOT_LINEAR_TC");
         if (n_batch >= 16 && !(tc && atoi(tc) == 0))
@@ -136,7 +237,8 @@ public:
         if (decode_graph_) cudaGraphDestroy(decode_graph_);
         for (void* p : allocs_) cudaFree(p);
         cudaFreeHost(pos_host_);
-        cudaFreeHost(x_host_);
+        cudaFreeHost(tok_host_);
+        cudaFreeHost(multi_host_);
         cudaFreeHost(logits_);
         ingot_linear_ws_destroy(lin_ws_);
         ingot_kv_destroy(kv_);
@@ -147,17 +249,20 @@ public:
 
     const float* forward_batch(const int32_t* tokens, int n, int pos) override {
         const Config& c = m_.cfg;
+        if (max_seqs_ > 0) throw std::runtime_error("cuda: this backend was built for forward_multi");
         if (n < 1 || n > n_batch_) throw std::runtime_error("cuda: batch size out of range");
         if (pos < 0 || pos + n > n_ctx_) throw std::runtime_error("context window exceeded");
         for (int i = 0; i < n; i++)
             if (tokens[i] < 0 || tokens[i] >= c.n_vocab) throw std::runtime_error("token id out of range");
 
-        // Embedding rows are dequantised on the host straight into pinned memory, as the Metal
-        // backend does (src/metal_backend.mm:426-428).
+        // Token ids go to the device; the embedding rows are gathered (and dequantised) there by the first kernel of
+        // the pass. (The reference dequantises them on the host into the shared x buffer, src/cpu_backend.cpp:33,
+        // src/metal_backend.mm:426-428.)
         const auto wall0 = std::chrono::steady_clock::now();
-        for (int i = 0; i < n; i++) ops::dequant_row(*m_.tok_embd, size_t(tokens[i]), x_host_ + size_t(i) * c.n_embd);
+        // a previous call's copy out of tok_host_ is complete: every call ends with a stream synchronisation
+        for (int i = 0; i < n; i++) tok_host_[i] = tokens[i];
         if (profile_) cuda_check(cudaEventRecord(ev0_, stream_), "cudaEventRecord");
-        cuda_check(cudaMemcpyAsync(x_, x_host_, size_t(n) * c.n_embd * sizeof(float), cudaMemcpyHostToDevice, stream_), "H2D x");
+        cuda_check(cudaMemcpyAsync(tok_dev_, tok_host_, size_t(n) * sizeof(int32_t), cudaMemcpyHostToDevice, stream_), "H2D tokens");
 
         if (n == 1) {
             // Single-token steps read their position and key count from device memory, so that the whole
@@ -208,8 +313,14 @@ public:
 
     // Every layer plus the final norm and logits projection for n tokens at positions pos..pos+n-1, queued
     // on stream_. device_pos: single-token form whose position / key count are read from pos_dev_.
-    void encode_layers(int n, int pos, bool device_pos) {
+    // multi: the n tokens belong to n different sequences of the paged cache (forward_multi); positions, key counts,
+    // row ids and block-table rows were copied to multi_dev_, max_len bounds the key counts.
+    void encode_layers(int n, int pos, bool device_pos, bool multi = false, int max_len = 0) {
         const Config& c = m_.cfg;
+        if (embd_.qtype >= 0)
+            cuda_check(ingot_quant_dequant_rows(x_, embd_.data, embd_.qtype, embd_.n_in, embd_.n_out, tok_dev_, n, embd_status_, stream_), "embedding rows");
+        else
+            cuda_check(ingot_support_embed_rows(x_, embd_.data, embd_.is_f16, embd_.n_in, embd_.n_out, tok_dev_, n, embd_status_, stream_), "embedding rows");
         bool norm_prepared = false;  // tensor-core path: the previous layer's last kernel already normalised and split x
         for (int l = 0; l < c.n_layer; l++) {
             const DevLayer& D = layers_[l];
@@ -232,15 +343,26 @@ public:
                 cuda_check(ingot_support_rmsnorm(h_, x_, D.attn_norm, n, c.n_embd, c.rms_eps, stream_), "rmsnorm");
                 linear_group(qkv_out, qkv, 3, h_, n, false);
             }
-            ingot_check(ingot_rope_kv_append(kv_, l, q_, q_rot_, k_, v_, inv_freq_, c.n_head, pos, n,
-                                             device_pos ? pos_dev_ : nullptr, nullptr, nullptr, 0, stream_));
-            if (n == 1)
-                ingot_check(ingot_attn_decode(kv_, l, q_rot_, INGOT_F16, attn_, INGOT_F32, c.n_head, 1,
-                                              device_pos ? pos_dev_ + 1 : nullptr, device_pos ? n_ctx_ : pos + 1, nullptr, 0, 0,
-                                              stream_));
-            else
-                ingot_check(ingot_attn_prefill(kv_, l, q_rot_, INGOT_F16, attn_, INGOT_F32, c.n_head, pos, n, nullptr, 0,
-                                               stream_));
+            if (multi) {
+                const int32_t* positions = multi_dev_;
+                const int32_t* key_counts = multi_dev_ + max_seqs_;
+                const int32_t* row_ids = multi_dev_ + 2 * size_t(max_seqs_);
+                const int32_t* tables = multi_dev_ + 3 * size_t(max_seqs_);
+                ingot_check(ingot_rope_kv_append(kv_, l, q_, q_rot_, k_, v_, inv_freq_, c.n_head, 0, n, positions, row_ids, tables,
+                                                 blocks_per_seq_, stream_));
+                ingot_check(ingot_attn_decode(kv_, l, q_rot_, INGOT_F16, attn_, INGOT_F32, c.n_head, n, key_counts, max_len, tables,
+                                              blocks_per_seq_, 0, stream_));
+            } else {
+                ingot_check(ingot_rope_kv_append(kv_, l, q_, q_rot_, k_, v_, inv_freq_, c.n_head, pos, n,
+                                                 device_pos ? pos_dev_ : nullptr, nullptr, nullptr, 0, stream_));
+                if (n == 1)
+                    ingot_check(ingot_attn_decode(kv_, l, q_rot_, INGOT_F16, attn_, INGOT_F32, c.n_head, 1,
+                                                  device_pos ? pos_dev_ + 1 : nullptr, device_pos ? n_ctx_ : pos + 1, nullptr, 0, 0,
+                                                  stream_));
+                else
+                    ingot_check(ingot_attn_prefill(kv_, l, q_rot_, INGOT_F16, attn_, INGOT_F32, c.n_head, pos, n, nullptr, 0,
+                                                   stream_));
+            }
             const DevWeight* wo[1] = {&D.wo};
             if (fused) {
                 gemv_group(&x_, wo, 1, false, attn_, nullptr, true);
@@ -277,6 +399,13 @@ public:
             } else linear_group(&x_, wd, 1, gate_, n, true);
             if (!tc_layer) norm_prepared = false;
         }
+        if (multi) {  // logits for every row: each belongs to another sequence
+            cuda_check(ingot_support_rmsnorm(h_, x_, output_norm_, n, c.n_embd, c.rms_eps, stream_), "rmsnorm");
+            const DevWeight* wl[1] = {&output_};
+            if (n == 1) linear(logits_dev_, output_, h_, 1, false);
+            else linear_group(&logits_dev_, wl, 1, h_, n, false);
+            return;
+        }
         // Logits for the last token only.
         if (fuse_decode_ && streamable(output_)) {
             const DevWeight* wl[1] = {&output_};
@@ -286,6 +415,60 @@ public:
             linear(logits_dev_, output_, h_, 1, false);
         }
     }
+
+    // ---- BatchedBackend ----
+    const float* forward_multi(const int32_t* tokens, const int32_t* seq_ids, const int32_t* positions, int n) override {
+        const Config& c = m_.cfg;
+        if (max_seqs_ == 0) throw std::runtime_error("cuda: this backend was built for single-sequence calls");
+        if (n < 1 || n > max_seqs_) throw std::runtime_error("cuda: batch size out of range");
+        std::vector<char> seen(size_t(max_seqs_), 0);
+        int max_len = 1;
+        int32_t* pos_h = multi_host_;
+        int32_t* len_h = multi_host_ + max_seqs_;
+        int32_t* row_h = multi_host_ + 2 * size_t(max_seqs_);
+        int32_t* tab_h = multi_host_ + 3 * size_t(max_seqs_);
+        for (int i = 0; i < n; i++) {
+            if (tokens[i] < 0 || tokens[i] >= c.n_vocab) throw std::runtime_error("token id out of range");
+            if (seq_ids[i] < 0 || seq_ids[i] >= max_seqs_) throw std::runtime_error("cuda: sequence id out of range");
+            if (seen[seq_ids[i]]++) throw std::runtime_error("cuda: a sequence appears twice in one forward_multi call");
+            if (positions[i] < 0 || positions[i] >= n_ctx_) throw std::runtime_error("context window exceeded");
+        }
+        for (int i = 0; i < n; i++) {
+            // the block that holds this position is taken from the pool when the sequence first reaches it
+            int32_t* row = block_table_.data() + size_t(seq_ids[i]) * blocks_per_seq_;
+            const int blk = positions[i] / INGOT_BLOCK_TOKENS;
+            for (int b = 0; b <= blk; b++) {  // a sequence may start beyond position 0 only over blocks it owns
+                if (row[b] >= 0) continue;
+                if (free_blocks_.empty()) throw std::runtime_error("context window exceeded");
+                row[b] = free_blocks_.back();
+                free_blocks_.pop_back();
+            }
+            tok_host_[i] = tokens[i];
+            pos_h[i] = positions[i];
+            len_h[i] = positions[i] + 1;
+            row_h[i] = i;
+            std::copy(row, row + blocks_per_seq_, tab_h + size_t(i) * blocks_per_seq_);
+            max_len = std::max(max_len, positions[i] + 1);
+        }
+        cuda_check(cudaMemcpyAsync(tok_dev_, tok_host_, size_t(n) * sizeof(int32_t), cudaMemcpyHostToDevice, stream_), "H2D tokens");
+        cuda_check(cudaMemcpyAsync(multi_dev_, multi_host_, (3 * size_t(max_seqs_) + size_t(n) * blocks_per_seq_) * sizeof(int32_t),
+                                   cudaMemcpyHostToDevice, stream_), "H2D step tables");
+        encode_layers(n, 0, false, true, max_len);
+        cuda_check(cudaMemcpyAsync(logits_, logits_dev_, size_t(n) * c.n_vocab * sizeof(float), cudaMemcpyDeviceToHost, stream_), "D2H logits");
+        cuda_check(cudaStreamSynchronize(stream_), "forward_multi");
+        int status = 0;
+        ingot_check(ingot_kv_status(kv_, stream_, &status));
+        if (status != 0) throw std::runtime_error("cuda: attention kernel reported status " + std::to_string(status));
+        return logits_;
+    }
+    void release_sequence(int seq_id) override {
+        if (seq_id < 0 || seq_id >= max_seqs_) throw std::runtime_error("cuda: sequence id out of range");
+        int32_t* row = block_table_.data() + size_t(seq_id) * blocks_per_seq_;
+        for (int b = 0; b < blocks_per_seq_; b++)
+            if (row[b] >= 0) { free_blocks_.push_back(row[b]); row[b] = -1; }
+    }
+    int max_seqs() const override { return max_seqs_; }
+    int n_ctx_per_seq() const override { return n_ctx_; }
 
     int n_ctx() const override { return n_ctx_; }
     const char* name() const override { return "cuda"; }
@@ -307,25 +490,49 @@ private:
         cuda_check(cudaMemcpy(p, v.data(), v.size() * sizeof(float), cudaMemcpyHostToDevice), "cudaMemcpy");
         return p;
     }
-    // Weights are read from the mmap (src/gguf.h:56) and kept in their stored float type.
+    // Weights are read from the mmap (src/gguf.h:56). F16 and F32 matrices keep their stored type; BF16 is widened
+    // to F32 on the device (exact); Q8_0 / Q4_0 / Q4_1 / Q6_K keep their bits and are repacked into aligned planes
+    // on the device (quant_kernels.cu). The types are those ops::type_supported accepts (src/ops.cpp:186-192).
     DevWeight upload(const gguf::TensorInfo& t) {
         DevWeight w;
-        if (t.type == gguf::TensorType::F16) w.is_f16 = 1;
-        else if (t.type == gguf::TensorType::F32) w.is_f16 = 0;
-        else throw std::runtime_error(std::string("cuda: tensor ") + t.name + " has type " + gguf::type_name(t.type) +
-                                      "; this backend reads F16 and F32 weights");
         w.n_in = int(t.dim(0));
         w.n_out = int(t.dim(1));
+        const int type = int(uint32_t(t.type));
+        const bool quant = ingot_quant_supported(type, w.n_in) != 0;
+        if (t.type == gguf::TensorType::F16) w.is_f16 = 1;
+        else if (t.type == gguf::TensorType::F32 || t.type == gguf::TensorType::BF16) w.is_f16 = 0;
+        else if (quant) w.qtype = type;
+        else throw std::runtime_error(std::string("cuda: tensor ") + t.name + " has type " + gguf::type_name(t.type) +
+                                      ", which this backend does not read (row length " + std::to_string(w.n_in) + ")");
         if (w.n_in % 8 != 0) throw std::runtime_error("cuda: tensor " + t.name + " row length must be a multiple of 8");
+        if (quant || t.type == gguf::TensorType::BF16) {
+            // file bytes -> device staging -> converted on the device (in stream order behind the copy)
+            if (t.nbytes() > raw_tmp_bytes_) {
+                loader_->finish();  // a conversion may still be reading the old staging buffer
+                if (raw_tmp_) cudaFree(raw_tmp_);
+                raw_tmp_ = nullptr;
+                cuda_check(cudaMalloc(&raw_tmp_, t.nbytes()), "cudaMalloc(weight staging)");
+                raw_tmp_bytes_ = t.nbytes();
+            }
+            const size_t out_bytes = quant ? ingot_quant_planar_bytes(type, w.n_in, w.n_out) : size_t(w.n_in) * w.n_out * sizeof(float);
+            cuda_check(cudaMalloc(&w.data, out_bytes), "cudaMalloc(weight)");
+            allocs_.push_back(w.data);
+            loader_->copy(raw_tmp_, t.data, t.nbytes());
+            if (quant) cuda_check(ingot_quant_repack(w.data, raw_tmp_, type, w.n_in, w.n_out, loader_->stream()), "repack");
+            else cuda_check(ingot_quant_bf16_to_f32(static_cast<float*>(w.data), raw_tmp_, size_t(w.n_in) * w.n_out, loader_->stream()), "bf16 -> f32");
+            if (quant && w.n_in * size_t(w.n_out) > max_quant_elems_ && &t != m_.output && &t != m_.tok_embd) max_quant_elems_ = w.n_in * size_t(w.n_out);
+            return w;
+        }
         cuda_check(cudaMalloc(&w.data, t.nbytes()), "cudaMalloc(weight)");
         allocs_.push_back(w.data);
-        cuda_check(cudaMemcpy(w.data, t.data, t.nbytes(), cudaMemcpyHostToDevice), "cudaMemcpy(weight)");
+        loader_->copy(w.data, t.data, t.nbytes());
         return w;
     }
     bool tc_group(const DevWeight* const* ws, int count, int n_tok) const {
         bool tc = lin_ws_ != nullptr;
         for (int i = 0; i < count && tc; i++)
-            tc = ws[i]->n_in == ws[0]->n_in && ingot_linear_tc_supported(lin_ws_, ws[i]->is_f16, ws[i]->n_in, ws[i]->n_out, n_tok);
+            tc = ws[i]->n_in == ws[0]->n_in &&
+                 ingot_linear_tc_supported(lin_ws_, ws[i]->is_f16 || ws[i]->qtype >= 0, ws[i]->n_in, ws[i]->n_out, n_tok);
         return tc;
     }
     bool layer_tc_ok(const DevLayer& D, int n_tok) const {
@@ -345,10 +552,28 @@ private:
             return;
         }
         cuda_check(ingot_linear_tc_prepare(lin_ws_, x, ws[0]->n_in, n_tok, stream_), "linear (split)");
-        for (int i = 0; i < count; i++)
-            cuda_check(ingot_linear_tc_run(lin_ws_, outs[i], ws[i]->data, ws[i]->n_in, ws[i]->n_out, accumulate ? 1 : 0, stream_), "linear (tensor core)");
+        for (int i = 0; i < count; i++) {
+            const DevWeight& w = *ws[i];
+            if (w.qtype < 0) {
+                cuda_check(ingot_linear_tc_run(lin_ws_, outs[i], w.data, w.n_in, w.n_out, accumulate ? 1 : 0, stream_), "linear (tensor core)");
+                continue;
+            }
+            // Block-quantised matrix: expanded into two f16 planes hi + lo = w (exact), each a tensor-core GEMM into
+            // the same output. The planes are scratch, rebuilt per use: the weights stay quantised in HBM.
+            __half* hi = quant_scratch(size_t(w.n_in) * w.n_out);
+            __half* lo = hi + size_t(w.n_in) * w.n_out;
+            cuda_check(ingot_quant_dequant_hilo(hi, lo, w.data, w.qtype, w.n_in, w.n_out, stream_), "dequantise (hi/lo)");
+            cuda_check(ingot_linear_tc_run(lin_ws_, outs[i], hi, w.n_in, w.n_out, accumulate ? 1 : 0, stream_), "linear (tensor core, hi)");
+            cuda_check(ingot_linear_tc_run(lin_ws_, outs[i], lo, w.n_in, w.n_out, 1, stream_), "linear (tensor core, lo)");
+        }
     }
-    static bool streamable(const DevWeight& w) { return w.is_f16 && w.n_in % 256 == 0 && w.n_in <= 12288; }
+    // Scratch for the f16 hi/lo planes (or, for the f32 fallback, the f32 copy) of one block-quantised matrix: sized at
+    // construction for the largest layer matrix, so nothing is allocated inside a forward pass.
+    __half* quant_scratch(size_t elems) {
+        if (elems > quant_scratch_elems_) throw std::runtime_error("cuda: quantised matrix larger than the dequantisation scratch");
+        return static_cast<__half*>(quant_scratch_);
+    }
+    static bool streamable(const DevWeight& w) { return w.is_f16 && w.n_in % 256 == 0 && w.n_in <= 12032; }  // bound of ingot_support_gemv_group
     void gemv_group(float* const* outs, const DevWeight* const* ws, int count, bool swiglu, const float* x, const float* norm_w,
                     bool accumulate) {
         const void* wp[3] = {};
@@ -358,22 +583,45 @@ private:
                                             accumulate ? 1 : 0, stream_), "gemv");
     }
     void linear(float* out, const DevWeight& w, const float* x, int n_tok, bool accumulate) {
+        if (w.qtype >= 0) {
+            if (n_tok == 1) {  // dequantise-in-GEMV: reads the quantised bytes once
+                cuda_check(ingot_quant_gemv(out, w.data, w.qtype, x, w.n_in, w.n_out, accumulate ? 1 : 0, stream_), "gemv (quantised)");
+                return;
+            }
+            // few tokens (below the tensor-core kernel's minimum): f32 copy of the matrix, then the f32 kernels
+            float* wf = reinterpret_cast<float*>(quant_scratch(size_t(w.n_in) * w.n_out));
+            cuda_check(ingot_quant_dequant_rows(wf, w.data, w.qtype, w.n_in, w.n_out, nullptr, w.n_out, nullptr, stream_), "dequantise (f32)");
+            cuda_check(ingot_support_linear(out, wf, 0, x, w.n_in, w.n_out, n_tok, accumulate ? 1 : 0, stream_), "linear");
+            return;
+        }
         cuda_check(ingot_support_linear(out, w.data, w.is_f16, x, w.n_in, w.n_out, n_tok, accumulate ? 1 : 0, stream_), "linear");
     }
 
     const Model& m_;
     int n_ctx_, n_batch_;
+    int max_seqs_ = 0, blocks_per_seq_ = 0;       // batched form: paged cache shared by max_seqs_ sequences
+    std::vector<int32_t> block_table_;            // [max_seqs_][blocks_per_seq_], -1 = not allocated
+    std::vector<int32_t> free_blocks_;
+    int32_t *multi_dev_ = nullptr, *multi_host_ = nullptr;  // per step: positions, key counts, row ids [max_seqs_ each], block-table rows
     cudaStream_t stream_ = nullptr;
     ingot_kv* kv_ = nullptr;
     ingot_linear_ws* lin_ws_ = nullptr;
     std::vector<DevLayer> layers_;
     std::vector<void*> allocs_;
     float *output_norm_ = nullptr, *inv_freq_ = nullptr;
-    DevWeight output_;
+    DevWeight output_, embd_;
+    WeightStreamer* loader_ = nullptr;        // alive during construction only
+    void* raw_tmp_ = nullptr;                 // device staging for tensors that are converted on the device at load
+    size_t raw_tmp_bytes_ = 0;
+    size_t max_quant_elems_ = 0;              // largest block-quantised layer matrix
+    void* quant_scratch_ = nullptr;           // 2 x max_quant_elems_ f16 (= max_quant_elems_ f32)
+    size_t quant_scratch_elems_ = 0;
+    int32_t *tok_dev_ = nullptr, *tok_host_ = nullptr;
+    int* embd_status_ = nullptr;
     float *x_ = nullptr, *h_ = nullptr, *q_ = nullptr, *k_ = nullptr, *v_ = nullptr, *attn_ = nullptr, *gate_ = nullptr,
           *up_ = nullptr, *logits_dev_ = nullptr;
     void* q_rot_ = nullptr;
-    float *x_host_ = nullptr, *logits_ = nullptr;
+    float* logits_ = nullptr;
     int32_t* pos_dev_ = nullptr;   // [0] = position of the single-token step, [1] = its key count
     int32_t* pos_host_ = nullptr;  // pinned
     int decode_calls_ = 0;
@@ -393,6 +641,11 @@ std::unique_ptr<Backend> make_cuda_backend(const gguf::File&, const Model& model
     return std::make_unique<CudaBackend>(model, n_ctx, n_batch);
 }
 
+std::unique_ptr<BatchedBackend> make_cuda_batched_backend(const gguf::File&, const Model& model, int n_ctx_per_seq, int max_seqs) {
+    if (max_seqs < 1 || n_ctx_per_seq < 1) throw std::runtime_error("cuda: the batched backend needs at least one sequence and one position");
+    return std::make_unique<CudaBackend>(model, n_ctx_per_seq, max_seqs, max_seqs);
+}
+
 // Link seam: engine.cpp (src/engine.cpp:9-13) knows the GPU backend as "metal".
 std::unique_ptr<Backend> make_metal_backend(const gguf::File& file, const Model& model, int n_ctx, int n_batch) {
     return make_cuda_backend(file, model, n_ctx, n_batch);
@@ -405,8 +658,21 @@ double metal_linear_bench(const gguf::File&, const Model&, const std::string&, i
 void metal_linear_check(const gguf::File&, const Model&, const std::string&, int) {
     throw std::runtime_error("kcheck is not available on the cuda backend");
 }
-void metal_bandwidth_test(const gguf::File&, const Model&, size_t) {
-    throw std::runtime_error("bwtest is not available on the cuda backend");
+// `bwtest` (src/metal_backend.mm:533-592): read bandwidth over growing read sizes. The Metal version reads a
+// private buffer, the shared KV cache and the no-copy model file; a discrete GPU has one kind of device memory,
+// so there is one row, from sizes that fit the L2 up to `bytes` (sizes beyond the 126 MB L2 measure HBM).
+void metal_bandwidth_test(const gguf::File&, const Model&, size_t bytes) {
+    std::vector<size_t> sizes = {size_t(4e6), size_t(16e6), size_t(64e6), size_t(256e6)};
+    if (bytes > sizes.back()) sizes.push_back(bytes);
+    fprintf(stderr, "%-22s", "read size ->");
+    for (size_t n : sizes) fprintf(stderr, " %7zu MB", n / 1000000);
+    fprintf(stderr, "\n-- 16-byte streaming loads\n%-22s", "device memory");
+    for (size_t n : sizes) {
+        double secs = 0.0;
+        ingot_check(ingot_hbm_read_probe(n, 5, &secs, nullptr));
+        fprintf(stderr, " %5.0f GB/s", double(n / 16 * 16) / secs / 1e9);
+    }
+    fprintf(stderr, "\n");
 }
 
 // Seconds per token spent in decode attention across all layers at position pos

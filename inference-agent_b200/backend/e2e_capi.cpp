@@ -9,6 +9,7 @@
 #include <string>
 #include <vector>
 
+#include "batched_backend.h"
 #include "engine.h"
 #include "gguf.h"
 #include "model.h"
@@ -89,6 +90,51 @@ int ingot_e2e_bench(const char* gguf_path, const char* backend_name, const int32
         }
         out[0] = pp / reps;
         out[1] = tg / reps;
+        return 0;
+    } catch (const std::exception& e) {
+        g_err = e.what();
+        return -1;
+    }
+}
+
+// Greedy generation for n_seq sequences at once through BatchedBackend::forward_multi, the way a continuous-batching
+// loop would drive it: at every step each unfinished sequence contributes one token - the next token of its
+// prompt while it is still being prefilled, afterwards the token it generated last - so sequences of different
+// prompt lengths are at different phases in the same call. prompts holds the prompts back to back, prompt_lens
+// their lengths. out_ids receives n_gen tokens per sequence ([n_seq][n_gen]). Returns 0, or -1 with
+// ingot_e2e_last_error() set.
+int ingot_e2e_multi_greedy(const char* gguf_path, const int32_t* prompts, const int32_t* prompt_lens, int n_seq, int n_gen,
+                           int n_ctx_per_seq, int32_t* out_ids) {
+    try {
+        gguf::File f = gguf::File::open(gguf_path);
+        Model model = Model::load(f);
+        auto backend = make_cuda_batched_backend(f, model, n_ctx_per_seq, n_seq);
+        const int n_vocab = model.cfg.n_vocab;
+        std::vector<const int32_t*> prompt(n_seq);
+        std::vector<int> fed(n_seq, 0), made(n_seq, 0);   // tokens fed so far / generated so far
+        std::vector<int32_t> last(n_seq, 0);
+        for (int s = 0, off = 0; s < n_seq; off += prompt_lens[s], s++) prompt[s] = prompts + off;
+        std::vector<int32_t> tok, seq, pos;
+        for (;;) {
+            tok.clear(); seq.clear(); pos.clear();
+            for (int s = 0; s < n_seq; s++) {
+                if (made[s] >= n_gen) continue;
+                tok.push_back(fed[s] < prompt_lens[s] ? prompt[s][fed[s]] : last[s]);
+                seq.push_back(s);
+                pos.push_back(fed[s]);
+            }
+            if (tok.empty()) break;
+            const float* logits = backend->forward_multi(tok.data(), seq.data(), pos.data(), int(tok.size()));
+            for (size_t i = 0; i < tok.size(); i++) {
+                const int s = seq[i];
+                fed[s]++;
+                if (fed[s] < prompt_lens[s]) continue;  // still inside the prompt: these logits are not sampled
+                const float* row = logits + i * size_t(n_vocab);
+                last[s] = int32_t(std::max_element(row, row + n_vocab) - row);
+                out_ids[size_t(s) * n_gen + made[s]++] = last[s];
+                if (made[s] >= n_gen) backend->release_sequence(s);
+            }
+        }
         return 0;
     } catch (const std::exception& e) {
         g_err = e.what();

@@ -10,6 +10,10 @@
 #include <stdint.h>
 #include <stdlib.h>
 
+// Longest input row the weight-streaming GEMV stages in shared memory: n_in floats plus a few words of static
+// shared memory must stay inside the 48 KB a kernel gets without an opt-in.
+constexpr int kGemvMaxIn = 12032;
+
 namespace {
 
 __device__ __forceinline__ float warp_sum(float v) {
@@ -339,9 +343,36 @@ __global__ void __launch_bounds__(256) gemm_kernel(float* out, const W* w, const
     }
 }
 
+__device__ __forceinline__ float embed_to_f32(float v) { return v; }
+__device__ __forceinline__ float embed_to_f32(__half v) { return __half2float(v); }
+
+// Embedding gather: out[r][:] = table[rows[r]][:] widened to f32 (src/cpu_backend.cpp:33 does this with
+// ops::dequant_row on the host). A row index outside the table gives zeros and raises *status.
+template <typename W>
+__global__ void embed_rows_kernel(float* out, const W* __restrict__ table, int n_in, int n_rows_table, const int32_t* __restrict__ rows,
+                                  int* status) {
+    const int row = rows[blockIdx.x];
+    float* o = out + (size_t)blockIdx.x * n_in;
+    if (row < 0 || row >= n_rows_table) {
+        if (threadIdx.x == 0 && status) atomicOr(status, 1);
+        for (int i = threadIdx.x; i < n_in; i += blockDim.x) o[i] = 0.f;
+        return;
+    }
+    const W* src = table + (size_t)row * n_in;
+    for (int i = threadIdx.x; i < n_in; i += blockDim.x) o[i] = embed_to_f32(src[i]);
+}
+
 }  // namespace
 
 extern "C" {
+
+cudaError_t ingot_support_embed_rows(float* out, const void* table, int is_f16, int n_in, int n_rows_table, const int32_t* rows_dev,
+                                     int n_rows, int* status_dev, cudaStream_t s) {
+    if (n_rows < 1 || n_in < 1) return cudaErrorInvalidValue;
+    if (is_f16) embed_rows_kernel<__half><<<n_rows, 256, 0, s>>>(out, static_cast<const __half*>(table), n_in, n_rows_table, rows_dev, status_dev);
+    else embed_rows_kernel<float><<<n_rows, 256, 0, s>>>(out, static_cast<const float*>(table), n_in, n_rows_table, rows_dev, status_dev);
+    return cudaGetLastError();
+}
 
 cudaError_t ingot_support_rmsnorm(float* out, const float* x, const float* w, int n_rows, int n, float eps, cudaStream_t s) {
     rmsnorm_kernel<<<n_rows, 256, 0, s>>>(out, x, w, n, eps);
@@ -358,7 +389,7 @@ cudaError_t ingot_support_silu_mul(float* gate, const float* up, size_t n, cudaS
 // height (gate, up) and outs[0] receives silu(gate) * up. n_in must be a multiple of 256.
 cudaError_t ingot_support_gemv_group(float* const* outs, const void* const* ws, const int* n_out, int n_mat, int swiglu, const float* x,
                                      const float* norm_w, float eps, int n_in, int accumulate, cudaStream_t s) {
-    if (n_mat < 1 || n_mat > 3 || n_in % 256 != 0 || n_in > 12288 || (swiglu && (n_mat != 2 || n_out[0] != n_out[1] || !norm_w)))
+    if (n_mat < 1 || n_mat > 3 || n_in % 256 != 0 || n_in > kGemvMaxIn || (swiglu && (n_mat != 2 || n_out[0] != n_out[1] || !norm_w)))
         return cudaErrorInvalidValue;
     GemvGroup g = {};
     int total = 0;
@@ -377,20 +408,18 @@ cudaError_t ingot_support_gemv_group(float* const* outs, const void* const* ws, 
         short_rows ? (swiglu ? gemv_stream_kernel<true, true, 6> : norm_w ? gemv_stream_kernel<true, false, 6> : gemv_stream_kernel<false, false, 6>)
                    : (swiglu ? gemv_stream_kernel<true, true, 4> : norm_w ? gemv_stream_kernel<true, false, 4> : gemv_stream_kernel<false, false, 4>);
     // one resident wave, every warp the same number of rows
-    static int num_sms = 0, ctas_per_sm_cap = 0;
-    static bool use_pdl = true;
-    if (num_sms == 0) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
-        use_pdl = getenv("INGOT_NO_PDL") == nullptr;
-        // CTAs of one launch per SM. Fewer than fit leaves room for the next launch's CTAs, which then request
-        // their first weights while this launch is still streaming (programmatic dependent launch).
-        const char* c = getenv("INGOT_GEMV_CTAS_PER_SM");
-        ctas_per_sm_cap = c ? atoi(c) : 0;
-    }
+    // Environment knobs are process-wide and read once; the SM count belongs to the current device and is looked up
+    // on every call (a cached attribute read), so that one process may drive several GPUs.
+    static const bool use_pdl = getenv("INGOT_NO_PDL") == nullptr;
+    // CTAs of one launch per SM. Fewer than fit leaves room for the next launch's CTAs, which then request
+    // their first weights while this launch is still streaming (programmatic dependent launch).
+    static const int ctas_per_sm_cap = [] { const char* c = getenv("INGOT_GEMV_CTAS_PER_SM"); return c ? atoi(c) : 0; }();
+    int dev = 0, num_sms = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e == cudaSuccess) e = cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess) return e;
     int occ = 0;
-    cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kernel, 256, smem);
+    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kernel, 256, smem);
     if (e != cudaSuccess) return e;
     if (occ < 1) occ = 1;
     if (ctas_per_sm_cap > 0) occ = occ < ctas_per_sm_cap ? occ : ctas_per_sm_cap;

@@ -83,6 +83,12 @@ struct Sm100Params {
     int n_outs;               // KV-head-sharded prefill, the peers' buffers: plain peer stores over NVLink)
     int out_n_head;           // heads per token in the destination layout [token][out_n_head][128]
     int out_head0;            // destination index of this call's first query head
+    // Completion signalling for the multi-destination form (null: none). The CTA that finishes last - found with a
+    // ticket in this GPU's memory - adds 1 to counter `src_index` of every destination's counter array, released
+    // at system scope behind all of the grid's stores.
+    unsigned int* signals[kMaxOutputs];
+    int src_index;
+    int* ticket;
     int* status;
     int q_dtype, out_dtype;
     int n_head, group;
@@ -538,6 +544,21 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_k, const __gri
     tc_fence_before();
     __syncthreads();
     if (threadIdx.x == 0 && *abort_flag) atomicOr(p.status, kDevErrBarrierTimeout);
+    if (threadIdx.x == 0 && p.ticket != nullptr) {
+        // Every thread's output stores precede the barrier above; the fence orders them, at system scope (they
+        // may have gone to peer GPUs), before this CTA's ticket. Whoever draws the last ticket has therefore
+        // every CTA's stores before its own fence, and releases one signal per destination.
+        __threadfence_system();
+        const int total = (int)(gridDim.x * gridDim.y * gridDim.z);
+        if (atomicAdd(p.ticket, 1) == total - 1) {
+            atomicExch(p.ticket, 0);
+            __threadfence_system();
+#pragma unroll
+            for (int d = 0; d < kMaxOutputs; d++)
+                if (d < p.n_outs && p.signals[d] != nullptr)
+                    asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(p.signals[d] + p.src_index) : "memory");
+        }
+    }
     if (warp == 1) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
@@ -574,6 +595,29 @@ __global__ void __launch_bounds__(256) prefill_merge_kernel(const float* __restr
     }
 }
 
+// Consumer side of the completion signalling: thread i waits until counter i is non-zero (its source's grid has
+// finished and all its stores are visible here), then takes the signal back off the counter, so that the same
+// counters serve the next call without any reset. Bounded: a source that never signals makes its thread give up
+// after limit_ns with the timeout bit in the status word; nothing spins for ever and nothing traps.
+__global__ void gather_wait_kernel(unsigned int* counters, int n_src, unsigned long long limit_ns, int* status) {
+    const int i = threadIdx.x;
+    if (i >= n_src) return;
+    const uint64_t t0 = globaltimer_ns();
+    for (;;) {
+        unsigned int v;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(counters + i) : "memory");
+        if (v != 0) {
+            atomicSub(counters + i, 1u);
+            return;
+        }
+        if (globaltimer_ns() - t0 > limit_ns) {
+            atomicOr(status, kDevErrBarrierTimeout);
+            return;
+        }
+        __nanosleep(200);
+    }
+}
+
 // ---- host side: tensor maps -------------------------------------------------------------------
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -598,10 +642,16 @@ struct Sm100State {
     std::vector<char> built;
     float* part = nullptr;          // key-split partials, grown on demand
     size_t part_floats = 0;
-    int num_sms = 0;
+    bool smem_opt_in = false;
 };
 
 }  // namespace
+
+int launch_gather_wait(ingot_kv* kv, void* counters, int n_src, int timeout_ms, cudaStream_t stream) {
+    gather_wait_kernel<<<1, 32, 0, stream>>>(static_cast<unsigned int*>(counters), n_src, (unsigned long long)timeout_ms * 1000000ull, kv->status_dev);
+    INGOT_CUDA_TRY(cudaGetLastError());
+    return INGOT_OK;
+}
 
 void free_prefill_sm100_state(ingot_kv* kv) {
     Sm100State* st = static_cast<Sm100State*>(kv->tmaps);
@@ -612,7 +662,7 @@ void free_prefill_sm100_state(ingot_kv* kv) {
 
 int launch_attn_prefill_sm100(ingot_kv* kv, int layer, const void* q, int q_dtype, void* const* outs, int n_outs,
                               int out_dtype, int n_head, int out_n_head, int out_head0, int q_pos0, int n_tok,
-                              const int32_t* block_table, cudaStream_t stream) {
+                              const int32_t* block_table, void* const* signals, int src_index, cudaStream_t stream) {
     if (n_outs < 1 || n_outs > kMaxOutputs) {
         ingot_set_error("tcgen05 prefill: between 1 and 8 output buffers");
         return INGOT_ERR_INVALID;
@@ -658,32 +708,32 @@ int launch_attn_prefill_sm100(ingot_kv* kv, int layer, const void* q, int q_dtyp
     p.q = q; p.status = kv->status_dev;
     for (int i = 0; i < kMaxOutputs; i++) p.outs[i] = i < n_outs ? outs[i] : nullptr;
     p.n_outs = n_outs; p.out_n_head = out_n_head; p.out_head0 = out_head0;
+    for (int i = 0; i < kMaxOutputs; i++) p.signals[i] = (signals && i < n_outs) ? static_cast<unsigned int*>(signals[i]) : nullptr;
+    p.src_index = src_index;
+    p.ticket = signals ? kv->status_dev + 1 : nullptr;
     p.q_dtype = q_dtype; p.out_dtype = out_dtype;
     p.n_head = n_head; p.group = n_head / kv->n_head_kv;
     p.q_pos0 = q_pos0; p.n_tok = n_tok;
     p.block_table = paged ? block_table : nullptr;
     p.capacity = kv->capacity;
     p.scale_log2 = 1.4426950408889634f / sqrtf(float(kHeadDim));
-    // Test hook for the bounded-wait path: INGOT_TEST_STALL_TMA=<milliseconds> makes the producer warp issue
-    // no copies and shortens the wait limit, so every role times out, the status word gets its bit and the
-    // kernel returns normally. Production: 2 s limit, producer active.
-    const char* stall = getenv("INGOT_TEST_STALL_TMA");
-    p.test_stall_producer = stall ? 1 : 0;
-    p.wait_limit_ns = stall ? (unsigned long long)std::max(1, atoi(stall)) * 1000000ull : 2000000000ull;
-    INGOT_CUDA_TRY(cudaFuncSetAttribute(attn_prefill_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+    // Test hook for the bounded-wait path (ingot_kv_test_stall_prefill): the producer warp issues no copies and the
+    // wait limit is shortened, so every role times out, the status word gets its bit and the kernel returns
+    // normally. Production: 2 s limit, producer active.
+    p.test_stall_producer = kv->test_stall_ms > 0 ? 1 : 0;
+    p.wait_limit_ns = kv->test_stall_ms > 0 ? (unsigned long long)kv->test_stall_ms * 1000000ull : 2000000000ull;
+    if (!st->smem_opt_in) {  // function attributes belong to a device context: once per handle
+        INGOT_CUDA_TRY(cudaFuncSetAttribute(attn_prefill_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+        st->smem_opt_in = true;
+    }
     const long long n_rows = (long long)n_tok * p.group;
     const unsigned row_tiles = unsigned((n_rows + 2 * kTileRows - 1) / (2 * kTileRows));
-    if (st->num_sms == 0) {
-        int dev = 0;
-        INGOT_CUDA_TRY(cudaGetDevice(&dev));
-        INGOT_CUDA_TRY(cudaDeviceGetAttribute(&st->num_sms, cudaDevAttrMultiProcessorCount, dev));
-    }
     // Too few row tiles to fill the GPU (one CTA per SM): split the keys over grid.z and merge afterwards.
     // Only the last row tile is guaranteed to have many key tiles, so the split count is bounded by them.
     const int row_ctas = int(row_tiles) * kv->n_head_kv;
     const int kv_tiles_last = (q_pos0 + n_tok + kTileKeys - 1) / kTileKeys;
     int n_split = 1;
-    if (n_outs == 1 && row_ctas * 2 <= st->num_sms) n_split = std::max(1, std::min({st->num_sms / row_ctas, 8, kv_tiles_last / 2}));
+    if (n_outs == 1 && !signals && row_ctas * 2 <= kv->num_sms) n_split = std::max(1, std::min({kv->num_sms / row_ctas, 8, kv_tiles_last / 2}));
     p.n_split = n_split;
     p.part = nullptr;
     if (n_split > 1) {

@@ -40,7 +40,7 @@ struct ingot_kv {
     size_t layer_elems = 0;  // f16 elements per layer in each of K and V
     __half* k = nullptr;
     __half* v = nullptr;
-    int* status_dev = nullptr;
+    int* status_dev = nullptr;  // [0] the status word, [1] the ticket of the signalling prefill form
     // split-KV decode scratch: part_bufs buffers of partials [n_seq][splits][n_head][kPartStride], each with its
     // arrival counters part_sync [max_seqs][n_head_kv][2] (zero when idle). A single decode call uses buffer 0;
     // the multi-layer call gives every launch chain two buffers that its consecutive launches alternate between.
@@ -52,7 +52,9 @@ struct ingot_kv {
     size_t part_floats = 0;  // floats per buffer
     int part_bufs = 0;
     std::vector<void*> retired;
-    bool prefill_mma_attr_set = false;  // the warp-MMA prefill kernel's shared-memory opt-in was made on `device`
+    size_t decode_smem_opt_in = 0;      // largest dynamic shared memory the decode kernel was opted in for on `device`
+    bool prefill_mma_attr_set = false;
+    int test_stall_ms = 0;              // test hook, see ingot_kv_test_stall_prefill  // the warp-MMA prefill kernel's shared-memory opt-in was made on `device`
     // staging for the host-buffer entry points (grown on demand)
     void* stage = nullptr;
     size_t stage_bytes = 0;
@@ -122,7 +124,7 @@ int launch_rope_kv_append(ingot_kv* kv, int layer, const float* q, __half* q_out
 int launch_kv_import_f16(ingot_kv* kv, int layer, const __half* k, const __half* v, int pos0, int n_tok,
                          const int32_t* block_table, cudaStream_t stream);
 struct DecodePlan { int chunk_keys, n_parts; };
-DecodePlan decode_plan(const ingot_kv* kv, int n_seq, int max_seq_len, int chunk_keys, int concurrency);
+DecodePlan decode_plan(const ingot_kv* kv, int n_seq, int max_seq_len, int chunk_keys, int concurrency, int n_head);
 size_t decode_part_floats(int n_seq, int n_parts, int n_head);
 int launch_attn_decode(ingot_kv* kv, int layer, const void* q, int q_dtype, void* out, int out_dtype, int n_head,
                        int n_seq, const int32_t* seq_lens, int max_seq_len, const int32_t* block_tables,
@@ -132,5 +134,6 @@ int launch_attn_prefill_mma(ingot_kv* kv, int layer, const void* q, int q_dtype,
                             int n_head, int q_pos0, int n_tok, const int32_t* block_table, cudaStream_t stream);
 int launch_attn_prefill_sm100(ingot_kv* kv, int layer, const void* q, int q_dtype, void* const* outs, int n_outs,
                               int out_dtype, int n_head, int out_n_head, int out_head0, int q_pos0, int n_tok,
-                              const int32_t* block_table, cudaStream_t stream);
+                              const int32_t* block_table, void* const* signals, int src_index, cudaStream_t stream);
+int launch_gather_wait(ingot_kv* kv, void* counters, int n_src, int timeout_ms, cudaStream_t stream);
 void free_prefill_sm100_state(ingot_kv* kv);

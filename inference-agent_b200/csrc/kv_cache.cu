@@ -70,12 +70,12 @@ int ingot_kv_create(ingot_kv** out, int layout, int n_layer, int n_head_kv, int 
     };
     if ((e = cudaMalloc(&kv->k, bytes)) != cudaSuccess) return fail(e, "cudaMalloc(K cache)");
     if ((e = cudaMalloc(&kv->v, bytes)) != cudaSuccess) return fail(e, "cudaMalloc(V cache)");
-    if ((e = cudaMalloc(&kv->status_dev, sizeof(int))) != cudaSuccess) return fail(e, "cudaMalloc(status)");
+    if ((e = cudaMalloc(&kv->status_dev, 2 * sizeof(int))) != cudaSuccess) return fail(e, "cudaMalloc(status)");
     // Zero-filled cache: rows that were never appended hold finite values, so a masked key can never
     // inject NaN through 0 * garbage.
     if ((e = cudaMemset(kv->k, 0, bytes)) != cudaSuccess) return fail(e, "cudaMemset(K)");
     if ((e = cudaMemset(kv->v, 0, bytes)) != cudaSuccess) return fail(e, "cudaMemset(V)");
-    if ((e = cudaMemset(kv->status_dev, 0, sizeof(int))) != cudaSuccess) return fail(e, "cudaMemset(status)");
+    if ((e = cudaMemset(kv->status_dev, 0, 2 * sizeof(int))) != cudaSuccess) return fail(e, "cudaMemset(status)");
     if ((e = cudaDeviceSynchronize()) != cudaSuccess) return fail(e, "cudaDeviceSynchronize");
     *out = kv;
     return INGOT_OK;
@@ -115,6 +115,12 @@ void* ingot_kv_v_dev(ingot_kv* kv, int layer) {
 }
 
 size_t ingot_kv_layer_bytes(const ingot_kv* kv) { return kv ? kv->layer_elems * sizeof(__half) : 0; }
+
+int ingot_kv_test_stall_prefill(ingot_kv* kv, int stall_ms) {
+    INGOT_REQUIRE(kv != nullptr && stall_ms >= 0, "ingot_kv_test_stall_prefill: bad argument");
+    kv->test_stall_ms = stall_ms;
+    return INGOT_OK;
+}
 
 int ingot_kv_status(ingot_kv* kv, void* stream, int* status_out) {
     INGOT_REQUIRE(kv && status_out, "ingot_kv_status: null argument");
@@ -235,7 +241,7 @@ int ingot_attn_decode(ingot_kv* kv, int layer, const void* q_dev, int q_dtype, v
                             block_tables_dev, max_blocks_per_seq, chunk_keys);
     if (rc != INGOT_OK) return rc;
     // One launch: the splits, and the merge by whichever split CTA of a (sequence, kv head) finishes last.
-    const DecodePlan plan = decode_plan(kv, n_seq, max_seq_len, chunk_keys, 1);
+    const DecodePlan plan = decode_plan(kv, n_seq, max_seq_len, chunk_keys, 1, n_head);
     rc = ensure_decode_scratch(kv, decode_part_floats(n_seq, plan.n_parts, n_head), 1);
     if (rc != INGOT_OK) return rc;
     return launch_attn_decode(kv, layer, q_dev, q_dtype, out_dev, out_dtype, n_head, n_seq, seq_lens_dev, max_seq_len,
@@ -273,7 +279,7 @@ int ingot_attn_decode_layers(ingot_kv* kv, int layer_begin, int layer_count, con
     const int max_streams = std::min(streams_cfg, layer_count);
     const int want_rounds = (layer_count + max_streams - 1) / max_streams;
     const int n_streams = (layer_count + want_rounds - 1) / want_rounds;
-    const DecodePlan plan = decode_plan(kv, n_seq, max_seq_len, chunk_keys, n_streams);
+    const DecodePlan plan = decode_plan(kv, n_seq, max_seq_len, chunk_keys, n_streams, n_head);
     rc = ensure_decode_scratch(kv, decode_part_floats(n_seq, plan.n_parts, n_head), 2 * n_streams);
     if (rc != INGOT_OK) return rc;
     if (!kv->fork_event) INGOT_CUDA_TRY(cudaEventCreateWithFlags(&kv->fork_event, cudaEventDisableTiming));
@@ -332,18 +338,16 @@ int ingot_attn_prefill(ingot_kv* kv, int layer, const void* q_dev, int q_dtype, 
     const bool use_sm100 = impl == 2 || (impl == 0 && size_t(n_tok) * n_head >= 4096);
     if (use_sm100)
         return launch_attn_prefill_sm100(kv, layer, q_dev, q_dtype, &out_dev, 1, out_dtype, n_head, n_head, 0, q_pos0, n_tok,
-                                         block_table_dev, s);
+                                         block_table_dev, nullptr, 0, s);
     return launch_attn_prefill_mma(kv, layer, q_dev, q_dtype, out_dev, out_dtype, n_head, q_pos0, n_tok, block_table_dev, s);
 }
 
-int ingot_attn_prefill_gather(ingot_kv* kv, int layer, const void* q_dev, int q_dtype, void* const* out_ptrs, int n_out,
-                              int out_dtype, int n_head, int out_n_head, int out_head0, int q_pos0, int n_tok,
-                              void* stream) {
+static int prefill_gather_checked(ingot_kv* kv, int layer, const void* q_dev, int q_dtype, void* const* out_ptrs, int n_out,
+                                  int out_dtype, int n_head, int out_n_head, int out_head0, int q_pos0, int n_tok) {
     INGOT_REQUIRE(kv != nullptr, "ingot_attn_prefill_gather: kv is null");
     INGOT_REQUIRE_DEVICE(kv);
     INGOT_REQUIRE(layer >= 0 && layer < kv->n_layer, "ingot_attn_prefill_gather: layer out of range");
-    INGOT_REQUIRE(n_tok >= 0 && q_pos0 >= 0, "ingot_attn_prefill_gather: negative range");
-    if (n_tok == 0) return INGOT_OK;
+    INGOT_REQUIRE(n_tok >= 1 && q_pos0 >= 0, "ingot_attn_prefill_gather: bad range");
     INGOT_REQUIRE(q_dev && out_ptrs && n_out >= 1 && n_out <= 8, "ingot_attn_prefill_gather: 1 to 8 output buffers");
     for (int i = 0; i < n_out; i++) INGOT_REQUIRE(out_ptrs[i] != nullptr, "ingot_attn_prefill_gather: null output buffer");
     INGOT_REQUIRE(n_head >= kv->n_head_kv && n_head % kv->n_head_kv == 0, "ingot_attn_prefill_gather: n_head must be a multiple of n_head_kv");
@@ -354,8 +358,35 @@ int ingot_attn_prefill_gather(ingot_kv* kv, int layer, const void* q_dev, int q_
         return INGOT_ERR_UNSUPPORTED;
     }
     INGOT_REQUIRE(size_t(q_pos0) + n_tok <= size_t(kv->capacity), "context window exceeded");
+    return INGOT_OK;
+}
+
+int ingot_attn_prefill_gather(ingot_kv* kv, int layer, const void* q_dev, int q_dtype, void* const* out_ptrs, int n_out,
+                              int out_dtype, int n_head, int out_n_head, int out_head0, int q_pos0, int n_tok,
+                              void* stream) {
+    if (kv && n_tok == 0) return INGOT_OK;
+    int rc = prefill_gather_checked(kv, layer, q_dev, q_dtype, out_ptrs, n_out, out_dtype, n_head, out_n_head, out_head0, q_pos0, n_tok);
+    if (rc != INGOT_OK) return rc;
     return launch_attn_prefill_sm100(kv, layer, q_dev, q_dtype, out_ptrs, n_out, out_dtype, n_head, out_n_head, out_head0,
-                                     q_pos0, n_tok, nullptr, static_cast<cudaStream_t>(stream));
+                                     q_pos0, n_tok, nullptr, nullptr, 0, static_cast<cudaStream_t>(stream));
+}
+
+int ingot_attn_prefill_gather_signal(ingot_kv* kv, int layer, const void* q_dev, int q_dtype, void* const* out_ptrs,
+                                     void* const* signal_ptrs, int n_out, int src_index, int out_dtype, int n_head,
+                                     int out_n_head, int out_head0, int q_pos0, int n_tok, void* stream) {
+    int rc = prefill_gather_checked(kv, layer, q_dev, q_dtype, out_ptrs, n_out, out_dtype, n_head, out_n_head, out_head0, q_pos0, n_tok);
+    if (rc != INGOT_OK) return rc;
+    INGOT_REQUIRE(signal_ptrs != nullptr && src_index >= 0 && src_index < 64, "ingot_attn_prefill_gather_signal: bad signal arguments");
+    for (int i = 0; i < n_out; i++) INGOT_REQUIRE(signal_ptrs[i] != nullptr, "ingot_attn_prefill_gather_signal: null counter array");
+    return launch_attn_prefill_sm100(kv, layer, q_dev, q_dtype, out_ptrs, n_out, out_dtype, n_head, out_n_head, out_head0,
+                                     q_pos0, n_tok, nullptr, signal_ptrs, src_index, static_cast<cudaStream_t>(stream));
+}
+
+int ingot_gather_wait(ingot_kv* kv, void* counters_dev, int n_src, int timeout_ms, void* stream) {
+    INGOT_REQUIRE(kv != nullptr && counters_dev != nullptr, "ingot_gather_wait: null argument");
+    INGOT_REQUIRE_DEVICE(kv);
+    INGOT_REQUIRE(n_src >= 1 && n_src <= 32 && timeout_ms >= 1, "ingot_gather_wait: 1 to 32 sources, timeout of at least 1 ms");
+    return launch_gather_wait(kv, counters_dev, n_src, timeout_ms, static_cast<cudaStream_t>(stream));
 }
 
 int ingot_attn_layers_host(ingot_kv* kv, int layer_begin, int layer_count, const float* q_host, const float* k_host,

@@ -28,6 +28,7 @@ ABI = {
     "ingot_kv_v_dev": (_P, [_P, _I]),
     "ingot_kv_layer_bytes": (_SZ, [_P]),
     "ingot_kv_status": (_I, [_P, _P, C.POINTER(_I)]),
+    "ingot_kv_test_stall_prefill": (_I, [_P, _I]),
     "ingot_rope_kv_append": (_I, [_P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _P, _P, _P, _I, _P]),
     "ingot_kv_import_f16": (_I, [_P, _I, _P, _P, _I, _I, _P, _P]),
     "ingot_attn_decode": (_I, [_P, _I, _P, _I, _P, _I, _I, _I, _P, _I, _P, _I, _I, _P]),
@@ -35,9 +36,12 @@ ABI = {
     "ingot_attn_decode_noalloc": (_I, [_P, _P, _I, _I, _P, _I, _P, _I, _I, _I, _I, _P]),
     "ingot_attn_prefill": (_I, [_P, _I, _P, _I, _P, _I, _I, _I, _I, _P, _I, _P]),
     "ingot_attn_prefill_gather": (_I, [_P, _I, _P, _I, C.POINTER(_P), _I, _I, _I, _I, _I, _I, _I, _P]),
+    "ingot_attn_prefill_gather_signal": (_I, [_P, _I, _P, _I, C.POINTER(_P), C.POINTER(_P), _I, _I, _I, _I, _I, _I, _I, _I, _P]),
+    "ingot_gather_wait": (_I, [_P, _P, _I, _I, _P]),
     "ingot_attn_layer_host": (_I, [_P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _P]),
     "ingot_attn_layers_host": (_I, [_P, _I, _I, _P, _P, _P, _P, _P, _I, _I, _I, _P]),
     "ingot_stream_sync": (_I, [_P]),
+    "ingot_hbm_read_probe": (_I, [_SZ, _I, C.POINTER(C.c_double), _P]),
 }
 
 
@@ -197,6 +201,20 @@ def attn_prefill_gather(kv, layer, q, q_pos0, out_ptrs, out_dtype_code, out_n_he
                                            q.shape[1], out_n_head, out_head0, q_pos0, q.shape[0], _stream()))
 
 
+def attn_prefill_gather_signal(kv, layer, q, q_pos0, out_ptrs, signal_ptrs, src_index, out_dtype_code, out_n_head, out_head0):
+    """attn_prefill_gather plus one completion signal per destination (counter src_index of each array in signal_ptrs)."""
+    assert q.is_contiguous() and len(out_ptrs) == len(signal_ptrs)
+    arr = (C.c_void_p * len(out_ptrs))(*[C.c_void_p(int(x)) for x in out_ptrs])
+    sig = (C.c_void_p * len(signal_ptrs))(*[C.c_void_p(int(x)) for x in signal_ptrs])
+    _check(lib().ingot_attn_prefill_gather_signal(kv.handle, layer, _ptr(q), _dtype_code(q), arr, sig, len(out_ptrs), src_index,
+                                                  out_dtype_code, q.shape[1], out_n_head, out_head0, q_pos0, q.shape[0], _stream()))
+
+
+def gather_wait(kv, counters, n_src, timeout_ms=2000):
+    """Queues the bounded wait for n_src completion signals on this GPU's counter array (an int32 cuda tensor)."""
+    _check(lib().ingot_gather_wait(kv.handle, _ptr(counters), n_src, timeout_ms, _stream()))
+
+
 def attn_layer_host(kv, layer, q_host, k_host, v_host, out_host, inv_freq_dev, pos0):
     """Pinned host tensors in/out; asynchronous on the current stream."""
     n_tok, n_head = q_host.shape[0], q_host.shape[1]
@@ -209,3 +227,10 @@ def attn_layers_host(kv, layer_begin, q_host, k_host, v_host, out_host, inv_freq
     n_layers, n_tok, n_head = q_host.shape[0], q_host.shape[1], q_host.shape[2]
     _check(lib().ingot_attn_layers_host(kv.handle, layer_begin, n_layers, _ptr(q_host), _ptr(k_host), _ptr(v_host),
                                         _ptr(out_host), _ptr(inv_freq_dev), n_head, pos0, n_tok, _stream()))
+
+
+def hbm_read_probe(n_bytes, reps=5):
+    """GB/s of a read-only sweep over n_bytes of device memory (best of reps)."""
+    best = C.c_double(0.0)
+    _check(lib().ingot_hbm_read_probe(n_bytes, reps, C.byref(best), _stream()))
+    return n_bytes / best.value / 1e9

@@ -13,9 +13,10 @@
 //                                     the lambda reads private members and cannot be called
 //                                     with injected Q/K/V
 //   ref_rope_inv_freq              -> src/model.cpp:59-69 restated (Model::load needs a file)
-//   ref_e2e_greedy                 -> genuine gguf::File + Model::load + make_backend("cpu")
-//                                     + prefill + greedy Sampler (src/engine.cpp:9-23,
-//                                     src/sampler.cpp:14-51)
+//   ref_dequant, ref_matvec        -> call ops::dequant_row / ops::matvec (src/ops.cpp:198-225) on
+//                                     caller-supplied block-quantised rows
+// (The end-to-end greedy check drives the reference's genuine CpuBackend through the engine library,
+// backend/e2e_capi.cpp, which links the same unmodified reference sources.)
 #include <algorithm>
 #include <cmath>
 #include <cstdint>
@@ -114,35 +115,30 @@ void ref_attn_forward(float* q, float* k, const float* v, float* kcache, float* 
     }
 }
 
-// Greedy generation through the reference's own glue on its CPU backend. Writes n_gen token
-// ids to out_ids and, per generated token, the top-1 minus top-2 logit margin to out_margin
-// (may be null). Returns 0, or -1 with ref_last_error() set.
-int ref_e2e_greedy(const char* gguf_path, const int32_t* prompt, int n_prompt, int n_gen, int n_batch,
-                   int32_t* out_ids, float* out_margin) {
+// ops::dequant_row (src/ops.cpp:198-200) on a caller-supplied row of `n` elements of ggml type `type`.
+// Returns 0, or -1 when the reference rejects the type.
+int ref_dequant(int type, const uint8_t* bytes, float* out, size_t n) {
     try {
-        gguf::File f = gguf::File::open(gguf_path);
-        Model model = Model::load(f);
-        auto backend = make_backend("cpu", f, model, n_prompt + n_gen + 8, n_batch);
-        SamplerParams sp;
-        sp.temperature = 0.0f;
-        Sampler sampler(sp, model.cfg.n_vocab);
-        std::vector<int32_t> ids(prompt, prompt + n_prompt);
-        int pos = 0;
-        const float* logits = prefill(*backend, ids, pos, n_batch);
-        for (int i = 0; i < n_gen; i++) {
-            if (out_margin) {
-                float a = -INFINITY, b = -INFINITY;
-                for (int t = 0; t < model.cfg.n_vocab; t++) {
-                    float x = logits[t];
-                    if (x > a) { b = a; a = x; } else if (x > b) { b = x; }
-                }
-                out_margin[i] = a - b;
-            }
-            int32_t next = sampler.sample(const_cast<float*>(logits), ids);
-            out_ids[i] = next;
-            ids.push_back(next);
-            if (i + 1 < n_gen) logits = backend->forward(next, pos++);
-        }
+        gguf::TensorInfo t;
+        t.ne = {uint64_t(n), 1};
+        t.type = gguf::TensorType(uint32_t(type));
+        t.data = bytes;
+        ops::dequant_row(t, 0, out);
+        return 0;
+    } catch (const std::exception& e) {
+        g_last_error = e.what();
+        return -1;
+    }
+}
+
+// ops::matvec (src/ops.cpp:217-225): out[r] = dot_row(W, r, x) for a [n_out][n_in] matrix of ggml type `type`.
+int ref_matvec(int type, const uint8_t* bytes, const float* x, size_t n_in, size_t n_out, float* out) {
+    try {
+        gguf::TensorInfo t;
+        t.ne = {uint64_t(n_in), uint64_t(n_out)};
+        t.type = gguf::TensorType(uint32_t(type));
+        t.data = bytes;
+        ops::matvec(out, t, x);
         return 0;
     } catch (const std::exception& e) {
         g_last_error = e.what();

@@ -32,14 +32,15 @@ def _engine():
     return lib
 
 
-def _model(tmp_dir, full=False):
+def _model(tmp_dir, full=False, wtype="F16", output_type=None):
     sys.path.insert(0, os.path.join(ROOT, "tests", "golden"))
     import make_random_gguf
     full = full and os.environ.get("INGOT_E2E_SMALL") != "1"
     n_layer, n_vocab = (28, 128256) if full else (2, 32064)
-    path = os.path.join(tmp_dir, f"ingot_random_l{n_layer}_v{n_vocab}_s0.gguf")
+    tag = "" if wtype == "F16" else f"_{wtype}_{output_type or wtype}"
+    path = os.path.join(tmp_dir, f"ingot_random_l{n_layer}_v{n_vocab}_s0{tag}.gguf")
     if not os.path.exists(path):
-        make_random_gguf.write(path + ".tmp", n_layer, n_vocab, seed=0)
+        make_random_gguf.write(path + ".tmp", n_layer, n_vocab, seed=0, wtype=wtype, output_type=output_type)
         os.replace(path + ".tmp", path)
     return path, n_vocab
 
@@ -64,6 +65,52 @@ def test_greedy_tokens_match_cpu_reference(full, n_batch):
                                            f"{want_margin[first_bad]:.3e}) vs cuda {got[first_bad]} (margin {got_margin[first_bad]:.3e})")
     assert first_bad is None, detail
     print(f"\n32 greedy tokens identical (n_batch={n_batch}); smallest reference top-2 margin {want_margin.min():.3e}")
+
+
+@pytest.mark.parametrize("wtype,output_type,n_batch", [
+    ("Q8_0", None, 512),     # one 128-token batch: hi/lo planes through the tensor-core GEMM
+    ("Q4_0", "Q6_K", 512),   # what llama.cpp's Q4_0 files look like: Q6_K embedding / output matrix
+    ("Q4_1", None, 512),
+    ("Q8_0", None, 48),      # chunked prefill
+    ("Q4_0", "Q6_K", 5),     # chunks below the tensor-core minimum: the f32 fallback
+])
+def test_greedy_tokens_match_cpu_reference_quantised(wtype, output_type, n_batch):
+    """The same check on block-quantised GGUFs (2 layers, 32064 tokens): weights stay quantised on the device,
+    single tokens go through the dequantise-in-GEMV kernels, batches through the hi/lo tensor-core path."""
+    lib = _engine()
+    path, n_vocab = _model(os.environ.get("INGOT_E2E_DIR", "/tmp"), False, wtype, output_type)
+    prompt = np.random.default_rng(0).integers(0, n_vocab, size=128).astype(np.int32)
+    want, want_margin = _greedy(lib, path, b"cpu", prompt, 32, n_batch)
+    got, got_margin = _greedy(lib, path, b"metal", prompt, 32, n_batch)
+    first_bad = next((i for i in range(32) if want[i] != got[i]), None)
+    detail = "" if first_bad is None else (f"first mismatch at step {first_bad}: cpu {want[first_bad]} (top-2 margin "
+                                           f"{want_margin[first_bad]:.3e}) vs cuda {got[first_bad]} (margin {got_margin[first_bad]:.3e})")
+    assert first_bad is None, detail
+    assert len(set(want.tolist())) > 8  # the random model does not collapse onto one token
+    print(f"\n{wtype}: 32 greedy tokens identical (n_batch={n_batch}); smallest reference top-2 margin {want_margin.min():.3e}")
+
+
+@pytest.mark.parametrize("n_seq,wtype", [(5, "F16"), (24, "F16"), (5, "Q8_0")])
+def test_batched_forward_multi_matches_single_sequence_reference(n_seq, wtype):
+    """The batched extension (BatchedBackend::forward_multi on the paged cache): n_seq sequences with prompts of
+    different lengths are prefilled and decoded together, each contributing one token per step, and every
+    sequence must produce exactly the tokens the reference CpuBackend produces when it runs that sequence alone.
+    24 sequences take the batched projections through the tensor-core kernels, 5 through the f32 ones."""
+    lib = _engine()
+    i32p = np.ctypeslib.ndpointer(dtype=np.int32, flags="C_CONTIGUOUS")
+    lib.ingot_e2e_multi_greedy.argtypes = [C.c_char_p, i32p, i32p, C.c_int, C.c_int, C.c_int, i32p]
+    lib.ingot_e2e_multi_greedy.restype = C.c_int
+    path, n_vocab = _model(os.environ.get("INGOT_E2E_DIR", "/tmp"), False, wtype)
+    rng = np.random.default_rng(100 + n_seq)
+    lens = rng.integers(3, 40, size=n_seq).astype(np.int32)
+    prompts = [rng.integers(0, n_vocab, size=int(n)).astype(np.int32) for n in lens]
+    n_gen = 12
+    got = np.zeros((n_seq, n_gen), dtype=np.int32)
+    rc = lib.ingot_e2e_multi_greedy(path.encode(), np.concatenate(prompts), lens, n_seq, n_gen, 64, got)
+    assert rc == 0, lib.ingot_e2e_last_error().decode()
+    for s in range(min(n_seq, 8)):  # the CPU reference is slow: the first eight sequences
+        want, margin = _greedy(lib, path, b"cpu", prompts[s], n_gen, 512)
+        assert np.array_equal(got[s], want), f"sequence {s} (prompt {lens[s]} tokens): batched {got[s]} vs reference {want}; margins {margin}"
 
 
 def test_backend_errors_match_reference():

@@ -28,6 +28,7 @@ def _lib():
     return lib
 
 
+@pytest.mark.parametrize("x_scale", [1.0, 3e-4])
 @pytest.mark.parametrize("n_tok,n_in,n_out,accumulate", [
     (128, 3072, 3072, 1),    # wo at the Llama-3.2-3B shape, one token tile, split-k
     (128, 3072, 1024, 0),    # wk / wv: few output tiles, deep split-k
@@ -36,16 +37,18 @@ def _lib():
     (16, 64, 4, 0),          # smallest supported shape: one k-step, four outputs
     (77, 256, 132, 1),       # output count that is not a multiple of the tile
 ])
-def test_linear_tc_matches_float64(n_tok, n_in, n_out, accumulate):
+def test_linear_tc_matches_float64(n_tok, n_in, n_out, accumulate, x_scale):
     import torch
     lib = _lib()
     ws = C.c_void_p()
     assert lib.ingot_linear_ws_create(C.byref(ws), 512, 8192) == 0
     try:
         g = torch.Generator(device="cuda").manual_seed(n_tok * 31 + n_out)
-        x = torch.randn(n_tok, n_in, device="cuda", generator=g)
+        # x_scale 3e-4: activations of magnitude 1e-4..1e-3 (a SwiGLU product on random-init weights), where the lo
+        # half of the split is an f16 subnormal and the split only bounds the ABSOLUTE error (2^-25 per element)
+        x = torch.randn(n_tok, n_in, device="cuda", generator=g) * x_scale
         w = (torch.randn(n_out, n_in, device="cuda", generator=g) * 0.02).half()
-        out0 = torch.randn(n_tok, n_out, device="cuda", generator=g)
+        out0 = torch.randn(n_tok, n_out, device="cuda", generator=g) * x_scale
         out = out0.clone()
         assert lib.ingot_linear_tc_supported(ws, 1, n_in, n_out, n_tok) == 1
         stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
@@ -58,7 +61,8 @@ def test_linear_tc_matches_float64(n_tok, n_in, n_out, accumulate):
         err = (out.double() - want).abs().max().item()
         scale = want.abs().max().item()
         # f32 accumulation over n_in terms plus the 2^-22 truncation of x; an f16-activation product would be ~1e-3
-        assert err <= 1e-5 * scale * max(1.0, (n_in / 1024) ** 0.5), (err, scale)
+        tol = (1e-5 if x_scale == 1.0 else 2e-4) * scale * max(1.0, (n_in / 1024) ** 0.5)
+        assert err <= tol, (err, scale)
         # a second run on the same workspace gives the same bits (fixed summation order over the k slices)
         out2 = out0.clone()
         assert lib.ingot_linear_tc_run(ws, out2.data_ptr(), w.data_ptr(), n_in, n_out, accumulate, stream) == 0

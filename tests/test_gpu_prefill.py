@@ -172,12 +172,48 @@ def test_bounded_waits_expire_cleanly(monkeypatch):
     kv = ib.KVCache(ib.KV_CONTIGUOUS, 1, HKV, 40)
     inv = helpers.to_dev(helpers.inv_freq())
     qr = ib.rope_kv_append(kv, 0, helpers.to_dev(wl.q), helpers.to_dev(wl.k), helpers.to_dev(wl.v), inv, 0)
-    monkeypatch.setenv("INGOT_TEST_STALL_TMA", "50")  # milliseconds
+    assert ib.lib().ingot_kv_test_stall_prefill(kv.handle, 50) == 0  # milliseconds; this handle only
     ib.attn_prefill(kv, 0, qr, 0, impl=2)
     torch.cuda.synchronize()
     assert kv.status() == 4  # kDevErrBarrierTimeout
-    monkeypatch.delenv("INGOT_TEST_STALL_TMA")
+    assert ib.lib().ingot_kv_test_stall_prefill(kv.handle, 0) == 0
     out = ib.attn_prefill(kv, 0, qr, 0, impl=2)
     torch.cuda.synchronize()
     assert kv.status() == 0
     helpers.assert_parity(out.cpu().numpy(), want, "prefill after an expired wait")
+
+
+def test_gather_signal_and_bounded_wait():
+    """The signalling form of the fused gather on one GPU. The call writes this GPU's own buffer and signals slot 0
+    of a two-slot counter array. A wait for ONE source completes, takes the signal back (counter 0 again) and leaves
+    the status word clear. A wait for TWO sources meets a peer that never signals - the host-made stand-in for a
+    rank that dropped out: it gives up after its limit, raises the timeout bit without hanging or trapping, and the
+    next call on the same handle is correct again."""
+    import torch
+    import ingot_b200 as ib
+    wl = W.c5_prefill32k(seed=9, n_tok=2048)
+    rows = np.array([0, 1, 700, 2047])
+    want, _, _ = helpers.oracle_prefill(wl, rows=rows)
+    kv = ib.KVCache(ib.KV_CONTIGUOUS, 1, HKV, 2048)
+    kv.import_f16(0, helpers.to_dev(wl.k), helpers.to_dev(wl.v), 0)
+    q = helpers.to_dev(wl.q, torch.bfloat16)
+    out = torch.zeros(2048, H, D, device="cuda", dtype=torch.float16)
+    sig = torch.zeros(2, device="cuda", dtype=torch.int32)
+    ib.attn_prefill_gather_signal(kv, 0, q, 0, [out.data_ptr()], [sig.data_ptr()], 0, ib.F16, H, 0)
+    ib.gather_wait(kv, sig, 1, timeout_ms=2000)
+    torch.cuda.synchronize()
+    assert kv.status() == 0 and sig.tolist() == [0, 0]
+    helpers.assert_parity(out[torch.from_numpy(rows).cuda()].float().cpu().numpy(), want, "gather_signal output")
+    # the second source never signals
+    out.zero_()
+    ib.attn_prefill_gather_signal(kv, 0, q, 0, [out.data_ptr()], [sig.data_ptr()], 0, ib.F16, H, 0)
+    ib.gather_wait(kv, sig, 2, timeout_ms=50)
+    torch.cuda.synchronize()
+    assert kv.status() == 4 and sig.tolist() == [0, 0]  # slot 0 was consumed, slot 1 never arrived
+    # and the handle is fine afterwards
+    out.zero_()
+    ib.attn_prefill_gather_signal(kv, 0, q, 0, [out.data_ptr()], [sig.data_ptr()], 0, ib.F16, H, 0)
+    ib.gather_wait(kv, sig, 1)
+    torch.cuda.synchronize()
+    assert kv.status() == 0
+    helpers.assert_parity(out[torch.from_numpy(rows).cuda()].float().cpu().numpy(), want, "gather_signal after an expired wait")
