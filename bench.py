@@ -182,7 +182,7 @@ def decode_bytes_per_step():
 def decode_config(world):
     """The workload description both arms (this library and the reference's CPU code) report."""
     return {"workload": "configs[1]: decode @4096 keys, batch 1 per GPU, 28 per-layer caches per step; the 28 layers are "
-                        "independent and run as one launch each on concurrent launch chains (see roofline.launch_chains)",
+                        "independent (as in the reference's abench) and share one grid plus one merge launch",
             "n_layer": N_LAYER, "n_keys": DECODE_KEYS, "n_head": H, "n_head_kv": HKV, "head_dim": D,
             "l2": "inputs larger than L2 (470 MB of KV per step, 28 distinct caches)",
             "parallelism": f"sequence sharding x{world} (one sequence per GPU, no collective)"}
@@ -193,14 +193,6 @@ def prefill_config(S, world):
                          else f"PROFILING CASE: {S}-token causal prefill (not the benchmark configuration)"), "n_tok": S,
             "n_head": H, "n_head_kv": HKV, "head_dim": D, "l2": "inputs larger than L2 (q+out 400 MB, K/V 134 MB)",
             "parallelism": f"KV-head sharding x{world}"}
-
-
-def decode_chains(n_layers):
-    """Launch chains ingot_attn_decode_layers uses for n_layers (csrc/kv_cache.cu: up to INGOT_DECODE_STREAMS, default 8,
-    then as few as give the same number of rounds)."""
-    cap = min(max(int(os.environ.get("INGOT_DECODE_STREAMS", "8")), 1), 8, n_layers)
-    rounds = -(-n_layers // cap)
-    return -(-n_layers // rounds)
 
 
 def captured(fn):
@@ -240,7 +232,6 @@ def run_decode(args, rank, world):
     # The 28 launches of a step are captured once in a CUDA graph (the reference encodes them into one
     # command buffer, src/metal_backend.mm:594-649); a step is one replay.
     step = launch_layers if args.no_graph else captured(launch_layers)
-    chains = decode_chains(N_LAYER)
 
     with ClockSampler(torch.cuda.current_device()) as clk:  # clocks are sampled while the timed region runs
         t = timed(step, args.steps, args.warmup, world, 0.0 if args.no_graph else MIN_TIMED_S)
@@ -258,7 +249,7 @@ def run_decode(args, rank, world):
            "within_tolerance": all(e["within_tolerance"] for e in errs),
            "checked": "layers 0 (the configs[1] seed-1 tensors), 14 and 27 of the timed call against the CPU reference"}
 
-    launches = args.steps * t["blocks"] * N_LAYER  # one launch per layer: splits and their merge in the same kernel
+    launches = args.steps * t["blocks"] * 2  # per step: one grid with every layer's split CTAs, one merge launch
     bytes_step = decode_bytes_per_step()
     value = world * bytes_step * args.steps / (ms * 1e-3) / 1e9
     per_launch_s = ms * 1e-3 / (args.steps * N_LAYER)
@@ -268,33 +259,23 @@ def run_decode(args, rank, world):
                 "frac": round(achieved / peaks["hbm_gbs"], 4), "traffic": NCU_TRAFFIC["attn_decode_kernel"],
                 "kernel": "attn_decode_kernel", "peak_source": f"of {peaks['source']} (STREAM-style copy)",
                 "frac_of_nominal_8000": round(achieved / 8000.0, 4),
-                "algorithmic_bytes_per_launch": bytes_step // N_LAYER, "us_per_launch": round(per_launch_s * 1e6, 3),
-                "launch_chains": chains,
-                "note": "us_per_launch is step time / 28 with `launch_chains` launches in flight, not one kernel's duration"}
+                "algorithmic_bytes_per_launch": bytes_step, "us_per_launch": round(ms * 1e3 / args.steps, 3),
+                "us_per_layer": round(per_launch_s * 1e6, 3),
+                "note": "one grid carries the split CTAs of all 28 layers (algorithmic bytes per launch = 28 x 16 777 216); "
+                        "us_per_layer is step time / 28. In a forward pass the layers depend on one another: see "
+                        "in_backend_us_per_layer"}
 
-    # The same 28 layers in the two forms a forward pass can use (its layers depend on one another):
-    # one launch chain, and one ingot_attn_decode call per layer on one stream (what the Backend issues).
+    # The same 28 layers the way a forward pass has to run them (its layers depend on one another): one
+    # ingot_attn_decode call per layer on one stream, i.e. a split launch and a merge launch per layer.
     if not args.no_graph and not args.no_secondary:
-        prev = os.environ.get("INGOT_DECODE_STREAMS")
-        os.environ["INGOT_DECODE_STREAMS"] = "1"
-        try:
-            t1 = timed(captured(launch_layers), args.steps, 3, world, 0.1)
-        finally:
-            if prev is None:
-                del os.environ["INGOT_DECODE_STREAMS"]
-            else:
-                os.environ["INGOT_DECODE_STREAMS"] = prev
-
         def per_layer_calls():
             for l in range(N_LAYER):
                 ib.attn_decode(kv, l, q[l], out=out[l], max_seq_len=DECODE_KEYS, chunk_keys=args.chunk_keys)
 
-        t2 = timed(captured(per_layer_calls), args.steps, 3, world, 0.1)
-        layer_bytes = bytes_step / N_LAYER
-        for name, tt in (("single_chain", t1), ("in_backend", t2)):
-            us = tt["ms"] * 1e3 / (args.steps * N_LAYER)
-            roofline[name + "_us_per_layer"] = round(us, 3)
-            roofline[name + "_gbs"] = round(layer_bytes / (us * 1e-6) / 1e9, 1)
+        t2 = timed(captured(per_layer_calls), args.steps, 3, world, min(0.1, MIN_TIMED_S))
+        us = t2["ms"] * 1e3 / (args.steps * N_LAYER)
+        roofline["in_backend_us_per_layer"] = round(us, 3)
+        roofline["in_backend_gbs"] = round(bytes_step / N_LAYER / (us * 1e-6) / 1e9, 1)
 
     # End to end through the host-buffer C-ABI call: per layer q/k/v rows host->device, RoPE+append,
     # decode at position 4095 (4096 keys), output device->host; one synchronisation per step.
@@ -308,11 +289,11 @@ def run_decode(args, rank, world):
         ib.attn_layers_host(kv, 0, qh, kh, vh, oh, inv, DECODE_KEYS - 1)
         torch.cuda.current_stream().synchronize()
 
-    te = timed(step_e2e, args.steps, args.warmup, world, 0.0 if args.no_graph else 0.25)
+    te = timed(step_e2e, args.steps, args.warmup, world, 0.0 if args.no_graph else min(0.25, MIN_TIMED_S))
     ms_e2e = te["ms"]
     e2e = {"value": round(world * bytes_step * args.steps / (ms_e2e * 1e-3) / 1e9, 1), "unit": "GB/s",
            "h2d_bytes_per_step": int(N_LAYER * (H + 2 * HKV) * D * 4 + 8), "d2h_bytes_per_step": int(N_LAYER * H * D * 4),
-           "ms_per_step": round(ms_e2e / args.steps, 4), "gpu_launches_per_step": 1 + N_LAYER,
+           "ms_per_step": round(ms_e2e / args.steps, 4), "gpu_launches_per_step": 3,
            "timed_region_s": te["timed_region_s"]}
     assert kv.status() == 0
     return {"metric": "decode attention KV-cache HBM GB/s (4096 keys, 24q/8kv heads, d128, f16 KV, 28 layers)",
@@ -400,9 +381,9 @@ def run_prefill(args, rank, world):
 
     steps = max(1, min(args.steps, args.prefill_steps))
     with ClockSampler(torch.cuda.current_device()) as clk:
-        t = timed(step, steps, args.warmup, world)
+        t = timed(step, steps, args.warmup, world, MIN_TIMED_S)
     ms = t["ms"]
-    tk = t if world == 1 else timed(step_kernel_only, steps, 3, world, 0.1)
+    tk = t if world == 1 else timed(step_kernel_only, steps, 3, world, min(0.1, MIN_TIMED_S))
     ms_kernel = tk["ms"]
     assert kv.status() == 0
 
@@ -443,7 +424,7 @@ def run_prefill(args, rank, world):
         oh.copy_(out, non_blocking=True)
         torch.cuda.current_stream().synchronize()
 
-    te = timed(step_e2e, min(steps, 5), 1, world, 0.1)
+    te = timed(step_e2e, min(steps, 5), 1, world, min(0.1, MIN_TIMED_S))
     ms_e2e = te["ms"] / min(steps, 5)
     e2e = {"value": round(flops / (ms_e2e * 1e-3) / 1e12, 1), "unit": "TFLOP/s",
            "h2d_bytes_per_step": int(q.numel() * 2), "d2h_bytes_per_step": int(out.numel() * 2),
@@ -545,7 +526,7 @@ def run_chunked(args, rank, world, wl, label):
                 ib.attn_prefill(kv, l, qr, pos0, out=out[l], impl=impl)
         # One CUDA graph per step (the 28 layers' launches), so that Python launch overhead is not timed.
         step = launch_layers if args.no_graph else captured(launch_layers)
-        t = timed(step, steps, args.warmup, world, 0.1)
+        t = timed(step, steps, args.warmup, world, min(0.1, MIN_TIMED_S))
         res[impl] = t["ms"] / steps / N_LAYER
         torch.cuda.synchronize()
         if rank == 0:
@@ -597,7 +578,7 @@ def run_batched_decode(args, rank, world):
 
     step = launch if args.no_graph else captured(launch)
     with ClockSampler(torch.cuda.current_device()) as clk:
-        t = timed(step, args.steps, args.warmup, world, 0.25)
+        t = timed(step, args.steps, args.warmup, world, min(0.25, MIN_TIMED_S))
     ms = t["ms"]
     assert kv.status() == 0
     # Parity outside the timed region: this rank's shortest, longest and one middle sequence of the last layer.
@@ -631,7 +612,7 @@ def run_batched_decode(args, rank, world):
             "roofline": {"bound": "hbm", "achieved": round(per_gpu, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
                          "frac": round(per_gpu / peaks["hbm_gbs"], 4), "traffic": None, "kernel": "attn_decode_kernel",
                          "note": "per GPU, on the most loaded rank"},
-            "gpu_launches": args.steps * t["blocks"] * n_layers, "clocks": clk.summary(),
+            "gpu_launches": args.steps * t["blocks"] * 2, "clocks": clk.summary(),
             "parity": {"max_abs": float(par[0].item()), "rel_l2": float(par[1].item()),
                        "within_tolerance": bool(par[0].item() <= 2e-3 and par[1].item() <= 1e-3),
                        "checked": "shortest, median and longest sequence of every rank (last layer) against the CPU reference"},
@@ -789,9 +770,13 @@ def main():
                     help="prefill at N > 1: kernel + NCCL all-gather instead of the fused peer-store epilogue")
     ap.add_argument("--gather-barrier", default="signal", choices=["signal", "nccl"],
                     help="prefill at N > 1: completion of the fused gather by in-kernel signals (default) or a 1-element NCCL all-reduce")
+    ap.add_argument("--min-timed-s", type=float, default=MIN_TIMED_S,
+                    help="minimum length of the headline timed region; 0 for a profiling run that should launch little")
     ap.add_argument("--no-graph", action="store_true", help="decode: launch the 28 layers from Python instead of replaying a CUDA graph")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
+    global MIN_TIMED_S
+    MIN_TIMED_S = args.min_timed_s
 
     if args.impl == "reference":
         line = run_reference(args)

@@ -21,6 +21,13 @@
  *   - The cache is a pure function of (layer, position): positions may be rewritten in any order
  *     and the caller owns the notion of sequence length (src/main.cpp:295,374-375 rewind `pos`
  *     without telling the backend).
+ *   - Scratch. The decode, prefill and host-buffer calls keep scratch on the handle, sized on first use and
+ *     grown when a later call needs more (nothing is ever freed before ingot_kv_destroy). Growing
+ *     allocates device memory, which is not allowed while a stream is being captured: run a call once
+ *     eagerly with the largest shape before capturing it into a CUDA graph. Graphs captured earlier stay
+ *     valid across a later growth.
+ *   - A handle belongs to the device that was current at ingot_kv_create; calls with another device
+ *     current are rejected with INGOT_ERR_INVALID.
  */
 #ifndef INGOT_CUDA_H
 #define INGOT_CUDA_H
@@ -53,6 +60,9 @@ const char* ingot_status_string(int status);
 const char* ingot_last_error(void);
 /* Library build: compiled architecture string, e.g. "sm_100a". */
 const char* ingot_build_arch(void);
+/* Build variant: "" for the production library, "bounds-check" for the build whose kernels range-check every
+ * offset they compute (see ingot_kv_test_shrink_extent). */
+const char* ingot_build_flags(void);
 
 /* ---- KV cache ------------------------------------------------------------------------------
  * Replaces the cache the reference backends own (src/backend.h:1; CPU: src/cpu_backend.h:23,
@@ -74,6 +84,11 @@ int ingot_kv_status(ingot_kv* kv, void* stream, int* status_out);
  * returns normally and status bit 4 is raised; 0 restores normal operation. Lets a test exercise the
  * bounded-wait exit without hanging or faulting anything. */
 int ingot_kv_test_stall_prefill(ingot_kv* kv, int stall_ms);
+/* TEST HOOK of the bounds-check build (no reference counterpart; no effect in the production library): the
+ * kernels' range checks treat each cache layer as only `elems` f16 elements long (0 restores the real extent).
+ * Accesses beyond that - which are inside the real allocation - are then skipped and raise status bit 8, which
+ * shows that the checks are live without any access ever leaving a buffer. */
+int ingot_kv_test_shrink_extent(ingot_kv* kv, size_t elems);
 
 /* ---- K1: fused RoPE + K/V append -------------------------------------------------------------
  * Replaces ops::rope on q and k plus the cache memcpy (src/ops.cpp:243-255,
@@ -118,8 +133,9 @@ int ingot_attn_decode(ingot_kv* kv, int layer, const void* q_dev, int q_dtype, v
 /* The same for `layer_count` consecutive layers in one call, with the same lengths and block tables:
  * q_dev [layer_count][n_seq][n_head][128], out_dev likewise. This is the shape of the reference's
  * decode-attention microbenchmark, which encodes every layer's attention for one token into one
- * command buffer (src/metal_backend.mm:594-649, src/main.cpp:441-449). The launches are chained with
- * programmatic dependent launch: a layer's K/V loads overlap the previous layer's split merge. */
+ * command buffer (src/metal_backend.mm:594-649, src/main.cpp:441-449). The layers are independent, so the
+ * split CTAs of all of them form ONE grid (no launch boundary between layers) and a second launch merges the
+ * split partials; ingot_attn_decode is the same with layer_count 1. */
 int ingot_attn_decode_layers(ingot_kv* kv, int layer_begin, int layer_count, const void* q_dev, int q_dtype,
                              void* out_dev, int out_dtype, int n_head, int n_seq, const int32_t* seq_lens_dev,
                              int max_seq_len, const int32_t* block_tables_dev, int max_blocks_per_seq,
@@ -187,6 +203,27 @@ int ingot_attn_prefill_gather_signal(ingot_kv* kv, int layer, const void* q_dev,
                                      void* const* signal_ptrs, int n_out, int src_index, int out_dtype, int n_head,
                                      int out_n_head, int out_head0, int q_pos0, int n_tok, void* stream);
 int ingot_gather_wait(ingot_kv* kv, void* counters_dev, int n_src, int timeout_ms, void* stream);
+
+/* ---- Several GPUs from one process (no counterpart in the reference, which is single-device) ---------------
+ * A handle that shards a long prefill by KV head over the first n_dev GPUs of this machine: it enables peer
+ * access, creates on every GPU a cache shard with n_head_kv / n_dev heads (ingot_mg_kv(dev): fill it with
+ * ingot_rope_kv_append / ingot_kv_import_f16 with that device current, that GPU's heads only), a token-major
+ * destination buffer [n_ctx][n_head][128] (ingot_mg_out(dev)) and a counter array, and a stream (ingot_mg_stream).
+ * ingot_mg_prefill runs ingot_attn_prefill_gather_signal on every GPU (q_dev[d]: GPU d's query heads
+ * [n_tok][n_head / n_dev][128], on GPU d) and the bounded ingot_gather_wait behind it, synchronises, and returns
+ * INGOT_OK when every GPU's buffer holds all heads of rows q_pos0..q_pos0+n_tok-1 (stored from row 0 of the buffer),
+ * or INGOT_ERR_DEVICE if a wait for a peer ran out after timeout_ms. Needs peer access between all pairs. */
+typedef struct ingot_mg ingot_mg;
+int ingot_mg_create(ingot_mg** out, int n_dev, int n_layer, int n_head, int n_head_kv, int n_ctx, int out_dtype);
+void ingot_mg_destroy(ingot_mg* mg);
+ingot_kv* ingot_mg_kv(ingot_mg* mg, int dev);
+void* ingot_mg_out(ingot_mg* mg, int dev);
+void* ingot_mg_stream(ingot_mg* mg, int dev);
+int ingot_mg_prefill(ingot_mg* mg, int layer, const void* const* q_dev, int q_dtype, int q_pos0, int n_tok, int timeout_ms);
+/* Length-balanced assignment of n_seq sequences (key counts lens[]) to n_ranks GPUs for the sequence-sharded
+ * batched decode: longest first, each to the least loaded rank (ties to the lower rank). rank_of_seq[i] receives
+ * the rank of sequence i. Pure host code. */
+int ingot_lpt_assign(const int32_t* lens, int n_seq, int n_ranks, int32_t* rank_of_seq);
 
 /* ---- Host-buffer convenience call ---------------------------------------------------------------
  * One layer of the reference's attention stage with HOST inputs/outputs, as a CPU-side caller sees

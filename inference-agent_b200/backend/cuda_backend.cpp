@@ -402,8 +402,13 @@ public:
         if (multi) {  // logits for every row: each belongs to another sequence
             cuda_check(ingot_support_rmsnorm(h_, x_, output_norm_, n, c.n_embd, c.rms_eps, stream_), "rmsnorm");
             const DevWeight* wl[1] = {&output_};
-            if (n == 1) linear(logits_dev_, output_, h_, 1, false);
-            else linear_group(&logits_dev_, wl, 1, h_, n, false);
+            if (n < 16 && output_.qtype >= 0) {  // few rows of a quantised matrix: one dequantise-in-GEMV pass per row
+                for (int i = 0; i < n; i++) linear(logits_dev_ + size_t(i) * c.n_vocab, output_, h_ + size_t(i) * c.n_embd, 1, false);
+            } else if (n == 1) {
+                linear(logits_dev_, output_, h_, 1, false);
+            } else {
+                linear_group(&logits_dev_, wl, 1, h_, n, false);
+            }
             return;
         }
         // Logits for the last token only.
@@ -520,7 +525,9 @@ private:
             loader_->copy(raw_tmp_, t.data, t.nbytes());
             if (quant) cuda_check(ingot_quant_repack(w.data, raw_tmp_, type, w.n_in, w.n_out, loader_->stream()), "repack");
             else cuda_check(ingot_quant_bf16_to_f32(static_cast<float*>(w.data), raw_tmp_, size_t(w.n_in) * w.n_out, loader_->stream()), "bf16 -> f32");
-            if (quant && w.n_in * size_t(w.n_out) > max_quant_elems_ && &t != m_.output && &t != m_.tok_embd) max_quant_elems_ = w.n_in * size_t(w.n_out);
+            // the output / embedding matrix is expanded only by the batched form with at least 16 rows per step
+            const bool layer_matrix = &t != m_.output && &t != m_.tok_embd;
+            if (quant && w.n_in * size_t(w.n_out) > max_quant_elems_ && (layer_matrix || max_seqs_ >= 16)) max_quant_elems_ = w.n_in * size_t(w.n_out);
             return w;
         }
         cuda_check(cudaMalloc(&w.data, t.nbytes()), "cudaMalloc(weight)");

@@ -4,16 +4,15 @@
 // (src/cpu_backend.cpp:51-69) and Metal's attn_decode_g3 + attn_combine pair
 // (shaders/kernels.metal:428-516, dispatch src/metal_backend.mm:340-360).
 //
-// Work decomposition. grid = (splits, kv heads, sequences). A CTA owns one KV head of one sequence
-// over one split of `chunk_keys` keys and serves ALL query heads that share that KV head (GQA), so
+// Work decomposition. grid = (splits, kv heads, layers x sequences). A CTA owns one KV head of one sequence
+// of one layer over one split of `chunk_keys` keys and serves ALL query heads that share that KV head (GQA), so
 // every K/V byte is fetched from HBM exactly once. Inside the CTA each warp walks its own 16-key
 // units with a private online-softmax state (m, l, o); the warp states are merged through shared
-// memory and the split's partial (o[128], m, l per head) goes to a global scratch. The partials are
-// merged with the attn_combine formula, out = sum_s o_s 2^(m_s-M) / sum_s l_s 2^(m_s-M), inside the
-// same launch: every split CTA of a (sequence, kv head) takes a ticket after its partial is fenced,
-// and the CTA that draws the last ticket reads all partials back from L2 and writes the output, so a
-// decode is ONE launch with no dependency on the launch before or after it. (Callers that bring
-// their own scratch without arrival counters use a second, merge-only launch of the same kernel.)
+// memory and the split's partial (o[128], m, l per head) goes to a global scratch. A small combine
+// kernel chained behind it with programmatic dependent launch merges the partials:
+// out = sum_s o_s 2^(m_s-M) / sum_s l_s 2^(m_s-M), the attn_combine formula. Split CTAs therefore
+// retire as soon as their partial is written (no fence, ticket or polling), and the combine of one
+// launch overlaps the K/V loads of the next.
 //
 // Data path. HBM-bound: 2 * len * 128 * 2 B per (sequence, kv head). Every lane issues 16-byte
 // loads straight from global memory into registers, 16 of them (one whole 16-key unit, 8 KB per
@@ -27,10 +26,8 @@
 // f16; scaling late keeps the error inside the f32-reference tolerance).
 #include "attn_common.cuh"
 #include "ingot_internal.cuh"
-#include "sm100_ptx.cuh"
 
 #include <algorithm>
-#include <cstring>
 #include <mutex>
 
 namespace {
@@ -46,18 +43,18 @@ struct DecodeParams {
     const int32_t* seq_lens;
     const int32_t* block_tables;
     float* part;          // split role: partials written here
-    const float* c_part;  // combine role: partials being merged (the same buffer when the merge is in-kernel)
+    const float* c_part;  // combine role: partials of the launch being merged
     void* c_out;          // combine role: its output
-    int* sync;            // in-kernel merge: {arrivals, owner} per (sequence, kv head) of this scratch buffer;
-                          // null: partials are left for a merge role of a later launch
-    int tag;              // in-kernel merge: non-zero id of this launch, distinct among launches that may overlap
     int* status;
+    // Several layers in one launch (blockIdx.z = layer * n_seq + sequence): strides between consecutive layers of
+    // the cache (elements), of q and out ([layer][sequence][head][128], elements) and of the partials (floats).
+    int n_seq;
+    size_t cache_layer_stride, qo_layer_stride, part_layer_stride;
+    size_t cache_extent, part_extent, out_extent;  // bounds-check build: elements of one cache layer, floats of the scratch, elements of out
     int q_dtype, out_dtype;
     int n_head, n_head_kv, group;
     int capacity, paged, max_blocks_per_seq;
     int len0, chunk_keys, n_parts_max;
-    int stages, ring_off;              // ring form: stages of 8 KB, byte offset of the ring in shared memory
-    unsigned long long wait_limit_ns;  // ring form: bound of every mbarrier wait
     int early_loads;  // the K/V rows and q read here are not written by the preceding kernel in the stream
     int split_parts;  // grid.x values below this are split CTAs; the one CTA above it (if any) merges
     float scale_log2;
@@ -80,7 +77,7 @@ __device__ __forceinline__ int load_seq_len(const DecodeParams& p, int seq) {
 // sequence) of the launch that FOLLOWS the one that wrote the partials (or of a merge-only launch):
 // programmatic dependent launch orders it behind that launch, so no fences, tickets or polling are
 // involved, and the merge overlaps the K/V loads of the split CTAs it shares the grid with.
-__device__ __forceinline__ void combine_splits(const DecodeParams& p, float* smem, int kvh, int seq) {
+__device__ __forceinline__ void combine_splits(const DecodeParams& p, float* smem, int kvh, int layer, int seq) {
     const int n_keys = load_seq_len(p, seq);
     if (n_keys < 1) return;
     const int n_chunks = (n_keys + p.chunk_keys - 1) / p.chunk_keys;
@@ -97,7 +94,13 @@ __device__ __forceinline__ void combine_splits(const DecodeParams& p, float* sme
     const bool active = slot < slots;
     const int gi_t = pair >> 5, col = pair & 31;
     const size_t step = (size_t)p.n_head * kPartStride;
-    const float* base = p.c_part + (((size_t)seq * p.n_parts_max) * p.n_head + (size_t)kvh * G) * kPartStride;
+    const size_t part0 = (size_t)layer * p.part_layer_stride, out0 = (size_t)layer * p.qo_layer_stride;
+    // bounds-check build: the last partial row this merge reads, and the output rows it writes
+    if (!INGOT_CHECK(part0 + (((size_t)seq * p.n_parts_max + (n_chunks - 1)) * p.n_head + (size_t)kvh * G) * kPartStride, (size_t)G * kPartStride,
+                     p.part_extent, p.status) ||
+        !INGOT_CHECK(out0 + ((size_t)seq * p.n_head + (size_t)kvh * G) * kHeadDim, (size_t)G * kHeadDim, p.out_extent, p.status))
+        return;
+    const float* base = p.c_part + part0 + (((size_t)seq * p.n_parts_max) * p.n_head + (size_t)kvh * G) * kPartStride;
     const float* my_rows = base + (size_t)gi_t * kPartStride + col * 4;
 
     float* mg_m = smem;                       // [G][kMaxParts] split maxima, then weights
@@ -187,7 +190,7 @@ __device__ __forceinline__ void combine_splits(const DecodeParams& p, float* sme
             acc.x += x.x; acc.y += x.y; acc.z += x.z; acc.w += x.w;
         }
         const float inv = L > 0.f ? 1.0f / L : 0.f;
-        const size_t e = ((size_t)seq * p.n_head + (size_t)kvh * G + gi) * kHeadDim + cl * 4;
+        const size_t e = out0 + ((size_t)seq * p.n_head + (size_t)kvh * G + gi) * kHeadDim + cl * 4;
         store_out(p.c_out, p.out_dtype, e + 0, acc.x * inv);
         store_out(p.c_out, p.out_dtype, e + 1, acc.y * inv);
         store_out(p.c_out, p.out_dtype, e + 2, acc.z * inv);
@@ -195,58 +198,26 @@ __device__ __forceinline__ void combine_splits(const DecodeParams& p, float* sme
     }
 }
 
-__device__ __forceinline__ unsigned long long globaltimer_now() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-
 struct KRegs { uint4 k[8]; };  // [n-tile 0/1][i=0..3]: key (nt*8 + g), 16-byte chunk (4i + j)
 struct VRegs { uint4 v[8]; };  // [slot 0..3 -> keys 2j, 2j+1, 2j+8, 2j+9][chunk g / g+8]
 
-__device__ __forceinline__ uint4 lds16(uint32_t addr) {
-    uint4 r;
-    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "r"(addr));
-    return r;
-}
-
-// Bulk copy global -> shared memory (16-byte aligned on both sides, size a multiple of 16), completing
-// `bytes` on the mbarrier at `bar`. This GPU's own memory only; no multicast.
-__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
-}
-
-constexpr int kUnitBytes = 16 * kHeadDim * 2;  // the K (or V) rows of one 16-key unit: 4 KB, contiguous in both layouts
-constexpr int kRingWarps = 4;                  // consumer warps of the ring form (one more warp feeds the ring)
-constexpr int kRingThreads = (kRingWarps + 1) * 32;
-constexpr int kMaxStages = 16;
-
-// Two forms of the same kernel.
-//   kRing = false: every lane loads its MMA fragments straight from global memory into registers, two units
-//                  (16 KB per warp) ahead. No shared-memory staging; ~250 registers per thread.
-//   kRing = true:  a producer warp streams the CTA's units through a shared-memory ring with bulk copies
-//                  (cp.async.bulk, 4 KB of K and 4 KB of V per stage, completion on an mbarrier); four consumer
-//                  warps take the units round-robin and read the same 16-byte fragments from shared memory.
-//                  The bytes in flight then cost no registers: a CTA keeps `stages` x 8 KB requested from its
-//                  first cycle on, and three CTAs fit an SM, so one CTA's start-up and merge tail are covered
-//                  by the others' streaming.
-template <bool kRing>
-__global__ void __launch_bounds__(kRing ? kRingThreads : kMaxDecodeWarps * 32, kRing ? 3 : 1)
-attn_decode_kernel(const DecodeParams p) {
-    extern __shared__ __align__(128) float smem[];
+__global__ void __launch_bounds__(kMaxDecodeWarps * 32, 1) attn_decode_kernel(const DecodeParams p) {
+    extern __shared__ float smem[];
     // Programmatic dependent launch: let the next kernel in the stream start as soon as SM resources
     // allow. Unless the caller vouches that nothing read here was written by the preceding kernel,
-    // wait for that kernel before the first global read.
+    // wait for that kernel before the first global read; otherwise only before the first global write
+    // (the split scratch and the output are shared with it).
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     if ((int)blockIdx.x >= p.split_parts) {  // merge role: partials of the preceding launch
         asm volatile("griddepcontrol.wait;" ::: "memory");
-        combine_splits(p, smem, blockIdx.y, blockIdx.z);
+        combine_splits(p, smem, blockIdx.y, blockIdx.z / p.n_seq, blockIdx.z % p.n_seq);
         return;
     }
     if (!p.early_loads) asm volatile("griddepcontrol.wait;" ::: "memory");
 
-    const int chunk = blockIdx.x, kvh = blockIdx.y, seq = blockIdx.z;
+    const int chunk = blockIdx.x, kvh = blockIdx.y, layer = blockIdx.z / p.n_seq, seq = blockIdx.z % p.n_seq;
+    const __half* const kc = p.kc + (size_t)layer * p.cache_layer_stride;
+    const __half* const vc = p.vc + (size_t)layer * p.cache_layer_stride;
     const int n_keys = load_seq_len(p, seq);
     if (n_keys < 1) return;
     const int n_chunks = (n_keys + p.chunk_keys - 1) / p.chunk_keys;
@@ -255,15 +226,7 @@ attn_decode_kernel(const DecodeParams p) {
     const int k_end = min(n_keys, k_begin + p.chunk_keys);
     const int n_units = (k_end - k_begin + 15) >> 4;
 
-    // In-kernel merge: the scratch rows of this (sequence, kv head) belong to one launch at a time. The
-    // first CTA to get here claims them for this launch's tag (the merging CTA of the previous user
-    // releases them when it has read its partials). The claim is requested now, so that its round trip
-    // to L2 hides behind the K/V loads, and looked at just before the partial is written.
-    int* const slot = (p.sync && n_chunks > 1) ? p.sync + 2 * ((size_t)seq * p.n_head_kv + kvh) : nullptr;
-    int claim = 0;
-    if (slot && threadIdx.x == 0) claim = atomicCAS(slot + 1, 0, p.tag);
-
-    const int n_warps = kRing ? kRingWarps : (int)(blockDim.x >> 5);  // warps that walk keys
+    const int n_warps = blockDim.x >> 5;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, j = lane & 3;
     const int G = p.group;
@@ -272,21 +235,21 @@ attn_decode_kernel(const DecodeParams p) {
 
     // Base element offset (within the layer) of the 16 rows of unit u; keys of a unit are contiguous
     // rows in both layouts (a unit is exactly one block of a paged cache).
-    auto unit_base_of_block = [&](int key0, int blk) -> size_t {
+    auto unit_base = [&](int u) -> size_t {
+        const int key0 = k_begin + (u << 4);
         if (!p.paged) return kv_row_offset_contig(p.capacity, kvh, key0);
+        int blk = bt[key0 >> 4];
         if (blk < 0 || blk >= p.capacity) {
-            atomicOr(p.status, kDevErrBlockRange);
+            if (lane == 0) atomicOr(p.status, kDevErrBlockRange);
             blk = 0;
         }
         return kv_row_offset_paged(p.n_head_kv, blk, kvh, 0);
     };
-    auto unit_base = [&](int u) -> size_t {
-        const int key0 = k_begin + (u << 4);
-        return unit_base_of_block(key0, p.paged ? bt[key0 >> 4] : 0);
-    };
     auto load_k = [&](KRegs& r, int u) {
         const int last = n_keys - 1 - (k_begin + (u << 4));  // last valid row of this unit (>= 0)
-        const __half* kb = p.kc + unit_base(u);
+        const size_t ub = unit_base(u);
+        if (!INGOT_CHECK(ub, (size_t)(last + 1 < 16 ? last + 1 : 16) * kHeadDim, p.cache_extent, p.status)) return;
+        const __half* kb = kc + ub;
 #pragma unroll
         for (int nt = 0; nt < 2; nt++) {
             const int row = min(nt * 8 + g, last);
@@ -296,29 +259,14 @@ attn_decode_kernel(const DecodeParams p) {
     };
     auto load_v = [&](VRegs& r, int u) {
         const int last = n_keys - 1 - (k_begin + (u << 4));
-        const __half* vb = p.vc + unit_base(u);
+        const size_t ub = unit_base(u);
+        if (!INGOT_CHECK(ub, (size_t)(last + 1 < 16 ? last + 1 : 16) * kHeadDim, p.cache_extent, p.status)) return;
+        const __half* vb = vc + ub;
 #pragma unroll
         for (int s = 0; s < 4; s++) {
             const int row = min(2 * j + (s & 1) + (s >> 1) * 8, last);
             r.v[s * 2 + 0] = ld_stream16(vb + (size_t)row * kHeadDim + g * 8);
             r.v[s * 2 + 1] = ld_stream16(vb + (size_t)row * kHeadDim + (g + 8) * 8);
-        }
-    };
-    // The same fragments out of a ring stage (K rows at `kb`, V rows at `vb`, 256 bytes per row).
-    auto lds_k = [&](KRegs& r, uint32_t kb, int last) {
-#pragma unroll
-        for (int nt = 0; nt < 2; nt++) {
-            const int row = min(nt * 8 + g, last);
-#pragma unroll
-            for (int i = 0; i < 4; i++) r.k[nt * 4 + i] = lds16(kb + row * 256 + (4 * i + j) * 16);
-        }
-    };
-    auto lds_v = [&](VRegs& r, uint32_t vb, int last) {
-#pragma unroll
-        for (int s = 0; s < 4; s++) {
-            const int row = min(2 * j + (s & 1) + (s >> 1) * 8, last);
-            r.v[s * 2 + 0] = lds16(vb + row * 256 + g * 16);
-            r.v[s * 2 + 1] = lds16(vb + row * 256 + (g + 8) * 16);
         }
     };
 
@@ -394,99 +342,24 @@ attn_decode_kernel(const DecodeParams p) {
                       prmt(vc1[w], vd1[w], sel), pa0, pa2);
         }
     };
-    auto load_q = [&]() {
-        // Query fragments (head row g, chunks 4i + j).
-        if (g < G) {
-            const size_t qbase = ((size_t)seq * p.n_head + (size_t)kvh * G + g) * kHeadDim;
-#pragma unroll
-            for (int i = 0; i < 4; i++) qa[i] = load_q8(p.q, p.q_dtype, qbase + (size_t)(4 * i + j) * 8);
-        }
-    };
 
-    if constexpr (kRing) {
-        // ---- ring form ----
-        // shared memory: [merge area p.ring_off bytes][stages x {K 4 KB, V 4 KB}][full[], empty[] mbarriers, abort flag]
-        const int S = p.stages;
-        const uint32_t ring = smem_u32(smem) + p.ring_off;
-        const uint32_t bars = ring + S * 2 * kUnitBytes;           // full[s] at bars + 8 s, empty[s] at bars + 8 (S + s)
-        volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(reinterpret_cast<unsigned char*>(smem) + p.ring_off +
-                                                                             S * 2 * kUnitBytes + 16 * S);
-        if (threadIdx.x == 0) {
-            for (int s = 0; s < 2 * S; s++) ingot_sm100::mbar_init(bars + 8 * s, 1);
-            *abort_flag = 0;
-            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        }
-        __syncthreads();
-        if (warp == kRingWarps) {
-            // Producer: the whole warp walks the units (paged caches: 32 block-table entries are fetched at a
-            // time, one per lane); lane 0 waits for the stage to be free and issues the two copies. The first
-            // `stages` units need no wait, so the CTA has stages x 8 KB requested a few cycles after it starts.
-            int blk_mine = 0;
-            bool ok = true;
-            for (int u = 0; u < n_units && ok; u++) {
-                if (p.paged && (u & 31) == 0) {
-                    const int b = ((k_begin >> 4) + u + lane);
-                    blk_mine = b < p.max_blocks_per_seq ? bt[b] : 0;
-                }
-                const int blk = p.paged ? __shfl_sync(0xffffffffu, blk_mine, u & 31) : 0;
-                if (lane == 0) {
-                    const int s = u % S;
-                    if (u >= S) ok = ingot_sm100::mbar_wait(bars + 8 * (S + s), (uint32_t)(((u / S) & 1) ^ 1), abort_flag, p.wait_limit_ns);
-                    if (ok) {
-                        const int key0 = k_begin + (u << 4);
-                        const uint32_t bytes = (uint32_t)min(16, n_keys - key0) * 256u;  // only rows that exist
-                        const size_t base = unit_base_of_block(key0, blk);
-                        ingot_sm100::mbar_expect_tx(bars + 8 * s, 2 * bytes);
-                        bulk_load(ring + s * 2 * kUnitBytes, p.kc + base, bytes, bars + 8 * s);
-                        bulk_load(ring + s * 2 * kUnitBytes + kUnitBytes, p.vc + base, bytes, bars + 8 * s);
-                    }
-                }
-                ok = __shfl_sync(0xffffffffu, ok, 0);
-            }
-        } else {
-            load_q();
-            KRegs kr;
-            VRegs vr;
-            for (int u = warp; u < n_units; u += kRingWarps) {
-                const int s = u % S;
-                bool landed = ingot_sm100::mbar_wait(bars + 8 * s, (uint32_t)((u / S) & 1), abort_flag, p.wait_limit_ns);
-                landed = __all_sync(0xffffffffu, landed);  // warp-uniform: the MMAs below need the whole warp
-                if (!landed) break;
-                const int last = n_keys - 1 - (k_begin + (u << 4));
-                const uint32_t kb = ring + s * 2 * kUnitBytes;
-                lds_k(kr, kb, last);
-                compute_qk(kr, u);
-                lds_v(vr, kb + kUnitBytes, last);
-                compute_pv(vr);
-                __syncwarp();
-                if (lane == 0) ingot_sm100::mbar_arrive(bars + 8 * (S + s));  // the stage may be refilled
-            }
-        }
-        __syncthreads();
-        if (*abort_flag) {
-            // A bounded wait ran out (never seen; it would mean a copy that does not land). Flag it, and give copies
-            // that may still be in flight a bounded time to land before the CTA's shared memory is released.
-            if (threadIdx.x == 0) {
-                if (p.status) atomicOr(p.status, kDevErrBarrierTimeout);
-                const unsigned long long t0 = globaltimer_now();
-                for (int u = max(0, n_units - S); u < n_units; u++)
-                    while (!ingot_sm100::mbar_try_wait(bars + 8 * (u % S), (uint32_t)((u / S) & 1)) && globaltimer_now() - t0 < 100000000ull) {}
-            }
-            __syncthreads();
-        }
-    } else {
-        // ---- register form ----
-        // Key loop, software-pipelined two units deep: both the K and the V rows of the warp's next two
-        // 16-key units (16 KB) are requested before anything is consumed, and a unit's registers are
-        // refilled as soon as it has been used. For a 4096-key decode every warp owns at most two units, so
-        // all of its loads are in flight at once and the kernel pays the DRAM latency once.
+    // Key loop, software-pipelined two units deep: both the K and the V rows of the warp's next two
+    // 16-key units (16 KB) are requested before anything is consumed, and a unit's registers are
+    // refilled as soon as it has been used. For a 4096-key decode every warp owns at most two units, so
+    // all of its loads are in flight at once and the kernel pays the DRAM latency once.
+    {
         KRegs k0, k1;
         VRegs v0, v1;
         int u0 = warp, u1 = warp + n_warps;
         if (u0 < n_units) { load_k(k0, u0); load_v(v0, u0); }
         if (u1 < n_units) { load_k(k1, u1); load_v(v1, u1); }
-        // requested after the K/V units so that the wait for them overlaps the K/V latency instead of preceding it
-        load_q();
+        // Query fragments (head row g, chunks 4i + j), requested after the K/V units so that the wait
+        // for them overlaps the K/V latency instead of preceding it.
+        if (g < G) {
+            const size_t qbase = (size_t)layer * p.qo_layer_stride + ((size_t)seq * p.n_head + (size_t)kvh * G + g) * kHeadDim;
+#pragma unroll
+            for (int i = 0; i < 4; i++) qa[i] = load_q8(p.q, p.q_dtype, qbase + (size_t)(4 * i + j) * 8);
+        }
         while (u0 < n_units) {
             compute_qk(k0, u0);
             compute_pv(v0);
@@ -501,7 +374,6 @@ attn_decode_kernel(const DecodeParams p) {
             u1 = u3;
         }
     }
-    const bool walker = warp < n_warps;  // the ring form's producer warp carries no softmax state
     l += __shfl_xor_sync(0xffffffffu, l, 1);
     l += __shfl_xor_sync(0xffffffffu, l, 2);
 
@@ -510,143 +382,67 @@ attn_decode_kernel(const DecodeParams p) {
     float* so = smem;
     float* sm = so + (size_t)n_warps * G * kHeadDim;
     float* sl = sm + n_warps * G;
-    if (walker) {
 #pragma unroll
-        for (int e = 0; e < 2; e++) {
-            const int head = 2 * j + e;
-            if (head < G) {
-                float* dst = so + ((size_t)warp * G + head) * kHeadDim + 8 * g;
-                *reinterpret_cast<float4*>(dst) = make_float4(o[0][e], o[1][e], o[2][e], o[3][e]);
-                *reinterpret_cast<float4*>(dst + 4) = make_float4(o[4][e], o[5][e], o[6][e], o[7][e]);
-                *reinterpret_cast<float4*>(dst + 64) = make_float4(o[0][2 + e], o[1][2 + e], o[2][2 + e], o[3][2 + e]);
-                *reinterpret_cast<float4*>(dst + 68) = make_float4(o[4][2 + e], o[5][2 + e], o[6][2 + e], o[7][2 + e]);
-            }
-        }
-        if (g < G && j == 0) { sm[warp * G + g] = m; sl[warp * G + g] = l; }
-    }
-    if (slot && threadIdx.x == 0 && claim != 0 && claim != p.tag) {
-        // An earlier launch still owns the rows (its merging CTA is running: it is resident, so this
-        // ends). Bounded all the same: after a second the status word is raised and the CTA goes on,
-        // which keeps the arrival counters consistent for the calls that follow.
-        const unsigned long long t0 = globaltimer_now();
-        for (;;) {
-            claim = atomicCAS(slot + 1, 0, p.tag);
-            if (claim == 0 || claim == p.tag) break;
-            if (globaltimer_now() - t0 > 1000000000ull) {
-                if (p.status) atomicOr(p.status, kDevErrBarrierTimeout);
-                break;
-            }
-            __nanosleep(64);
+    for (int e = 0; e < 2; e++) {
+        const int head = 2 * j + e;
+        if (head < G) {
+            float* dst = so + ((size_t)warp * G + head) * kHeadDim + 8 * g;
+            *reinterpret_cast<float4*>(dst) = make_float4(o[0][e], o[1][e], o[2][e], o[3][e]);
+            *reinterpret_cast<float4*>(dst + 4) = make_float4(o[4][e], o[5][e], o[6][e], o[7][e]);
+            *reinterpret_cast<float4*>(dst + 64) = make_float4(o[0][2 + e], o[1][2 + e], o[2][2 + e], o[3][2 + e]);
+            *reinterpret_cast<float4*>(dst + 68) = make_float4(o[4][2 + e], o[5][2 + e], o[6][2 + e], o[7][2 + e]);
         }
     }
+    if (g < G && j == 0) { sm[warp * G + g] = m; sl[warp * G + g] = l; }
     __syncthreads();
-    if (p.early_loads && !p.sync) asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (p.early_loads) asm volatile("griddepcontrol.wait;" ::: "memory");
 
     const bool single = n_chunks == 1;
     const size_t part_row0 = ((size_t)seq * p.n_parts_max + chunk) * p.n_head + (size_t)kvh * G;
+    const size_t part0 = (size_t)layer * p.part_layer_stride, out0 = (size_t)layer * p.qo_layer_stride;
     for (int idx = threadIdx.x; idx < G * kHeadDim; idx += blockDim.x) {
         const int gi = idx >> 7, dim = idx & 127;
         float M = -INFINITY;
         for (int w = 0; w < n_warps; w++) M = fmaxf(M, sm[w * G + gi]);
         float L = 0.f, O = 0.f;
         for (int w = 0; w < n_warps; w++) {
-            const float mw = sm[w * G + gi];
-            const float wgt = mw == -INFINITY ? 0.f : exp2f(mw - M);  // a warp that walked no unit
+            const float wgt = exp2f(sm[w * G + gi] - M);
             L += sl[w * G + gi] * wgt;
             O += so[((size_t)w * G + gi) * kHeadDim + dim] * wgt;
         }
         if (single) {
-            store_out(p.out, p.out_dtype, ((size_t)seq * p.n_head + (size_t)kvh * G + gi) * kHeadDim + dim, O / L);
-        } else {
-            float* row = p.part + (part_row0 + gi) * kPartStride;
+            const size_t e = out0 + ((size_t)seq * p.n_head + (size_t)kvh * G + gi) * kHeadDim + dim;
+            if (INGOT_CHECK(e, 1, p.out_extent, p.status)) store_out(p.out, p.out_dtype, e, O / L);
+        } else if (INGOT_CHECK(part0 + (part_row0 + gi) * kPartStride, kPartStride, p.part_extent, p.status)) {
+            float* row = p.part + part0 + (part_row0 + gi) * kPartStride;
             row[dim] = O;
             if (dim == 0) { row[128] = M; row[129] = L; }
         }
     }
-    if (slot) {
-        // Ticket: partial fenced, then one arrival per CTA; the CTA that draws the last ticket merges.
-        __shared__ int s_ticket;
-        __threadfence();
-        __syncthreads();
-        if (threadIdx.x == 0) s_ticket = atomicAdd(slot, 1);
-        __syncthreads();
-        if (s_ticket == n_chunks - 1) {
-            __threadfence();
-            combine_splits(p, smem, kvh, seq);
-            __syncthreads();
-            if (threadIdx.x == 0) {  // counter back to zero, then the rows are released to the next launch
-                slot[0] = 0;
-                __threadfence();
-                atomicExch(slot + 1, 0);
-            }
-        }
-    }
 }
 
-// Tuning knobs, process-wide and read once (like the reference's LLM_ATTN_SPLITS).
-// INGOT_DECODE_IMPL=regs selects the register form of the kernel (default: the shared-memory ring form);
-// INGOT_DECODE_STAGES the ring depth in 8 KB stages; INGOT_DECODE_WARPS (register form) 4 or 8 warps per CTA;
-// INGOT_NO_PDL=1 launches in plain stream order (diagnostics).
-bool decode_use_ring() {
-    static const bool v = [] { const char* e = getenv("INGOT_DECODE_IMPL"); return !(e && strcmp(e, "regs") == 0); }();
-    return v;
-}
-// The ring depth must be a multiple of the consumer warp count: a stage is then always consumed by the same warp,
-// which waits for fill k only after it has consumed fill k-1. (With any other depth two warps share a stage and the
-// one that is ahead would ask the stage's mbarrier for a phase two ahead of the current one; a parity wait cannot
-// tell that from the phase that just completed, the warp would read a stage that has not landed and release it
-// early, and the producer would re-arm a barrier that still has a copy pending.)
-int decode_stages_cfg() {
-    static const int v = [] {
-        const char* e = getenv("INGOT_DECODE_STAGES");
-        const int want = e ? atoi(e) : 8;
-        return std::min(std::max(want / kRingWarps * kRingWarps, kRingWarps), kMaxStages);
-    }();
-    return v;
-}
+// Tuning knob, process-wide and read once (like the reference's LLM_ATTN_SPLITS): warps per CTA, 4 (two CTAs
+// per SM) or 8.
 int decode_warps_cfg() {
     static const int v = [] { const char* e = getenv("INGOT_DECODE_WARPS"); return (e && atoi(e) == 8) ? 8 : 4; }();
     return v;
 }
-bool decode_use_pdl() {
-    static const bool v = getenv("INGOT_NO_PDL") == nullptr;
-    return v;
-}
-
-// Shared memory of one CTA: the area the warps' states and the split merge use, then (ring form) the ring and
-// its barriers.
-struct DecodeSmem { size_t merge_bytes, total_bytes; int threads; };
-DecodeSmem decode_smem(int group, bool ring) {
-    const int n_warps = ring ? kRingWarps : decode_warps_cfg();
-    const int threads = ring ? kRingThreads : n_warps * 32;
-    const size_t split = (size_t)n_warps * group * (kHeadDim + 2);
-    const size_t merge = (size_t)2 * group * kMaxParts + (size_t)4 * std::max(threads, group * 32);
-    DecodeSmem r;
-    r.threads = threads;
-    r.merge_bytes = (std::max(split, merge) * sizeof(float) + 127) / 128 * 128;
-    r.total_bytes = ring ? r.merge_bytes + (size_t)decode_stages_cfg() * (2 * kUnitBytes + 16) + 16 : r.merge_bytes;
-    return r;
-}
 
 }  // namespace
 
-// Split size and split count of a decode call. Small jobs: fill every CTA slot of the GPU once with whole 16-key
-// units per warp. Large jobs: 512 keys per split, which keeps variable-length batches balanced across SMs.
-// `concurrency` launches share the GPU (the multi-layer call keeps several layers in flight).
-DecodePlan decode_plan(const ingot_kv* kv, int n_seq, int max_seq_len, int chunk_keys, int concurrency, int n_head) {
-    const bool ring = decode_use_ring();
-    const int n_warps = ring ? kRingWarps : decode_warps_cfg();
-    int ctas_per_sm = 8 / n_warps;  // register form: ~250 registers per thread, an SM holds 8 warps
-    if (ring) {
-        const size_t per_cta = decode_smem(n_head / kv->n_head_kv, true).total_bytes + 1024;
-        ctas_per_sm = (int)std::min<size_t>(3, std::max<size_t>(1, (size_t)227 * 1024 / per_cta));
-    }
+// Split size and split count of a decode call over n_units = layers x sequences x kv heads independent key ranges
+// of up to max_seq_len keys. Small jobs: fill every CTA slot of the GPU once (the kernel needs ~245 registers per
+// thread, so an SM holds 8 warps) with whole 16-key units per warp. Large jobs: 512 keys per split (256 when several
+// layers share a launch), which keeps variable-length batches balanced across SMs and the last wave short.
+DecodePlan decode_plan(const ingot_kv* kv, int n_layers, int n_seq, int max_seq_len, int chunk_keys) {
+    const int n_warps = decode_warps_cfg();
     if (chunk_keys == 0) {
-        const int slots = kv->num_sms * ctas_per_sm / std::max(1, concurrency);
-        const int per_head = std::max(1, slots / (n_seq * kv->n_head_kv));
+        const int slots = kv->num_sms * (8 / n_warps);
+        const long long ranges = (long long)n_layers * n_seq * kv->n_head_kv;
+        const int per_range = (int)std::max<long long>(1, slots / ranges);
         const int quantum = n_warps * 16;
-        chunk_keys = ((max_seq_len + per_head - 1) / per_head + quantum - 1) / quantum * quantum;
-        chunk_keys = std::min(std::max(chunk_keys, quantum), 512);
+        chunk_keys = ((max_seq_len + per_range - 1) / per_range + quantum - 1) / quantum * quantum;
+        chunk_keys = std::min(std::max(chunk_keys, quantum), n_layers > 1 ? 256 : 512);
     }
     const int min_chunk = ((max_seq_len + kMaxParts - 1) / kMaxParts + 15) / 16 * 16;
     chunk_keys = std::max(chunk_keys, min_chunk);
@@ -660,49 +456,43 @@ size_t decode_part_floats(int n_seq, int n_parts, int n_head) {
     return (size_t)n_seq * n_parts * n_head * kPartStride;
 }
 
-// One decode launch for `layer`: split CTAs that leave their partials in `part` and merge them in-kernel
-// through the arrival counters in `sync` (one {arrivals, owner} pair per (sequence, kv head), zero when idle).
-// `tag` must differ between launches that can be in flight together on the same `part`/`sync`.
-// early_loads: the caller vouches that nothing this launch reads was written by the kernel before it in the
-// stream, so it need not wait for that kernel at all.
-int launch_attn_decode(ingot_kv* kv, int layer, const void* q, int q_dtype, void* out, int out_dtype, int n_head,
+// One launch of the decode kernel over `n_layers` consecutive layers starting at `layer`: either the split CTAs
+// (merge_only == 0; partials of split ranges into `part`, outputs of single-split ranges straight into `out`) or
+// one merge CTA per (kv head, layer, sequence) that turns the partials in `part` into `out` (merge_only != 0; a
+// no-op when the plan has a single split). q and out are [n_layers][n_seq][n_head][128], `part` holds n_layers
+// blocks of decode_part_floats(). early_loads: the caller vouches that nothing the split CTAs read was written by the
+// kernel before them in the stream, so they wait for it only before their first global write.
+int launch_attn_decode(ingot_kv* kv, int layer, int n_layers, const void* q, int q_dtype, void* out, int out_dtype, int n_head,
                        int n_seq, const int32_t* seq_lens, int max_seq_len, const int32_t* block_tables,
-                       int max_blocks_per_seq, DecodePlan plan, float* part, int* sync, int tag, int early_loads,
+                       int max_blocks_per_seq, DecodePlan plan, float* part, int merge_only, int early_loads,
                        cudaStream_t stream) {
-    const bool ring = decode_use_ring();
+    if (merge_only && plan.n_parts <= 1) return INGOT_OK;
+    const int n_warps = decode_warps_cfg();
     DecodeParams p;
     p.kc = kv->k + size_t(layer) * kv->layer_elems;
     p.vc = kv->v + size_t(layer) * kv->layer_elems;
     p.q = q; p.out = out; p.seq_lens = seq_lens; p.block_tables = block_tables;
-    p.part = part; p.c_part = part; p.c_out = out; p.sync = sync; p.tag = tag; p.status = kv->status_dev;
+    p.part = part; p.c_part = part; p.c_out = out; p.status = kv->status_dev;
+    p.n_seq = n_seq;
+    p.cache_layer_stride = kv->layer_elems;
+    p.qo_layer_stride = (size_t)n_seq * n_head * kHeadDim;
+    p.part_layer_stride = decode_part_floats(n_seq, plan.n_parts, n_head);
+    p.cache_extent = kv->checked_cache_elems();
+    p.part_extent = p.part_layer_stride * n_layers;
+    p.out_extent = p.qo_layer_stride * n_layers;
     p.q_dtype = q_dtype; p.out_dtype = out_dtype;
     p.n_head = n_head; p.n_head_kv = kv->n_head_kv; p.group = n_head / kv->n_head_kv;
     p.capacity = kv->capacity; p.paged = kv->layout == INGOT_KV_PAGED; p.max_blocks_per_seq = max_blocks_per_seq;
     p.len0 = max_seq_len; p.chunk_keys = plan.chunk_keys; p.n_parts_max = plan.n_parts;
     p.early_loads = early_loads;
-    p.split_parts = plan.n_parts;
+    p.split_parts = merge_only ? 0 : plan.n_parts;
     p.scale_log2 = 1.4426950408889634f / sqrtf(float(kHeadDim));
-    const DecodeSmem sm = decode_smem(p.group, ring);
-    p.stages = decode_stages_cfg();
-    p.ring_off = (int)sm.merge_bytes;
-    p.wait_limit_ns = 2000000000ull;
-    if (ring && sm.total_bytes > kv->decode_smem_opt_in) {  // function attributes belong to a device context: per handle
-        INGOT_CUDA_TRY(cudaFuncSetAttribute(attn_decode_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm.total_bytes));
-        kv->decode_smem_opt_in = sm.total_bytes;
-    }
-
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(plan.n_parts, kv->n_head_kv, n_seq);
-    cfg.blockDim = dim3(sm.threads);
-    cfg.dynamicSmemBytes = sm.total_bytes;
-    cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = decode_use_pdl() ? 1 : 0;
-    if (ring) INGOT_CUDA_TRY(cudaLaunchKernelEx(&cfg, attn_decode_kernel<true>, p));
-    else INGOT_CUDA_TRY(cudaLaunchKernelEx(&cfg, attn_decode_kernel<false>, p));
+    const int threads = n_warps * 32;
+    const size_t smem_split = (size_t)n_warps * p.group * (kHeadDim + 2);
+    const size_t smem_merge = (size_t)2 * p.group * kMaxParts + (size_t)4 * std::max(threads, p.group * 32);
+    const size_t smem = std::max(smem_split, smem_merge) * sizeof(float);
+    const dim3 grid(merge_only ? 1 : plan.n_parts, kv->n_head_kv, (unsigned)(n_layers * n_seq));
+    INGOT_CUDA_TRY(ingot_launch_pdl(attn_decode_kernel, grid, dim3(threads), smem, stream, p));
     return INGOT_OK;
 }
 
@@ -771,13 +561,16 @@ extern "C" int ingot_attn_decode_noalloc(const void* k_dev, const void* v_dev, i
     p.kc = static_cast<const __half*>(k_dev);
     p.vc = static_cast<const __half*>(v_dev);
     p.q = q_dev; p.out = out_dev; p.seq_lens = nullptr; p.block_tables = nullptr;
-    p.part = scratch; p.c_part = scratch; p.c_out = out_dev; p.sync = nullptr; p.tag = 0; p.status = nullptr;
+    p.part = scratch; p.c_part = scratch; p.c_out = out_dev; p.status = nullptr;
+    p.n_seq = 1; p.cache_layer_stride = 0; p.qo_layer_stride = 0; p.part_layer_stride = 0;
+    p.cache_extent = (size_t)n_head_kv * n_ctx * kHeadDim;
+    p.part_extent = (size_t)kMaxParts * kStaticMaxHeads * kPartStride;
+    p.out_extent = (size_t)n_head * kHeadDim;
     p.q_dtype = q_dtype; p.out_dtype = out_dtype;
     p.n_head = n_head; p.n_head_kv = n_head_kv; p.group = n_head / n_head_kv;
     p.capacity = n_ctx; p.paged = 0; p.max_blocks_per_seq = 0;
     p.len0 = n_keys; p.chunk_keys = chunk_keys; p.n_parts_max = n_parts;
     p.early_loads = 0;
-    p.stages = 0; p.ring_off = 0; p.wait_limit_ns = 0;
     p.scale_log2 = 1.4426950408889634f / sqrtf(float(kHeadDim));
     const int threads = n_warps * 32;
     const size_t smem_split = (size_t)n_warps * p.group * (kHeadDim + 2);
@@ -785,11 +578,11 @@ extern "C" int ingot_attn_decode_noalloc(const void* k_dev, const void* v_dev, i
     const size_t smem = max(smem_split, smem_merge) * sizeof(float);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     p.split_parts = n_parts;
-    attn_decode_kernel<false><<<dim3(n_parts, n_head_kv, 1), threads, smem, s>>>(p);
+    attn_decode_kernel<<<dim3(n_parts, n_head_kv, 1), threads, smem, s>>>(p);
     INGOT_CUDA_TRY(cudaGetLastError());
     if (n_parts > 1) {  // merge-only launch; stream order makes the partials visible
         p.split_parts = 0;
-        attn_decode_kernel<false><<<dim3(1, n_head_kv, 1), threads, smem, s>>>(p);
+        attn_decode_kernel<<<dim3(1, n_head_kv, 1), threads, smem, s>>>(p);
         INGOT_CUDA_TRY(cudaGetLastError());
     }
     return INGOT_OK;

@@ -39,6 +39,7 @@ struct PrefillParams {
     int capacity, paged;
     int q_pos0, n_tok;
     float scale_log2;
+    size_t cache_extent;  // bounds-check build: elements of one cache layer
 };
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
@@ -55,6 +56,8 @@ __global__ void __launch_bounds__(kPrefillThreads) attn_prefill_mma_kernel(const
     __half* sK = reinterpret_cast<__half*>(smem_raw);                 // [2][kBN][kKStride]
     __half* sV = sK + 2 * kBN * kKStride;                            // [2][kBN][kVStride]
 
+    INGOT_PDL_TRIGGER();
+    INGOT_PDL_WAIT();  // q and the newest cache rows come from the kernel before
     const int G = p.group;
     const int kvh = blockIdx.y;
     const int n_rows = p.n_tok * G;
@@ -108,6 +111,7 @@ __global__ void __launch_bounds__(kPrefillThreads) attn_prefill_mma_kernel(const
                 }
                 off = kv_row_offset_paged(p.n_head_kv, blk, kvh, key);
             }
+            if (!INGOT_CHECK(off + c * 8, 8, p.cache_extent, p.status)) off = 0;  // flagged; a harmless row instead
             cp_async16(smem_u32(dK + row * kKStride + c * 8), p.kc + off + c * 8);
             cp_async16(smem_u32(dV + row * kVStride + c * 8), p.vc + off + c * 8);
         }
@@ -266,6 +270,7 @@ int launch_attn_prefill_mma(ingot_kv* kv, int layer, const void* q, int q_dtype,
     p.n_head = n_head; p.n_head_kv = kv->n_head_kv; p.group = n_head / kv->n_head_kv;
     p.capacity = kv->capacity; p.paged = kv->layout == INGOT_KV_PAGED;
     p.q_pos0 = q_pos0; p.n_tok = n_tok;
+    p.cache_extent = kv->checked_cache_elems();
     p.scale_log2 = 1.4426950408889634f / sqrtf(float(kHeadDim));
     const size_t smem = size_t(2) * kBN * (kKStride + kVStride) * sizeof(__half);
     if (!kv->prefill_mma_attr_set) {  // function attributes belong to a device context: once per handle, not per process
@@ -274,7 +279,6 @@ int launch_attn_prefill_mma(ingot_kv* kv, int layer, const void* q, int q_dtype,
     }
     const long long n_rows = (long long)n_tok * p.group;
     dim3 grid(unsigned((n_rows + kBM - 1) / kBM), kv->n_head_kv);
-    attn_prefill_mma_kernel<<<grid, kPrefillThreads, smem, stream>>>(p);
-    INGOT_CUDA_TRY(cudaGetLastError());
+    INGOT_CUDA_TRY(ingot_launch_pdl(attn_prefill_mma_kernel, grid, dim3(kPrefillThreads), smem, stream, p));
     return INGOT_OK;
 }

@@ -100,6 +100,7 @@ struct Sm100Params {
     unsigned long long wait_limit_ns;  // bound of every mbarrier wait
     int test_stall_producer;  // test hook: the TMA producer issues nothing, so that the bounded waits expire
     float scale_log2;
+    size_t q_extent, out_extent, part_extent;  // bounds-check build: elements of q, of each output, floats of the partials
 };
 
 // Build with -DINGOT_PREFILL_TIMING to make CTA (0,0,0) print, per key tile, the cycles its MMA warp and
@@ -159,6 +160,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                           const Sm100Params p) {
     extern __shared__ unsigned char smem_dyn[];
+    INGOT_PDL_TRIGGER();
     const uint32_t smem_base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
     unsigned char* smem_al = smem_dyn + (smem_base - smem_u32(smem_dyn));
     Bars* bars = reinterpret_cast<Bars*>(smem_al + kOffBar);
@@ -196,6 +198,9 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_k, const __gri
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&bars->tmem_base)), "r"(kTmemCols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
+    // Everything above (barriers, tensor memory) is this CTA's own; from here on the kernel reads what the kernel
+    // before it in the stream produced (q, the newest cache rows) and writes what that kernel may still be reading.
+    INGOT_PDL_WAIT();
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -350,7 +355,8 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_k, const __gri
             const size_t qbase = ((size_t)tok * p.n_head + head) * kHeadDim;
 #pragma unroll
             for (int c = 0; c < 16; c++) {
-                const uint4 val = valid ? load_q8(p.q, p.q_dtype, qbase + c * 8) : make_uint4(0, 0, 0, 0);
+                const uint4 val = valid && INGOT_CHECK(qbase + c * 8, 8, p.q_extent, p.status) ? load_q8(p.q, p.q_dtype, qbase + c * 8)
+                                                                                                   : make_uint4(0, 0, 0, 0);
                 *reinterpret_cast<uint4*>(qdst + (c >> 3) * kHalfBytes + (((c & 7) ^ (row_in_tile & 7)) << 4)) = val;
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy stores -> async proxy (MMA)
@@ -528,8 +534,9 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_k, const __gri
                             byte_off = f32_out ? (row_elem + ps * 64) * 4 + piece * 16 : row_elem * 2 + piece * 16;
                         }
                         if (partial) {
-                            *reinterpret_cast<uint4*>(reinterpret_cast<unsigned char*>(p.part) + byte_off) = val;
-                        } else {
+                            if (INGOT_CHECK(byte_off / 4, 4, p.part_extent, p.status))
+                                *reinterpret_cast<uint4*>(reinterpret_cast<unsigned char*>(p.part) + byte_off) = val;
+                        } else if (INGOT_CHECK(byte_off / (f32_out ? 4 : 2), f32_out ? 4 : 8, p.out_extent, p.status)) {
 #pragma unroll
                             for (int d = 0; d < kMaxOutputs; d++)  // unrolled: keeps the pointer table in the parameter bank
                                 if (d < p.n_outs) *reinterpret_cast<uint4*>(static_cast<unsigned char*>(p.outs[d]) + byte_off) = val;
@@ -569,6 +576,8 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_k, const __gri
 // out = sum_s o_s 2^(m_s-M) / sum_s l_s 2^(m_s-M), the same formula the decode merge uses.
 __global__ void __launch_bounds__(256) prefill_merge_kernel(const float* __restrict__ part, void* out, int out_dtype, int n_split,
                                                             int n_kvh, int n_rows, int G, int out_n_head, int out_head0) {
+    INGOT_PDL_TRIGGER();
+    INGOT_PDL_WAIT();  // the partials come from the kernel before
     const long long w = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
     if (w >= (long long)n_kvh * n_rows) return;
@@ -717,6 +726,9 @@ int launch_attn_prefill_sm100(ingot_kv* kv, int layer, const void* q, int q_dtyp
     p.block_table = paged ? block_table : nullptr;
     p.capacity = kv->capacity;
     p.scale_log2 = 1.4426950408889634f / sqrtf(float(kHeadDim));
+    p.q_extent = (size_t)n_tok * n_head * kHeadDim;
+    p.out_extent = (size_t)n_tok * out_n_head * kHeadDim;
+    p.part_extent = 0;
     // Test hook for the bounded-wait path (ingot_kv_test_stall_prefill): the producer warp issues no copies and the
     // wait limit is shortened, so every role times out, the status word gets its bit and the kernel returns
     // normally. Production: 2 s limit, producer active.
@@ -739,23 +751,25 @@ int launch_attn_prefill_sm100(ingot_kv* kv, int layer, const void* q, int q_dtyp
     if (n_split > 1) {
         const size_t need = size_t(n_split) * kv->n_head_kv * n_rows * kPartStride;
         if (need > st->part_floats) {
-            INGOT_CUDA_TRY(cudaDeviceSynchronize());
-            cudaFree(st->part);
-            st->part = nullptr;
-            st->part_floats = 0;
-            INGOT_CUDA_TRY(cudaMalloc(&st->part, need * sizeof(float)));
+            // Grown, never shrunk or freed before the handle goes: a graph captured earlier may point into the old
+            // buffer. (Growing allocates: the first call with a larger shape must not run under stream capture.)
+            float* bigger = nullptr;
+            INGOT_CUDA_TRY(cudaMalloc(&bigger, need * sizeof(float)));
+            if (st->part) kv->retired.push_back(st->part);
+            st->part = bigger;
             st->part_floats = need;
         }
         p.part = st->part;
+        p.part_extent = st->part_floats;
     }
     dim3 grid(row_tiles, kv->n_head_kv, n_split);
-    attn_prefill_sm100_kernel<<<grid, kThreads, kSmemBytes, stream>>>(st->maps[size_t(layer) * 2], st->maps[size_t(layer) * 2 + 1], p);
-    INGOT_CUDA_TRY(cudaGetLastError());
+    INGOT_CUDA_TRY(ingot_launch_pdl(attn_prefill_sm100_kernel, grid, dim3(kThreads), size_t(kSmemBytes), stream, st->maps[size_t(layer) * 2],
+                                    st->maps[size_t(layer) * 2 + 1], p));
     if (n_split > 1) {
         const long long warps = (long long)kv->n_head_kv * n_rows;
-        prefill_merge_kernel<<<unsigned((warps * 32 + 255) / 256), 256, 0, stream>>>(st->part, outs[0], out_dtype, n_split, kv->n_head_kv,
-                                                                                    int(n_rows), p.group, out_n_head, out_head0);
-        INGOT_CUDA_TRY(cudaGetLastError());
+        INGOT_CUDA_TRY(ingot_launch_pdl(prefill_merge_kernel, dim3(unsigned((warps * 32 + 255) / 256)), dim3(256), 0, stream,
+                                        (const float*)st->part, outs[0], out_dtype, n_split, kv->n_head_kv, int(n_rows), p.group, out_n_head,
+                                        out_head0));
     }
     return INGOT_OK;
 }

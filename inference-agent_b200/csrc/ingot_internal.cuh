@@ -8,6 +8,7 @@
 #include <stdint.h>
 
 #include <string>
+#include <utility>
 #include <vector>
 
 #include "ingot_cuda.h"
@@ -18,17 +19,31 @@ constexpr int kBlockTokens = INGOT_BLOCK_TOKENS;
 // padded to a 16-byte multiple. The Metal reference keeps the same triple with stride 130
 // (shaders/kernels.metal:291).
 constexpr int kPartStride = 132;
-// Most independent launch chains the multi-layer decode call spreads its layers over
-// (INGOT_DECODE_STREAMS picks how many are used; the default is this bound).
-constexpr int kDecodeStreams = 8;
 constexpr int kHostPosSlots = 256;  // host-buffer calls that may be queued before the caller synchronises
 
 // Bits of the device status word (ingot_kv::status_dev).
 enum : int {
     kDevErrPosRange = 1,      // K1: a position fell outside the cache; the row was skipped
     kDevErrBlockRange = 2,    // a block-table entry fell outside the pool; the access was skipped
-    kDevErrBarrierTimeout = 4 // prefill: a bounded mbarrier wait expired; the CTA gave up cleanly
+    kDevErrBarrierTimeout = 4,// a bounded wait expired; the kernel gave up cleanly
+    kDevErrBounds = 8         // bounds-check build only: an offset fell outside its buffer; the access was skipped
 };
+
+// Bounds-check build (-DINGOT_BOUNDS_CHECK, `make check` -> libingot_cuda_check.so). Every offset the kernels
+// compute into the KV cache, the split scratch, the query and the output is compared with the extent of its
+// buffer before the access; a violation raises kDevErrBounds in the status word and the access is skipped - no
+// trap, no assert, the context stays usable. It stands in for a memory checker on machines where none can run,
+// and is compiled out of the production library.
+#ifdef INGOT_BOUNDS_CHECK
+__device__ __forceinline__ bool ingot_in_bounds(size_t first, size_t count, size_t extent, int* status) {
+    if (first + count <= extent && first + count >= first) return true;
+    if (status) atomicOr(status, kDevErrBounds);
+    return false;
+}
+#define INGOT_CHECK(first, count, extent, status) ingot_in_bounds((size_t)(first), (size_t)(count), (size_t)(extent), (status))
+#else
+#define INGOT_CHECK(first, count, extent, status) true
+#endif
 
 struct ingot_kv {
     int device = 0;
@@ -41,20 +56,17 @@ struct ingot_kv {
     __half* k = nullptr;
     __half* v = nullptr;
     int* status_dev = nullptr;  // [0] the status word, [1] the ticket of the signalling prefill form
-    // split-KV decode scratch: part_bufs buffers of partials [n_seq][splits][n_head][kPartStride], each with its
-    // arrival counters part_sync [max_seqs][n_head_kv][2] (zero when idle). A single decode call uses buffer 0;
-    // the multi-layer call gives every launch chain two buffers that its consecutive launches alternate between.
+    // split-KV decode scratch: partials [layer][n_seq][splits][n_head][kPartStride] of the layers one launch covers.
     // Sized on first use from the split count actually needed and only ever grown; a buffer that is outgrown is
     // parked in `retired` until the handle is destroyed, because a CUDA graph captured earlier may still point
     // into it.
     float* part = nullptr;
-    int* part_sync = nullptr;
-    size_t part_floats = 0;  // floats per buffer
-    int part_bufs = 0;
+    size_t part_floats = 0;
     std::vector<void*> retired;
-    size_t decode_smem_opt_in = 0;      // largest dynamic shared memory the decode kernel was opted in for on `device`
     bool prefill_mma_attr_set = false;
-    int test_stall_ms = 0;              // test hook, see ingot_kv_test_stall_prefill  // the warp-MMA prefill kernel's shared-memory opt-in was made on `device`
+    int test_stall_ms = 0;              // test hook, see ingot_kv_test_stall_prefill
+    size_t test_cache_extent = 0;       // test hook of the bounds-check build, see ingot_kv_test_shrink_extent (0: real extent)
+    size_t checked_cache_elems() const { return test_cache_extent ? test_cache_extent : layer_elems; }  // the warp-MMA prefill kernel's shared-memory opt-in was made on `device`
     // staging for the host-buffer entry points (grown on demand)
     void* stage = nullptr;
     size_t stage_bytes = 0;
@@ -69,10 +81,6 @@ struct ingot_kv {
     int32_t* host_pos_dev = nullptr;     // {position, key count}
     int32_t* host_pos_pinned = nullptr;  // kHostPosSlots pairs
     unsigned host_pos_next = 0;
-    // side streams of the multi-layer decode call (created on first use) and their fork/join events
-    cudaStream_t side_stream[kDecodeStreams] = {};
-    cudaEvent_t side_done[kDecodeStreams] = {};
-    cudaEvent_t fork_event = nullptr;
     // tensor maps for the TMA prefill kernel, one per layer and per tile height, built on first use
     void* tmaps = nullptr;  // host array, see attn_prefill_sm100.cu
 };
@@ -116,6 +124,29 @@ __host__ __device__ inline size_t kv_row_offset_paged(int n_head_kv, int blk, in
     return ((size_t(blk) * n_head_kv + h) * kBlockTokens + (pos % kBlockTokens)) * kHeadDim;
 }
 
+// Launch with programmatic dependent launch allowed: the kernel may start while the kernel before it in the stream
+// is still running. Every kernel launched this way executes griddepcontrol.launch_dependents early and
+// griddepcontrol.wait before it touches anything the preceding kernel may have written (or may still be reading),
+// so only its set-up - barrier initialisation, tensor-memory allocation, index arithmetic - overlaps the
+// predecessor's tail. INGOT_NO_PDL=1 turns the attribute off (plain stream order; diagnostics).
+bool ingot_use_pdl();
+template <typename... KArgs, typename... Args>
+inline cudaError_t ingot_launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = ingot_use_pdl() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
+#define INGOT_PDL_TRIGGER() asm volatile("griddepcontrol.launch_dependents;" ::: "memory")
+#define INGOT_PDL_WAIT() asm volatile("griddepcontrol.wait;" ::: "memory")
+
 // Launchers implemented in the kernel files.
 int launch_rope_kv_append(ingot_kv* kv, int layer, const float* q, __half* q_out, const float* k, const float* v,
                           const float* inv_freq, int n_head, int pos0, int n_tok, const int32_t* positions,
@@ -124,11 +155,11 @@ int launch_rope_kv_append(ingot_kv* kv, int layer, const float* q, __half* q_out
 int launch_kv_import_f16(ingot_kv* kv, int layer, const __half* k, const __half* v, int pos0, int n_tok,
                          const int32_t* block_table, cudaStream_t stream);
 struct DecodePlan { int chunk_keys, n_parts; };
-DecodePlan decode_plan(const ingot_kv* kv, int n_seq, int max_seq_len, int chunk_keys, int concurrency, int n_head);
+DecodePlan decode_plan(const ingot_kv* kv, int n_layers, int n_seq, int max_seq_len, int chunk_keys);
 size_t decode_part_floats(int n_seq, int n_parts, int n_head);
-int launch_attn_decode(ingot_kv* kv, int layer, const void* q, int q_dtype, void* out, int out_dtype, int n_head,
+int launch_attn_decode(ingot_kv* kv, int layer, int n_layers, const void* q, int q_dtype, void* out, int out_dtype, int n_head,
                        int n_seq, const int32_t* seq_lens, int max_seq_len, const int32_t* block_tables,
-                       int max_blocks_per_seq, DecodePlan plan, float* part, int* sync, int tag, int early_loads,
+                       int max_blocks_per_seq, DecodePlan plan, float* part, int merge_only, int early_loads,
                        cudaStream_t stream);
 int launch_attn_prefill_mma(ingot_kv* kv, int layer, const void* q, int q_dtype, void* out, int out_dtype,
                             int n_head, int q_pos0, int n_tok, const int32_t* block_table, cudaStream_t stream);

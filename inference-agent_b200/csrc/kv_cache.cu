@@ -21,6 +21,11 @@ int ingot_cuda_fail(cudaError_t e, const char* what) {
     return e == cudaErrorMemoryAllocation ? INGOT_ERR_NOMEM : INGOT_ERR_CUDA;
 }
 
+bool ingot_use_pdl() {
+    static const bool v = getenv("INGOT_NO_PDL") == nullptr;
+    return v;
+}
+
 extern "C" {
 
 const char* ingot_status_string(int status) {
@@ -38,6 +43,14 @@ const char* ingot_status_string(int status) {
 const char* ingot_last_error(void) { return g_last_error.c_str(); }
 
 const char* ingot_build_arch(void) { return "sm_100a"; }
+
+const char* ingot_build_flags(void) {
+#ifdef INGOT_BOUNDS_CHECK
+    return "bounds-check";
+#else
+    return "";
+#endif
+}
 
 int ingot_kv_create(ingot_kv** out, int layout, int n_layer, int n_head_kv, int head_dim, int capacity,
                     int max_seqs) {
@@ -88,7 +101,6 @@ void ingot_kv_destroy(ingot_kv* kv) {
     cudaFree(kv->v);
     cudaFree(kv->status_dev);
     cudaFree(kv->part);
-    cudaFree(kv->part_sync);
     for (void* p : kv->retired) cudaFree(p);
     cudaFree(kv->stage);
     if (kv->host_exec) cudaGraphExecDestroy(kv->host_exec);
@@ -96,11 +108,6 @@ void ingot_kv_destroy(ingot_kv* kv) {
     cudaFree(kv->host_pos_dev);
     cudaFreeHost(kv->host_pos_pinned);
     if (kv->capture_stream) cudaStreamDestroy(kv->capture_stream);
-    for (int i = 0; i < kDecodeStreams; i++) {
-        if (kv->side_stream[i]) cudaStreamDestroy(kv->side_stream[i]);
-        if (kv->side_done[i]) cudaEventDestroy(kv->side_done[i]);
-    }
-    if (kv->fork_event) cudaEventDestroy(kv->fork_event);
     delete kv;
 }
 
@@ -115,6 +122,12 @@ void* ingot_kv_v_dev(ingot_kv* kv, int layer) {
 }
 
 size_t ingot_kv_layer_bytes(const ingot_kv* kv) { return kv ? kv->layer_elems * sizeof(__half) : 0; }
+
+int ingot_kv_test_shrink_extent(ingot_kv* kv, size_t elems) {
+    INGOT_REQUIRE(kv != nullptr && elems <= kv->layer_elems, "ingot_kv_test_shrink_extent: bad argument");
+    kv->test_cache_extent = elems;
+    return INGOT_OK;
+}
 
 int ingot_kv_test_stall_prefill(ingot_kv* kv, int stall_ms) {
     INGOT_REQUIRE(kv != nullptr && stall_ms >= 0, "ingot_kv_test_stall_prefill: bad argument");
@@ -177,31 +190,16 @@ int ingot_kv_import_f16(ingot_kv* kv, int layer, const void* k_f16_dev, const vo
                                 pos0, n_tok, block_table_dev, static_cast<cudaStream_t>(stream));
 }
 
-// Makes sure the handle owns `bufs` scratch buffers of `floats` floats each (plus their arrival counters).
-// Growing allocates, so the first call with a larger shape must not happen under stream capture; buffers that
-// are outgrown stay allocated until the handle is destroyed (a graph captured earlier may point into them).
-static int ensure_decode_scratch(ingot_kv* kv, size_t floats, int bufs) {
-    if (floats <= kv->part_floats && bufs <= kv->part_bufs) return INGOT_OK;
-    floats = std::max(floats, kv->part_floats);
-    bufs = std::max(bufs, kv->part_bufs);
+// Makes sure the handle's split scratch holds `floats` floats. Growing allocates, so the first call with a larger
+// shape must not happen under stream capture; a buffer that is outgrown stays allocated until the handle is
+// destroyed (a graph captured earlier may point into it).
+static int ensure_decode_scratch(ingot_kv* kv, size_t floats) {
+    if (floats <= kv->part_floats) return INGOT_OK;
     float* part = nullptr;
-    int* sync = nullptr;
-    const size_t sync_ints = size_t(bufs) * kv->max_seqs * kv->n_head_kv * 2;
-    INGOT_CUDA_TRY(cudaMalloc(&part, size_t(bufs) * floats * sizeof(float)));
-    cudaError_t e = cudaMalloc(&sync, sync_ints * sizeof(int));
-    if (e == cudaSuccess) e = cudaMemset(sync, 0, sync_ints * sizeof(int));
-    if (e == cudaSuccess) e = cudaDeviceSynchronize();  // the counters are zero before any stream can use them
-    if (e != cudaSuccess) {
-        cudaFree(part);
-        cudaFree(sync);
-        return ingot_cuda_fail(e, "decode scratch");
-    }
+    INGOT_CUDA_TRY(cudaMalloc(&part, floats * sizeof(float)));
     if (kv->part) kv->retired.push_back(kv->part);
-    if (kv->part_sync) kv->retired.push_back(kv->part_sync);
     kv->part = part;
-    kv->part_sync = sync;
     kv->part_floats = floats;
-    kv->part_bufs = bufs;
     kv->host_key[0] = -1;  // the host-buffer call's captured graph points into the old scratch
     return INGOT_OK;
 }
@@ -237,16 +235,8 @@ static int decode_checked(ingot_kv* kv, int layer, const void* q_dev, int q_dtyp
 int ingot_attn_decode(ingot_kv* kv, int layer, const void* q_dev, int q_dtype, void* out_dev, int out_dtype,
                       int n_head, int n_seq, const int32_t* seq_lens_dev, int max_seq_len,
                       const int32_t* block_tables_dev, int max_blocks_per_seq, int chunk_keys, void* stream) {
-    int rc = decode_checked(kv, layer, q_dev, q_dtype, out_dev, out_dtype, n_head, n_seq, seq_lens_dev, max_seq_len,
-                            block_tables_dev, max_blocks_per_seq, chunk_keys);
-    if (rc != INGOT_OK) return rc;
-    // One launch: the splits, and the merge by whichever split CTA of a (sequence, kv head) finishes last.
-    const DecodePlan plan = decode_plan(kv, n_seq, max_seq_len, chunk_keys, 1, n_head);
-    rc = ensure_decode_scratch(kv, decode_part_floats(n_seq, plan.n_parts, n_head), 1);
-    if (rc != INGOT_OK) return rc;
-    return launch_attn_decode(kv, layer, q_dev, q_dtype, out_dev, out_dtype, n_head, n_seq, seq_lens_dev, max_seq_len,
-                              block_tables_dev, max_blocks_per_seq, plan, kv->part, kv->part_sync, layer + 1, 0,
-                              static_cast<cudaStream_t>(stream));
+    return ingot_attn_decode_layers(kv, layer, 1, q_dev, q_dtype, out_dev, out_dtype, n_head, n_seq, seq_lens_dev, max_seq_len,
+                                    block_tables_dev, max_blocks_per_seq, chunk_keys, stream);
 }
 
 int ingot_attn_decode_layers(ingot_kv* kv, int layer_begin, int layer_count, const void* q_dev, int q_dtype,
@@ -260,53 +250,39 @@ int ingot_attn_decode_layers(ingot_kv* kv, int layer_begin, int layer_count, con
     int rc = decode_checked(kv, layer_begin, q_dev, q_dtype, out_dev, out_dtype, n_head, n_seq, seq_lens_dev, max_seq_len,
                             block_tables_dev, max_blocks_per_seq, chunk_keys);
     if (rc != INGOT_OK) return rc;
-    cudaStream_t user = static_cast<cudaStream_t>(stream);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
     const size_t q_bytes = size_t(n_seq) * n_head * kHeadDim * (q_dtype == INGOT_F32 ? 4 : 2);
     const size_t o_bytes = size_t(n_seq) * n_head * kHeadDim * (out_dtype == INGOT_F32 ? 4 : 2);
-    // The layers are independent of one another. Every layer is one self-contained launch (splits + in-kernel
-    // merge) that neither reads nor writes anything another layer's launch touches, except the split scratch;
-    // so the launches are chained with programmatic dependent launch and never wait for one another: a
-    // launch starts as soon as the one before it is resident, and its K/V loads overlap the tail of that
-    // launch. They are dealt round-robin to a few side streams (forked from and joined back into the caller's
-    // stream with events; capturable in a CUDA graph), which lets the block scheduler interleave launches
-    // freely. A chain alternates between two scratch buffers; the kernel's owner word makes the (never
-    // observed) case of a launch catching up with the launch two before it wait instead of overwrite.
-    // The first launch of every chain waits for the work before it in the stream (the fork event).
-    int streams_cfg = kDecodeStreams;
-    if (const char* e = getenv("INGOT_DECODE_STREAMS")) streams_cfg = std::min(std::max(atoi(e), 1), kDecodeStreams);
-    // as many chains as allowed, then as few as give the same number of rounds: 28 layers on up to 8 chains are
-    // 4 rounds, which 7 chains do evenly
-    const int max_streams = std::min(streams_cfg, layer_count);
-    const int want_rounds = (layer_count + max_streams - 1) / max_streams;
-    const int n_streams = (layer_count + want_rounds - 1) / want_rounds;
-    const DecodePlan plan = decode_plan(kv, n_seq, max_seq_len, chunk_keys, n_streams, n_head);
-    rc = ensure_decode_scratch(kv, decode_part_floats(n_seq, plan.n_parts, n_head), 2 * n_streams);
-    if (rc != INGOT_OK) return rc;
-    if (!kv->fork_event) INGOT_CUDA_TRY(cudaEventCreateWithFlags(&kv->fork_event, cudaEventDisableTiming));
-    for (int t = 0; t < n_streams; t++) {
-        if (!kv->side_stream[t]) INGOT_CUDA_TRY(cudaStreamCreateWithFlags(&kv->side_stream[t], cudaStreamNonBlocking));
-        if (!kv->side_done[t]) INGOT_CUDA_TRY(cudaEventCreateWithFlags(&kv->side_done[t], cudaEventDisableTiming));
+    // The layers are independent of one another, so they go into ONE grid: blockIdx.z runs over (layer, sequence)
+    // and the block scheduler keeps every SM fed from the first CTA of the first layer to the last CTA of the
+    // last - no launch boundary, no dependency between layers. A second, merge-only launch (chained with
+    // programmatic dependent launch, so its CTAs are resident and waiting when the first grid drains) turns the
+    // split partials into the outputs. A single layer is the same two launches.
+    // Only the size of the split scratch (one block of partials per layer) bounds how many layers share a
+    // launch: INGOT_DECODE_SCRATCH_MB (default 256) caps it, and more layers than fit are done in groups.
+    const DecodePlan plan = decode_plan(kv, layer_count, n_seq, max_seq_len, chunk_keys);
+    const size_t per_layer = decode_part_floats(n_seq, plan.n_parts, n_head);
+    size_t cap_mb = 256;
+    if (const char* e = getenv("INGOT_DECODE_SCRATCH_MB")) cap_mb = size_t(std::max(1, atoi(e)));
+    int group = plan.n_parts > 1 ? int(std::max<size_t>(1, std::min<size_t>(size_t(layer_count), (cap_mb << 20) / (per_layer * sizeof(float)))))
+                                 : layer_count;
+    group = std::min(group, std::max(1, 65535 / n_seq));  // gridDim.z
+    if (plan.n_parts > 1) {
+        rc = ensure_decode_scratch(kv, per_layer * size_t(group));
+        if (rc != INGOT_OK) return rc;
     }
-    INGOT_CUDA_TRY(cudaEventRecord(kv->fork_event, user));
-    for (int t = 0; t < n_streams; t++) INGOT_CUDA_TRY(cudaStreamWaitEvent(kv->side_stream[t], kv->fork_event, 0));
-    const size_t sync_ints = size_t(kv->max_seqs) * kv->n_head_kv * 2;
-    const int rounds = (layer_count + n_streams - 1) / n_streams;
-    for (int r = 0; r < rounds; r++) {
-        for (int t = 0; t < n_streams; t++) {
-            const int li = r * n_streams + t;
-            if (li >= layer_count) continue;
-            const int buf = 2 * t + (r & 1);
-            rc = launch_attn_decode(kv, layer_begin + li, static_cast<const char*>(q_dev) + size_t(li) * q_bytes, q_dtype,
-                                    static_cast<char*>(out_dev) + size_t(li) * o_bytes, out_dtype, n_head, n_seq, seq_lens_dev,
-                                    max_seq_len, block_tables_dev, max_blocks_per_seq, plan,
-                                    kv->part + size_t(buf) * kv->part_floats, kv->part_sync + size_t(buf) * sync_ints,
-                                    layer_begin + li + 1, r > 0 ? 1 : 0, kv->side_stream[t]);
-            if (rc != INGOT_OK) return rc;
-        }
-    }
-    for (int t = 0; t < n_streams; t++) {
-        INGOT_CUDA_TRY(cudaEventRecord(kv->side_done[t], kv->side_stream[t]));
-        INGOT_CUDA_TRY(cudaStreamWaitEvent(user, kv->side_done[t], 0));
+    for (int l0 = 0; l0 < layer_count; l0 += group) {
+        const int n = std::min(group, layer_count - l0);
+        const void* q_l = static_cast<const char*>(q_dev) + size_t(l0) * q_bytes;
+        void* out_l = static_cast<char*>(out_dev) + size_t(l0) * o_bytes;
+        // From the second group on nothing a split CTA READS was written by the launch before it (the previous
+        // group's merge): it starts loading at once and waits for that launch only before it overwrites the scratch.
+        rc = launch_attn_decode(kv, layer_begin + l0, n, q_l, q_dtype, out_l, out_dtype, n_head, n_seq, seq_lens_dev, max_seq_len,
+                                block_tables_dev, max_blocks_per_seq, plan, kv->part, 0, l0 > 0 ? 1 : 0, s);
+        if (rc != INGOT_OK) return rc;
+        rc = launch_attn_decode(kv, layer_begin + l0, n, q_l, q_dtype, out_l, out_dtype, n_head, n_seq, seq_lens_dev, max_seq_len,
+                                block_tables_dev, max_blocks_per_seq, plan, kv->part, 1, 0, s);
+        if (rc != INGOT_OK) return rc;
     }
     return INGOT_OK;
 }
@@ -409,13 +385,12 @@ int ingot_attn_layers_host(ingot_kv* kv, int layer_begin, int layer_count, const
     // whole call needs three host->device copies and one device->host copy.
     const size_t need = L * (q_elems * 4 + kv_elems * 8 + q_elems * 4 + q_elems * 2);
     if (need > kv->stage_bytes) {
-        INGOT_CUDA_TRY(cudaDeviceSynchronize());
-        cudaFree(kv->stage);
-        kv->stage = nullptr;
-        kv->stage_bytes = 0;
-        INGOT_CUDA_TRY(cudaMalloc(&kv->stage, need));
+        void* bigger = nullptr;
+        INGOT_CUDA_TRY(cudaMalloc(&bigger, need));
+        if (kv->stage) kv->retired.push_back(kv->stage);  // kernels in flight (or a captured graph) may still use it
+        kv->stage = bigger;
         kv->stage_bytes = need;
-        kv->host_key[0] = -1;  // a captured graph points into the old staging area
+        kv->host_key[0] = -1;  // the captured graph of the single-token form points into the old staging area
     }
     float* q_d = static_cast<float*>(kv->stage);
     float* k_d = q_d + L * q_elems;

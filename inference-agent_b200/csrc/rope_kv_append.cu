@@ -33,6 +33,7 @@ struct AppendParams {
     int max_blocks_per_seq;
     int paged;
     size_t layer_elems;      // cache elements between consecutive layers (blockIdx.y = layer offset)
+    size_t cache_extent;     // elements of one layer the kernel may touch (bounds-check build)
 };
 
 __device__ __forceinline__ uint32_t pack_half2(float a, float b) {
@@ -56,6 +57,8 @@ __device__ __forceinline__ long long cache_row(const AppendParams& p, int tok, i
 }
 
 __global__ void __launch_bounds__(256) rope_kv_append_kernel(const AppendParams p) {
+    INGOT_PDL_TRIGGER();
+    INGOT_PDL_WAIT();  // q/k/v come from the kernel before; the cache rows written here may still be read by it
     const int q_units = p.q ? p.n_head * 16 : 0;  // 16 units of 8 elements per head
     const int kv_units = p.n_head_kv * 16;
     const int units_per_tok = q_units + 2 * kv_units;
@@ -85,6 +88,7 @@ __global__ void __launch_bounds__(256) rope_kv_append_kernel(const AppendParams 
             if ((r & 15) == 0) atomicOr(p.status, row == -1 ? kDevErrPosRange : kDevErrBlockRange);
             return;
         }
+        if (!INGOT_CHECK(row + (size_t)(r & 15) * 8, 8, p.cache_extent, p.status)) return;
         src = (is_v ? p.v : p.k) + lkv + ((size_t)tok * p.n_head_kv) * kHeadDim + (size_t)r * 8;
         dst = (is_v ? p.vc : p.kc) + lc + row + (size_t)(r & 15) * 8;
         rotate = !is_v;
@@ -120,6 +124,7 @@ struct ImportParams {
     const int32_t* block_table;
     int* status;
     int n_head_kv, n_tok, pos0, capacity, paged;
+    size_t cache_extent;
 };
 
 // Token-major [n_tok][n_head_kv][128] f16 rows -> cache layout. One 16-byte chunk per thread.
@@ -144,6 +149,7 @@ __global__ void __launch_bounds__(256) kv_import_f16_kernel(const ImportParams p
         }
         row = kv_row_offset_paged(p.n_head_kv, blk, h, pos);
     }
+    if (!INGOT_CHECK(row + (size_t)c * 8, 8, p.cache_extent, p.status)) return;
     const uint4 val = __ldg(reinterpret_cast<const uint4*>((is_v ? p.v : p.k) + (size_t)tok * units_per_tok * 8) + r);
     *reinterpret_cast<uint4*>((is_v ? p.vc : p.kc) + row + (size_t)c * 8) = val;
 }
@@ -164,10 +170,10 @@ int launch_rope_kv_append(ingot_kv* kv, int layer, const float* q, __half* q_out
     p.capacity = kv->capacity; p.max_blocks_per_seq = max_blocks_per_seq;
     p.paged = kv->layout == INGOT_KV_PAGED;
     p.layer_elems = kv->layer_elems;
+    p.cache_extent = kv->checked_cache_elems();
     const long long units = (long long)((q ? n_head : 0) + 2 * kv->n_head_kv) * 16 * n_tok;
     const unsigned blocks = unsigned((units + 255) / 256);
-    rope_kv_append_kernel<<<dim3(blocks, layer_count), 256, 0, stream>>>(p);
-    INGOT_CUDA_TRY(cudaGetLastError());
+    INGOT_CUDA_TRY(ingot_launch_pdl(rope_kv_append_kernel, dim3(blocks, layer_count), dim3(256), 0, stream, p));
     return INGOT_OK;
 }
 
@@ -180,6 +186,7 @@ int launch_kv_import_f16(ingot_kv* kv, int layer, const __half* k, const __half*
     p.block_table = block_table; p.status = kv->status_dev;
     p.n_head_kv = kv->n_head_kv; p.n_tok = n_tok; p.pos0 = pos0; p.capacity = kv->capacity;
     p.paged = kv->layout == INGOT_KV_PAGED;
+    p.cache_extent = kv->checked_cache_elems();
     const long long units = (long long)kv->n_head_kv * 16 * n_tok * 2;
     const unsigned blocks = unsigned((units + 255) / 256);
     kv_import_f16_kernel<<<blocks, 256, 0, stream>>>(p);

@@ -22,6 +22,7 @@ ABI = {
     "ingot_status_string": (C.c_char_p, [_I]),
     "ingot_last_error": (C.c_char_p, []),
     "ingot_build_arch": (C.c_char_p, []),
+    "ingot_build_flags": (C.c_char_p, []),
     "ingot_kv_create": (_I, [C.POINTER(_P), _I, _I, _I, _I, _I, _I]),
     "ingot_kv_destroy": (None, [_P]),
     "ingot_kv_k_dev": (_P, [_P, _I]),
@@ -29,6 +30,7 @@ ABI = {
     "ingot_kv_layer_bytes": (_SZ, [_P]),
     "ingot_kv_status": (_I, [_P, _P, C.POINTER(_I)]),
     "ingot_kv_test_stall_prefill": (_I, [_P, _I]),
+    "ingot_kv_test_shrink_extent": (_I, [_P, _SZ]),
     "ingot_rope_kv_append": (_I, [_P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _P, _P, _P, _I, _P]),
     "ingot_kv_import_f16": (_I, [_P, _I, _P, _P, _I, _I, _P, _P]),
     "ingot_attn_decode": (_I, [_P, _I, _P, _I, _P, _I, _I, _I, _P, _I, _P, _I, _I, _P]),
@@ -38,11 +40,56 @@ ABI = {
     "ingot_attn_prefill_gather": (_I, [_P, _I, _P, _I, C.POINTER(_P), _I, _I, _I, _I, _I, _I, _I, _P]),
     "ingot_attn_prefill_gather_signal": (_I, [_P, _I, _P, _I, C.POINTER(_P), C.POINTER(_P), _I, _I, _I, _I, _I, _I, _I, _I, _P]),
     "ingot_gather_wait": (_I, [_P, _P, _I, _I, _P]),
+    "ingot_mg_create": (_I, [C.POINTER(_P), _I, _I, _I, _I, _I, _I]),
+    "ingot_mg_destroy": (None, [_P]),
+    "ingot_mg_kv": (_P, [_P, _I]),
+    "ingot_mg_out": (_P, [_P, _I]),
+    "ingot_mg_stream": (_P, [_P, _I]),
+    "ingot_mg_prefill": (_I, [_P, _I, C.POINTER(_P), _I, _I, _I, _I]),
+    "ingot_lpt_assign": (_I, [C.POINTER(C.c_int32), _I, _I, C.POINTER(C.c_int32)]),
     "ingot_attn_layer_host": (_I, [_P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _P]),
     "ingot_attn_layers_host": (_I, [_P, _I, _I, _P, _P, _P, _P, _P, _I, _I, _I, _P]),
     "ingot_stream_sync": (_I, [_P]),
     "ingot_hbm_read_probe": (_I, [_SZ, _I, C.POINTER(C.c_double), _P]),
 }
+
+
+# Canary-padded device allocations for the tests (INGOT_TEST_CANARY=1): every tensor this module allocates for a
+# caller - and every input the test helpers upload - sits between two guard zones filled with a byte pattern;
+# check_guards() verifies that no kernel wrote into them. A stand-in for a memory checker on the output side.
+_CANARY = os.environ.get("INGOT_TEST_CANARY") == "1"
+_GUARD_ELEMS = 256
+_GUARD_BYTE = 0xA5
+_guards = []
+
+
+def guarded_empty(shape, dtype, device="cuda"):
+    import torch
+    if not _CANARY:
+        return torch.empty(shape, dtype=dtype, device=device)
+    n = 1
+    for d in shape:
+        n *= int(d)
+    base = torch.empty(n + 2 * _GUARD_ELEMS, dtype=dtype, device=device)
+    raw = base.view(torch.uint8)
+    g = _GUARD_ELEMS * base.element_size()
+    raw[:g] = _GUARD_BYTE
+    raw[raw.numel() - g:] = _GUARD_BYTE
+    _guards.append(base)
+    return base[_GUARD_ELEMS:_GUARD_ELEMS + n].view(tuple(int(d) for d in shape))
+
+
+def check_guards():
+    """Number of guarded allocations whose guard zones were written to since the last call (0 = clean)."""
+    import torch
+    bad = 0
+    for base in _guards:
+        raw = base.view(torch.uint8)
+        g = _GUARD_ELEMS * base.element_size()
+        if not (bool((raw[:g] == _GUARD_BYTE).all()) and bool((raw[raw.numel() - g:] == _GUARD_BYTE).all())):
+            bad += 1
+    _guards.clear()
+    return bad
 
 
 class IngotError(RuntimeError):
@@ -148,7 +195,7 @@ def rope_kv_append(kv, layer, q, k, v, inv_freq, pos0=0, positions=None, seq_ids
     if q is not None:
         assert q.is_contiguous() and q.dtype == torch.float32
         n_head = q.shape[1]
-        q_out = torch.empty(q.shape, dtype=torch.float16, device=q.device)
+        q_out = guarded_empty(q.shape, torch.float16, q.device)
     assert k.is_contiguous() and v.is_contiguous() and k.dtype == torch.float32 and v.dtype == torch.float32
     mb = 0 if block_tables is None else block_tables.shape[-1]
     _check(lib().ingot_rope_kv_append(kv.handle, layer, _ptr(q), _ptr(q_out), _ptr(k), _ptr(v), _ptr(inv_freq), n_head,
@@ -163,7 +210,7 @@ def attn_decode(kv, layer, q, out=None, out_dtype=None, seq_lens=None, max_seq_l
     assert q.is_contiguous()
     n_seq, n_head = q.shape[0], q.shape[1]
     if out is None:
-        out = torch.empty(q.shape, dtype=out_dtype or torch.float32, device=q.device)
+        out = guarded_empty(q.shape, out_dtype or torch.float32, q.device)
     mb = 0 if block_tables is None else block_tables.shape[-1]
     _check(lib().ingot_attn_decode(kv.handle, layer, _ptr(q), _dtype_code(q), _ptr(out), _dtype_code(out), n_head, n_seq,
                                    _ptr(seq_lens), int(max_seq_len), _ptr(block_tables), mb, chunk_keys, _stream()))
@@ -187,7 +234,7 @@ def attn_prefill(kv, layer, q, q_pos0, out=None, out_dtype=None, block_table=Non
     assert q.is_contiguous()
     n_tok, n_head = q.shape[0], q.shape[1]
     if out is None:
-        out = torch.empty(q.shape, dtype=out_dtype or torch.float32, device=q.device)
+        out = guarded_empty(q.shape, out_dtype or torch.float32, q.device)
     _check(lib().ingot_attn_prefill(kv.handle, layer, _ptr(q), _dtype_code(q), _ptr(out), _dtype_code(out), n_head,
                                     q_pos0, n_tok, _ptr(block_table), impl, _stream()))
     return out

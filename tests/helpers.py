@@ -82,9 +82,13 @@ def oracle_decode(wl):
 # ---- CUDA-path drivers (need a GPU) ----
 
 def to_dev(x, dtype=None):
+    """Uploads a numpy array (optionally converted to `dtype`) into a canary-guarded device tensor."""
     import torch
-    t = torch.from_numpy(np.ascontiguousarray(x)).cuda()
-    return t if dtype is None else t.to(dtype)
+    import ingot_b200 as ib
+    src = torch.from_numpy(np.ascontiguousarray(x))
+    t = ib.guarded_empty(src.shape, dtype or src.dtype)
+    t.copy_(src)
+    return t
 
 
 def gpu_prefill(wl, impl=0, paged=False, out_f16=False, seed=0, extra_ctx=0):

@@ -55,3 +55,20 @@ def test_argument_errors_need_no_gpu():
     assert lib.ingot_kv_create(C.byref(h), 0, 1, 8, 64, 16, 1) == 3           # head_dim != 128: unsupported
     assert lib.ingot_attn_decode_noalloc(None, None, 1, 1, None, 0, None, 0, 1, 1, 0, None) == 1
     lib.ingot_kv_destroy(None)  # no-op
+
+
+def test_lpt_assign_in_the_library_matches_the_python_one():
+    """ingot_lpt_assign is pure host code: the C assignment equals workloads.lpt_assign for the configs[3] lengths."""
+    import ctypes as C
+    import numpy as np
+    import ingot_b200 as ib
+    from ingot_b200 import workloads as W
+    lens = W.c4_lengths()
+    for n in (1, 2, 4, 8):
+        got = np.zeros(len(lens), dtype=np.int32)
+        rc = ib.lib().ingot_lpt_assign(lens.ctypes.data_as(C.POINTER(C.c_int32)), len(lens), n, got.ctypes.data_as(C.POINTER(C.c_int32)))
+        assert rc == 0
+        want = np.zeros(len(lens), dtype=np.int32)
+        for r, idx in enumerate(W.lpt_assign(lens, n)):
+            want[idx] = r
+        assert np.array_equal(got, want)

@@ -22,8 +22,8 @@ def _fill_layers(kv, n_layers, n_keys, rng):
 
 @pytest.mark.parametrize("n_layers,n_keys", [(1, 300), (3, 1000), (6, 4096), (9, 77)])
 def test_decode_layers_matches_reference_per_layer(n_layers, n_keys):
-    """ingot_attn_decode_layers deals layers over side streams with chained launches; every layer's output
-    must still be the reference's, and a second call on the same handle must give identical bits."""
+    """ingot_attn_decode_layers runs all layers in one grid plus a merge launch; every layer's output must be
+    the reference's, and a second call on the same handle must give identical bits."""
     import torch
     import ingot_b200 as ib
     rng = np.random.default_rng(n_layers * 1000 + n_keys)
@@ -45,7 +45,7 @@ def test_decode_layers_matches_reference_per_layer(n_layers, n_keys):
 
 
 def test_decode_layers_in_a_cuda_graph():
-    """The fork/join over side streams is capturable: replaying the graph reproduces the eager result."""
+    """The call is capturable: replaying the graph reproduces the eager result."""
     import torch
     import ingot_b200 as ib
     rng = np.random.default_rng(5)
@@ -189,15 +189,15 @@ def test_decode_layers_paged_batch_of_uneven_lengths():
     assert torch.equal(out, first) and kv.status() == 0
 
 
-@pytest.mark.parametrize("streams", [None, "1"])
-def test_decode_28_layers_4096_keys_replayed_from_a_graph(streams, monkeypatch):
+@pytest.mark.parametrize("scratch_mb", [None, "1"])
+def test_decode_28_layers_4096_keys_replayed_from_a_graph(scratch_mb, monkeypatch):
     """The call the benchmark times: 28 layers x 4096 keys through ingot_attn_decode_layers, captured once into a
     CUDA graph and replayed. Every layer of the replay must match the reference, a second replay must give the
-    same bits, and the same holds when all layers share one launch chain."""
+    same bits, and the same holds when a small scratch forces the layers into several groups of launches."""
     import torch
     import ingot_b200 as ib
-    if streams is not None:
-        monkeypatch.setenv("INGOT_DECODE_STREAMS", streams)
+    if scratch_mb is not None:
+        monkeypatch.setenv("INGOT_DECODE_SCRATCH_MB", scratch_mb)
     n_layers, n_keys = W.N_LAYER, 4096
     rng = np.random.default_rng(2024)
     kv = ib.KVCache(ib.KV_CONTIGUOUS, n_layers, HKV, n_keys)
@@ -244,7 +244,7 @@ def test_decode_scratch_follows_the_split_count():
     with torch.cuda.graph(g):
         ib.attn_decode(kv, 0, qd[0], out=small, max_seq_len=300, chunk_keys=64)
     big = torch.zeros(2, 1, H, D, device="cuda")
-    ib.attn_decode_layers(kv, 0, qd, big, max_seq_len=4096, chunk_keys=64)  # 64 splits, two chains: the scratch grows
+    ib.attn_decode_layers(kv, 0, qd, big, max_seq_len=4096, chunk_keys=64)  # 64 splits, two layers: the scratch grows
     torch.cuda.synchronize()
     for l in range(2):
         wl = W.Decode(q[l], [ks[l]], [vs[l]], np.array([4096], dtype=np.int32))

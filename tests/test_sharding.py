@@ -97,3 +97,68 @@ def test_head_output_gather_layout_two_ranks():
         p.join(120)
         assert p.exitcode == 0
     assert ret.get(0) is True and ret.get(1) is True
+
+
+def _monitor_worker(rank, world, port, steps_alive, ret):
+    """Rank `rank` runs `steps_alive[rank]` steps, then leaves between steps (no work in flight)."""
+    from datetime import timedelta
+    import torch.distributed as dist
+    from ingot_b200.sharding import PeerLost, PeerMonitor
+    store = dist.TCPStore("127.0.0.1", port, world, is_master=(rank == 0), timeout=timedelta(seconds=30), wait_for_workers=False)
+    mon = PeerMonitor(store, rank, world)
+    done = 0
+    try:
+        for step in range(steps_alive[rank]):
+            mon.begin_step(step, timeout_s=1.0)
+            done += 1  # the sharded kernels of this step would be launched here
+        ret[rank] = ("left", done)
+    except PeerLost as e:
+        ret[rank] = ("peer lost", done, e.step, e.missing)
+    if rank == 0:  # the store's host stays up until the other rank has stopped using it
+        import time
+        time.sleep(1.5)
+
+
+def test_a_rank_that_leaves_is_noticed_on_the_host_before_the_next_launch():
+    """Two CPU ranks share a store. Rank 1 leaves after three steps; rank 0 must complete exactly those three steps
+    and then get PeerLost for step 3 within its time limit - on the host, with nothing launched for that step."""
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    ret = ctx.Manager().dict()
+    port = _free_port()
+    procs = [ctx.Process(target=_monitor_worker, args=(r, 2, port, {0: 10, 1: 3}, ret)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(60)
+        assert p.exitcode == 0
+    assert ret.get(1) == ("left", 3)
+    assert ret.get(0) == ("peer lost", 3, 3, [1])
+
+
+def test_peer_monitor_with_a_fake_store_that_drops_a_message():
+    """The same logic against a fake store: a peer's announcement that is dropped looks like a peer that left."""
+    from ingot_b200.sharding import PeerLost, PeerMonitor
+
+    class FakeStore:
+        def __init__(self, drop):
+            self.keys, self.drop = set(), drop
+
+        def set(self, k, v):
+            if k not in self.drop:
+                self.keys.add(k)
+
+        def check(self, ks):
+            return all(k in self.keys for k in ks)
+
+    shared = FakeStore(drop={"ingot/step/1/2"})  # rank 2's announcement of step 1 never arrives
+    mons = [PeerMonitor(shared, r, 3) for r in range(3)]
+    for m in mons:
+        m.announce(0)
+    for m in mons:
+        m.begin_step(0, timeout_s=0.2)  # everybody present
+    for m in mons:
+        m.announce(1)
+    with pytest.raises(PeerLost) as e:
+        mons[0].begin_step(1, timeout_s=0.1)
+    assert e.value.missing == [2] and e.value.step == 1
