@@ -636,10 +636,15 @@ def run_e2e_model(args):
     lib.ingot_e2e_bench.argtypes = [C.c_char_p, C.c_char_p, i32p, C.c_int, C.c_int, C.c_int, C.c_int, f64p]
     lib.ingot_e2e_last_error.restype = C.c_char_p
     n_layer, n_vocab = (28, 128256) if not args.small_model else (2, 32064)
-    path = os.path.join(os.environ.get("INGOT_E2E_DIR", "/tmp"), f"ingot_random_l{n_layer}_v{n_vocab}_s0.gguf")
+    tag = "" if args.wtype == "F16" else f"_{args.wtype}_{args.output_type or args.wtype}"
+    path = os.path.join(os.environ.get("INGOT_E2E_DIR", "/tmp"), f"ingot_random_l{n_layer}_v{n_vocab}_s0{tag}.gguf")
     if not os.path.exists(path):
-        make_random_gguf.write(path + ".tmp", n_layer, n_vocab, seed=0)
+        make_random_gguf.write(path + ".tmp", n_layer, n_vocab, seed=0, wtype=args.wtype, output_type=args.output_type)
         os.replace(path + ".tmp", path)
+    # bytes of weights one generated token has to read: every layer matrix and the output matrix (not the embedding table)
+    bpw = {"F16": 2.0, "Q8_0": 34 / 32, "Q4_0": 18 / 32, "Q4_1": 20 / 32, "Q6_K": 210 / 256}
+    layer_params = n_layer * (3072 * 3072 * 2 + 3072 * 1024 * 2 + 3 * 3072 * 8192)
+    weight_bytes = layer_params * bpw[args.wtype] + n_vocab * 3072 * bpw[args.output_type or args.wtype]
     prompt = np.random.default_rng(0).integers(0, n_vocab, size=128).astype(np.int32)
     res = {}
     res["cpu"] = None
@@ -653,8 +658,14 @@ def run_e2e_model(args):
     return {"metric": "whole-model tokens/s, pp128 / tg32 (the reference's `ingot bench` measurement)", "value": res["cuda"]["tg32_tok_s"],
             "unit": "tok/s (tg32)", "n_gpus": 1, "steps": 3, "warmup": 1, "ms_per_step": None, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f16 weights, f32 activations, f16 KV", "data": "synthetic",
-            "config": {"workload": f"random-init Llama-3.2-3B-shaped F16 GGUF, {n_layer} layers, vocab {n_vocab}; 128 prompt ids, 32 greedy steps"},
+            "config": {"workload": f"random-init Llama-3.2-3B-shaped {args.wtype} GGUF (output matrix {args.output_type or args.wtype}), "
+                                   f"{n_layer} layers, vocab {n_vocab}; 128 prompt ids, 32 greedy steps"},
             "cuda_backend": res["cuda"], "cpu_reference_backend": res["cpu"],
+            "roofline": {"bound": "hbm", "unit": "GB/s", "peak": measured_peaks()["hbm_gbs"],
+                         "achieved": round(weight_bytes * res["cuda"]["tg32_tok_s"] / 1e9, 1),
+                         "frac": round(weight_bytes * res["cuda"]["tg32_tok_s"] / 1e9 / measured_peaks()["hbm_gbs"], 4),
+                         "traffic": None, "weight_bytes_per_token": int(weight_bytes),
+                         "note": "single-token steps are bound by reading every weight once per token"},
             "note": "reference README (Apple M5, Metal, F16): pp128 864 tok/s, tg32 15.6 tok/s"}
 
 # ------------------------------------------------------------------------------------------------
@@ -753,6 +764,7 @@ def run_reference(args):
 
 
 def main():
+    global MIN_TIMED_S
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
@@ -760,6 +772,9 @@ def main():
     ap.add_argument("--impl", default="ingot", choices=["ingot", "reference"])
     ap.add_argument("--workload", default="decode_c2", choices=["decode_c2", "prefill_c5", "c1_prefill128", "c3_chunked", "c4_batched", "e2e_model"])
     ap.add_argument("--small-model", action="store_true", help="e2e_model: 2 layers and a 32064-token vocabulary")
+    ap.add_argument("--wtype", default="F16", choices=["F16", "Q8_0", "Q4_0", "Q4_1", "Q6_K"], help="e2e_model: weight type of the GGUF")
+    ap.add_argument("--output-type", default=None, choices=["F16", "Q8_0", "Q4_0", "Q4_1", "Q6_K"],
+                    help="e2e_model: type of the embedding / output matrix (default: --wtype)")
     ap.add_argument("--chunk-keys", type=int, default=0, help="decode split size (0 = library default)")
     ap.add_argument("--prefill-steps", type=int, default=10, help="cap on timed prefill steps (each is ~10 ms)")
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS,
@@ -775,7 +790,6 @@ def main():
     ap.add_argument("--no-graph", action="store_true", help="decode: launch the 28 layers from Python instead of replaying a CUDA graph")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
-    global MIN_TIMED_S
     MIN_TIMED_S = args.min_timed_s
 
     if args.impl == "reference":

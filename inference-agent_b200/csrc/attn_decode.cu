@@ -26,51 +26,16 @@
 // f16; scaling late keeps the error inside the f32-reference tolerance).
 #include "attn_common.cuh"
 #include "ingot_internal.cuh"
+#include "attn_decode_params.cuh"
 
 #include <algorithm>
+#include <cstring>
 #include <mutex>
 
 namespace {
 
 constexpr int kMaxDecodeWarps = 8;
 constexpr int kMaxParts = 64;
-
-struct DecodeParams {
-    const __half* kc;   // layer base
-    const __half* vc;
-    const void* q;
-    void* out;
-    const int32_t* seq_lens;
-    const int32_t* block_tables;
-    float* part;          // split role: partials written here
-    const float* c_part;  // combine role: partials of the launch being merged
-    void* c_out;          // combine role: its output
-    int* status;
-    // Several layers in one launch (blockIdx.z = layer * n_seq + sequence): strides between consecutive layers of
-    // the cache (elements), of q and out ([layer][sequence][head][128], elements) and of the partials (floats).
-    int n_seq;
-    size_t cache_layer_stride, qo_layer_stride, part_layer_stride;
-    size_t cache_extent, part_extent, out_extent;  // bounds-check build: elements of one cache layer, floats of the scratch, elements of out
-    int q_dtype, out_dtype;
-    int n_head, n_head_kv, group;
-    int capacity, paged, max_blocks_per_seq;
-    int len0, chunk_keys, n_parts_max;
-    int early_loads;  // the K/V rows and q read here are not written by the preceding kernel in the stream
-    int split_parts;  // grid.x values below this are split CTAs; the one CTA above it (if any) merges
-    float scale_log2;
-};
-
-// Number of keys of sequence `seq`. Lengths that come from device memory cannot be checked on the host:
-// one that exceeds what the cache (or the block table) can hold is clamped and raises the status word.
-__device__ __forceinline__ int load_seq_len(const DecodeParams& p, int seq) {
-    int n = p.seq_lens ? p.seq_lens[seq] : p.len0;
-    const int bound = p.paged ? p.max_blocks_per_seq * kBlockTokens : p.capacity;
-    if (n > bound) {
-        if (threadIdx.x == 0 && p.status) atomicOr(p.status, kDevErrPosRange);
-        n = bound;
-    }
-    return n;
-}
 
 // Merges the splits of one (sequence, kv head): out = sum_s o_s 2^(m_s-M) / sum_s l_s 2^(m_s-M)
 // (the attn_combine formula, shaders/kernels.metal:502-516). Runs in one extra CTA per (kv head,
@@ -203,17 +168,15 @@ struct VRegs { uint4 v[8]; };  // [slot 0..3 -> keys 2j, 2j+1, 2j+8, 2j+9][chunk
 
 __global__ void __launch_bounds__(kMaxDecodeWarps * 32, 1) attn_decode_kernel(const DecodeParams p) {
     extern __shared__ float smem[];
-    // Programmatic dependent launch: let the next kernel in the stream start as soon as SM resources
-    // allow. Unless the caller vouches that nothing read here was written by the preceding kernel,
-    // wait for that kernel before the first global read; otherwise only before the first global write
-    // (the split scratch and the output are shared with it).
+    // Programmatic dependent launch: let the next kernel in the stream start as soon as SM resources allow, and
+    // wait for the kernel before this one according to p.pdl_mode (see DecodeParams).
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     if ((int)blockIdx.x >= p.split_parts) {  // merge role: partials of the preceding launch
         asm volatile("griddepcontrol.wait;" ::: "memory");
         combine_splits(p, smem, blockIdx.y, blockIdx.z / p.n_seq, blockIdx.z % p.n_seq);
         return;
     }
-    if (!p.early_loads) asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (p.pdl_mode == kPdlWaitFirst) asm volatile("griddepcontrol.wait;" ::: "memory");
 
     const int chunk = blockIdx.x, kvh = blockIdx.y, layer = blockIdx.z / p.n_seq, seq = blockIdx.z % p.n_seq;
     const __half* const kc = p.kc + (size_t)layer * p.cache_layer_stride;
@@ -395,7 +358,7 @@ __global__ void __launch_bounds__(kMaxDecodeWarps * 32, 1) attn_decode_kernel(co
     }
     if (g < G && j == 0) { sm[warp * G + g] = m; sl[warp * G + g] = l; }
     __syncthreads();
-    if (p.early_loads) asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (p.pdl_mode == kPdlEarlyLoads) asm volatile("griddepcontrol.wait;" ::: "memory");
 
     const bool single = n_chunks == 1;
     const size_t part_row0 = ((size_t)seq * p.n_parts_max + chunk) * p.n_head + (size_t)kvh * G;
@@ -430,27 +393,51 @@ int decode_warps_cfg() {
 
 }  // namespace
 
-// Split size and split count of a decode call over n_units = layers x sequences x kv heads independent key ranges
-// of up to max_seq_len keys. Small jobs: fill every CTA slot of the GPU once (the kernel needs ~245 registers per
-// thread, so an SM holds 8 warps) with whole 16-key units per warp. Large jobs: 512 keys per split (256 when several
-// layers share a launch), which keeps variable-length batches balanced across SMs and the last wave short.
+// Split size and split count of one decode launch over `ranges` = layers x sequences x kv heads independent key
+// ranges of up to max_seq_len keys (chunk_keys == 0: chosen here).
+// A split CTA costs about 1.5 us of start-up and drain whatever its size - at a slot's share of the HBM bandwidth
+// that is the time of ~64 keys - so long splits are the efficient ones, but the last wave of long splits leaves
+// SMs idle. Measured on a B200, 28 layers x 4096 keys in one grid: 3.2 / 4.4 / 5.2 / 5.4 / 5.1 / 5.3 TB/s with
+// 128 / 256 / 512 / 768 / 1024 / 2048 keys per split; a 64-sequence paged batch (lengths 256..8192, 4 layers):
+// 5.4 / 5.7 / 5.9 / 6.1 TB/s with 512 / 768 / 1024 / 2048.
+//   * Up to 256 keys: one split (the CTA writes the output itself; a merge launch would cost more than it saves).
+//   * Jobs that do not fill the CTA slots of the GPU even with 512-key splits (a single layer of one sequence):
+//     fill every slot once with whole 16-key units per warp.
+//   * Batches (lengths differ, many items): 2048 keys per split.
+//   * Otherwise the split size, in multiples of 64 keys, that maximises (share of a CTA's life spent streaming) x
+//     (fill of the last wave) = c / (c + 64) x items / (slots x ceil(items / slots)).
 DecodePlan decode_plan(const ingot_kv* kv, int n_layers, int n_seq, int max_seq_len, int chunk_keys) {
     const int n_warps = decode_warps_cfg();
+    const int min_chunk = ((max_seq_len + kMaxParts - 1) / kMaxParts + 15) / 16 * 16;
     if (chunk_keys == 0) {
         const int slots = kv->num_sms * (8 / n_warps);
         const long long ranges = (long long)n_layers * n_seq * kv->n_head_kv;
-        const int per_range = (int)std::max<long long>(1, slots / ranges);
-        const int quantum = n_warps * 16;
-        chunk_keys = ((max_seq_len + per_range - 1) / per_range + quantum - 1) / quantum * quantum;
-        chunk_keys = std::min(std::max(chunk_keys, quantum), n_layers > 1 ? 256 : 512);
+        if (max_seq_len <= 256) {
+            chunk_keys = 256;  // one split per range: its CTA writes the output itself and no merge launch is needed
+        } else if (ranges * ((max_seq_len + 511) / 512) <= slots) {
+            const int per_range = (int)std::max<long long>(1, slots / ranges);
+            const int quantum = n_warps * 16;
+            chunk_keys = ((max_seq_len + per_range - 1) / per_range + quantum - 1) / quantum * quantum;
+            chunk_keys = std::min(std::max(chunk_keys, quantum), 512);
+        } else if (n_seq > 1) {
+            chunk_keys = 2048;
+        } else {
+            double best = -1.0;
+            for (int c = 256; c <= 4096 && c < max_seq_len + 64; c += 64) {
+                const long long items = ranges * ((max_seq_len + c - 1) / c);
+                const long long rounds = (items + slots - 1) / slots;
+                const double score = (double)c / (c + 64) * (double)items / ((double)slots * rounds);
+                if (score > best) { best = score; chunk_keys = c; }
+            }
+        }
     }
-    const int min_chunk = ((max_seq_len + kMaxParts - 1) / kMaxParts + 15) / 16 * 16;
     chunk_keys = std::max(chunk_keys, min_chunk);
     DecodePlan plan;
     plan.chunk_keys = chunk_keys;
     plan.n_parts = (max_seq_len + chunk_keys - 1) / chunk_keys;
     return plan;
 }
+int decode_slots(const ingot_kv* kv) { return kv->num_sms * (8 / decode_warps_cfg()); }
 
 size_t decode_part_floats(int n_seq, int n_parts, int n_head) {
     return (size_t)n_seq * n_parts * n_head * kPartStride;
@@ -460,12 +447,10 @@ size_t decode_part_floats(int n_seq, int n_parts, int n_head) {
 // (merge_only == 0; partials of split ranges into `part`, outputs of single-split ranges straight into `out`) or
 // one merge CTA per (kv head, layer, sequence) that turns the partials in `part` into `out` (merge_only != 0; a
 // no-op when the plan has a single split). q and out are [n_layers][n_seq][n_head][128], `part` holds n_layers
-// blocks of decode_part_floats(). early_loads: the caller vouches that nothing the split CTAs read was written by the
-// kernel before them in the stream, so they wait for it only before their first global write.
+// blocks of decode_part_floats(). pdl_mode: kPdlWaitFirst or kPdlEarlyLoads (see DecodeParams).
 int launch_attn_decode(ingot_kv* kv, int layer, int n_layers, const void* q, int q_dtype, void* out, int out_dtype, int n_head,
                        int n_seq, const int32_t* seq_lens, int max_seq_len, const int32_t* block_tables,
-                       int max_blocks_per_seq, DecodePlan plan, float* part, int merge_only, int early_loads,
-                       cudaStream_t stream) {
+                       int max_blocks_per_seq, DecodePlan plan, float* part, int merge_only, int pdl_mode, cudaStream_t stream) {
     if (merge_only && plan.n_parts <= 1) return INGOT_OK;
     const int n_warps = decode_warps_cfg();
     DecodeParams p;
@@ -484,7 +469,7 @@ int launch_attn_decode(ingot_kv* kv, int layer, int n_layers, const void* q, int
     p.n_head = n_head; p.n_head_kv = kv->n_head_kv; p.group = n_head / kv->n_head_kv;
     p.capacity = kv->capacity; p.paged = kv->layout == INGOT_KV_PAGED; p.max_blocks_per_seq = max_blocks_per_seq;
     p.len0 = max_seq_len; p.chunk_keys = plan.chunk_keys; p.n_parts_max = plan.n_parts;
-    p.early_loads = early_loads;
+    p.pdl_mode = pdl_mode;
     p.split_parts = merge_only ? 0 : plan.n_parts;
     p.scale_log2 = 1.4426950408889634f / sqrtf(float(kHeadDim));
     const int threads = n_warps * 32;
@@ -570,7 +555,7 @@ extern "C" int ingot_attn_decode_noalloc(const void* k_dev, const void* v_dev, i
     p.n_head = n_head; p.n_head_kv = n_head_kv; p.group = n_head / n_head_kv;
     p.capacity = n_ctx; p.paged = 0; p.max_blocks_per_seq = 0;
     p.len0 = n_keys; p.chunk_keys = chunk_keys; p.n_parts_max = n_parts;
-    p.early_loads = 0;
+    p.pdl_mode = 0;
     p.scale_log2 = 1.4426950408889634f / sqrtf(float(kHeadDim));
     const int threads = n_warps * 32;
     const size_t smem_split = (size_t)n_warps * p.group * (kHeadDim + 2);

@@ -156,11 +156,11 @@ int launch_kv_import_f16(ingot_kv* kv, int layer, const __half* k, const __half*
                          const int32_t* block_table, cudaStream_t stream);
 struct DecodePlan { int chunk_keys, n_parts; };
 DecodePlan decode_plan(const ingot_kv* kv, int n_layers, int n_seq, int max_seq_len, int chunk_keys);
+int decode_slots(const ingot_kv* kv);
 size_t decode_part_floats(int n_seq, int n_parts, int n_head);
 int launch_attn_decode(ingot_kv* kv, int layer, int n_layers, const void* q, int q_dtype, void* out, int out_dtype, int n_head,
                        int n_seq, const int32_t* seq_lens, int max_seq_len, const int32_t* block_tables,
-                       int max_blocks_per_seq, DecodePlan plan, float* part, int merge_only, int early_loads,
-                       cudaStream_t stream);
+                       int max_blocks_per_seq, DecodePlan plan, float* part, int merge_only, int pdl_mode, cudaStream_t stream);
 int launch_attn_prefill_mma(ingot_kv* kv, int layer, const void* q, int q_dtype, void* out, int out_dtype,
                             int n_head, int q_pos0, int n_tok, const int32_t* block_table, cudaStream_t stream);
 int launch_attn_prefill_sm100(ingot_kv* kv, int layer, const void* q, int q_dtype, void* const* outs, int n_outs,

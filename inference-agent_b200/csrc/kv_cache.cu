@@ -11,6 +11,7 @@
 #include <new>
 
 #include "ingot_internal.cuh"
+#include "attn_decode_params.cuh"
 
 static thread_local std::string g_last_error;
 
@@ -235,6 +236,8 @@ static int decode_checked(ingot_kv* kv, int layer, const void* q_dev, int q_dtyp
 int ingot_attn_decode(ingot_kv* kv, int layer, const void* q_dev, int q_dtype, void* out_dev, int out_dtype,
                       int n_head, int n_seq, const int32_t* seq_lens_dev, int max_seq_len,
                       const int32_t* block_tables_dev, int max_blocks_per_seq, int chunk_keys, void* stream) {
+    INGOT_REQUIRE(kv != nullptr, "ingot_attn_decode: kv is null");
+    INGOT_REQUIRE(layer >= 0 && layer < kv->n_layer, "ingot_attn_decode: layer out of range");
     return ingot_attn_decode_layers(kv, layer, 1, q_dev, q_dtype, out_dev, out_dtype, n_head, n_seq, seq_lens_dev, max_seq_len,
                                     block_tables_dev, max_blocks_per_seq, chunk_keys, stream);
 }
@@ -253,13 +256,12 @@ int ingot_attn_decode_layers(ingot_kv* kv, int layer_begin, int layer_count, con
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const size_t q_bytes = size_t(n_seq) * n_head * kHeadDim * (q_dtype == INGOT_F32 ? 4 : 2);
     const size_t o_bytes = size_t(n_seq) * n_head * kHeadDim * (out_dtype == INGOT_F32 ? 4 : 2);
-    // The layers are independent of one another, so they go into ONE grid: blockIdx.z runs over (layer, sequence)
-    // and the block scheduler keeps every SM fed from the first CTA of the first layer to the last CTA of the
-    // last - no launch boundary, no dependency between layers. A second, merge-only launch (chained with
-    // programmatic dependent launch, so its CTAs are resident and waiting when the first grid drains) turns the
-    // split partials into the outputs. A single layer is the same two launches.
-    // Only the size of the split scratch (one block of partials per layer) bounds how many layers share a
-    // launch: INGOT_DECODE_SCRATCH_MB (default 256) caps it, and more layers than fit are done in groups.
+    // The layers are independent of one another, so their split CTAs share a grid: blockIdx.z runs over (layer,
+    // sequence), there is no launch boundary between layers and the block scheduler refills an SM the moment a CTA
+    // retires. A merge-only launch (chained with programmatic dependent launch, so its CTAs are resident and
+    // waiting when the split grid drains) then turns the split partials into the outputs. A single layer is the
+    // same two launches. Only the size of the split scratch bounds how many layers share a launch:
+    // INGOT_DECODE_SCRATCH_MB (default 256) caps it, and more layers than fit are done in groups.
     const DecodePlan plan = decode_plan(kv, layer_count, n_seq, max_seq_len, chunk_keys);
     const size_t per_layer = decode_part_floats(n_seq, plan.n_parts, n_head);
     size_t cap_mb = 256;
@@ -278,10 +280,10 @@ int ingot_attn_decode_layers(ingot_kv* kv, int layer_begin, int layer_count, con
         // From the second group on nothing a split CTA READS was written by the launch before it (the previous
         // group's merge): it starts loading at once and waits for that launch only before it overwrites the scratch.
         rc = launch_attn_decode(kv, layer_begin + l0, n, q_l, q_dtype, out_l, out_dtype, n_head, n_seq, seq_lens_dev, max_seq_len,
-                                block_tables_dev, max_blocks_per_seq, plan, kv->part, 0, l0 > 0 ? 1 : 0, s);
+                                block_tables_dev, max_blocks_per_seq, plan, kv->part, 0, l0 > 0 ? kPdlEarlyLoads : kPdlWaitFirst, s);
         if (rc != INGOT_OK) return rc;
         rc = launch_attn_decode(kv, layer_begin + l0, n, q_l, q_dtype, out_l, out_dtype, n_head, n_seq, seq_lens_dev, max_seq_len,
-                                block_tables_dev, max_blocks_per_seq, plan, kv->part, 1, 0, s);
+                                block_tables_dev, max_blocks_per_seq, plan, kv->part, 1, kPdlWaitFirst, s);
         if (rc != INGOT_OK) return rc;
     }
     return INGOT_OK;
