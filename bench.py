@@ -1,16 +1,27 @@
 #!/usr/bin/env python
 """Benchmark of the B200 attention path: decode KV-cache HBM GB/s and causal-prefill TFLOP/s.
 
-    python bench.py --gpus N --steps K --warmup W [--workload decode_c2|prefill_c5] [--impl reference]
+    python bench.py --gpus N --steps K --warmup W [--workload decode_c2|prefill_c5|c1_prefill128|c3_chunked|c4_batched|e2e_model]
+                    [--impl reference]
 
 Headline (`metric`/`value`): single-token decode attention at 4096 keys, 24 query / 8 KV heads,
 head_dim 128, f16 KV cache, one pass over 28 distinct per-layer caches per step (470 MB, larger than
 L2), reported as KV-cache bytes per second with the reference's own `abench` byte formula
 (2 * n_layer * (pos+1) * n_head_kv * head_dim * 2, src/main.cpp:446). With N > 1 every rank decodes its
 own sequence (sequence sharding, no collective on the data path): weak scaling.
-The same line carries a `prefill` object: 32768-token causal GQA prefill (bf16 q, f16 K/V) in TFLOP/s
-counting 4*S^2*H*d/2, sharded by KV head over the N ranks with an NCCL all-gather of the head outputs
-inside the timed region (strong scaling). `--workload prefill_c5` makes that the headline instead.
+
+The same JSON line carries, as objects of their own:
+  prefill        32768-token causal GQA prefill (bf16 q, f16 K/V) in TFLOP/s counting 4*S^2*H*d/2, sharded by KV head
+                 over the N ranks with the gather of the head outputs fused into the kernel (strong scaling);
+  c4_batched     64-sequence paged decode, sequences sharded over the N ranks by length (strong scaling);
+  c1_prefill128, c3_chunked   the two chunked-prefill configurations (N = 1 only: they are replicas).
+Every object has `parity` (max-abs and relative L2 error against the CPU reference on the tensors that were timed,
+computed outside the timed region), `roofline`, and where it applies `e2e` (host buffers, copies inside the timed
+region) and `clocks` (NVML, sampled while the timed region runs).
+
+Timing: W warm-up steps, then blocks of K steps, each block timed with CUDA events on the launching stream, repeated
+back to back between two barriers until at least --min-timed-s (0.5 s) have been timed; `ms_per_step` is the median
+block divided by K, `timed_region_s` the sum of the blocks, MAX over ranks.
 
 `--impl reference` times the reference's own CPU attention (oracle/_ref, the reference sources compiled
 unmodified; the plain-C restatement if that is absent) on the host cores for the same workload.

@@ -41,13 +41,14 @@ cudaError_t ingot_support_rmsnorm(float* out, const float* x, const float* w, in
 cudaError_t ingot_support_silu_mul(float* gate, const float* up, size_t n, cudaStream_t s);
 cudaError_t ingot_support_linear(float* out, const void* w, int w_is_f16, const float* x, int n_in, int n_out, int n_tok,
                                  int accumulate, cudaStream_t s);
-cudaError_t ingot_support_gemv_group(float* const* outs, const void* const* ws, const int* n_out, int n_mat, int swiglu, const float* x,
-                                     const float* norm_w, float eps, int n_in, int accumulate, cudaStream_t s);
+cudaError_t ingot_support_gemv_group(float* const* outs, const void* const* ws, const void* const* scales, int fmt, const int* n_out, int n_mat,
+                                     int swiglu, const float* x, const float* norm_w, float eps, int n_in, int accumulate, cudaStream_t s);
 cudaError_t ingot_support_embed_rows(float* out, const void* table, int is_f16, int n_in, int n_rows_table, const int32_t* rows_dev,
                                      int n_rows, int* status_dev, cudaStream_t s);
 // GGUF block-quantised weights (quant_kernels.cu); `type` is the ggml type code (gguf::TensorType)
 int ingot_quant_supported(int type, int n_in);
 size_t ingot_quant_planar_bytes(int type, int n_in, int n_out);
+size_t ingot_quant_scale_offset(int type, int n_in, int n_out);
 cudaError_t ingot_quant_repack(void* planar_dev, const void* raw_dev, int type, int n_in, int n_out, cudaStream_t s);
 cudaError_t ingot_quant_dequant_rows(float* out, const void* planar_dev, int type, int n_in, int n_out, const int32_t* rows_dev, int n_rows,
                                      int* status_dev, cudaStream_t s);
@@ -83,6 +84,10 @@ struct DevWeight {
     void* data = nullptr;  // f32 / f16 rows, or the repacked planes of a block-quantised matrix (quant_kernels.cu)
     int is_f16 = 0;
     int qtype = -1;        // ggml type code of a block-quantised matrix (Q8_0, Q4_0, Q4_1, Q6_K), else -1
+    void* scales = nullptr;  // block-quantised: the f16 block-scale plane inside `data`
+    void* planes = nullptr;  // block-quantised, optional: resident f16 hi / lo planes (2 x n_in x n_out f16) for batches
+    // format code of the weight-streaming single-token kernel (support_kernels.cu): 0 f16, 1 Q8_0, 2 Q4_0, -1 none
+    int stream_fmt() const { return is_f16 ? 0 : qtype == 8 ? 1 : qtype == 2 ? 2 : -1; }
     int n_in = 0, n_out = 0;
 };
 
@@ -188,6 +193,31 @@ public:
             quant_scratch_elems_ = max_quant_elems_;
             cuda_check(cudaMalloc(&quant_scratch_, 2 * quant_scratch_elems_ * sizeof(__half)), "cudaMalloc(dequantisation scratch)");
             allocs_.push_back(quant_scratch_);
+        }
+        // Batches (16 tokens and up) multiply with the f16 hi / lo planes of a quantised matrix. On a 180 GB part there is
+        // room to keep those planes resident for the layer matrices (4 bytes per weight: 11.6 GB for a 3-billion-parameter
+        // model) next to the quantised copy that single-token steps stream, which saves re-expanding every matrix in every
+        // batch. They are kept only while they fit a quarter of the free memory; INGOT_QUANT_PLANES=0 keeps nothing
+        // resident (the planes are then rebuilt in scratch per use).
+        if (n_batch >= 16 && lin_ws_hint_planes()) {
+            size_t want = 0;
+            for (const DevLayer& D : layers_)
+                for (const DevWeight* w : {&D.wq, &D.wk, &D.wv, &D.wo, &D.w_gate, &D.w_up, &D.w_down})
+                    if (w->qtype >= 0) want += size_t(w->n_in) * w->n_out * 4;
+            size_t free_b = 0, total_b = 0;
+            cuda_check(cudaMemGetInfo(&free_b, &total_b), "cudaMemGetInfo");
+            if (want > 0 && want <= free_b / 4) {
+                for (DevLayer& D : layers_)
+                    for (DevWeight* w : {&D.wq, &D.wk, &D.wv, &D.wo, &D.w_gate, &D.w_up, &D.w_down}) {
+                        if (w->qtype < 0) continue;
+                        const size_t elems = size_t(w->n_in) * w->n_out;
+                        cuda_check(cudaMalloc(&w->planes, 2 * elems * sizeof(__half)), "cudaMalloc(f16 planes)");
+                        allocs_.push_back(w->planes);
+                        cuda_check(ingot_quant_dequant_hilo(w->planes, static_cast<__half*>(w->planes) + elems, w->data, w->qtype, w->n_in,
+                                                            w->n_out, stream_), "dequantise (resident planes)");
+                    }
+                cuda_check(cudaStreamSynchronize(stream_), "resident planes");
+            }
         }
         const size_t nb = size_t(n_batch);
         const size_t q_dim = size_t(c.n_head) * c.head_dim, kv_dim = size_t(c.n_head_kv) * c.head_dim;
@@ -328,7 +358,8 @@ public:
             float* qkv_out[3] = {q_, k_, v_};
             // single token, f16 weights: the weight-streaming kernel; the norm and the projections that share it are one launch
             const bool fused = n == 1 && fuse_decode_ && streamable(D.wq) && streamable(D.wk) && streamable(D.wv) && streamable(D.wo) &&
-                               streamable(D.w_gate) && streamable(D.w_up) && streamable(D.w_down);
+                               streamable(D.w_gate) && streamable(D.w_up) && streamable(D.w_down) && same_fmt(D.wq, D.wk) &&
+                               same_fmt(D.wq, D.wv) && same_fmt(D.w_gate, D.w_up);
             // batches on the tensor-core path: the norm (and below the SwiGLU product) writes the f16 hi/lo activations directly
             const bool tc_layer = n > 1 && lin_ws_ != nullptr && layer_tc_ok(D, n);
             if (fused) {
@@ -523,7 +554,10 @@ private:
             cuda_check(cudaMalloc(&w.data, out_bytes), "cudaMalloc(weight)");
             allocs_.push_back(w.data);
             loader_->copy(raw_tmp_, t.data, t.nbytes());
-            if (quant) cuda_check(ingot_quant_repack(w.data, raw_tmp_, type, w.n_in, w.n_out, loader_->stream()), "repack");
+            if (quant) {
+                cuda_check(ingot_quant_repack(w.data, raw_tmp_, type, w.n_in, w.n_out, loader_->stream()), "repack");
+                w.scales = static_cast<char*>(w.data) + ingot_quant_scale_offset(type, w.n_in, w.n_out);
+            }
             else cuda_check(ingot_quant_bf16_to_f32(static_cast<float*>(w.data), raw_tmp_, size_t(w.n_in) * w.n_out, loader_->stream()), "bf16 -> f32");
             // the output / embedding matrix is expanded only by the batched form with at least 16 rows per step
             const bool layer_matrix = &t != m_.output && &t != m_.tok_embd;
@@ -565,14 +599,18 @@ private:
                 cuda_check(ingot_linear_tc_run(lin_ws_, outs[i], w.data, w.n_in, w.n_out, accumulate ? 1 : 0, stream_), "linear (tensor core)");
                 continue;
             }
-            // Block-quantised matrix: expanded into two f16 planes hi + lo = w (exact), each a tensor-core GEMM into
-            // the same output. The planes are scratch, rebuilt per use: the weights stay quantised in HBM.
-            __half* hi = quant_scratch(size_t(w.n_in) * w.n_out);
+            // Block-quantised matrix: two f16 planes hi + lo = w (exact), each a tensor-core GEMM into the same output.
+            // The planes are resident when memory allows (see the constructor), else rebuilt in scratch per use.
+            __half* hi = w.planes ? static_cast<__half*>(w.planes) : quant_scratch(size_t(w.n_in) * w.n_out);
             __half* lo = hi + size_t(w.n_in) * w.n_out;
-            cuda_check(ingot_quant_dequant_hilo(hi, lo, w.data, w.qtype, w.n_in, w.n_out, stream_), "dequantise (hi/lo)");
+            if (!w.planes) cuda_check(ingot_quant_dequant_hilo(hi, lo, w.data, w.qtype, w.n_in, w.n_out, stream_), "dequantise (hi/lo)");
             cuda_check(ingot_linear_tc_run(lin_ws_, outs[i], hi, w.n_in, w.n_out, accumulate ? 1 : 0, stream_), "linear (tensor core, hi)");
             cuda_check(ingot_linear_tc_run(lin_ws_, outs[i], lo, w.n_in, w.n_out, 1, stream_), "linear (tensor core, lo)");
         }
+    }
+    static bool lin_ws_hint_planes() {
+        const char* e = getenv("INGOT_QUANT_PLANES");
+        return !(e && atoi(e) == 0);
     }
     // Scratch for the f16 hi/lo planes (or, for the f32 fallback, the f32 copy) of one block-quantised matrix: sized at
     // construction for the largest layer matrix, so nothing is allocated inside a forward pass.
@@ -580,14 +618,20 @@ private:
         if (elems > quant_scratch_elems_) throw std::runtime_error("cuda: quantised matrix larger than the dequantisation scratch");
         return static_cast<__half*>(quant_scratch_);
     }
-    static bool streamable(const DevWeight& w) { return w.is_f16 && w.n_in % 256 == 0 && w.n_in <= 12032; }  // bound of ingot_support_gemv_group
+    // what ingot_support_gemv_group takes: f16, Q8_0 or Q4_0 rows whose length is a multiple of one warp-wide load
+    static bool streamable(const DevWeight& w) {
+        const int fmt = w.stream_fmt();
+        return fmt >= 0 && w.n_in % (fmt == 0 ? 256 : fmt == 1 ? 512 : 1024) == 0 && w.n_in <= 12032;
+    }
+    static bool same_fmt(const DevWeight& a, const DevWeight& b) { return a.stream_fmt() == b.stream_fmt(); }
     void gemv_group(float* const* outs, const DevWeight* const* ws, int count, bool swiglu, const float* x, const float* norm_w,
                     bool accumulate) {
         const void* wp[3] = {};
+        const void* sp[3] = {};
         int rows[3] = {};
-        for (int i = 0; i < count; i++) { wp[i] = ws[i]->data; rows[i] = ws[i]->n_out; }
-        cuda_check(ingot_support_gemv_group(outs, wp, rows, count, swiglu ? 1 : 0, x, norm_w, m_.cfg.rms_eps, ws[0]->n_in,
-                                            accumulate ? 1 : 0, stream_), "gemv");
+        for (int i = 0; i < count; i++) { wp[i] = ws[i]->data; sp[i] = ws[i]->scales; rows[i] = ws[i]->n_out; }
+        cuda_check(ingot_support_gemv_group(outs, wp, sp, ws[0]->stream_fmt(), rows, count, swiglu ? 1 : 0, x, norm_w, m_.cfg.rms_eps,
+                                            ws[0]->n_in, accumulate ? 1 : 0, stream_), "gemv");
     }
     void linear(float* out, const DevWeight& w, const float* x, int n_tok, bool accumulate) {
         if (w.qtype >= 0) {

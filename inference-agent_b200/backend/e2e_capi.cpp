@@ -11,6 +11,7 @@
 
 #include "batched_backend.h"
 #include "engine.h"
+#include "metal_backend.h"
 #include "gguf.h"
 #include "model.h"
 #include "sampler.h"
@@ -135,6 +136,34 @@ int ingot_e2e_multi_greedy(const char* gguf_path, const int32_t* prompts, const 
                 if (made[s] >= n_gen) backend->release_sequence(s);
             }
         }
+        return 0;
+    } catch (const std::exception& e) {
+        g_err = e.what();
+        return -1;
+    }
+}
+
+// The reference CLI's `abench` and `bwtest` verbs (src/main.cpp:441-455) as C calls: seconds per token of decode
+// attention over all layers at position `pos` (metal_attention_bench), and the read-bandwidth table on stderr
+// (metal_bandwidth_test) - both resolve to the CUDA backend of this build.
+int ingot_e2e_abench(const char* gguf_path, int pos, int iters, double* secs_per_token, double* kv_bytes) {
+    try {
+        gguf::File f = gguf::File::open(gguf_path);
+        Model model = Model::load(f);
+        *secs_per_token = metal_attention_bench(f, model, pos, iters);
+        *kv_bytes = 2.0 * model.cfg.n_layer * double(pos + 1) * model.cfg.n_head_kv * model.cfg.head_dim * 2;  // src/main.cpp:446
+        return 0;
+    } catch (const std::exception& e) {
+        g_err = e.what();
+        return -1;
+    }
+}
+
+int ingot_e2e_bwtest(const char* gguf_path, double megabytes) {
+    try {
+        gguf::File f = gguf::File::open(gguf_path);
+        Model model = Model::load(f);
+        metal_bandwidth_test(f, model, size_t(megabytes * 1e6));
         return 0;
     } catch (const std::exception& e) {
         g_err = e.what();

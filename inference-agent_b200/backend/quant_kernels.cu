@@ -276,6 +276,8 @@ extern "C" {
 int ingot_quant_supported(int type, int n_in) { return is_block_type(type) && n_in > 0 && n_in % block_elems(type) == 0 && n_in % 32 == 0; }
 
 size_t ingot_quant_planar_bytes(int type, int n_in, int n_out) { return planes_of(type, (size_t)n_in, (size_t)n_out).total; }
+// Byte offset of the f16 block-scale plane inside a repacked matrix (the quant plane starts at offset 0).
+size_t ingot_quant_scale_offset(int type, int n_in, int n_out) { return planes_of(type, (size_t)n_in, (size_t)n_out).d; }
 size_t ingot_quant_raw_bytes(int type, int n_in, int n_out) { return (size_t)n_in * n_out / block_elems(type) * block_bytes(type); }
 
 // raw_dev: the matrix as it lies in the GGUF file, already copied to the device. planar_dev: ingot_quant_planar_bytes.

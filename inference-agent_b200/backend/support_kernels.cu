@@ -6,6 +6,7 @@
 // Single-token steps with f16 weights use the weight-streaming kernel (gemv_stream_kernel); batches use the
 // tensor-core kernel of linear_sm100.cu; the plain kernels here cover f32 weights and odd shapes.
 #include <cuda_fp16.h>
+#include <type_traits>
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <stdlib.h>
@@ -150,7 +151,8 @@ __global__ void __launch_bounds__(256) gemv_kernel(float* out, const W* w, const
 // the wait for the preceding kernel (weights never depend on it), which hides the ramp of every launch
 // behind the tail of the previous one.
 struct GemvGroup {
-    const __half* w[3];
+    const void* w[3];      // weight rows: f16 values, or the quant plane of a repacked Q8_0 / Q4_0 matrix
+    const __half* d[3];    // block scales of a quantised matrix (one per 32 weights), else null
     float* out[3];
     int row_end[3];  // running totals of the matrices' row counts
     int n_mat;
@@ -161,9 +163,13 @@ __device__ __forceinline__ uint4 ld_stream_u4(const void* p) {
     asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
     return v;
 }
-__device__ __forceinline__ float dot8(const uint4& raw, const float* xs) {
+// x' is staged in shared memory in the order the lanes consume it: the j-th float4 that lane l needs for a chunk
+// sits at float4 index (chunk * J + j) * 32 + l (J = float4s per lane and chunk), so that the 32 lanes of a warp
+// read 32 consecutive float4s - conflict-free - instead of 32 segments that are 32 to 128 bytes apart (a 2- to 8-way
+// bank conflict on every read, which cost more shared-memory cycles than the weights cost HBM cycles).
+__device__ __forceinline__ float dot8(const uint4& raw, const float4* x4) {
     const __half2* h = reinterpret_cast<const __half2*>(&raw);
-    const float4 xa = *reinterpret_cast<const float4*>(xs), xb = *reinterpret_cast<const float4*>(xs + 4);
+    const float4 xa = x4[0], xb = x4[32];
     const float2 w0 = __half22float2(h[0]), w1 = __half22float2(h[1]), w2 = __half22float2(h[2]), w3 = __half22float2(h[3]);
     float acc = w0.x * xa.x;
     acc = fmaf(w0.y, xa.y, acc); acc = fmaf(w1.x, xa.z, acc); acc = fmaf(w1.y, xa.w, acc);
@@ -171,9 +177,61 @@ __device__ __forceinline__ float dot8(const uint4& raw, const float* xs) {
     return acc;
 }
 
+// Weight formats of the streaming kernel. A lane's 16-byte load covers kElems weights: 8 f16 values, 16 Q8_0
+// quants (half a block) or the 32 nibbles of one Q4_0 block; the 32 lanes of a warp therefore cover 512 bytes =
+// 256 / 512 / 1024 consecutive weights per load. Quantised rows come from the repacked planes of
+// quant_kernels.cu: quants contiguous per row, one f16 scale per 32 weights in a plane of its own.
+enum : int { kFmtF16 = 0, kFmtQ8_0 = 1, kFmtQ4_0 = 2 };
+template <int kFmt> struct FmtTraits { static constexpr int kElems = kFmt == kFmtF16 ? 8 : kFmt == kFmtQ8_0 ? 16 : 32; };
+
+__device__ __forceinline__ uint32_t prmt_b(uint32_t a, uint32_t b, uint32_t sel) {
+    uint32_t r;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
+    return r;
+}
+// byte k of `word` as a float: the byte becomes the low mantissa bits of 2^23, then 2^23 + bias is subtracted
+__device__ __forceinline__ float byte_f(uint32_t word, int k, float bias) {
+    return __uint_as_float(prmt_b(word, 0x4B000000u, 0x7650u + (uint32_t)k)) - bias;
+}
+// d * sum_i q_i x_i over the weights of one 16-byte load (the grouping of dot_q8_0 / dot_q4_0, src/ops.cpp:143-180)
+template <int kFmt>
+__device__ __forceinline__ float dot_load(const uint4& raw, const float4* x4, unsigned short scale_bits) {
+    if (kFmt == kFmtF16) return dot8(raw, x4);
+    const float d = __half2float(__ushort_as_half(scale_bits));
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+    float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+    if (kFmt == kFmtQ8_0) {
+#pragma unroll
+        for (int j = 0; j < 4; j++) {  // signed byte = (byte ^ 0x80) - 128
+            const uint32_t u = w[j] ^ 0x80808080u;
+            const float4 xv = x4[j * 32];
+            s0 = fmaf(byte_f(u, 0, 8388608.f + 128.f), xv.x, s0);
+            s1 = fmaf(byte_f(u, 1, 8388608.f + 128.f), xv.y, s1);
+            s2 = fmaf(byte_f(u, 2, 8388608.f + 128.f), xv.z, s2);
+            s3 = fmaf(byte_f(u, 3, 8388608.f + 128.f), xv.w, s3);
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 4; j++) {  // bytes 4j..4j+3: low nibbles are weights 4j.., high nibbles weights 16+4j..
+            const uint32_t lo = w[j] & 0x0F0F0F0Fu, hi = (w[j] >> 4) & 0x0F0F0F0Fu;
+            const float4 xl = x4[j * 32];
+            const float4 xh = x4[(4 + j) * 32];
+            s0 = fmaf(byte_f(lo, 0, 8388608.f + 8.f), xl.x, s0);
+            s1 = fmaf(byte_f(lo, 1, 8388608.f + 8.f), xl.y, s1);
+            s2 = fmaf(byte_f(lo, 2, 8388608.f + 8.f), xl.z, s2);
+            s3 = fmaf(byte_f(lo, 3, 8388608.f + 8.f), xl.w, s3);
+            s0 = fmaf(byte_f(hi, 0, 8388608.f + 8.f), xh.x, s0);
+            s1 = fmaf(byte_f(hi, 1, 8388608.f + 8.f), xh.y, s1);
+            s2 = fmaf(byte_f(hi, 2, 8388608.f + 8.f), xh.z, s2);
+            s3 = fmaf(byte_f(hi, 3, 8388608.f + 8.f), xh.w, s3);
+        }
+    }
+    return ((s0 + s1) + (s2 + s3)) * d;
+}
+
 // kLoads: 16-byte weight loads per lane and step (split between gate and up under kSwiGLU). Current and next step
 // are in flight together, so with kLoads = 6 a whole row of 3072 weights (12 chunks) is requested at once.
-template <bool kNorm, bool kSwiGLU, int kLoads>
+template <bool kNorm, bool kSwiGLU, int kLoads, int kFmt>
 __global__ void __launch_bounds__(256) gemv_stream_kernel(const GemvGroup g, const float* x, const float* norm_w, float eps, int n_in,
                                                           int total_rows, int accumulate, int use_pdl) {
     extern __shared__ float xs[];  // x', n_in floats
@@ -181,38 +239,53 @@ __global__ void __launch_bounds__(256) gemv_stream_kernel(const GemvGroup g, con
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int W = gridDim.x * (blockDim.x >> 5), gw = blockIdx.x * (blockDim.x >> 5) + warp;
     if (use_pdl) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    constexpr int kPer = kSwiGLU ? kLoads / 2 : kLoads;  // 256-element chunks per matrix and step
-    const int n_chunks = n_in >> 8;
+    constexpr int kPer = kSwiGLU ? kLoads / 2 : kLoads;  // 512-byte chunks per matrix and step
+    constexpr int kElems = FmtTraits<kFmt>::kElems;       // weights per lane and load
+    const int n_chunks = n_in / (32 * kElems);
     const int steps = (n_chunks + kPer - 1) / kPer;
+    const size_t row_bytes = (size_t)n_chunks * 512;
+    const int row_scales = n_in >> 5;
 
-    auto row_base = [&](int r, const __half*& wa, const __half*& wb) {
+    auto row_base = [&](int r, const char*& wa, const char*& wb, const __half*& da, const __half*& db) {
         if (kSwiGLU) {
-            wa = g.w[0] + (size_t)r * n_in;
-            wb = g.w[1] + (size_t)r * n_in;
+            wa = static_cast<const char*>(g.w[0]) + (size_t)r * row_bytes;
+            wb = static_cast<const char*>(g.w[1]) + (size_t)r * row_bytes;
+            da = kFmt == kFmtF16 ? nullptr : g.d[0] + (size_t)r * row_scales;
+            db = kFmt == kFmtF16 ? nullptr : g.d[1] + (size_t)r * row_scales;
         } else {
             const int m = (r >= g.row_end[0]) + (r >= g.row_end[1] && g.n_mat > 2);
             const int local = m == 0 ? r : r - (m == 1 ? g.row_end[0] : g.row_end[1]);
-            wa = (m == 0 ? g.w[0] : m == 1 ? g.w[1] : g.w[2]) + (size_t)local * n_in;
+            wa = static_cast<const char*>(m == 0 ? g.w[0] : m == 1 ? g.w[1] : g.w[2]) + (size_t)local * row_bytes;
+            da = kFmt == kFmtF16 ? nullptr : (m == 0 ? g.d[0] : m == 1 ? g.d[1] : g.d[2]) + (size_t)local * row_scales;
             wb = nullptr;
+            db = nullptr;
         }
     };
-    auto issue = [&](uint4 (&A)[kPer], uint4 (&B)[kPer], int r, int st) {
-        const __half *wa, *wb;
-        row_base(r, wa, wb);
+    // SA / SB: the block scale that goes with each load (quantised formats)
+    auto issue = [&](uint4 (&A)[kPer], uint4 (&B)[kPer], unsigned short (&SA)[kPer], unsigned short (&SB)[kPer], int r, int st) {
+        const char *wa, *wb;
+        const __half *da, *db;
+        row_base(r, wa, wb, da, db);
 #pragma unroll
         for (int h = 0; h < kPer; h++) {
             const int c = st * kPer + h;
             if (c < n_chunks) {
-                A[h] = ld_stream_u4(wa + (c << 8) + lane * 8);
-                if (kSwiGLU) B[h] = ld_stream_u4(wb + (c << 8) + lane * 8);
+                A[h] = ld_stream_u4(wa + (size_t)c * 512 + lane * 16);
+                if (kSwiGLU) B[h] = ld_stream_u4(wb + (size_t)c * 512 + lane * 16);
+                if (kFmt != kFmtF16) {
+                    const int blk = ((c * 32 + lane) * kElems) >> 5;
+                    SA[h] = __ldg(reinterpret_cast<const unsigned short*>(da) + blk);
+                    if (kSwiGLU) SB[h] = __ldg(reinterpret_cast<const unsigned short*>(db) + blk);
+                }
             }
         }
     };
 
     uint4 cur_a[kPer], cur_b[kPer], nxt_a[kPer], nxt_b[kPer];
+    unsigned short cs_a[kPer] = {}, cs_b[kPer] = {}, ns_a[kPer] = {}, ns_b[kPer] = {};
     int r = gw, st = 0;
     bool have = r < total_rows;
-    if (have) issue(cur_a, cur_b, r, 0);  // before the wait below: weights do not depend on the preceding kernel
+    if (have) issue(cur_a, cur_b, cs_a, cs_b, r, 0);  // before the wait below: weights do not depend on the preceding kernel
 
     if (use_pdl) asm volatile("griddepcontrol.wait;" ::: "memory");
     float ss = 0.f;
@@ -223,7 +296,9 @@ __global__ void __launch_bounds__(256) gemv_stream_kernel(const GemvGroup g, con
             const float4 n = *reinterpret_cast<const float4*>(norm_w + i);
             v.x *= n.x; v.y *= n.y; v.z *= n.z; v.w *= n.w;
         }
-        *reinterpret_cast<float4*>(xs + i) = v;
+        // element i = chunk * 32 * kElems + lane * kElems + 4 j + t  ->  float4 index (chunk * J + j) * 32 + lane
+        const int chunk_e = 32 * kElems, c = i / chunk_e, rem = i - c * chunk_e, l = rem / kElems, jj = (rem - l * kElems) >> 2;
+        reinterpret_cast<float4*>(xs)[(c * (kElems / 4) + jj) * 32 + l] = v;
     }
     if (kNorm) {
         ss = warp_sum(ss);
@@ -242,14 +317,14 @@ __global__ void __launch_bounds__(256) gemv_stream_kernel(const GemvGroup g, con
         int r2 = r, st2 = st + 1;
         if (st2 == steps) { st2 = 0; r2 = r + W; }
         const bool have2 = r2 < total_rows;
-        if (have2) issue(nxt_a, nxt_b, r2, st2);
+        if (have2) issue(nxt_a, nxt_b, ns_a, ns_b, r2, st2);
 #pragma unroll
         for (int h = 0; h < kPer; h++) {
             const int c = st * kPer + h;
             if (c < n_chunks) {
-                const float* xp = xs + (c << 8) + lane * 8;
-                acc_a += dot8(cur_a[h], xp);
-                if (kSwiGLU) acc_b += dot8(cur_b[h], xp);
+                const float4* xp = reinterpret_cast<const float4*>(xs) + c * (kElems / 4) * 32 + lane;
+                acc_a += dot_load<kFmt>(cur_a[h], xp, cs_a[h]);
+                if (kSwiGLU) acc_b += dot_load<kFmt>(cur_b[h], xp, cs_b[h]);
             }
         }
         if (st == steps - 1) {
@@ -271,7 +346,7 @@ __global__ void __launch_bounds__(256) gemv_stream_kernel(const GemvGroup g, con
             acc_b = 0.f;
         }
 #pragma unroll
-        for (int h = 0; h < kPer; h++) { cur_a[h] = nxt_a[h]; if (kSwiGLU) cur_b[h] = nxt_b[h]; }
+        for (int h = 0; h < kPer; h++) { cur_a[h] = nxt_a[h]; cs_a[h] = ns_a[h]; if (kSwiGLU) { cur_b[h] = nxt_b[h]; cs_b[h] = ns_b[h]; } }
         r = r2; st = st2; have = have2;
     }
 }
@@ -384,18 +459,23 @@ cudaError_t ingot_support_silu_mul(float* gate, const float* up, size_t n, cudaS
     return cudaGetLastError();
 }
 
-// One token, f16 weights: out_m (+)= W_m . x' for n_mat <= 3 matrices [n_out[m]][n_in] that share x (see
-// gemv_stream_kernel). norm_w != nullptr folds the RMS norm in; swiglu != 0 takes exactly two matrices of equal
-// height (gate, up) and outs[0] receives silu(gate) * up. n_in must be a multiple of 256.
-cudaError_t ingot_support_gemv_group(float* const* outs, const void* const* ws, const int* n_out, int n_mat, int swiglu, const float* x,
-                                     const float* norm_w, float eps, int n_in, int accumulate, cudaStream_t s) {
-    if (n_mat < 1 || n_mat > 3 || n_in % 256 != 0 || n_in > kGemvMaxIn || (swiglu && (n_mat != 2 || n_out[0] != n_out[1] || !norm_w)))
+// One token: out_m (+)= W_m . x' for n_mat <= 3 matrices [n_out[m]][n_in] of one format that share x (see
+// gemv_stream_kernel). fmt: 0 f16 rows, 1 Q8_0, 2 Q4_0 (ws[m] = the quant plane, scales[m] = the scale plane of a
+// matrix repacked by ingot_quant_repack). norm_w != nullptr folds the RMS norm in; swiglu != 0 takes exactly two
+// matrices of equal height (gate, up) and outs[0] receives silu(gate) * up. n_in must be a multiple of 256 (f16),
+// 512 (Q8_0) or 1024 (Q4_0).
+cudaError_t ingot_support_gemv_group(float* const* outs, const void* const* ws, const void* const* scales, int fmt, const int* n_out, int n_mat,
+                                     int swiglu, const float* x, const float* norm_w, float eps, int n_in, int accumulate, cudaStream_t s) {
+    const int chunk = fmt == kFmtF16 ? 256 : fmt == kFmtQ8_0 ? 512 : 1024;
+    if (fmt < 0 || fmt > 2 || n_mat < 1 || n_mat > 3 || n_in % chunk != 0 || n_in > kGemvMaxIn ||
+        (swiglu && (n_mat != 2 || n_out[0] != n_out[1] || !norm_w)) || (fmt != kFmtF16 && !scales))
         return cudaErrorInvalidValue;
     GemvGroup g = {};
     int total = 0;
     for (int m = 0; m < 3; m++) {
         const int mm = m < n_mat ? m : n_mat - 1;
-        g.w[m] = static_cast<const __half*>(ws[mm]);
+        g.w[m] = ws[mm];
+        g.d[m] = fmt == kFmtF16 ? nullptr : static_cast<const __half*>(scales[mm]);
         g.out[m] = outs[mm];
         if (m < n_mat) total += n_out[m];
         g.row_end[m] = swiglu ? n_out[0] : total;
@@ -403,10 +483,16 @@ cudaError_t ingot_support_gemv_group(float* const* outs, const void* const* ws, 
     g.n_mat = n_mat;
     const int rows = swiglu ? n_out[0] : total;
     const size_t smem = (size_t)n_in * sizeof(float);
-    const bool short_rows = n_in <= 3072;  // short rows: the whole row in flight at once
-    void (*kernel)(GemvGroup, const float*, const float*, float, int, int, int, int) =
-        short_rows ? (swiglu ? gemv_stream_kernel<true, true, 6> : norm_w ? gemv_stream_kernel<true, false, 6> : gemv_stream_kernel<false, false, 6>)
-                   : (swiglu ? gemv_stream_kernel<true, true, 4> : norm_w ? gemv_stream_kernel<true, false, 4> : gemv_stream_kernel<false, false, 4>);
+    // kLoads = 6 for short rows: with the current and the next step in flight the whole row is requested at once
+    const bool short_rows = n_in / chunk <= 12;  // current and next step together cover the row
+    typedef void (*Kernel)(GemvGroup, const float*, const float*, float, int, int, int, int);
+    auto pick = [&](auto fmt_tag) -> Kernel {
+        constexpr int F = decltype(fmt_tag)::value;
+        return short_rows ? (swiglu ? gemv_stream_kernel<true, true, 6, F> : norm_w ? gemv_stream_kernel<true, false, 6, F> : gemv_stream_kernel<false, false, 6, F>)
+                          : (swiglu ? gemv_stream_kernel<true, true, 4, F> : norm_w ? gemv_stream_kernel<true, false, 4, F> : gemv_stream_kernel<false, false, 4, F>);
+    };
+    Kernel kernel = fmt == kFmtF16 ? pick(std::integral_constant<int, kFmtF16>()) : fmt == kFmtQ8_0 ? pick(std::integral_constant<int, kFmtQ8_0>())
+                                                                                               : pick(std::integral_constant<int, kFmtQ4_0>());
     // one resident wave, every warp the same number of rows
     // Environment knobs are process-wide and read once; the SM count belongs to the current device and is looked up
     // on every call (a cached attribute read), so that one process may drive several GPUs.

@@ -67,16 +67,19 @@ def test_greedy_tokens_match_cpu_reference(full, n_batch):
     print(f"\n32 greedy tokens identical (n_batch={n_batch}); smallest reference top-2 margin {want_margin.min():.3e}")
 
 
-@pytest.mark.parametrize("wtype,output_type,n_batch", [
-    ("Q8_0", None, 512),     # one 128-token batch: hi/lo planes through the tensor-core GEMM
-    ("Q4_0", "Q6_K", 512),   # what llama.cpp's Q4_0 files look like: Q6_K embedding / output matrix
-    ("Q4_1", None, 512),
-    ("Q8_0", None, 48),      # chunked prefill
-    ("Q4_0", "Q6_K", 5),     # chunks below the tensor-core minimum: the f32 fallback
+@pytest.mark.parametrize("wtype,output_type,n_batch,resident_planes", [
+    ("Q8_0", None, 512, True),     # one 128-token batch: resident hi/lo planes through the tensor-core GEMM
+    ("Q4_0", "Q6_K", 512, True),   # what llama.cpp's Q4_0 files look like: Q6_K embedding / output matrix
+    ("Q4_1", None, 512, True),     # no streaming kernel for this format: the unfused single-token path
+    ("Q8_0", None, 48, False),     # chunked prefill, hi/lo planes rebuilt in scratch per use
+    ("Q4_0", "Q6_K", 5, True),     # chunks below the tensor-core minimum: the f32 fallback
 ])
-def test_greedy_tokens_match_cpu_reference_quantised(wtype, output_type, n_batch):
+def test_greedy_tokens_match_cpu_reference_quantised(wtype, output_type, n_batch, resident_planes, monkeypatch):
     """The same check on block-quantised GGUFs (2 layers, 32064 tokens): weights stay quantised on the device,
-    single tokens go through the dequantise-in-GEMV kernels, batches through the hi/lo tensor-core path."""
+    single tokens go through the weight-streaming (Q8_0, Q4_0) or dequantise-in-GEMV kernels, batches through the
+    hi/lo tensor-core path."""
+    if not resident_planes:
+        monkeypatch.setenv("INGOT_QUANT_PLANES", "0")
     lib = _engine()
     path, n_vocab = _model(os.environ.get("INGOT_E2E_DIR", "/tmp"), False, wtype, output_type)
     prompt = np.random.default_rng(0).integers(0, n_vocab, size=128).astype(np.int32)
@@ -111,6 +114,21 @@ def test_batched_forward_multi_matches_single_sequence_reference(n_seq, wtype):
     for s in range(min(n_seq, 8)):  # the CPU reference is slow: the first eight sequences
         want, margin = _greedy(lib, path, b"cpu", prompts[s], n_gen, 512)
         assert np.array_equal(got[s], want), f"sequence {s} (prompt {lens[s]} tokens): batched {got[s]} vs reference {want}; margins {margin}"
+
+
+def test_abench_and_bwtest_verbs():
+    """The reference's diagnostics verbs through the link seam: `abench` (seconds per token of decode attention over
+    all layers, bytes by the formula of src/main.cpp:446) and `bwtest` (read-bandwidth table)."""
+    lib = _engine()
+    path, _ = _model(os.environ.get("INGOT_E2E_DIR", "/tmp"))
+    lib.ingot_e2e_abench.argtypes = [C.c_char_p, C.c_int, C.c_int, C.POINTER(C.c_double), C.POINTER(C.c_double)]
+    secs, nbytes = C.c_double(0), C.c_double(0)
+    assert lib.ingot_e2e_abench(path.encode(), 4095, 10, C.byref(secs), C.byref(nbytes)) == 0, lib.ingot_e2e_last_error()
+    assert nbytes.value == 2.0 * 2 * 4096 * 8 * 128 * 2  # the 2-layer test model
+    gbs = nbytes.value / secs.value / 1e9
+    assert 100.0 < gbs < 20000.0, gbs  # a GPU-speed figure, not a CPU one and not a nonsense one
+    lib.ingot_e2e_bwtest.argtypes = [C.c_char_p, C.c_double]
+    assert lib.ingot_e2e_bwtest(path.encode(), 300.0) == 0, lib.ingot_e2e_last_error()
 
 
 def test_backend_errors_match_reference():

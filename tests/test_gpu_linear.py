@@ -7,6 +7,7 @@ src/ops.cpp:127-141), not an f16-activation one.
 import ctypes as C
 import os
 
+import numpy as np
 import pytest
 
 pytestmark = pytest.mark.gpu
@@ -73,15 +74,37 @@ def test_linear_tc_matches_float64(n_tok, n_in, n_out, accumulate, x_scale):
         lib.ingot_linear_ws_destroy(ws)
 
 
+def _quant_planes(lib, type_name, raw, n_in, n_out):
+    """Raw GGUF rows -> repacked device planes and the address of their scale plane."""
+    import torch
+    from oracle import loader
+    P, I = C.c_void_p, C.c_int
+    lib.ingot_quant_planar_bytes.argtypes = [I, I, I]
+    lib.ingot_quant_planar_bytes.restype = C.c_size_t
+    lib.ingot_quant_scale_offset.argtypes = [I, I, I]
+    lib.ingot_quant_scale_offset.restype = C.c_size_t
+    lib.ingot_quant_repack.argtypes = [P, P, I, I, I, P]
+    t = loader.GGML_TYPES[type_name]
+    raw_d = torch.from_numpy(np.ascontiguousarray(raw)).cuda()
+    planar = torch.empty(lib.ingot_quant_planar_bytes(t, n_in, n_out), dtype=torch.uint8, device="cuda")
+    assert lib.ingot_quant_repack(planar.data_ptr(), raw_d.data_ptr(), t, n_in, n_out, None) == 0
+    torch.cuda.synchronize()
+    return planar, planar.data_ptr() + lib.ingot_quant_scale_offset(t, n_in, n_out)
+
+
+@pytest.mark.parametrize("wtype", ["F16", "Q8_0", "Q4_0"])
 @pytest.mark.parametrize("mode", ["qkv_norm", "swiglu", "plain_accumulate", "many_rows"])
-def test_gemv_group_matches_float64(mode):
+def test_gemv_group_matches_float64(mode, wtype):
     """The single-token weight-streaming launch: RMS norm folded into up to three matrix-vector products,
     SwiGLU as the epilogue of gate/up, plain accumulate (wo / down), and a row count far above one wave (logits):
-    against rmsnorm (src/ops.cpp:227-232) and float64 products."""
+    against rmsnorm (src/ops.cpp:227-232) and float64 products - for f16 rows and for Q8_0 / Q4_0 rows read from
+    their repacked planes (values decoded by the CPU checker)."""
     import torch
+    from oracle import loader
     lib = _lib()
-    lib.ingot_support_gemv_group.argtypes = [C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.POINTER(C.c_int), C.c_int, C.c_int,
-                                             C.c_void_p, C.c_void_p, C.c_float, C.c_int, C.c_int, C.c_void_p]
+    lib.ingot_support_gemv_group.argtypes = [C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.c_int,
+                                             C.POINTER(C.c_int), C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_float, C.c_int,
+                                             C.c_int, C.c_void_p]
     swiglu = int(mode == "swiglu")
     norm = mode != "plain_accumulate"
     accumulate = int(mode == "plain_accumulate")
@@ -90,21 +113,38 @@ def test_gemv_group_matches_float64(mode):
     g = torch.Generator(device="cuda").manual_seed(len(mode))
     x = torch.randn(n_in, device="cuda", generator=g) * 3
     nw = 1 + 0.1 * torch.randn(n_in, device="cuda", generator=g)
-    ws = [(torch.randn(r, n_in, device="cuda", generator=g) * 0.02).half() for r in rows]
+    keep = []
+    if wtype == "F16":
+        ws = [(torch.randn(r, n_in, device="cuda", generator=g) * 0.02).half() for r in rows]
+        w_ptrs, s_ptrs, fmt = [w.data_ptr() for w in ws], [None] * len(rows), 0
+        w64 = [w.double() for w in ws]
+    else:
+        rng = np.random.default_rng([len(mode), len(wtype)])
+        orc = loader.load_oracle()
+        w_ptrs, s_ptrs, w64, fmt = [], [], [], {"Q8_0": 1, "Q4_0": 2}[wtype]
+        for r in rows:
+            raw = loader.random_blocks(wtype, r, n_in, rng)
+            planar, scale_ptr = _quant_planes(lib, wtype, raw, n_in, r)
+            keep.append(planar)
+            w_ptrs.append(planar.data_ptr())
+            s_ptrs.append(scale_ptr)
+            vals = np.stack([loader.dequant(orc, "oracle_", wtype, raw[i], n_in) for i in range(r)])
+            w64.append(torch.from_numpy(vals).cuda().double())
     outs0 = [torch.randn(r, device="cuda", generator=g) for r in rows]
     outs = [o.clone() for o in outs0]
     eps = 1e-5
     outs_p = (C.c_void_p * len(rows))(*[o.data_ptr() for o in outs])
-    ws_p = (C.c_void_p * len(rows))(*[w.data_ptr() for w in ws])
+    ws_p = (C.c_void_p * len(rows))(*w_ptrs)
+    sc_p = (C.c_void_p * len(rows))(*s_ptrs)
     rows_p = (C.c_int * len(rows))(*rows)
     stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
     for _ in range(2 if not accumulate else 1):  # a second launch right behind the first (dependent launch) gives the same result
-        assert lib.ingot_support_gemv_group(outs_p, ws_p, rows_p, len(rows), swiglu, x.data_ptr(), nw.data_ptr() if norm else None, eps,
-                                            n_in, accumulate, stream) == 0
+        assert lib.ingot_support_gemv_group(outs_p, ws_p, sc_p, fmt, rows_p, len(rows), swiglu, x.data_ptr(),
+                                            nw.data_ptr() if norm else None, eps, n_in, accumulate, stream) == 0
     torch.cuda.synchronize()
     xd = x.double()
     h = xd * torch.rsqrt((xd * xd).mean() + eps) * nw.double() if norm else xd
-    want = [w.double() @ h for w in ws]
+    want = [w @ h for w in w64]
     if swiglu:
         gate, up = want
         ref = gate / (1 + torch.exp(-gate)) * up
