@@ -160,6 +160,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                           const Sm100Params p) {
     extern __shared__ unsigned char smem_dyn[];
+    TIMING(const long long t_entry = clock64();)
     INGOT_PDL_TRIGGER();
     const uint32_t smem_base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
     unsigned char* smem_al = smem_dyn + (smem_base - smem_u32(smem_dyn));
@@ -205,6 +206,7 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_k, const __gri
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = bars->tmem_base;
+    TIMING(const long long t_setup = clock64();)
 
     if (warp_u < 4) {
         asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
@@ -348,21 +350,68 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_k, const __gri
         const uint32_t s_tmem = tmem + q * 128 + lane_sel;
         const uint32_t o_tmem = tmem + 256 + q * 128 + lane_sel;
 
-        // Stage this row of Q into the 128-byte-swizzled K-major layout the MMA descriptor expects:
-        // 16-byte chunk c of row r lands at r*128 + ((c & 7) ^ (r & 7))*16 in the box of dims (c>>3)*64.
+        // Q_q in shared memory is a [128 rows][128 dims] f16 K-major operand with 128-byte swizzle: 16-byte chunk c of
+        // row r lands at r*128 + ((c & 7) ^ (r & 7))*16 in the box of dims (c>>3)*64.
         {
-            unsigned char* qdst = smem_al + kOffQ + q * kQBytes + row_in_tile * 128;
-            const size_t qbase = ((size_t)tok * p.n_head + head) * kHeadDim;
+            // Stage the tile's Q rows. Each warp stages the 32 rows of its own lanes, two rows (2 x 256 bytes of f16) per
+            // load instruction with lane = 16-byte piece, so that global reads are whole 128-byte lines; the owner
+            // of a row hands its source row index to the copying lanes. All sixteen loads are issued before the
+            // first store: one round trip to L2 instead of sixteen.
+            const int my_src = valid ? tok * p.n_head + head : -1;  // row of q [n_tok * n_head][128]
+            unsigned char* qtile = smem_al + kOffQ + q * kQBytes;
+            const int piece = lane & 15, warp_row0 = (warp & 3) << 5;
+            auto put = [&](int it, const uint4& v) {
+                const int r = warp_row0 + it * 2 + (lane >> 4);
+                *reinterpret_cast<uint4*>(qtile + (piece >> 3) * kHalfBytes + r * 128 + (((piece & 7) ^ (r & 7)) << 4)) = v;
+            };
+            // One loop per element type, so that the loads of a loop are straight-line code the compiler can issue together.
+            if (p.q_dtype == INGOT_F32) {
 #pragma unroll
-            for (int c = 0; c < 16; c++) {
-                const uint4 val = valid && INGOT_CHECK(qbase + c * 8, 8, p.q_extent, p.status) ? load_q8(p.q, p.q_dtype, qbase + c * 8)
-                                                                                                   : make_uint4(0, 0, 0, 0);
-                *reinterpret_cast<uint4*>(qdst + (c >> 3) * kHalfBytes + (((c & 7) ^ (row_in_tile & 7)) << 4)) = val;
+                for (int half = 0; half < 2; half++) {
+                    float4 lo[8], hi[8];
+#pragma unroll
+                    for (int i = 0; i < 8; i++) {
+                        const int it = half * 8 + i;
+                        const int src = __shfl_sync(0xffffffffu, my_src, it * 2 + (lane >> 4));
+                        const size_t e = (size_t)max(src, 0) * kHeadDim + piece * 8;
+                        const bool in = src >= 0 && INGOT_CHECK(e, 8, p.q_extent, p.status);
+                        const float4* g = reinterpret_cast<const float4*>(static_cast<const float*>(p.q) + e);
+                        lo[i] = in ? __ldg(g) : make_float4(0.f, 0.f, 0.f, 0.f);
+                        hi[i] = in ? __ldg(g + 1) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    }
+#pragma unroll
+                    for (int i = 0; i < 8; i++)
+                        put(half * 8 + i, make_uint4(pack_half2_rn(lo[i].x, lo[i].y), pack_half2_rn(lo[i].z, lo[i].w),
+                                                     pack_half2_rn(hi[i].x, hi[i].y), pack_half2_rn(hi[i].z, hi[i].w)));
+                }
+            } else {
+                const bool bf16 = p.q_dtype == INGOT_BF16;  // same size as f16: the raw loads are the same
+                uint4 qv[16];
+#pragma unroll
+                for (int it = 0; it < 16; it++) {
+                    const int src = __shfl_sync(0xffffffffu, my_src, it * 2 + (lane >> 4));
+                    const size_t e = (size_t)max(src, 0) * kHeadDim + piece * 8;
+                    qv[it] = src >= 0 && INGOT_CHECK(e, 8, p.q_extent, p.status)
+                                 ? __ldg(reinterpret_cast<const uint4*>(static_cast<const unsigned short*>(p.q) + e))
+                                 : make_uint4(0, 0, 0, 0);
+                }
+#pragma unroll
+                for (int it = 0; it < 16; it++) {
+                    uint4 v = qv[it];
+                    if (bf16) {  // bf16 -> f32 is a 16-bit shift; f32 -> f16 rounds to nearest
+                        uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                        for (int i = 0; i < 4; i++) w[i] = pack_half2_rn(__uint_as_float(w[i] << 16), __uint_as_float(w[i] & 0xffff0000u));
+                        v = make_uint4(w[0], w[1], w[2], w[3]);
+                    }
+                    put(it, v);
+                }
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy stores -> async proxy (MMA)
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_addr(&bars->q_ready));
         }
+        TIMING(const long long t_q = clock64(); long long t_s0 = 0;)
 
         float m_ref = 0.f, l = 0.f;
         bool ok = true;
@@ -372,7 +421,7 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_k, const __gri
             const int j = j0 + jj;
             TIMING(c0 = clock64();)
             ok = mbar_wait(bar_addr(&bars->s_ready[q]), (uint32_t)(jj & 1), abort_flag, p.wait_limit_ns);
-            TIMING(c1 = clock64();)
+            TIMING(c1 = clock64(); if (jj == 0) t_s0 = c1;)
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after();
@@ -457,10 +506,12 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_k, const __gri
                           (clock64() - t_begin) / n_it, t_w / n_it, t_ld / n_it, t_mx / n_it, t_ex / n_it, t_st / n_it);)
 
         // ---------------- epilogue: O / l -> global ----------------
+        TIMING(const long long t_loop = clock64();)
         if (ok && n_it > 0) {
             ok = mbar_wait(bar_addr(&bars->o_final[q]), 0, abort_flag, p.wait_limit_ns);
             ok = __all_sync(0xffffffffu, ok);
         }
+        TIMING(const long long t_of = clock64();)
         const bool partial = p.n_split > 1;
         float* part_row = nullptr;
         if (partial && valid) {
@@ -484,6 +535,12 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_k, const __gri
             unsigned char* stage = smem_al + kOffQ + q * kQBytes;  // [128 rows][256 B], 16-byte pieces XOR-swizzled by row
             const int n_pass = f32_out ? 2 : 1;
             const int warp_row0 = (warp & 3) << 5;
+            // Destination row of this thread's query row, handed to the lanes that copy it out (no division there):
+            // a row of the partials, or (token, head) of the output; -1 past the end.
+            const int my_dst = !valid ? -1 : partial ? R : tok * p.out_n_head + p.out_head0 + head;
+            const size_t dst_row_bytes = partial ? (size_t)kPartStride * 4 : (size_t)kHeadDim * (f32_out ? 4 : 2);
+            unsigned char* dst0 = partial ? reinterpret_cast<unsigned char*>(p.part + ((size_t)split * gridDim.y + kvh) * n_rows * kPartStride)
+                                          : static_cast<unsigned char*>(p.outs[0]);
             for (int ps = 0; ps < n_pass; ps++) {
                 if (ps) __syncwarp();
                 unsigned char* my = stage + row_in_tile * 256;
@@ -520,31 +577,35 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_k, const __gri
                 __syncwarp();
                 // Each warp copies out the 32 rows its own lanes staged: two rows per instruction.
                 const int piece = lane & 15;
+                const size_t col_bytes = (size_t)(f32_out ? ps * 256 : 0) + piece * 16;
 #pragma unroll 4
                 for (int it = 0; it < 16; it++) {
-                    const int r = warp_row0 + it * 2 + (lane >> 4);
-                    const int Rr = row_base + q * kTileRows + r;
-                    if (Rr < n_rows) {
+                    const int owner = it * 2 + (lane >> 4);
+                    const int dr = __shfl_sync(0xffffffffu, my_dst, owner);
+                    if (dr >= 0) {
+                        const int r = warp_row0 + owner;
                         const uint4 val = *reinterpret_cast<const uint4*>(stage + r * 256 + ((piece ^ (r & 7)) << 4));
-                        size_t byte_off;
+                        const size_t byte_off = (size_t)dr * dst_row_bytes + col_bytes;
                         if (partial) {
-                            byte_off = ((((size_t)split * gridDim.y + kvh) * n_rows + Rr) * kPartStride + ps * 64) * 4 + piece * 16;
-                        } else {
-                            const size_t row_elem = ((size_t)(Rr / G) * p.out_n_head + p.out_head0 + kvh * G + Rr % G) * kHeadDim;
-                            byte_off = f32_out ? (row_elem + ps * 64) * 4 + piece * 16 : row_elem * 2 + piece * 16;
-                        }
-                        if (partial) {
-                            if (INGOT_CHECK(byte_off / 4, 4, p.part_extent, p.status))
-                                *reinterpret_cast<uint4*>(reinterpret_cast<unsigned char*>(p.part) + byte_off) = val;
+                            if (INGOT_CHECK((reinterpret_cast<unsigned char*>(dst0) - reinterpret_cast<unsigned char*>(p.part) + byte_off) / 4, 4,
+                                            p.part_extent, p.status))
+                                *reinterpret_cast<uint4*>(dst0 + byte_off) = val;
                         } else if (INGOT_CHECK(byte_off / (f32_out ? 4 : 2), f32_out ? 4 : 8, p.out_extent, p.status)) {
+                            *reinterpret_cast<uint4*>(dst0 + byte_off) = val;
+                            if (p.n_outs > 1) {
 #pragma unroll
-                            for (int d = 0; d < kMaxOutputs; d++)  // unrolled: keeps the pointer table in the parameter bank
-                                if (d < p.n_outs) *reinterpret_cast<uint4*>(static_cast<unsigned char*>(p.outs[d]) + byte_off) = val;
+                                for (int d = 1; d < kMaxOutputs; d++)  // unrolled: keeps the pointer table in the parameter bank
+                                    if (d < p.n_outs) *reinterpret_cast<uint4*>(static_cast<unsigned char*>(p.outs[d]) + byte_off) = val;
+                            }
                         }
                     }
                 }
             }
         }
+        TIMING(if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && warp == 4 && lane == 0)
+                   printf("CTA phases (cycles): set-up + wait for the kernel before %lld, Q staged %lld, first S ready %lld, %d key tiles %lld, "
+                          "last PV retired %lld, O stored %lld\n", t_setup - t_entry, t_q - t_setup, t_s0 - t_q, n_it, t_loop - t_s0, t_of - t_loop,
+                          clock64() - t_of);)
     }
 
     // ---------------- teardown ----------------

@@ -310,10 +310,12 @@ int ingot_attn_prefill(ingot_kv* kv, int layer, const void* q_dev, int q_dtype, 
         INGOT_REQUIRE(block_table_dev != nullptr, "ingot_attn_prefill: paged cache needs a block table");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     // The tcgen05 kernel works on 256-row tiles of one KV head (and splits the keys over CTAs when there
-    // are few row tiles). Measured on a B200: a 512-token chunk onto 3584 cached positions takes 47 us
-    // against 162 us for the warp-MMA kernel; at 128 tokens the warp-MMA kernel's finer 64-row tiles win
-    // (11.5 us against 20 us).
-    const bool use_sm100 = impl == 2 || (impl == 0 && size_t(n_tok) * n_head >= 4096);
+    // are few row tiles). Measured on a B200, K1 + K2 per layer: a 512-token chunk onto 3584 cached positions takes
+    // 42 us against 162 us for the warp-MMA kernel, 128 tokens at position 0 take 11.9 us against 13.4 us.
+    // The tcgen05 kernel has a floor of about 10 us per launch; the warp-MMA kernel undercuts it only for a short chunk
+    // at the very start of a sequence (measured at 24/8 heads: 64 tokens at position 0 are a tie, 16 tokens onto 1024
+    // keys already take twice as long on the warp-MMA kernel).
+    const bool use_sm100 = impl == 2 || (impl == 0 && q_pos0 + n_tok > 64);
     if (use_sm100)
         return launch_attn_prefill_sm100(kv, layer, q_dev, q_dtype, &out_dev, 1, out_dtype, n_head, n_head, 0, q_pos0, n_tok,
                                          block_table_dev, nullptr, 0, s);
