@@ -49,7 +49,7 @@ PREFILL_TOKENS = 32768
 # the same kernels. decode: captured at the benchmark shape. prefill: reads captured at 8192 tokens (84.0 MB) and
 # scaled by the 4x token count (compulsory q/K/V traffic grows in proportion); writes are the 32768 x 24 x 128 f16
 # output, 201 MB, which unlike the 8192-token case (50 MB, absorbed by L2 during the capture) cannot stay in L2.
-NCU_TRAFFIC = {"attn_decode_kernel": 16947456, "attn_prefill_sm100_kernel": 4 * 83955712 + PREFILL_TOKENS * H * D * 2}
+NCU_TRAFFIC = {"attn_decode_kernel": 470275840 + 4313344, "attn_prefill_sm100_kernel": 4 * 83955712 + PREFILL_TOKENS * H * D * 2}
 MIN_TIMED_S = 0.5  # the timed region is repeated in blocks of `steps` steps until it is at least this long
 
 
