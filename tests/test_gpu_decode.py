@@ -161,6 +161,25 @@ def test_batched_append_then_decode_paged():
         helpers.assert_parity(out[s].cpu().numpy(), want[0], f"batched append+decode, sequence {s}")
 
 
+@pytest.mark.parametrize("lens", [(2100, 300, 20), (1023, 1024, 1025, 257), (4096,), (300,)])
+def test_decode_ragged_batches_library_plan_vs_explicit_split(lens):
+    """Few sequences of very different lengths in one call: the library's own split plan and an explicit 256-key
+    split (many empty split CTAs for the short sequences, single-split ranges written directly) against the CPU
+    reference and against each other."""
+    rng = np.random.default_rng(len(lens) * 1000 + lens[0])
+    lens = np.array(lens, dtype=np.int32)
+    q = rng.standard_normal((len(lens), H, D), dtype=np.float32)
+    ks = [rng.standard_normal((n, HKV, D), dtype=np.float32).astype(np.float16) for n in lens]
+    vs = [rng.standard_normal((n, HKV, D), dtype=np.float32).astype(np.float16) for n in lens]
+    wl = W.Decode(q, ks, vs, lens)
+    want = helpers.oracle_decode(wl)
+    planned, _ = helpers.gpu_decode(wl, paged=True)
+    launched, _ = helpers.gpu_decode(wl, paged=True, chunk_keys=256)
+    helpers.assert_parity(planned.cpu().numpy(), want, "library plan")
+    helpers.assert_parity(launched.cpu().numpy(), want, "256-key splits")
+    assert np.abs(planned.cpu().numpy() - launched.cpu().numpy()).max() < 1e-4  # two summation orders of the same f16 products
+
+
 def test_empty_calls_are_no_ops():
     import ingot_b200 as ib
     lib = ib.lib()
