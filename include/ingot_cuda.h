@@ -220,6 +220,19 @@ ingot_kv* ingot_mg_kv(ingot_mg* mg, int dev);
 void* ingot_mg_out(ingot_mg* mg, int dev);
 void* ingot_mg_stream(ingot_mg* mg, int dev);
 int ingot_mg_prefill(ingot_mg* mg, int layer, const void* const* q_dev, int q_dtype, int q_pos0, int n_tok, int timeout_ms);
+/* Prefill attention with the queries and the output in HOST memory and the cache resident on the device (the keys of
+ * positions 0 .. q_pos0+n_tok-1 are in the cache already, e.g. after ingot_rope_kv_append or ingot_kv_import_f16):
+ * q_host [n_tok][n_head][128] (f32, f16 or bf16) in, out_host [n_tok][n_head][128] (f32 or f16) out. The rows are
+ * processed in chunks of chunk_tokens tokens (0: three full waves of CTAs, 4693 tokens at 24/8 heads) so that the copy of the next chunk in, the attention of the
+ * current one and the copy of the previous one out overlap (copy streams of the handle's own; the caller's stream
+ * carries the kernels and, at the end, waits for the last copy out). Asynchronous: synchronise `stream` before
+ * reading out_host. Host buffers should be pinned. Not capturable into a CUDA graph. block_table_dev as for
+ * ingot_attn_prefill. Replaces: a host-side loop over src/cpu_backend.cpp:51-69 for a block of tokens whose q rows
+ * live in host memory. */
+int ingot_attn_prefill_host(ingot_kv* kv, int layer, const void* q_host, int q_dtype, void* out_host, int out_dtype,
+                            int n_head, int q_pos0, int n_tok, const int32_t* block_table_dev, int chunk_tokens,
+                            void* stream);
+
 /* Length-balanced assignment of n_seq sequences (key counts lens[]) to n_ranks GPUs for the sequence-sharded
  * batched decode: longest first, each to the least loaded rank (ties to the lower rank). rank_of_seq[i] receives
  * the rank of sequence i. Pure host code. */

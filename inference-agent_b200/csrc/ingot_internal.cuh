@@ -75,6 +75,9 @@ struct ingot_kv {
     cudaGraph_t host_graph = nullptr;
     cudaGraphExec_t host_exec = nullptr;
     cudaStream_t capture_stream = nullptr;
+    // ingot_attn_prefill_host: copy streams and the events that hand its two staging buffers round
+    cudaStream_t copy_in_stream = nullptr, copy_out_stream = nullptr;
+    cudaEvent_t ev_entry = nullptr, ev_in[2] = {nullptr, nullptr}, ev_done[2] = {nullptr, nullptr}, ev_out[2] = {nullptr, nullptr};
     int host_key[3] = {-1, -1, -1};      // layer_begin, layer_count, n_head the graph was captured for
     const float* host_inv_freq = nullptr;
     int host_calls = 0;                  // calls seen with this key (the first runs eagerly and sizes the scratch)

@@ -109,6 +109,14 @@ void ingot_kv_destroy(ingot_kv* kv) {
     cudaFree(kv->host_pos_dev);
     cudaFreeHost(kv->host_pos_pinned);
     if (kv->capture_stream) cudaStreamDestroy(kv->capture_stream);
+    if (kv->copy_in_stream) cudaStreamDestroy(kv->copy_in_stream);
+    if (kv->copy_out_stream) cudaStreamDestroy(kv->copy_out_stream);
+    if (kv->ev_entry) cudaEventDestroy(kv->ev_entry);
+    for (int b = 0; b < 2; b++) {
+        if (kv->ev_in[b]) cudaEventDestroy(kv->ev_in[b]);
+        if (kv->ev_done[b]) cudaEventDestroy(kv->ev_done[b]);
+        if (kv->ev_out[b]) cudaEventDestroy(kv->ev_out[b]);
+    }
     delete kv;
 }
 
@@ -468,6 +476,93 @@ int ingot_attn_layers_host(ingot_kv* kv, int layer_begin, int layer_count, const
         if (rc != INGOT_OK) return rc;
     }
     INGOT_CUDA_TRY(cudaMemcpyAsync(out_host, o_d, L * q_elems * 4, cudaMemcpyDeviceToHost, s));
+    return INGOT_OK;
+}
+
+// Prefill with the queries and the output in host memory, the cache resident: the rows are cut into chunks and the
+// copy of chunk c+1 in, the attention of chunk c and the copy of chunk c-1 out run at the same time (two copy streams
+// of the handle's own beside the caller's stream, two staging buffers in each direction handed round with events).
+int ingot_attn_prefill_host(ingot_kv* kv, int layer, const void* q_host, int q_dtype, void* out_host, int out_dtype, int n_head,
+                            int q_pos0, int n_tok, const int32_t* block_table_dev, int chunk_tokens, void* stream) {
+    INGOT_REQUIRE(kv != nullptr, "ingot_attn_prefill_host: kv is null");
+    INGOT_REQUIRE_DEVICE(kv);
+    INGOT_REQUIRE(layer >= 0 && layer < kv->n_layer, "ingot_attn_prefill_host: layer out of range");
+    INGOT_REQUIRE(n_tok >= 0 && q_pos0 >= 0 && chunk_tokens >= 0, "ingot_attn_prefill_host: negative range");
+    if (n_tok == 0) return INGOT_OK;
+    INGOT_REQUIRE(q_host && out_host, "ingot_attn_prefill_host: null q/out");
+    INGOT_REQUIRE(n_head >= kv->n_head_kv && n_head % kv->n_head_kv == 0, "ingot_attn_prefill_host: n_head must be a multiple of n_head_kv");
+    if ((q_dtype != INGOT_F32 && q_dtype != INGOT_F16 && q_dtype != INGOT_BF16) || (out_dtype != INGOT_F32 && out_dtype != INGOT_F16)) {
+        ingot_set_error("ingot_attn_prefill_host: unsupported dtype");
+        return INGOT_ERR_UNSUPPORTED;
+    }
+    if (kv->layout == INGOT_KV_CONTIGUOUS)
+        INGOT_REQUIRE(size_t(q_pos0) + n_tok <= size_t(kv->capacity), "context window exceeded");
+    else
+        INGOT_REQUIRE(block_table_dev != nullptr, "ingot_attn_prefill_host: paged cache needs a block table");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    INGOT_CUDA_TRY(cudaStreamIsCapturing(s, &cap));
+    INGOT_REQUIRE(cap == cudaStreamCaptureStatusNone, "ingot_attn_prefill_host: not capturable (it uses streams of its own)");
+    // Default chunk: as many tokens as give three full waves of the tcgen05 kernel's CTAs (one CTA per SM, 256 (token,
+    // head) rows of one KV head each) - 4693 tokens at 24/8 heads on 148 SMs; a 4096-token chunk is 2.6 waves.
+    const int group = n_head / kv->n_head_kv;
+    const int auto_chunk = std::max(512, (3 * kv->num_sms / kv->n_head_kv) * 256 / group);
+    const int chunk = std::min(n_tok, chunk_tokens > 0 ? chunk_tokens : auto_chunk);
+    // (Smaller first and last chunks, whose copies overlap nothing, were measured and are not faster: 901 against 918 TFLOP/s.)
+    const int n_chunks = (n_tok + chunk - 1) / chunk;
+    const size_t q_row = size_t(n_head) * kHeadDim * (q_dtype == INGOT_F32 ? 4 : 2);
+    const size_t o_row = size_t(n_head) * kHeadDim * (out_dtype == INGOT_F32 ? 4 : 2);
+    const size_t q_buf = (size_t(chunk) * q_row + 255) / 256 * 256, o_buf = (size_t(chunk) * o_row + 255) / 256 * 256;
+    const size_t need = 2 * (q_buf + o_buf);
+    if (need > kv->stage_bytes) {
+        void* bigger = nullptr;
+        INGOT_CUDA_TRY(cudaMalloc(&bigger, need));
+        if (kv->stage) kv->retired.push_back(kv->stage);  // kernels in flight (or a captured graph) may still use it
+        kv->stage = bigger;
+        kv->stage_bytes = need;
+        kv->host_key[0] = -1;  // the captured graph of the single-token host form points into the old staging area
+    }
+    if (!kv->copy_in_stream) {
+        INGOT_CUDA_TRY(cudaStreamCreateWithFlags(&kv->copy_in_stream, cudaStreamNonBlocking));
+        INGOT_CUDA_TRY(cudaStreamCreateWithFlags(&kv->copy_out_stream, cudaStreamNonBlocking));
+        INGOT_CUDA_TRY(cudaEventCreateWithFlags(&kv->ev_entry, cudaEventDisableTiming));
+        for (int b = 0; b < 2; b++) {
+            INGOT_CUDA_TRY(cudaEventCreateWithFlags(&kv->ev_in[b], cudaEventDisableTiming));
+            INGOT_CUDA_TRY(cudaEventCreateWithFlags(&kv->ev_done[b], cudaEventDisableTiming));
+            INGOT_CUDA_TRY(cudaEventCreateWithFlags(&kv->ev_out[b], cudaEventDisableTiming));
+        }
+    }
+    char* base = static_cast<char*>(kv->stage);
+    char* q_stage[2] = {base, base + q_buf};
+    char* o_stage[2] = {base + 2 * q_buf, base + 2 * q_buf + o_buf};
+    // Whatever the caller's stream still has to do with the staging buffers (an earlier call of this function ends with
+    // the stream waiting for its last copy out) comes before the first copy in.
+    INGOT_CUDA_TRY(cudaEventRecord(kv->ev_entry, s));
+    INGOT_CUDA_TRY(cudaStreamWaitEvent(kv->copy_in_stream, kv->ev_entry, 0));
+    for (int c = 0; c < n_chunks; c++) {
+        const int b = c & 1;
+        const int t0 = c * chunk, n = std::min(chunk, n_tok - t0);
+        // in: buffer b is free once the attention of chunk c-2 has read it
+        if (c >= 2) INGOT_CUDA_TRY(cudaStreamWaitEvent(kv->copy_in_stream, kv->ev_done[b], 0));
+        INGOT_CUDA_TRY(cudaMemcpyAsync(q_stage[b], static_cast<const char*>(q_host) + size_t(t0) * q_row, size_t(n) * q_row,
+                                       cudaMemcpyHostToDevice, kv->copy_in_stream));
+        INGOT_CUDA_TRY(cudaEventRecord(kv->ev_in[b], kv->copy_in_stream));
+        // attention on the caller's stream: needs the chunk's rows, and the output buffer back from the copy of chunk c-2
+        INGOT_CUDA_TRY(cudaStreamWaitEvent(s, kv->ev_in[b], 0));
+        if (c >= 2) INGOT_CUDA_TRY(cudaStreamWaitEvent(s, kv->ev_out[b], 0));
+        const int rc = ingot_attn_prefill(kv, layer, q_stage[b], q_dtype, o_stage[b], out_dtype, n_head, q_pos0 + t0, n, block_table_dev,
+                                          0, s);
+        if (rc != INGOT_OK) return rc;
+        INGOT_CUDA_TRY(cudaEventRecord(kv->ev_done[b], s));
+        // out
+        INGOT_CUDA_TRY(cudaStreamWaitEvent(kv->copy_out_stream, kv->ev_done[b], 0));
+        INGOT_CUDA_TRY(cudaMemcpyAsync(static_cast<char*>(out_host) + size_t(t0) * o_row, o_stage[b], size_t(n) * o_row,
+                                       cudaMemcpyDeviceToHost, kv->copy_out_stream));
+        INGOT_CUDA_TRY(cudaEventRecord(kv->ev_out[b], kv->copy_out_stream));
+    }
+    // the caller's stream is done when the last copies out are
+    INGOT_CUDA_TRY(cudaStreamWaitEvent(s, kv->ev_out[(n_chunks - 1) & 1], 0));
+    if (n_chunks >= 2) INGOT_CUDA_TRY(cudaStreamWaitEvent(s, kv->ev_out[(n_chunks - 2) & 1], 0));
     return INGOT_OK;
 }
 

@@ -47,6 +47,7 @@ ABI = {
     "ingot_mg_stream": (_P, [_P, _I]),
     "ingot_mg_prefill": (_I, [_P, _I, C.POINTER(_P), _I, _I, _I, _I]),
     "ingot_lpt_assign": (_I, [C.POINTER(C.c_int32), _I, _I, C.POINTER(C.c_int32)]),
+    "ingot_attn_prefill_host": (_I, [_P, _I, _P, _I, _P, _I, _I, _I, _I, _P, _I, _P]),
     "ingot_attn_layer_host": (_I, [_P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _P]),
     "ingot_attn_layers_host": (_I, [_P, _I, _I, _P, _P, _P, _P, _P, _I, _I, _I, _P]),
     "ingot_stream_sync": (_I, [_P]),
@@ -260,6 +261,15 @@ def attn_prefill_gather_signal(kv, layer, q, q_pos0, out_ptrs, signal_ptrs, src_
 def gather_wait(kv, counters, n_src, timeout_ms=2000):
     """Queues the bounded wait for n_src completion signals on this GPU's counter array (an int32 cuda tensor)."""
     _check(lib().ingot_gather_wait(kv.handle, _ptr(counters), n_src, timeout_ms, _stream()))
+
+
+def attn_prefill_host(kv, layer, q_host, q_pos0, out_host, block_table=None, chunk_tokens=0):
+    """q_host, out_host [n_tok,H,128]: (pinned) host tensors; the cache holds the keys already. Copies in, attention and
+    copies out are pipelined chunk by chunk; asynchronous on the current stream."""
+    assert q_host.is_contiguous() and out_host.is_contiguous() and not q_host.is_cuda and not out_host.is_cuda
+    n_tok, n_head = q_host.shape[0], q_host.shape[1]
+    _check(lib().ingot_attn_prefill_host(kv.handle, layer, _ptr(q_host), _dtype_code(q_host), _ptr(out_host), _dtype_code(out_host),
+                                         n_head, q_pos0, n_tok, _ptr(block_table), chunk_tokens, _stream()))
 
 
 def attn_layer_host(kv, layer, q_host, k_host, v_host, out_host, inv_freq_dev, pos0):

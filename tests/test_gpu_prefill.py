@@ -217,3 +217,39 @@ def test_gather_signal_and_bounded_wait():
     torch.cuda.synchronize()
     assert kv.status() == 0
     helpers.assert_parity(out[torch.from_numpy(rows).cuda()].float().cpu().numpy(), want, "gather_signal after an expired wait")
+
+
+@pytest.mark.parametrize("n_tok,pos0,chunk,q_dtype,out_dtype", [(700, 0, 256, "float32", "float32"), (1300, 260, 512, "bfloat16", "float16"),
+                                                             (100, 0, 0, "float16", "float32"), (513, 3584, 128, "float32", "float32")])
+def test_prefill_host_pipelined_chunks(n_tok, pos0, chunk, q_dtype, out_dtype):
+    """ingot_attn_prefill_host: queries and output in pinned host memory, the rows cut into chunks whose copies in,
+    attention and copies out overlap on three streams. Against the CPU reference, against the device-buffer call on the
+    same cache, and twice in a row (the staging buffers and events of the first call are reused by the second)."""
+    import torch
+    import ingot_b200 as ib
+    rng = np.random.default_rng(n_tok + pos0)
+    n_keys = pos0 + n_tok
+    q = rng.standard_normal((n_tok, H, D), dtype=np.float32)
+    k = rng.standard_normal((n_keys, HKV, D), dtype=np.float32).astype(np.float16)
+    v = rng.standard_normal((n_keys, HKV, D), dtype=np.float32).astype(np.float16)
+    tq, to = getattr(torch, q_dtype), getattr(torch, out_dtype)
+    q_t = torch.from_numpy(q).to(tq)
+    q_used = q_t.float().numpy()  # what the kernel sees (bf16 / f16 rounding of q is part of the input)
+    kv = ib.KVCache(ib.KV_CONTIGUOUS, 1, HKV, n_keys)
+    kv.import_f16(0, helpers.to_dev(k), helpers.to_dev(v), 0)
+    want, _, _ = helpers.oracle_prefill(W.Prefill(q_used, k, v, pos0, False))  # k, v: every cache row, already rotated
+    dev = ib.attn_prefill(kv, 0, helpers.to_dev(q_used, tq), pos0, out_dtype=to, impl=2)
+    q_host = q_t.contiguous().pin_memory()
+    outs = []
+    for rep in range(2):
+        out_host = torch.full((n_tok, H, D), 7.0, dtype=to).pin_memory()
+        ib.attn_prefill_host(kv, 0, q_host, pos0, out_host, chunk_tokens=chunk)
+        outs.append(out_host)
+    torch.cuda.synchronize()
+    assert kv.status() == 0
+    for out_host in outs:
+        got = out_host.float().numpy()
+        helpers.assert_parity(got, want, "host-buffer prefill")
+        # chunk boundaries move the key-tile boundaries, and with them the reference maxima P is rounded against
+        assert np.abs(got - dev.float().cpu().numpy()).max() < 2e-3
+    assert np.array_equal(outs[0].numpy(), outs[1].numpy())  # the second call reuses buffers and events: same bits
