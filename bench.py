@@ -291,9 +291,10 @@ def run_decode(args, rank, world):
     # End to end through the host-buffer C-ABI call: per layer q/k/v rows host->device, RoPE+append,
     # decode at position 4095 (4096 keys), output device->host; one synchronisation per step.
     inv = torch.from_numpy(inv_freq_table()).cuda()
-    qh = torch.randn(N_LAYER, 1, H, D).pin_memory()
-    kh = torch.randn(N_LAYER, 1, HKV, D).pin_memory()
-    vh = torch.randn(N_LAYER, 1, HKV, D).pin_memory()
+    # q, k and v rows sit in one pinned block (q of all layers, then k, then v): the call then needs one copy in.
+    nq, nk = N_LAYER * H * D, N_LAYER * HKV * D
+    blk = torch.randn(nq + 2 * nk).pin_memory()
+    qh, kh, vh = blk[:nq].view(N_LAYER, 1, H, D), blk[nq:nq + nk].view(N_LAYER, 1, HKV, D), blk[nq + nk:].view(N_LAYER, 1, HKV, D)
     oh = torch.empty(N_LAYER, 1, H, D).pin_memory()
 
     def step_e2e():

@@ -250,7 +250,8 @@ int ingot_attn_layer_host(ingot_kv* kv, int layer, const float* q_host, const fl
                           void* stream);
 /* The same for `layer_count` consecutive layers starting at `layer_begin` in one call, as the
  * reference's attention microbenchmark drives its backend (every layer's attention for one step,
- * src/metal_backend.mm:594-649): host arrays are [layer_count][n_tok][heads][128], one slice per layer. */
+ * src/metal_backend.mm:594-649): host arrays are [layer_count][n_tok][heads][128], one slice per layer.
+ * If k_host directly follows q_host and v_host directly follows k_host in memory, the three arrays travel in one copy. */
 int ingot_attn_layers_host(ingot_kv* kv, int layer_begin, int layer_count, const float* q_host, const float* k_host,
                            const float* v_host, float* out_host, const float* inv_freq_dev, int n_head, int pos0,
                            int n_tok, void* stream);

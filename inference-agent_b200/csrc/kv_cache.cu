@@ -409,9 +409,14 @@ int ingot_attn_layers_host(ingot_kv* kv, int layer_begin, int layer_count, const
     float* v_d = k_d + L * kv_elems;
     float* o_d = v_d + L * kv_elems;
     __half* qh_d = reinterpret_cast<__half*>(o_d + L * q_elems);
-    INGOT_CUDA_TRY(cudaMemcpyAsync(q_d, q_host, L * q_elems * 4, cudaMemcpyHostToDevice, s));
-    INGOT_CUDA_TRY(cudaMemcpyAsync(k_d, k_host, L * kv_elems * 4, cudaMemcpyHostToDevice, s));
-    INGOT_CUDA_TRY(cudaMemcpyAsync(v_d, v_host, L * kv_elems * 4, cudaMemcpyHostToDevice, s));
+    if (k_host == q_host + L * q_elems && v_host == k_host + L * kv_elems) {
+        // the caller keeps q, k and v in one block, in the order of the device staging area: one copy instead of three
+        INGOT_CUDA_TRY(cudaMemcpyAsync(q_d, q_host, L * (q_elems + 2 * kv_elems) * 4, cudaMemcpyHostToDevice, s));
+    } else {
+        INGOT_CUDA_TRY(cudaMemcpyAsync(q_d, q_host, L * q_elems * 4, cudaMemcpyHostToDevice, s));
+        INGOT_CUDA_TRY(cudaMemcpyAsync(k_d, k_host, L * kv_elems * 4, cudaMemcpyHostToDevice, s));
+        INGOT_CUDA_TRY(cudaMemcpyAsync(v_d, v_host, L * kv_elems * 4, cudaMemcpyHostToDevice, s));
+    }
     int rc = INGOT_OK;
     if (n_tok == 1) {
         // Single token: about 35 launches over several side streams. They are captured once per (layer range, head
@@ -430,6 +435,18 @@ int ingot_attn_layers_host(ingot_kv* kv, int layer_begin, int layer_count, const
             kv->host_inv_freq = inv_freq_dev;
             kv->host_calls = 0;
         }
+        static const bool use_graph = getenv("INGOT_HOST_GRAPH") == nullptr || atoi(getenv("INGOT_HOST_GRAPH")) != 0;
+        if (!use_graph) {
+            // Plain launches: position and key count travel as kernel arguments, so there is no position copy either.
+            rc = launch_rope_kv_append(kv, layer_begin, q_d, qh_d, k_d, v_d, inv_freq_dev, n_head, pos0, 1, nullptr, nullptr, nullptr, 0,
+                                       layer_count, s);
+            if (rc != INGOT_OK) return rc;
+            rc = ingot_attn_decode_layers(kv, layer_begin, layer_count, qh_d, INGOT_F16, o_d, INGOT_F32, n_head, 1, nullptr, pos0 + 1,
+                                          nullptr, 0, 0, s);
+            if (rc != INGOT_OK) return rc;
+            INGOT_CUDA_TRY(cudaMemcpyAsync(out_host, o_d, L * q_elems * 4, cudaMemcpyDeviceToHost, s));
+            return INGOT_OK;
+        }
         int32_t* slot = kv->host_pos_pinned + 2 * (kv->host_pos_next++ % kHostPosSlots);
         slot[0] = pos0;
         slot[1] = pos0 + 1;
@@ -441,10 +458,9 @@ int ingot_attn_layers_host(ingot_kv* kv, int layer_begin, int layer_count, const
             return ingot_attn_decode_layers(kv, layer_begin, layer_count, qh_d, INGOT_F16, o_d, INGOT_F32, n_head, 1,
                                             kv->host_pos_dev + 1, kv->capacity, nullptr, 0, 0, on);
         };
-        static const bool use_graph = getenv("INGOT_HOST_GRAPH") == nullptr || atoi(getenv("INGOT_HOST_GRAPH")) != 0;
         if (kv->host_exec) {
             INGOT_CUDA_TRY(cudaGraphLaunch(kv->host_exec, s));
-        } else if (kv->host_calls++ == 0 || !use_graph) {
+        } else if (kv->host_calls++ == 0) {
             rc = encode(s);  // first call with this shape: eager (it sizes the decode scratch, which cannot happen under capture)
             if (rc != INGOT_OK) return rc;
         } else {
