@@ -51,6 +51,27 @@ constexpr unsigned long long kWaitLimitNs = 2000000000ull;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
+// Programmatic dependent launch, as in the attention kernels: every kernel of the batched path lets its successor
+// start early (launch_dependents at its top) and waits for its predecessor before it touches anything the predecessor
+// wrote; launch latency and per-CTA set-up then overlap the predecessor's tail. INGOT_NO_PDL=1: plain stream order.
+#define LINEAR_PDL_TRIGGER() asm volatile("griddepcontrol.launch_dependents;" ::: "memory")
+#define LINEAR_PDL_WAIT() asm volatile("griddepcontrol.wait;" ::: "memory")
+template <typename... KArgs, typename... Args>
+static cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+    static const bool use_pdl = getenv("INGOT_NO_PDL") == nullptr;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = use_pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
+
 struct Bars {
     uint64_t full[kStages];
     uint64_t empty[kStages];
@@ -71,6 +92,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 linear_sm100_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_constant__ CUtensorMap map_lo,
                     const __grid_constant__ CUtensorMap map_w, const GemmParams p) {
     extern __shared__ unsigned char smem_dyn[];
+    LINEAR_PDL_TRIGGER();
     const uint32_t smem_base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
     unsigned char* smem_al = smem_dyn + (smem_base - smem_u32(smem_dyn));
     Bars* bars = reinterpret_cast<Bars*>(smem_al + kOffBar);
@@ -92,6 +114,8 @@ linear_sm100_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_con
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&bars->tmem_base)), "r"(kTmemCols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
+    // barriers and tensor memory are this CTA's own; the activations (and the output, under accumulate) are the predecessor's
+    LINEAR_PDL_WAIT();
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -193,6 +217,8 @@ linear_sm100_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_con
 
 // out (+)= sum over the k slices, in slice order
 __global__ void splitk_reduce_kernel(float* out, const float* partial, int n_split, size_t n, int accumulate) {
+    LINEAR_PDL_TRIGGER();
+    LINEAR_PDL_WAIT();
     const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
     if (i >= n) return;
     float4 acc = accumulate ? *reinterpret_cast<const float4*>(out + i) : make_float4(0.f, 0.f, 0.f, 0.f);
@@ -205,6 +231,8 @@ __global__ void splitk_reduce_kernel(float* out, const float* partial, int n_spl
 
 // hi = f16(x), lo = f16(x - hi)
 __global__ void split_f16_kernel(__half* hi, __half* lo, const float* x, size_t n) {
+    LINEAR_PDL_TRIGGER();
+    LINEAR_PDL_WAIT();
     const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
     if (i >= n) return;
     const float4 v = *reinterpret_cast<const float4*>(x + i);
@@ -233,6 +261,8 @@ __device__ __forceinline__ void store_split4(__half* hi, __half* lo, size_t i, c
 // hi/lo of rmsnorm(x) = x * rsqrt(mean(x^2) + eps) * w, one CTA per token row (ops::rmsnorm, src/ops.cpp:227-232,
 // with the same expression order as the standalone norm kernel, so the split sees the same f32 values).
 __global__ void rmsnorm_split_kernel(__half* hi, __half* lo, const float* x, const float* w, int n, float eps) {
+    LINEAR_PDL_TRIGGER();
+    LINEAR_PDL_WAIT();
     __shared__ float red[32];
     const float* xr = x + (size_t)blockIdx.x * n;
     float ss = 0.f;
@@ -277,6 +307,8 @@ struct FinishGroup {
     int n_out[3];
 };
 __global__ void finish_group_kernel(const FinishGroup g, int n_tok) {
+    LINEAR_PDL_TRIGGER();
+    LINEAR_PDL_WAIT();
     const int m = blockIdx.y;
     const Slices in = m == 0 ? g.in[0] : m == 1 ? g.in[1] : g.in[2];
     float* out = m == 0 ? g.out[0] : m == 1 ? g.out[1] : g.out[2];
@@ -291,6 +323,8 @@ __global__ void finish_group_kernel(const FinishGroup g, int n_tok) {
 __global__ void finish_residual_norm_kernel(float* x, const Slices in, __half* hi, __half* lo, const float* norm_w, int n, int n_tok,
                                             float eps) {
     __shared__ float red[32];
+    LINEAR_PDL_TRIGGER();
+    LINEAR_PDL_WAIT();
     const size_t row = (size_t)blockIdx.x * n;
     const size_t slice = (size_t)n_tok * n;
     float ss = 0.f;
@@ -321,6 +355,8 @@ __global__ void finish_residual_norm_kernel(float* x, const Slices in, __half* h
 
 // hi/lo of silu(sum of gate slices) * (sum of up slices)
 __global__ void finish_swiglu_kernel(__half* hi, __half* lo, const Slices gate, const Slices up, size_t n) {
+    LINEAR_PDL_TRIGGER();
+    LINEAR_PDL_WAIT();
     const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
     if (i >= n) return;
     const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -425,7 +461,8 @@ int ingot_linear_tc_supported(const ingot_linear_ws* ws, int w_is_f16, int n_in,
 cudaError_t ingot_linear_tc_prepare(ingot_linear_ws* ws, const float* x, int n_in, int n_tok, cudaStream_t s) {
     const size_t n = (size_t)n_tok * n_in;
     if (n > ws->act_elems || n_in % kBK != 0) return cudaErrorInvalidValue;
-    split_f16_kernel<<<(unsigned)((n / 4 + 255) / 256), 256, 0, s>>>(ws->hi, ws->lo, x, n);
+    cudaError_t le = launch_pdl(split_f16_kernel, dim3((unsigned)((n / 4 + 255) / 256)), dim3(256), 0, s, ws->hi, ws->lo, x, n);
+    if (le != cudaSuccess) return le;
     return set_prepared(ws, n_in, n_tok);
 }
 
@@ -433,7 +470,8 @@ cudaError_t ingot_linear_tc_prepare(ingot_linear_ws* ws, const float* x, int n_i
 cudaError_t ingot_linear_tc_prepare_norm(ingot_linear_ws* ws, const float* x, const float* norm_w, float eps, int n_in, int n_tok,
                                          cudaStream_t s) {
     if ((size_t)n_tok * n_in > ws->act_elems || n_in % kBK != 0) return cudaErrorInvalidValue;
-    rmsnorm_split_kernel<<<n_tok, 256, 0, s>>>(ws->hi, ws->lo, x, norm_w, n_in, eps);
+    cudaError_t le = launch_pdl(rmsnorm_split_kernel, dim3(n_tok), dim3(256), 0, s, ws->hi, ws->lo, x, norm_w, n_in, eps);
+    if (le != cudaSuccess) return le;
     return set_prepared(ws, n_in, n_tok);
 }
 
@@ -459,12 +497,14 @@ static cudaError_t launch_gemm(ingot_linear_ws* ws, float* out, const void* w, i
     p.n_tok = n_tok; p.n_out = n_out; p.k_steps = k_steps; p.n_split = n_split; p.accumulate = accumulate;
     p.to_partial = to_partial ? 1 : 0;
     dim3 grid((n_out + kBN - 1) / kBN, (n_tok + kBM - 1) / kBM, n_split);
-    linear_sm100_kernel<<<grid, kThreads, kSmemBytes, s>>>(ws->map_hi, ws->map_lo, it->second, p);
+    cudaError_t le = launch_pdl(linear_sm100_kernel, grid, dim3(kThreads), (size_t)kSmemBytes, s, ws->map_hi, ws->map_lo, it->second, p);
+    if (le != cudaSuccess) return le;
     ws->slot_split[slot] = n_split;
     ws->slot_out[slot] = n_out;
     if (!to_partial && n_split > 1) {
         const size_t n = (size_t)n_tok * n_out;
-        splitk_reduce_kernel<<<(unsigned)((n / 4 + 255) / 256), 256, 0, s>>>(out, p.partial, n_split, n, accumulate);
+        le = launch_pdl(splitk_reduce_kernel, dim3((unsigned)((n / 4 + 255) / 256)), dim3(256), 0, s, out, (const float*)p.partial, n_split, n, accumulate);
+        if (le != cudaSuccess) return le;
     }
     return cudaGetLastError();
 }
@@ -495,7 +535,8 @@ cudaError_t ingot_linear_tc_finish_group(ingot_linear_ws* ws, float* const* outs
         widest = std::max(widest, ws->slot_out[m]);
     }
     const size_t n = (size_t)ws->prepared_tok * widest;
-    finish_group_kernel<<<dim3((unsigned)((n / 4 + 255) / 256), count), 256, 0, s>>>(g, ws->prepared_tok);
+    cudaError_t le = launch_pdl(finish_group_kernel, dim3((unsigned)((n / 4 + 255) / 256), count), dim3(256), 0, s, g, ws->prepared_tok);
+    if (le != cudaSuccess) return le;
     return cudaGetLastError();
 }
 
@@ -504,7 +545,8 @@ cudaError_t ingot_linear_tc_finish_group(ingot_linear_ws* ws, float* const* outs
 cudaError_t ingot_linear_tc_finish_residual_norm(ingot_linear_ws* ws, float* x, const float* norm_w, float eps, int slot, cudaStream_t s) {
     const int n = ws->slot_out[slot], n_tok = ws->prepared_tok;
     if (n % 4 != 0 || (norm_w && ((size_t)n_tok * n > ws->act_elems || n % kBK != 0))) return cudaErrorInvalidValue;
-    finish_residual_norm_kernel<<<n_tok, 256, 0, s>>>(x, slices_of(ws, slot), ws->hi, ws->lo, norm_w, n, n_tok, eps);
+    cudaError_t le = launch_pdl(finish_residual_norm_kernel, dim3(n_tok), dim3(256), 0, s, x, slices_of(ws, slot), ws->hi, ws->lo, norm_w, n, n_tok, eps);
+    if (le != cudaSuccess) return le;
     return norm_w ? set_prepared(ws, n, n_tok) : cudaGetLastError();
 }
 
@@ -513,7 +555,8 @@ cudaError_t ingot_linear_tc_finish_swiglu(ingot_linear_ws* ws, int slot_gate, in
     const int n_in = ws->slot_out[slot_gate], n_tok = ws->prepared_tok;
     const size_t n = (size_t)n_tok * n_in;
     if (ws->slot_out[slot_up] != n_in || n > ws->act_elems || n_in % kBK != 0) return cudaErrorInvalidValue;
-    finish_swiglu_kernel<<<(unsigned)((n / 4 + 255) / 256), 256, 0, s>>>(ws->hi, ws->lo, slices_of(ws, slot_gate), slices_of(ws, slot_up), n);
+    cudaError_t le = launch_pdl(finish_swiglu_kernel, dim3((unsigned)((n / 4 + 255) / 256)), dim3(256), 0, s, ws->hi, ws->lo, slices_of(ws, slot_gate), slices_of(ws, slot_up), n);
+    if (le != cudaSuccess) return le;
     return set_prepared(ws, n_in, n_tok);
 }
 
