@@ -114,12 +114,22 @@ linear_sm100_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_con
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&bars->tmem_base)), "r"(kTmemCols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
-    // barriers and tensor memory are this CTA's own; the activations (and the output, under accumulate) are the predecessor's
-    LINEAR_PDL_WAIT();
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = bars->tmem_base;
+    // Barriers and tensor memory are this CTA's own and the weights never depend on the kernel before: the W boxes of
+    // the first ring stages are requested now, the activation boxes (and, under accumulate, the output) only after the
+    // wait for the predecessor. A stage's barrier is armed once for all three boxes.
+    const int n_pre = min(n_it, kStages);
+    if (warp_u == 0 && lane == 0) {
+        for (int it = 0; it < n_pre; it++) {
+            const uint32_t full = smem_u32(&bars->full[it]);
+            mbar_expect_tx(full, kStageBytes);
+            tma_load_2d(smem_base + it * kStageBytes + 2 * kBoxBytes, &map_w, (ks_begin + it) * kBK, n0, full);
+        }
+    }
+    LINEAR_PDL_WAIT();
 
     if (warp_u == 0) {
         // ---------------- TMA producer ----------------
@@ -129,14 +139,19 @@ linear_sm100_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_con
             const int s = it % kStages;
             const uint32_t full = smem_u32(&bars->full[s]);
             if (lane == 0) {
-                ok = mbar_wait(smem_u32(&bars->empty[s]), (uint32_t)(((it / kStages) & 1) ^ 1), abort_flag, kWaitLimitNs);
-                if (ok) {
-                    mbar_expect_tx(full, kStageBytes);
-                    const uint32_t dst = smem_base + s * kStageBytes;
-                    const int k = (ks_begin + it) * kBK;
+                const uint32_t dst = smem_base + s * kStageBytes;
+                const int k = (ks_begin + it) * kBK;
+                if (it < n_pre) {  // first use of the slot: armed and its W box requested before the wait above
                     tma_load_2d(dst, &map_hi, k, m0, full);
                     tma_load_2d(dst + kBoxBytes, &map_lo, k, m0, full);
-                    tma_load_2d(dst + 2 * kBoxBytes, &map_w, k, n0, full);
+                } else {
+                    ok = mbar_wait(smem_u32(&bars->empty[s]), (uint32_t)(((it / kStages) & 1) ^ 1), abort_flag, kWaitLimitNs);
+                    if (ok) {
+                        mbar_expect_tx(full, kStageBytes);
+                        tma_load_2d(dst, &map_hi, k, m0, full);
+                        tma_load_2d(dst + kBoxBytes, &map_lo, k, m0, full);
+                        tma_load_2d(dst + 2 * kBoxBytes, &map_w, k, n0, full);
+                    }
                 }
             }
             ok = __shfl_sync(0xffffffffu, ok, 0);
