@@ -64,6 +64,8 @@ cudaError_t ingot_linear_tc_prepare(ingot_linear_ws* ws, const float* x, int n_i
 cudaError_t ingot_linear_tc_prepare_norm(ingot_linear_ws* ws, const float* x, const float* norm_w, float eps, int n_in, int n_tok,
                                          cudaStream_t s);
 cudaError_t ingot_linear_tc_run_partial(ingot_linear_ws* ws, const void* w, int n_in, int n_out, int slot, cudaStream_t s);
+cudaError_t ingot_linear_tc_run_partial_group(ingot_linear_ws* ws, const void* const* w, int n_in, const int* n_out, int count,
+                                              int first_slot, int append, cudaStream_t s);
 cudaError_t ingot_linear_tc_finish_group(ingot_linear_ws* ws, float* const* outs, int count, cudaStream_t s);
 cudaError_t ingot_linear_tc_finish_residual_norm(ingot_linear_ws* ws, float* x, const float* norm_w, float eps, int slot, cudaStream_t s);
 cudaError_t ingot_linear_tc_finish_swiglu(ingot_linear_ws* ws, int slot_gate, int slot_up, cudaStream_t s);
@@ -368,7 +370,7 @@ public:
                 // Every split-k product stays in scratch as k slices; the kernel that consumes it sums them.
                 if (!norm_prepared)
                     cuda_check(ingot_linear_tc_prepare_norm(lin_ws_, x_, D.attn_norm, c.rms_eps, c.n_embd, n, stream_), "rmsnorm (split)");
-                for (int i = 0; i < 3; i++) tc_partial(*qkv[i], i);
+                tc_partial_group(qkv, 3);  // one launch, slots 0..2
                 cuda_check(ingot_linear_tc_finish_group(lin_ws_, qkv_out, 3, stream_), "q/k/v (slice sum)");
             } else {
                 cuda_check(ingot_support_rmsnorm(h_, x_, D.attn_norm, n, c.n_embd, c.rms_eps, stream_), "rmsnorm");
@@ -410,8 +412,7 @@ public:
             if (fused) {
                 gemv_group(gu_out, gu, 2, true, x_, D.ffn_norm, false);  // gate_ <- silu(gate) * up
             } else if (tc_layer) {
-                tc_partial(D.w_gate, 0);
-                tc_partial(D.w_up, 1);
+                tc_partial_group(gu, 2);  // one launch, slots 0 and 1
                 cuda_check(ingot_linear_tc_finish_swiglu(lin_ws_, 0, 1, stream_), "silu_mul (split)");
             } else {
                 cuda_check(ingot_support_rmsnorm(h_, x_, D.ffn_norm, n, c.n_embd, c.rms_eps, stream_), "rmsnorm");
@@ -576,14 +577,31 @@ private:
                  ingot_linear_tc_supported(lin_ws_, ws[i]->is_f16 || ws[i]->qtype >= 0, ws[i]->n_in, ws[i]->n_out, n_tok);
         return tc;
     }
+    // f16 matrices, or block-quantised ones whose f16 hi/lo planes are resident (two products into the same slices)
     bool layer_tc_ok(const DevLayer& D, int n_tok) const {
         const DevWeight* all[7] = {&D.wq, &D.wk, &D.wv, &D.wo, &D.w_gate, &D.w_up, &D.w_down};
         for (const DevWeight* w : all)
-            if (!ingot_linear_tc_supported(lin_ws_, w->is_f16, w->n_in, w->n_out, n_tok)) return false;
+            if (!ingot_linear_tc_supported(lin_ws_, w->is_f16 || (w->qtype >= 0 && w->planes), w->n_in, w->n_out, n_tok)) return false;
+        if ((D.wq.planes != nullptr) != (D.wk.planes != nullptr) || (D.wq.planes != nullptr) != (D.wv.planes != nullptr) ||
+            (D.w_gate.planes != nullptr) != (D.w_up.planes != nullptr))
+            return false;  // a group is one launch per plane
         return D.wq.n_in == m_.cfg.n_embd && D.w_gate.n_in == m_.cfg.n_embd && D.w_down.n_in == m_.cfg.n_ff;
     }
+    // Products of count matrices that read the prepared activations, left as k slices in slots first_slot.. for the consumer
+    // kernels. A quantised matrix is its hi plane and then its lo plane (hi + lo = w exactly), the second launch adding slices.
+    void tc_partial_group(const DevWeight* const* ws, int count, int first_slot = 0) {
+        const void* wp[3] = {};
+        int rows[3] = {};
+        const bool planes = ws[0]->planes != nullptr;
+        for (int i = 0; i < count; i++) { wp[i] = planes ? ws[i]->planes : ws[i]->data; rows[i] = ws[i]->n_out; }
+        cuda_check(ingot_linear_tc_run_partial_group(lin_ws_, wp, ws[0]->n_in, rows, count, first_slot, 0, stream_), "linear (tensor core, grouped)");
+        if (!planes) return;
+        for (int i = 0; i < count; i++) wp[i] = static_cast<const __half*>(ws[i]->planes) + size_t(ws[i]->n_in) * ws[i]->n_out;
+        cuda_check(ingot_linear_tc_run_partial_group(lin_ws_, wp, ws[0]->n_in, rows, count, first_slot, 1, stream_), "linear (tensor core, grouped, lo plane)");
+    }
     void tc_partial(const DevWeight& w, int slot) {
-        cuda_check(ingot_linear_tc_run_partial(lin_ws_, w.data, w.n_in, w.n_out, slot, stream_), "linear (tensor core)");
+        const DevWeight* one[1] = {&w};
+        tc_partial_group(one, 1, slot);
     }
     // Projections that read the same activations. Batches go to the tensor-core kernel (the activations are split
     // into f16 hi/lo parts once per group); single tokens and unsupported shapes to the f32 kernels.

@@ -80,17 +80,21 @@ struct Bars {
     uint32_t abort_flag;
 };
 
+// One launch covers up to three weight matrices that read the same activations (q/k/v, gate/up): grid.x runs over
+// the output tiles of all of them, tile_end[m] being the running total of tiles up to and including matrix m.
 struct GemmParams {
-    float* out;        // [n_tok][n_out]
-    float* partial;    // [n_split][n_tok][n_out] when n_split > 1
+    float* out;           // [n_tok][n_out] (single matrix only)
+    float* partial[3];    // per matrix: [n_split][n_tok][n_out] when n_split > 1 or to_partial
     int* status;
-    int n_tok, n_out, k_steps, n_split, accumulate;
+    int n_tok, k_steps, n_split, accumulate;
+    int n_out[3], tile_end[3];
     int to_partial;  // write the slice(s) to `partial` even when there is only one (a consumer kernel sums them)
 };
 
 __global__ void __launch_bounds__(kThreads, 1)
 linear_sm100_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_constant__ CUtensorMap map_lo,
-                    const __grid_constant__ CUtensorMap map_w, const GemmParams p) {
+                    const __grid_constant__ CUtensorMap map_w0, const __grid_constant__ CUtensorMap map_w1,
+                    const __grid_constant__ CUtensorMap map_w2, const GemmParams p) {
     extern __shared__ unsigned char smem_dyn[];
     LINEAR_PDL_TRIGGER();
     const uint32_t smem_base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
@@ -99,7 +103,12 @@ linear_sm100_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_con
     volatile uint32_t* abort_flag = &bars->abort_flag;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int warp_u = __shfl_sync(0xffffffffu, warp, 0);
-    const int n0 = blockIdx.x * kBN, m0 = blockIdx.y * kBM, split = blockIdx.z;
+    const int mat = ((int)blockIdx.x >= p.tile_end[0]) + ((int)blockIdx.x >= p.tile_end[1]);  // warp-uniform
+    const CUtensorMap* const map_w_p = mat == 0 ? &map_w0 : mat == 1 ? &map_w1 : &map_w2;
+    const int mat_n_out = mat == 0 ? p.n_out[0] : mat == 1 ? p.n_out[1] : p.n_out[2];
+    float* const mat_partial = mat == 0 ? p.partial[0] : mat == 1 ? p.partial[1] : p.partial[2];
+    const int n0 = ((int)blockIdx.x - (mat == 0 ? 0 : mat == 1 ? p.tile_end[0] : p.tile_end[1])) * kBN;
+    const int m0 = blockIdx.y * kBM, split = blockIdx.z;
     const int ks_begin = (int)((long long)p.k_steps * split / p.n_split);
     const int ks_end = (int)((long long)p.k_steps * (split + 1) / p.n_split);
     const int n_it = ks_end - ks_begin;
@@ -126,7 +135,7 @@ linear_sm100_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_con
         for (int it = 0; it < n_pre; it++) {
             const uint32_t full = smem_u32(&bars->full[it]);
             mbar_expect_tx(full, kStageBytes);
-            tma_load_2d(smem_base + it * kStageBytes + 2 * kBoxBytes, &map_w, (ks_begin + it) * kBK, n0, full);
+            tma_load_2d(smem_base + it * kStageBytes + 2 * kBoxBytes, map_w_p, (ks_begin + it) * kBK, n0, full);
         }
     }
     LINEAR_PDL_WAIT();
@@ -150,7 +159,7 @@ linear_sm100_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_con
                         mbar_expect_tx(full, kStageBytes);
                         tma_load_2d(dst, &map_hi, k, m0, full);
                         tma_load_2d(dst + kBoxBytes, &map_lo, k, m0, full);
-                        tma_load_2d(dst + 2 * kBoxBytes, &map_w, k, n0, full);
+                        tma_load_2d(dst + 2 * kBoxBytes, map_w_p, k, n0, full);
                     }
                 }
             }
@@ -195,7 +204,7 @@ linear_sm100_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_con
         const bool split_k = p.n_split > 1 || p.to_partial;
         if (ok) {
             tc_fence_after();
-            float* dst = (split_k ? p.partial + (size_t)split * p.n_tok * p.n_out : p.out) + (size_t)row * p.n_out + n0;
+            float* dst = (split_k ? mat_partial + (size_t)split * p.n_tok * mat_n_out : p.out) + (size_t)row * mat_n_out + n0;
             const bool add = !split_k && p.accumulate;
 #pragma unroll
             for (int c = 0; c < kBN / 32; c++) {
@@ -206,14 +215,14 @@ linear_sm100_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_con
 #pragma unroll
                     for (int i = 0; i < 32; i += 4) {
                         const int col = n0 + c * 32 + i;
-                        if (col + 3 < p.n_out) {
+                        if (col + 3 < mat_n_out) {
                             float4* d4 = reinterpret_cast<float4*>(dst + c * 32 + i);
                             float4 o = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
                             if (add) { const float4 old = *d4; o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w; }
                             *d4 = o;
                         } else {
                             for (int e = 0; e < 4; e++)
-                                if (col + e < p.n_out) dst[c * 32 + i + e] = add ? dst[c * 32 + i + e] + v[i + e] : v[i + e];
+                                if (col + e < mat_n_out) dst[c * 32 + i + e] = add ? dst[c * 32 + i + e] + v[i + e] : v[i + e];
                         }
                     }
                 }
@@ -443,8 +452,9 @@ cudaError_t ingot_linear_ws_create(ingot_linear_ws** out, int max_tok, int max_i
     *out = nullptr;
     ingot_linear_ws* ws = new ingot_linear_ws();
     ws->act_elems = (size_t)max_tok * max_in;
-    // k-slice partials: three slots, each at least one full-width slice of the largest batch (24 MB or more)
-    ws->partial_floats = std::max((size_t)6 << 20, ws->act_elems);
+    // k-slice partials: three slots, each at least two full-width slices of the largest batch (the hi-plane and the
+    // lo-plane product of a quantised matrix), 24 MB or more
+    ws->partial_floats = std::max((size_t)6 << 20, 2 * ws->act_elems);
     int dev = 0;
     cudaError_t e;
     if ((e = cudaGetDevice(&dev)) != cudaSuccess ||
@@ -490,35 +500,59 @@ cudaError_t ingot_linear_tc_prepare_norm(ingot_linear_ws* ws, const float* x, co
     return set_prepared(ws, n_in, n_tok);
 }
 
-static cudaError_t launch_gemm(ingot_linear_ws* ws, float* out, const void* w, int n_in, int n_out, int accumulate, int slot,
-                               bool to_partial, cudaStream_t s) {
+// count <= 3 matrices W_m [n_out_m][n_in] in one launch; matrix m goes to `out` (count == 1, !to_partial) or as k slices to
+// scratch slot first_slot + m.
+// append: the slices are written behind the ones the slots already hold (all slots of the group must hold the same
+// number), so that a second product - the lo plane of a quantised matrix after its hi plane - simply adds k slices
+// for the consumer kernel to sum.
+static cudaError_t launch_gemm(ingot_linear_ws* ws, float* out, const void* const* w, int n_in, const int* n_out, int count,
+                               int accumulate, int first_slot, bool to_partial, bool append, cudaStream_t s) {
     const int n_tok = ws->prepared_tok;
-    if (n_in != ws->prepared_in || n_tok < 1 || slot < 0 || slot > 2) return cudaErrorInvalidValue;
-    const auto key = std::make_tuple(w, n_out, n_in);
-    auto it = ws->w_maps.find(key);
-    if (it == ws->w_maps.end()) {
-        CUtensorMap m;
-        if (!make_map(&m, w, n_out, n_in, kBN)) return cudaErrorUnknown;
-        it = ws->w_maps.emplace(key, m).first;
+    if (n_in != ws->prepared_in || n_tok < 1 || count < 1 || first_slot < 0 || first_slot + count > 3 || (count > 1 && !to_partial) ||
+        (append && !to_partial))
+        return cudaErrorInvalidValue;
+    const int held = append ? ws->slot_split[first_slot] : 0;
+    for (int m = 0; m < count && append; m++)
+        if (ws->slot_split[first_slot + m] != held || ws->slot_out[first_slot + m] != n_out[m]) return cudaErrorInvalidValue;
+    const CUtensorMap* maps[3] = {nullptr, nullptr, nullptr};
+    GemmParams p = {};
+    int tiles_n = 0, fit = 1 << 30;
+    for (int m = 0; m < count; m++) {
+        const auto key = std::make_tuple(w[m], n_out[m], n_in);
+        auto it = ws->w_maps.find(key);
+        if (it == ws->w_maps.end()) {
+            CUtensorMap tm;
+            if (!make_map(&tm, w[m], n_out[m], n_in, kBN)) return cudaErrorUnknown;
+            it = ws->w_maps.emplace(key, tm).first;
+        }
+        maps[m] = &it->second;
+        tiles_n += (n_out[m] + kBN - 1) / kBN;
+        p.tile_end[m] = tiles_n;
+        p.n_out[m] = n_out[m];
+        p.partial[m] = ws->partial + (size_t)(first_slot + m) * ws->partial_floats + (size_t)held * n_tok * n_out[m];
+        fit = std::min(fit, (int)(ws->partial_floats / ((size_t)n_tok * n_out[m])) - held);
     }
-    const int tiles = ((n_out + kBN - 1) / kBN) * ((n_tok + kBM - 1) / kBM);
+    for (int m = count; m < 3; m++) { maps[m] = maps[count - 1]; p.tile_end[m] = tiles_n; p.n_out[m] = n_out[count - 1]; p.partial[m] = p.partial[count - 1]; }
+    const int tiles = tiles_n * ((n_tok + kBM - 1) / kBM);
     const int k_steps = n_in / kBK;
-    // enough k slices to give every SM a CTA, at least 4 k-steps each, and no more than the slot holds
-    const int fit = (int)(ws->partial_floats / ((size_t)n_tok * n_out));
+    // enough k slices to give every SM a CTA, at least 4 k-steps each, and no more than the slots hold
     if (to_partial && fit < 1) return cudaErrorInvalidValue;
     const int n_split = std::max(1, std::min({ws->num_sms / tiles, k_steps / 4, fit}));
-    GemmParams p;
-    p.out = out; p.partial = ws->partial + (size_t)slot * ws->partial_floats; p.status = ws->status;
-    p.n_tok = n_tok; p.n_out = n_out; p.k_steps = k_steps; p.n_split = n_split; p.accumulate = accumulate;
+    p.out = out; p.status = ws->status;
+    p.n_tok = n_tok; p.k_steps = k_steps; p.n_split = n_split; p.accumulate = accumulate;
     p.to_partial = to_partial ? 1 : 0;
-    dim3 grid((n_out + kBN - 1) / kBN, (n_tok + kBM - 1) / kBM, n_split);
-    cudaError_t le = launch_pdl(linear_sm100_kernel, grid, dim3(kThreads), (size_t)kSmemBytes, s, ws->map_hi, ws->map_lo, it->second, p);
+    dim3 grid(tiles_n, (n_tok + kBM - 1) / kBM, n_split);
+    cudaError_t le = launch_pdl(linear_sm100_kernel, grid, dim3(kThreads), (size_t)kSmemBytes, s, ws->map_hi, ws->map_lo, *maps[0], *maps[1],
+                                *maps[2], p);
     if (le != cudaSuccess) return le;
-    ws->slot_split[slot] = n_split;
-    ws->slot_out[slot] = n_out;
+    for (int m = 0; m < count; m++) {
+        ws->slot_split[first_slot + m] = held + n_split;
+        ws->slot_out[first_slot + m] = n_out[m];
+    }
     if (!to_partial && n_split > 1) {
-        const size_t n = (size_t)n_tok * n_out;
-        le = launch_pdl(splitk_reduce_kernel, dim3((unsigned)((n / 4 + 255) / 256)), dim3(256), 0, s, out, (const float*)p.partial, n_split, n, accumulate);
+        const size_t n = (size_t)n_tok * n_out[0];
+        le = launch_pdl(splitk_reduce_kernel, dim3((unsigned)((n / 4 + 255) / 256)), dim3(256), 0, s, out, (const float*)p.partial[0], n_split, n,
+                        accumulate);
         if (le != cudaSuccess) return le;
     }
     return cudaGetLastError();
@@ -526,12 +560,20 @@ static cudaError_t launch_gemm(ingot_linear_ws* ws, float* out, const void* w, i
 
 // out [n_tok][n_out] (+)= prepared activations x W^T, W f16 [n_out][n_in] on the device.
 cudaError_t ingot_linear_tc_run(ingot_linear_ws* ws, float* out, const void* w, int n_in, int n_out, int accumulate, cudaStream_t s) {
-    return launch_gemm(ws, out, w, n_in, n_out, accumulate, 0, false, s);
+    return launch_gemm(ws, out, &w, n_in, &n_out, 1, accumulate, 0, false, false, s);
 }
 
 // The same product left as k slices in scratch slot 0..2 for one of the ingot_linear_tc_finish_* calls below.
 cudaError_t ingot_linear_tc_run_partial(ingot_linear_ws* ws, const void* w, int n_in, int n_out, int slot, cudaStream_t s) {
-    return launch_gemm(ws, nullptr, w, n_in, n_out, 0, slot, true, s);
+    return launch_gemm(ws, nullptr, &w, n_in, &n_out, 1, 0, slot, true, false, s);
+}
+
+// The products of count <= 3 matrices that read the same prepared activations (q/k/v, gate/up), as one launch:
+// matrix m is left as k slices in scratch slot m.
+// append != 0: the slices are added behind those the slots hold from the call before (same widths).
+cudaError_t ingot_linear_tc_run_partial_group(ingot_linear_ws* ws, const void* const* w, int n_in, const int* n_out, int count,
+                                              int first_slot, int append, cudaStream_t s) {
+    return launch_gemm(ws, nullptr, w, n_in, n_out, count, 0, first_slot, true, append != 0, s);
 }
 
 static Slices slices_of(const ingot_linear_ws* ws, int slot) {

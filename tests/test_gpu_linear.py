@@ -220,3 +220,43 @@ def test_slice_consumers_match_float64():
         assert lib.ingot_linear_ws_status(ws) == 0
     finally:
         lib.ingot_linear_ws_destroy(ws)
+
+
+def test_grouped_projection_launch_matches_float64():
+    """q/k/v (and gate/up) as ONE tensor-core launch over the output tiles of all matrices, k slices left in scratch
+    slots 0..2 and summed by the consumer kernel: against float64, with widths that are not multiples of the tile."""
+    import torch
+    lib = _lib()
+    vp, ci, cf = C.c_void_p, C.c_int, C.c_float
+    lib.ingot_linear_tc_run_partial_group.argtypes = [vp, C.POINTER(vp), ci, C.POINTER(ci), ci, ci, ci, vp]
+    lib.ingot_linear_tc_finish_group.argtypes = [vp, C.POINTER(vp), ci, vp]
+    lib.ingot_linear_tc_prepare_norm.argtypes = [vp, vp, vp, cf, ci, ci, vp]
+    ws = vp()
+    assert lib.ingot_linear_ws_create(C.byref(ws), 256, 2048) == 0
+    try:
+        n_tok, d, eps = 130, 1024, 1e-5
+        g = torch.Generator(device="cuda").manual_seed(21)
+        rnd = lambda *shape: torch.randn(*shape, device="cuda", generator=g)
+        x, nw = rnd(n_tok, d), 1 + 0.1 * rnd(d)
+        mats = [(rnd(r, d) * 0.05).half() for r in (640, 132, 256)]
+        st = vp(torch.cuda.current_stream().cuda_stream)
+        assert lib.ingot_linear_tc_prepare_norm(ws, x.data_ptr(), nw.data_ptr(), eps, d, n_tok, st) == 0
+        for count in (3, 2, 1):
+            wp = (vp * count)(*[m.data_ptr() for m in mats[:count]])
+            rows = (ci * count)(*[m.shape[0] for m in mats[:count]])
+            assert lib.ingot_linear_tc_run_partial_group(ws, wp, d, rows, count, 0, 0, st) == 0
+            if count == 2:  # a second product appended to the same slots: W + 0.5 W, as hi and lo planes of a quantised matrix would be
+                halves = [(m * 0.5).contiguous() for m in mats[:count]]
+                hp = (vp * count)(*[m.data_ptr() for m in halves])
+                assert lib.ingot_linear_tc_run_partial_group(ws, hp, d, rows, count, 0, 1, st) == 0
+            outs = [torch.zeros(n_tok, m.shape[0], device="cuda") for m in mats[:count]]
+            assert lib.ingot_linear_tc_finish_group(ws, (vp * count)(*[o.data_ptr() for o in outs]), count, st) == 0
+            torch.cuda.synchronize()
+            xd = x.double()
+            h = xd * torch.rsqrt((xd * xd).mean(dim=1, keepdim=True) + eps) * nw.double()
+            for o, m in zip(outs, mats):
+                want = h @ m.double().t() * (1.5 if count == 2 else 1.0)
+                assert (o.double() - want).abs().max().item() <= 2e-5 * max(1.0, want.abs().max().item())
+        assert lib.ingot_linear_ws_status(ws) == 0
+    finally:
+        lib.ingot_linear_ws_destroy(ws)
