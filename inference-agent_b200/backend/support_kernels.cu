@@ -231,11 +231,17 @@ __device__ __forceinline__ float dot_load(const uint4& raw, const float4* x4, un
 
 // kLoads: 16-byte weight loads per lane and step (split between gate and up under kSwiGLU). Current and next step
 // are in flight together, so with kLoads = 6 a whole row of 3072 weights (12 chunks) is requested at once.
+// Threads per CTA: every CTA stages x' (and reads the norm weights) for itself, so fewer, larger CTAs mean less of that
+// L2 traffic per launch. f16 rows need 80 registers per thread and fit 768 threads (24 warps, one CTA per SM);
+// the quantised formats need up to 122 and stay at 256 threads (two or three CTAs per SM).
+template <int kFmt>
+struct StreamThreads { static constexpr int value = kFmt == 0 ? 768 : 256; };
+
 template <bool kNorm, bool kSwiGLU, int kLoads, int kFmt>
-__global__ void __launch_bounds__(256) gemv_stream_kernel(const GemvGroup g, const float* x, const float* norm_w, float eps, int n_in,
+__global__ void __launch_bounds__(StreamThreads<kFmt>::value) gemv_stream_kernel(const GemvGroup g, const float* x, const float* norm_w, float eps, int n_in,
                                                           int total_rows, int accumulate, int use_pdl) {
     extern __shared__ float xs[];  // x', n_in floats
-    __shared__ float red[9];
+    __shared__ float red[25];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int W = gridDim.x * (blockDim.x >> 5), gw = blockIdx.x * (blockDim.x >> 5) + warp;
     if (use_pdl) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -505,16 +511,17 @@ cudaError_t ingot_support_gemv_group(float* const* outs, const void* const* ws, 
     if (e == cudaSuccess) e = cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
     if (e != cudaSuccess) return e;
     int occ = 0;
-    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kernel, 256, smem);
+    const int threads = fmt == kFmtF16 ? StreamThreads<kFmtF16>::value : StreamThreads<kFmtQ8_0>::value, cta_warps = threads / 32;
+    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kernel, threads, smem);
     if (e != cudaSuccess) return e;
     if (occ < 1) occ = 1;
     if (ctas_per_sm_cap > 0) occ = occ < ctas_per_sm_cap ? occ : ctas_per_sm_cap;
-    const int capacity = num_sms * occ * 8;
+    const int capacity = num_sms * occ * cta_warps;
     const int rows_per_warp = (rows + capacity - 1) / capacity;
     const int warps = (rows + rows_per_warp - 1) / rows_per_warp;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((warps + 7) / 8);
-    cfg.blockDim = dim3(256);
+    cfg.gridDim = dim3((warps + cta_warps - 1) / cta_warps);
+    cfg.blockDim = dim3(threads);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = s;
     cudaLaunchAttribute attr[1];
