@@ -220,6 +220,16 @@ ingot_kv* ingot_mg_kv(ingot_mg* mg, int dev);
 void* ingot_mg_out(ingot_mg* mg, int dev);
 void* ingot_mg_stream(ingot_mg* mg, int dev);
 int ingot_mg_prefill(ingot_mg* mg, int layer, const void* const* q_dev, int q_dtype, int q_pos0, int n_tok, int timeout_ms);
+/* One token of the one sequence of a CONTIGUOUS cache, K1 and K3 in one launch: q_dev [n_head][128], k_dev and v_dev
+ * [n_head_kv][128] are the f32 projections of the token at position `pos`; the kernel rotates q and k
+ * (src/ops.cpp:243-255), writes the K/V row of that position to the cache and attends over keys 0..pos
+ * (src/cpu_backend.cpp:43-69 for one token), out_dev [n_head][128] f32 or f16. Bit-identical to ingot_rope_kv_append
+ * followed by ingot_attn_decode. key_count_dev: null, or a device int32 holding pos + 1 (then `pos` is ignored and
+ * max_seq_len bounds it, for CUDA graphs that are replayed at growing positions). */
+int ingot_rope_append_decode(ingot_kv* kv, int layer, const float* q_dev, const float* k_dev, const float* v_dev,
+                             const float* inv_freq_dev, void* out_dev, int out_dtype, int n_head, const int32_t* key_count_dev,
+                             int pos, int max_seq_len, void* stream);
+
 /* Prefill attention with the queries and the output in HOST memory and the cache resident on the device (the keys of
  * positions 0 .. q_pos0+n_tok-1 are in the cache already, e.g. after ingot_rope_kv_append or ingot_kv_import_f16):
  * q_host [n_tok][n_head][128] (f32, f16 or bf16) in, out_host [n_tok][n_head][128] (f32 or f16) out. The rows are

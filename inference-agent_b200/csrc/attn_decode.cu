@@ -28,6 +28,28 @@
 #include "ingot_internal.cuh"
 #include "attn_decode_params.cuh"
 
+// This file is compiled twice. attn_decode_append.cu defines INGOT_DECODE_APPEND and includes it: the kernel then is
+// the single-token form that also does K1's work (RoPE on q and on the new k, the K/V row written to the cache by the
+// CTA that owns the last key, that row fed to the MMAs from the projections instead of from the cache) - one launch
+// for what is otherwise rope_kv_append + decode. Everything outside the kernel is compiled in the plain build only,
+// so this build's kernel is the same code as before.
+#ifdef INGOT_DECODE_APPEND
+#include "rope_unit.cuh"
+#define DECODE_KERNEL attn_decode_append_kernel
+#define DECODE_PARAMS DecodeAppendParams
+struct DecodeAppendParams : DecodeParams {
+    const float* q_f32;     // [n_head][128] projections of the token
+    const float* k_new;     // [n_head_kv][128]
+    const float* v_new;
+    const float* inv_freq;  // [64]
+    __half* kc_w;           // writable aliases of kc / vc
+    __half* vc_w;
+};
+#else
+#define DECODE_KERNEL attn_decode_kernel
+#define DECODE_PARAMS DecodeParams
+#endif
+
 #include <algorithm>
 #include <cstring>
 #include <mutex>
@@ -166,7 +188,7 @@ __device__ __forceinline__ void combine_splits(const DecodeParams& p, float* sme
 struct KRegs { uint4 k[8]; };  // [n-tile 0/1][i=0..3]: key (nt*8 + g), 16-byte chunk (4i + j)
 struct VRegs { uint4 v[8]; };  // [slot 0..3 -> keys 2j, 2j+1, 2j+8, 2j+9][chunk g / g+8]
 
-__global__ void __launch_bounds__(kMaxDecodeWarps * 32, 1) attn_decode_kernel(const DecodeParams p) {
+__global__ void __launch_bounds__(kMaxDecodeWarps * 32, 1) DECODE_KERNEL(const DECODE_PARAMS p) {
     extern __shared__ float smem[];
     // Programmatic dependent launch: let the next kernel in the stream start as soon as SM resources allow, and
     // wait for the kernel before this one according to p.pdl_mode (see DecodeParams).
@@ -196,6 +218,27 @@ __global__ void __launch_bounds__(kMaxDecodeWarps * 32, 1) attn_decode_kernel(co
 
     const int32_t* bt = p.paged ? p.block_tables + (size_t)seq * p.max_blocks_per_seq : nullptr;
 
+#ifdef INGOT_DECODE_APPEND
+    // The token's projections, rotated for position n_keys - 1 and rounded to f16 once per CTA: the G query heads of this
+    // KV head (the MMA A operand), the new K row and the new V row (what K1 writes to the cache). One 8-element unit
+    // per thread.
+    __shared__ __align__(16) __half new_q[8 * kHeadDim];
+    __shared__ __align__(16) __half new_kv[2 * kHeadDim];
+    {
+        const float fpos = float(n_keys - 1);
+        for (int u = threadIdx.x; u < (G + 2) * 16; u += blockDim.x) {
+            const int h = u >> 4, c = u & 15;
+            if (h < G)
+                *reinterpret_cast<uint4*>(new_q + h * kHeadDim + c * 8) =
+                    rope_pack8(p.q_f32 + ((size_t)kvh * G + h) * kHeadDim + c * 8, c * 4, fpos, p.inv_freq, true);
+            else
+                *reinterpret_cast<uint4*>(new_kv + (h - G) * kHeadDim + c * 8) =
+                    rope_pack8((h == G ? p.k_new : p.v_new) + (size_t)kvh * kHeadDim + c * 8, c * 4, fpos, p.inv_freq, h == G);
+        }
+        __syncthreads();
+    }
+#endif
+
     // Base element offset (within the layer) of the 16 rows of unit u; keys of a unit are contiguous
     // rows in both layouts (a unit is exactly one block of a paged cache).
     auto unit_base = [&](int u) -> size_t {
@@ -216,6 +259,20 @@ __global__ void __launch_bounds__(kMaxDecodeWarps * 32, 1) attn_decode_kernel(co
 #pragma unroll
         for (int nt = 0; nt < 2; nt++) {
             const int row = min(nt * 8 + g, last);
+#ifdef INGOT_DECODE_APPEND
+            if (row == last && last < 16) {
+                // The newest key (position n_keys - 1): taken from the CTA's rotated copy of the projection, and written to
+                // the cache by the lanes whose own row it is (rows past the last key are clamped onto it and only read it).
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const int c = 4 * i + j;
+                    const uint4 val = *reinterpret_cast<const uint4*>(new_kv + c * 8);
+                    r.k[nt * 4 + i] = val;
+                    if (nt * 8 + g == last) *reinterpret_cast<uint4*>(p.kc_w + (size_t)layer * p.cache_layer_stride + ub + (size_t)row * kHeadDim + c * 8) = val;
+                }
+                continue;
+            }
+#endif
 #pragma unroll
             for (int i = 0; i < 4; i++) r.k[nt * 4 + i] = ld_stream16(kb + (size_t)row * kHeadDim + (4 * i + j) * 8);
         }
@@ -227,7 +284,20 @@ __global__ void __launch_bounds__(kMaxDecodeWarps * 32, 1) attn_decode_kernel(co
         const __half* vb = vc + ub;
 #pragma unroll
         for (int s = 0; s < 4; s++) {
-            const int row = min(2 * j + (s & 1) + (s >> 1) * 8, last);
+            const int row_own = 2 * j + (s & 1) + (s >> 1) * 8;
+            const int row = min(row_own, last);
+#ifdef INGOT_DECODE_APPEND
+            if (row == last && last < 16) {  // the newest V row: from the CTA's f16 copy of the projection, stored by its owner lanes
+#pragma unroll
+                for (int hgh = 0; hgh < 2; hgh++) {
+                    const int c = g + 8 * hgh;
+                    const uint4 val = *reinterpret_cast<const uint4*>(new_kv + kHeadDim + c * 8);
+                    r.v[s * 2 + hgh] = val;
+                    if (row_own == last) *reinterpret_cast<uint4*>(p.vc_w + (size_t)layer * p.cache_layer_stride + ub + (size_t)row * kHeadDim + c * 8) = val;
+                }
+                continue;
+            }
+#endif
             r.v[s * 2 + 0] = ld_stream16(vb + (size_t)row * kHeadDim + g * 8);
             r.v[s * 2 + 1] = ld_stream16(vb + (size_t)row * kHeadDim + (g + 8) * 8);
         }
@@ -319,9 +389,14 @@ __global__ void __launch_bounds__(kMaxDecodeWarps * 32, 1) attn_decode_kernel(co
         // Query fragments (head row g, chunks 4i + j), requested after the K/V units so that the wait
         // for them overlaps the K/V latency instead of preceding it.
         if (g < G) {
+#ifdef INGOT_DECODE_APPEND
+#pragma unroll
+            for (int i = 0; i < 4; i++) qa[i] = *reinterpret_cast<const uint4*>(new_q + g * kHeadDim + (4 * i + j) * 8);
+#else
             const size_t qbase = (size_t)layer * p.qo_layer_stride + ((size_t)seq * p.n_head + (size_t)kvh * G + g) * kHeadDim;
 #pragma unroll
             for (int i = 0; i < 4; i++) qa[i] = load_q8(p.q, p.q_dtype, qbase + (size_t)(4 * i + j) * 8);
+#endif
         }
         while (u0 < n_units) {
             compute_qk(k0, u0);
@@ -384,14 +459,15 @@ __global__ void __launch_bounds__(kMaxDecodeWarps * 32, 1) attn_decode_kernel(co
     }
 }
 
+}  // namespace
+
+#ifndef INGOT_DECODE_APPEND
 // Tuning knob, process-wide and read once (like the reference's LLM_ATTN_SPLITS): warps per CTA, 4 (two CTAs
 // per SM) or 8.
 int decode_warps_cfg() {
     static const int v = [] { const char* e = getenv("INGOT_DECODE_WARPS"); return (e && atoi(e) == 8) ? 8 : 4; }();
     return v;
 }
-
-}  // namespace
 
 // Split size and split count of one decode launch over `ranges` = layers x sequences x kv heads independent key
 // ranges of up to max_seq_len keys (chunk_keys == 0: chosen here).
@@ -575,3 +651,44 @@ extern "C" int ingot_attn_decode_noalloc(const void* k_dev, const void* v_dev, i
     }
     return INGOT_OK;
 }
+#endif  // !INGOT_DECODE_APPEND
+
+#ifdef INGOT_DECODE_APPEND
+// One launch of the fused form for one token of one sequence on a contiguous cache: q/k/v are the f32 projections, the
+// key count (position + 1) comes from seq_lens (device) or max_seq_len. Splits and partials as in launch_attn_decode;
+// with more than one split the caller follows up with the plain kernel's merge-only launch.
+int launch_attn_decode_append(ingot_kv* kv, int layer, const float* q, const float* k, const float* v, const float* inv_freq, void* out,
+                              int out_dtype, int n_head, const int32_t* seq_lens, int max_seq_len, DecodePlan plan, float* part,
+                              cudaStream_t stream) {
+    const int n_warps = decode_warps_cfg();
+    DecodeAppendParams p;
+    p.kc = kv->k + size_t(layer) * kv->layer_elems;
+    p.vc = kv->v + size_t(layer) * kv->layer_elems;
+    p.kc_w = kv->k + size_t(layer) * kv->layer_elems;
+    p.vc_w = kv->v + size_t(layer) * kv->layer_elems;
+    p.q = nullptr; p.out = out; p.seq_lens = seq_lens; p.block_tables = nullptr;
+    p.part = part; p.c_part = part; p.c_out = out; p.status = kv->status_dev;
+    p.q_f32 = q; p.k_new = k; p.v_new = v; p.inv_freq = inv_freq;
+    p.n_seq = 1;
+    p.cache_layer_stride = kv->layer_elems;
+    p.qo_layer_stride = (size_t)n_head * kHeadDim;
+    p.part_layer_stride = decode_part_floats(1, plan.n_parts, n_head);
+    p.cache_extent = kv->checked_cache_elems();
+    p.part_extent = p.part_layer_stride;
+    p.out_extent = p.qo_layer_stride;
+    p.q_dtype = INGOT_F32; p.out_dtype = out_dtype;
+    p.n_head = n_head; p.n_head_kv = kv->n_head_kv; p.group = n_head / kv->n_head_kv;
+    p.capacity = kv->capacity; p.paged = 0; p.max_blocks_per_seq = 0;
+    p.len0 = max_seq_len; p.chunk_keys = plan.chunk_keys; p.n_parts_max = plan.n_parts;
+    p.pdl_mode = kPdlWaitFirst;
+    p.split_parts = plan.n_parts;
+    p.scale_log2 = 1.4426950408889634f / sqrtf(float(kHeadDim));
+    const int threads = n_warps * 32;
+    const size_t smem_split = (size_t)n_warps * p.group * (kHeadDim + 2);
+    const size_t smem_merge = (size_t)2 * p.group * kMaxParts + (size_t)4 * std::max(threads, p.group * 32);
+    const size_t smem = std::max(smem_split, smem_merge) * sizeof(float);
+    const dim3 grid(plan.n_parts, kv->n_head_kv, 1);
+    INGOT_CUDA_TRY(ingot_launch_pdl(attn_decode_append_kernel, grid, dim3(threads), smem, stream, p));
+    return INGOT_OK;
+}
+#endif

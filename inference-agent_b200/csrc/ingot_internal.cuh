@@ -160,6 +160,10 @@ int launch_kv_import_f16(ingot_kv* kv, int layer, const __half* k, const __half*
 struct DecodePlan { int chunk_keys, n_parts; };
 DecodePlan decode_plan(const ingot_kv* kv, int n_layers, int n_seq, int max_seq_len, int chunk_keys);
 int decode_slots(const ingot_kv* kv);
+int decode_warps_cfg();
+int launch_attn_decode_append(ingot_kv* kv, int layer, const float* q, const float* k, const float* v, const float* inv_freq, void* out,
+                              int out_dtype, int n_head, const int32_t* seq_lens, int max_seq_len, DecodePlan plan, float* part,
+                              cudaStream_t stream);
 size_t decode_part_floats(int n_seq, int n_parts, int n_head);
 int launch_attn_decode(ingot_kv* kv, int layer, int n_layers, const void* q, int q_dtype, void* out, int out_dtype, int n_head,
                        int n_seq, const int32_t* seq_lens, int max_seq_len, const int32_t* block_tables,

@@ -297,6 +297,39 @@ int ingot_attn_decode_layers(ingot_kv* kv, int layer_begin, int layer_count, con
     return INGOT_OK;
 }
 
+// K1 + K3 for one token of the one sequence of a contiguous cache, in one launch (plus the merge launch when the keys
+// are split): see attn_decode_append.cu.
+int ingot_rope_append_decode(ingot_kv* kv, int layer, const float* q_dev, const float* k_dev, const float* v_dev,
+                             const float* inv_freq_dev, void* out_dev, int out_dtype, int n_head, const int32_t* key_count_dev,
+                             int pos, int max_seq_len, void* stream) {
+    INGOT_REQUIRE(kv != nullptr, "ingot_rope_append_decode: kv is null");
+    INGOT_REQUIRE_DEVICE(kv);
+    INGOT_REQUIRE(kv->layout == INGOT_KV_CONTIGUOUS, "ingot_rope_append_decode: contiguous cache only");
+    INGOT_REQUIRE(layer >= 0 && layer < kv->n_layer, "ingot_rope_append_decode: layer out of range");
+    INGOT_REQUIRE(q_dev && k_dev && v_dev && inv_freq_dev && out_dev, "ingot_rope_append_decode: null argument");
+    INGOT_REQUIRE(n_head >= kv->n_head_kv && n_head % kv->n_head_kv == 0, "ingot_rope_append_decode: n_head must be a multiple of n_head_kv");
+    if (n_head / kv->n_head_kv > 8 || (out_dtype != INGOT_F32 && out_dtype != INGOT_F16)) {
+        ingot_set_error("ingot_rope_append_decode: group size > 8 or unsupported dtype");
+        return INGOT_ERR_UNSUPPORTED;
+    }
+    if (key_count_dev == nullptr) {
+        INGOT_REQUIRE(pos >= 0 && size_t(pos) + 1 <= size_t(kv->capacity), "context window exceeded");
+        max_seq_len = pos + 1;
+    }
+    INGOT_REQUIRE(max_seq_len >= 1 && max_seq_len <= kv->capacity, "ingot_rope_append_decode: max_seq_len out of range");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const DecodePlan plan = decode_plan(kv, 1, 1, max_seq_len, 0);
+    if (plan.n_parts > 1) {
+        const int rc = ensure_decode_scratch(kv, decode_part_floats(1, plan.n_parts, n_head));
+        if (rc != INGOT_OK) return rc;
+    }
+    int rc = launch_attn_decode_append(kv, layer, q_dev, k_dev, v_dev, inv_freq_dev, out_dev, out_dtype, n_head, key_count_dev, max_seq_len,
+                                       plan, kv->part, s);
+    if (rc != INGOT_OK) return rc;
+    return launch_attn_decode(kv, layer, 1, nullptr, INGOT_F16, out_dev, out_dtype, n_head, 1, key_count_dev, max_seq_len, nullptr, 0, plan,
+                              kv->part, 1, kPdlWaitFirst, s);  // a no-op with a single split
+}
+
 int ingot_attn_prefill(ingot_kv* kv, int layer, const void* q_dev, int q_dtype, void* out_dev, int out_dtype,
                        int n_head, int q_pos0, int n_tok, const int32_t* block_table_dev, int impl, void* stream) {
     INGOT_REQUIRE(kv != nullptr, "ingot_attn_prefill: kv is null");

@@ -13,6 +13,7 @@
 // one 16-byte f16 store), fully coalesced on both sides. Algorithmic bytes per token:
 // (n_head + 2*n_head_kv) * 128 * (4 in + 2 out).
 #include "ingot_internal.cuh"
+#include "rope_unit.cuh"
 
 namespace {
 
@@ -35,11 +36,6 @@ struct AppendParams {
     size_t layer_elems;      // cache elements between consecutive layers (blockIdx.y = layer offset)
     size_t cache_extent;     // elements of one layer the kernel may touch (bounds-check build)
 };
-
-__device__ __forceinline__ uint32_t pack_half2(float a, float b) {
-    __half2 h = __floats2half2_rn(a, b);
-    return *reinterpret_cast<uint32_t*>(&h);
-}
 
 // Destination element offset of (kv head h, position pos) for token `tok`, or -1 if out of range.
 __device__ __forceinline__ long long cache_row(const AppendParams& p, int tok, int h, int pos) {
@@ -93,27 +89,7 @@ __global__ void __launch_bounds__(256) rope_kv_append_kernel(const AppendParams 
         dst = (is_v ? p.vc : p.kc) + lc + row + (size_t)(r & 15) * 8;
         rotate = !is_v;
     }
-    const float4 a = __ldg(reinterpret_cast<const float4*>(src));
-    const float4 b = __ldg(reinterpret_cast<const float4*>(src) + 1);
-    float x[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
-    if (rotate) {
-        const int pair0 = (r & 15) * 4;  // first of this unit's 4 rotation pairs within the head
-        const float fpos = float(pos);
-#pragma unroll
-        for (int i = 0; i < 4; i++) {
-            const float angle = fpos * __ldg(p.inv_freq + pair0 + i);
-            const float c = cosf(angle), s = sinf(angle);
-            const float x0 = x[2 * i], x1 = x[2 * i + 1];
-            x[2 * i] = x0 * c - x1 * s;
-            x[2 * i + 1] = x0 * s + x1 * c;
-        }
-    }
-    uint4 o;
-    o.x = pack_half2(x[0], x[1]);
-    o.y = pack_half2(x[2], x[3]);
-    o.z = pack_half2(x[4], x[5]);
-    o.w = pack_half2(x[6], x[7]);
-    *reinterpret_cast<uint4*>(dst) = o;
+    *reinterpret_cast<uint4*>(dst) = rope_pack8(src, (r & 15) * 4, float(pos), p.inv_freq, rotate);
 }
 
 struct ImportParams {

@@ -47,6 +47,7 @@ ABI = {
     "ingot_mg_stream": (_P, [_P, _I]),
     "ingot_mg_prefill": (_I, [_P, _I, C.POINTER(_P), _I, _I, _I, _I]),
     "ingot_lpt_assign": (_I, [C.POINTER(C.c_int32), _I, _I, C.POINTER(C.c_int32)]),
+    "ingot_rope_append_decode": (_I, [_P, _I, _P, _P, _P, _P, _P, _I, _I, _P, _I, _I, _P]),
     "ingot_attn_prefill_host": (_I, [_P, _I, _P, _I, _P, _I, _I, _I, _I, _P, _I, _P]),
     "ingot_attn_layer_host": (_I, [_P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _P]),
     "ingot_attn_layers_host": (_I, [_P, _I, _I, _P, _P, _P, _P, _P, _I, _I, _I, _P]),
@@ -261,6 +262,18 @@ def attn_prefill_gather_signal(kv, layer, q, q_pos0, out_ptrs, signal_ptrs, src_
 def gather_wait(kv, counters, n_src, timeout_ms=2000):
     """Queues the bounded wait for n_src completion signals on this GPU's counter array (an int32 cuda tensor)."""
     _check(lib().ingot_gather_wait(kv.handle, _ptr(counters), n_src, timeout_ms, _stream()))
+
+
+def rope_append_decode(kv, layer, q, k, v, inv_freq, pos, out=None, out_dtype=None, key_count=None, max_seq_len=0):
+    """One token: q [H,128], k, v [Hkv,128] f32 projections (cuda). RoPE, append at `pos`, attention over keys 0..pos in one
+    launch. key_count: optional int32 cuda tensor holding pos + 1 (then max_seq_len bounds it)."""
+    import torch
+    assert q.is_contiguous() and k.is_contiguous() and v.is_contiguous() and q.dtype == torch.float32
+    if out is None:
+        out = guarded_empty(q.shape, out_dtype or torch.float32, q.device)
+    _check(lib().ingot_rope_append_decode(kv.handle, layer, _ptr(q), _ptr(k), _ptr(v), _ptr(inv_freq), _ptr(out), _dtype_code(out),
+                                          q.shape[0], _ptr(key_count), pos, max_seq_len, _stream()))
+    return out
 
 
 def attn_prefill_host(kv, layer, q_host, q_pos0, out_host, block_table=None, chunk_tokens=0):

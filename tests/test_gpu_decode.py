@@ -180,6 +180,47 @@ def test_decode_ragged_batches_library_plan_vs_explicit_split(lens):
     assert np.abs(planned.cpu().numpy() - launched.cpu().numpy()).max() < 1e-4  # two summation orders of the same f16 products
 
 
+@pytest.mark.parametrize("pos", [0, 1, 14, 15, 16, 17, 255, 256, 300, 1000, 4095])
+def test_rope_append_decode_equals_k1_then_k3(pos):
+    """ingot_rope_append_decode (RoPE, cache append and attention of one token in one launch) against
+    ingot_rope_kv_append followed by ingot_attn_decode on a second, identically filled cache: the outputs and the
+    appended K/V rows must be the same bits; and against the CPU reference. Once with the key count as an argument,
+    once read from device memory with the capacity as the bound (the form a replayed CUDA graph uses)."""
+    import torch
+    import ingot_b200 as ib
+    rng = np.random.default_rng(900 + pos)
+    cap = max(pos + 1, 4096 if pos >= 256 else pos + 1)
+    k_old = rng.standard_normal((pos, HKV, D), dtype=np.float32).astype(np.float16)
+    v_old = rng.standard_normal((pos, HKV, D), dtype=np.float32).astype(np.float16)
+    q = rng.standard_normal((1, H, D), dtype=np.float32)
+    k_new = rng.standard_normal((1, HKV, D), dtype=np.float32)
+    v_new = rng.standard_normal((1, HKV, D), dtype=np.float32)
+    inv = helpers.to_dev(helpers.inv_freq())
+    caches = []
+    for _ in range(3):
+        kv = ib.KVCache(ib.KV_CONTIGUOUS, 1, HKV, cap)
+        if pos:
+            kv.import_f16(0, helpers.to_dev(k_old), helpers.to_dev(v_old), 0)
+        caches.append(kv)
+    qd, kd, vd = helpers.to_dev(q), helpers.to_dev(k_new), helpers.to_dev(v_new)
+    q_rot = ib.rope_kv_append(caches[0], 0, qd, kd, vd, inv, pos)
+    two = ib.attn_decode(caches[0], 0, q_rot, max_seq_len=pos + 1)
+    one = ib.rope_append_decode(caches[1], 0, qd[0], kd[0], vd[0], inv, pos)
+    count = helpers.to_dev(np.array([pos + 1], dtype=np.int32))
+    one_dev = ib.rope_append_decode(caches[2], 0, qd[0], kd[0], vd[0], inv, 0, key_count=count, max_seq_len=cap)
+    torch.cuda.synchronize()
+    for kv in caches:
+        assert kv.status() == 0
+    for which in ("k", "v"):
+        want_rows = caches[0].layer_view(0, which)
+        assert torch.equal(caches[1].layer_view(0, which), want_rows) and torch.equal(caches[2].layer_view(0, which), want_rows)
+    assert torch.equal(one, two[0])
+    wl = W.Prefill(q, k_new, v_new, pos, True, k_old if pos else None, v_old if pos else None)
+    want, _, _ = helpers.oracle_prefill(wl)
+    helpers.assert_parity(one.cpu().numpy()[None], want, "fused rope + append + decode")
+    helpers.assert_parity(one_dev.cpu().numpy()[None], want, "fused, key count from device memory")
+
+
 def test_empty_calls_are_no_ops():
     import ingot_b200 as ib
     lib = ib.lib()
