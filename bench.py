@@ -37,6 +37,8 @@ import time
 
 import numpy as np
 
+_T0 = time.time()
+
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 sys.path.insert(0, os.path.join(ROOT, "inference-agent_b200"))
@@ -105,15 +107,43 @@ class ClockSampler:
                 "reasons": [n for n, b in bits.items() if self.reasons & b], "samples": len(self.samples)}
 
 
+def stage(msg):
+    """Progress marker on stderr (every rank): if a multi-GPU run ever stalls, the log says where."""
+    print(f"[bench rank {os.environ.get('RANK', '0')} +{time.time() - _T0:6.1f}s] {msg}", file=sys.stderr, flush=True)
+
+
+def start_watchdog(world):
+    """A multi-rank run that has not finished after INGOT_BENCH_LIMIT_S seconds (default 420) ends itself with a message
+    instead of occupying the GPUs until somebody else's limit: a stalled collective would otherwise wait for ever."""
+    if world <= 1:
+        return
+    import threading
+    limit = float(os.environ.get("INGOT_BENCH_LIMIT_S", "420"))
+
+    def bail():
+        stage(f"watchdog: not finished after {limit:.0f} s - giving up")
+        if os.environ.get("RANK", "0") == "0":
+            print(json.dumps({"error": f"bench.py --gpus {world} did not finish within {limit:.0f} s (see the stage markers on stderr)"}), flush=True)
+        os._exit(3)
+
+    t = threading.Timer(limit, bail)
+    t.daemon = True
+    t.start()
+
+
 def dist_setup(n_gpus):
     import torch
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     if world > 1:
+        import datetime
         import torch.distributed as dist
         torch.cuda.set_device(local)
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        # a collective that a rank never joins ends with an error after this long instead of the default ten minutes
+        limit = datetime.timedelta(seconds=float(os.environ.get("INGOT_BENCH_PG_TIMEOUT_S", "180")))
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local), timeout=limit)
+        stage("process group up")
     else:
         torch.cuda.set_device(0)
     if world != n_gpus:
@@ -366,8 +396,16 @@ def run_prefill(args, rank, world):
                 full, peer_ptrs = gs.full, gs.peer_ptrs
                 gather_mode = gs.mode
             except Exception as e:  # noqa: BLE001
-                peer_ptrs = None
+                peer_ptrs, gs = None, None
                 gather_mode += f" (symmetric memory unavailable: {type(e).__name__}: {e})"
+            # Every rank takes the same path: the fused form only if symmetric memory came up on all of them.
+            agreed = torch.tensor([1 if peer_ptrs is not None else 0], device="cuda", dtype=torch.int32)
+            dist.all_reduce(agreed, op=dist.ReduceOp.MIN)
+            if int(agreed.item()) == 0 and peer_ptrs is not None:
+                peer_ptrs, gs, full = None, None, None
+                gather_mode = "NCCL all_gather_into_tensor after the kernel (symmetric memory unavailable on another rank)"
+            dist.barrier()  # every rank's signal counters are zero before anyone signals
+        stage(f"prefill: gather mode = {gather_mode}")
 
     def step():
         if peer_ptrs is not None:
@@ -383,6 +421,19 @@ def run_prefill(args, rank, world):
     gather_checked = None
     if peer_ptrs is not None:  # one-time check of the fused gather against kernel + NCCL all-gather
         step()
+        torch.cuda.synchronize()
+        # If some rank's bounded wait for the signals ran out, every rank switches to the all-reduce barrier (and says so).
+        waited_out = torch.tensor([kv.status()], device="cuda", dtype=torch.int32)
+        dist.all_reduce(waited_out, op=dist.ReduceOp.MAX)
+        if int(waited_out.item()) != 0 and gs.barrier == "signal":
+            gs.barrier = "nccl"
+            gs.mode = ("fused: peer stores from the kernel epilogue + 1-element all-reduce barrier "
+                       f"(the wait for the in-kernel signals ran out on some rank, status {int(waited_out.item())})")
+            gather_mode = gs.mode
+            stage("prefill: signal wait timed out, falling back to the all-reduce barrier")
+            step()
+            torch.cuda.synchronize()
+            kv.status()
         step_kernel_only()
         dist.all_gather_into_tensor(gathered, out)
         torch.cuda.synchronize()
@@ -390,6 +441,7 @@ def run_prefill(args, rank, world):
         gather_checked = bool(torch.equal(ref, full))
         if not gather_checked:
             raise SystemExit("fused gather differs from kernel + NCCL all-gather")
+        stage("prefill: fused gather verified")
 
     steps = max(1, min(args.steps, args.prefill_steps))
     with ClockSampler(torch.cuda.current_device()) as clk:
@@ -477,7 +529,6 @@ class GatherSync:
             torch.cuda.synchronize()
             sh = symm.rendezvous(self.sig, dist.group.WORLD)
             self.sig_ptrs = [int(x) for x in sh.buffer_ptrs]
-            dist.barrier()  # every rank's counters are zero before anyone signals
             self.mode = "fused: peer stores from the kernel epilogue + released per-source signals, bounded wait kernel"
         else:
             self.mode = "fused: peer stores from the kernel epilogue + 1-element all-reduce barrier"
@@ -820,6 +871,7 @@ def main():
         return
 
     rank, world, _ = dist_setup(args.gpus)
+    start_watchdog(world)
     from ingot_b200 import workloads as W
     others = {
         "c1_prefill128": lambda a, r, w: run_chunked(a, r, w, W.c1_prefill128(), "configs[0]: 128-token prefill at position 0"),
@@ -833,12 +885,18 @@ def main():
     else:
         primary, secondary = (run_decode, run_prefill) if args.workload == "decode_c2" else (run_prefill, run_decode)
     line = primary(args, rank, world)
+    if world > 1:
+        stage("primary workload done")
     other = None if args.no_secondary else secondary(args, rank, world)
+    if world > 1:
+        stage("secondary workload done")
     if not args.no_secondary:
         # The remaining configurations ride along as objects of their own: the two chunked-prefill shapes on one GPU
         # (they are replicas at N > 1), the sequence-sharded batched decode at every N.
         for name in (("c1_prefill128", "c3_chunked") if world == 1 else ()) + ("c4_batched",):
             extra[name] = others[name](args, rank, world)
+            if world > 1:
+                stage(f"{name} done")
     if rank == 0:
         out = {"metric": line.pop("metric"), "value": line.pop("value"), "unit": line.pop("unit"), "n_gpus": world,
                "steps": line.pop("steps", args.steps), "warmup": args.warmup, "ms_per_step": line.pop("ms_per_step"),
