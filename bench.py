@@ -113,12 +113,12 @@ def stage(msg):
 
 
 def start_watchdog(world):
-    """A multi-rank run that has not finished after INGOT_BENCH_LIMIT_S seconds (default 420) ends itself with a message
+    """A multi-rank run that has not finished after INGOT_BENCH_LIMIT_S seconds (default 540) ends itself with a message
     instead of occupying the GPUs until somebody else's limit: a stalled collective would otherwise wait for ever."""
     if world <= 1:
         return
     import threading
-    limit = float(os.environ.get("INGOT_BENCH_LIMIT_S", "420"))
+    limit = float(os.environ.get("INGOT_BENCH_LIMIT_S", "540"))
 
     def bail():
         stage(f"watchdog: not finished after {limit:.0f} s - giving up")
@@ -140,8 +140,9 @@ def dist_setup(n_gpus):
         import datetime
         import torch.distributed as dist
         torch.cuda.set_device(local)
-        # a collective that a rank never joins ends with an error after this long instead of the default ten minutes
-        limit = datetime.timedelta(seconds=float(os.environ.get("INGOT_BENCH_PG_TIMEOUT_S", "180")))
+        # a collective that a rank never joins ends with an error after this long instead of the default ten minutes (long
+        # enough for the slowest rank of a fresh machine to get through its imports)
+        limit = datetime.timedelta(seconds=float(os.environ.get("INGOT_BENCH_PG_TIMEOUT_S", "300")))
         dist.init_process_group("nccl", device_id=torch.device("cuda", local), timeout=limit)
         stage("process group up")
     else:
