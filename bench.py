@@ -367,6 +367,24 @@ def prefill_flops(n_tok=None):
     return 4 * n_tok * n_tok * H * D // 2
 
 
+def all_ranks_agree(ok, device):
+    """True only if `ok` is true on every rank (one MIN all-reduce): all ranks then take the same branch."""
+    import torch
+    import torch.distributed as dist
+    t = torch.tensor([1 if ok else 0], device=device, dtype=torch.int32)
+    dist.all_reduce(t, op=dist.ReduceOp.MIN)
+    return bool(int(t.item()))
+
+
+def worst_status(status, device):
+    """The largest status word over all ranks (0 = no rank reported an error)."""
+    import torch
+    import torch.distributed as dist
+    t = torch.tensor([int(status)], device=device, dtype=torch.int32)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return int(t.item())
+
+
 def run_prefill(args, rank, world):
     import torch
     import ingot_b200 as ib
@@ -400,9 +418,7 @@ def run_prefill(args, rank, world):
                 peer_ptrs, gs = None, None
                 gather_mode += f" (symmetric memory unavailable: {type(e).__name__}: {e})"
             # Every rank takes the same path: the fused form only if symmetric memory came up on all of them.
-            agreed = torch.tensor([1 if peer_ptrs is not None else 0], device="cuda", dtype=torch.int32)
-            dist.all_reduce(agreed, op=dist.ReduceOp.MIN)
-            if int(agreed.item()) == 0 and peer_ptrs is not None:
+            if not all_ranks_agree(peer_ptrs is not None, "cuda") and peer_ptrs is not None:
                 peer_ptrs, gs, full = None, None, None
                 gather_mode = "NCCL all_gather_into_tensor after the kernel (symmetric memory unavailable on another rank)"
             dist.barrier()  # every rank's signal counters are zero before anyone signals
@@ -424,12 +440,11 @@ def run_prefill(args, rank, world):
         step()
         torch.cuda.synchronize()
         # If some rank's bounded wait for the signals ran out, every rank switches to the all-reduce barrier (and says so).
-        waited_out = torch.tensor([kv.status()], device="cuda", dtype=torch.int32)
-        dist.all_reduce(waited_out, op=dist.ReduceOp.MAX)
-        if int(waited_out.item()) != 0 and gs.barrier == "signal":
+        waited_out = worst_status(kv.status(), "cuda")
+        if waited_out != 0 and gs.barrier == "signal":
             gs.barrier = "nccl"
             gs.mode = ("fused: peer stores from the kernel epilogue + 1-element all-reduce barrier "
-                       f"(the wait for the in-kernel signals ran out on some rank, status {int(waited_out.item())})")
+                       f"(the wait for the in-kernel signals ran out on some rank, status {waited_out})")
             gather_mode = gs.mode
             stage("prefill: signal wait timed out, falling back to the all-reduce barrier")
             step()
