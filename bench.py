@@ -107,6 +107,11 @@ class ClockSampler:
                 "reasons": [n for n, b in bits.items() if self.reasons & b], "samples": len(self.samples)}
 
 
+# Rank 0's output line as far as it is complete: "line" is set once the headline workload has been measured, "pending"
+# names the remaining workloads. The watchdog of a multi-rank run prints it if a later workload stalls.
+_PARTIAL = {"line": None, "pending": []}
+
+
 def stage(msg):
     """Progress marker on stderr (every rank): if a multi-GPU run ever stalls, the log says where."""
     print(f"[bench rank {os.environ.get('RANK', '0')} +{time.time() - _T0:6.1f}s] {msg}", file=sys.stderr, flush=True)
@@ -122,9 +127,14 @@ def start_watchdog(world):
 
     def bail():
         stage(f"watchdog: not finished after {limit:.0f} s - giving up")
+        why = f"bench.py --gpus {world} did not finish within {limit:.0f} s (see the stage markers on stderr)"
+        done = _PARTIAL.get("line")
         if os.environ.get("RANK", "0") == "0":
-            print(json.dumps({"error": f"bench.py --gpus {world} did not finish within {limit:.0f} s (see the stage markers on stderr)"}), flush=True)
-        os._exit(3)
+            if done is not None:  # the headline workload was measured in full: report it and say what is missing
+                print(json.dumps(dict(done, incomplete=f"{why}; not finished: {', '.join(_PARTIAL['pending'])}")), flush=True)
+            else:
+                print(json.dumps({"error": why}), flush=True)
+        os._exit(0 if done is not None or os.environ.get("RANK", "0") != "0" else 3)
 
     t = threading.Timer(limit, bail)
     t.daemon = True
@@ -533,6 +543,9 @@ class GatherSync:
     def __init__(self, S, world, rank, barrier="signal"):
         import torch
         import torch.distributed as dist
+        # The kernels here use plain peer stores only; no multicast object is wanted on these buffers (a rank that leaves
+        # early - the watchdog, a collective time-out - must not leave peers with memory bound to one).
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         import torch.distributed._symmetric_memory as symm
         self.full = symm.empty((S, H, D), dtype=torch.float16, device="cuda")
         hdl = symm.rendezvous(self.full, dist.group.WORLD)
@@ -894,25 +907,13 @@ def main():
         "c3_chunked": lambda a, r, w: run_chunked(a, r, w, W.c3_chunked(), "configs[2]: 512-token chunk onto 3584 cached positions"),
         "c4_batched": run_batched_decode,
     }
-    extra = {}
     if args.workload in others:
         args.no_secondary = args.no_cpu = True
         primary, secondary = others[args.workload], None
     else:
         primary, secondary = (run_decode, run_prefill) if args.workload == "decode_c2" else (run_prefill, run_decode)
     line = primary(args, rank, world)
-    if world > 1:
-        stage("primary workload done")
-    other = None if args.no_secondary else secondary(args, rank, world)
-    if world > 1:
-        stage("secondary workload done")
-    if not args.no_secondary:
-        # The remaining configurations ride along as objects of their own: the two chunked-prefill shapes on one GPU
-        # (they are replicas at N > 1), the sequence-sharded batched decode at every N.
-        for name in (("c1_prefill128", "c3_chunked") if world == 1 else ()) + ("c4_batched",):
-            extra[name] = others[name](args, rank, world)
-            if world > 1:
-                stage(f"{name} done")
+    out = None
     if rank == 0:
         out = {"metric": line.pop("metric"), "value": line.pop("value"), "unit": line.pop("unit"), "n_gpus": world,
                "steps": line.pop("steps", args.steps), "warmup": args.warmup, "ms_per_step": line.pop("ms_per_step"),
@@ -921,9 +922,25 @@ def main():
         line.setdefault("clocks", None)
         line.setdefault("e2e", None)
         out.update(line)
-        if other is not None:
-            out["prefill" if args.workload == "decode_c2" else "decode"] = other
-        out.update(extra)
+    other_name = "prefill" if args.workload == "decode_c2" else "decode"
+    # the remaining configurations ride along as objects of their own: the other headline shape, the two chunked-prefill
+    # shapes on one GPU (they are replicas at N > 1) and the sequence-sharded batched decode at every N
+    rest = [] if args.no_secondary else [other_name] + (["c1_prefill128", "c3_chunked"] if world == 1 else []) + ["c4_batched"]
+    _PARTIAL["pending"] = list(rest)
+    _PARTIAL["line"] = out
+    if world > 1:
+        stage("primary workload done")
+    other = None
+    for name in rest:
+        res = secondary(args, rank, world) if name == other_name else others[name](args, rank, world)
+        if name == other_name:
+            other = res
+        if rank == 0:
+            out[name] = res
+        _PARTIAL["pending"].remove(name)
+        if world > 1:
+            stage(f"{name} done")
+    if rank == 0:
         if world == 1 and not args.no_cpu:
             if args.workload == "decode_c2":
                 gbs, kind, cores, per_layer = cpu_decode_sample(N_LAYER, 3)

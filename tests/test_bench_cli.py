@@ -31,6 +31,23 @@ def test_watchdog_ends_a_stalled_multi_rank_run_with_a_message():
     assert "[bench rank 0" in r.stderr and "started" in r.stderr and "watchdog" in r.stderr
 
 
+def test_watchdog_reports_a_finished_headline_when_a_later_workload_stalls():
+    code = (
+        "import importlib.util, time\n"
+        f"spec = importlib.util.spec_from_file_location('bench', {BENCH!r})\n"
+        "b = importlib.util.module_from_spec(spec); spec.loader.exec_module(b)\n"
+        "b._PARTIAL['line'] = {'metric': 'm', 'value': 1.5, 'n_gpus': 2}\n"
+        "b._PARTIAL['pending'] = ['prefill', 'c4_batched']\n"
+        "b.start_watchdog(2)\n"
+        "time.sleep(20)\n")
+    env = dict(os.environ, INGOT_BENCH_LIMIT_S="1", RANK="0")
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=120, env=env)
+    assert r.returncode == 0
+    import json
+    line = json.loads(r.stdout.strip().splitlines()[-1])
+    assert line["value"] == 1.5 and "prefill, c4_batched" in line["incomplete"] and "error" not in line
+
+
 def _agree_worker(rank, world, port, ret):
     import importlib.util
     import torch.distributed as dist
@@ -64,3 +81,52 @@ def test_ranks_take_the_same_gather_path_two_ranks():
         p.join(120)
         assert p.exitcode == 0
     assert ret.get(0) == (True, False, 0, 16) and ret.get(1) == (True, False, 0, 16)
+
+
+def _load_bench():
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("bench_under_test", BENCH)
+    b = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(b)
+    return b
+
+
+def _fake_leg(name, unit):
+    def run(args, rank, world, *rest):
+        return {"metric": name, "value": 2.0, "unit": unit, "ms_per_step": 0.5, "scaling": "weak", "dtype": "f16",
+                "roofline": {"frac": 0.5}, "e2e": {"value": 1.0}, "gpu_launches": 4, "clocks": {"sm_mhz": 1900}}
+    return run
+
+
+def test_main_assembles_one_line_from_the_workloads(monkeypatch, capsys):
+    """The order and the keys of bench.py's output line, with every GPU workload replaced by a stand-in."""
+    import json
+    b = _load_bench()
+    monkeypatch.setattr(b, "dist_setup", lambda n: (0, 1, 0))
+    monkeypatch.setattr(b, "run_decode", _fake_leg("decode", "GB/s"))
+    monkeypatch.setattr(b, "run_prefill", _fake_leg("prefill", "TFLOP/s"))
+    monkeypatch.setattr(b, "run_chunked", _fake_leg("chunked", "us"))
+    monkeypatch.setattr(b, "run_batched_decode", _fake_leg("batched", "GB/s"))
+    monkeypatch.setattr(b, "cpu_decode_sample", lambda n, reps: (5.0, "reference", 16, 0.003))
+    monkeypatch.setattr(b, "cpu_prefill_sample", lambda: (0.01, "reference", 16, 48))
+
+    monkeypatch.setattr(sys, "argv", ["bench.py", "--steps", "7", "--warmup", "1"])
+    b.main()
+    line = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert line["metric"] == "decode" and line["value"] == 2.0 and line["unit"] == "GB/s" and line["n_gpus"] == 1
+    assert line["steps"] == 7 and line["warmup"] == 3 and line["higher_is_better"] is True and line["vs_baseline"] is None
+    assert line["roofline"]["frac"] == 0.5 and line["e2e"]["value"] == 1.0 and line["gpu_launches"] == 4
+    assert line["cpu_baseline"]["kind"] == "reference" and line["cpu_baseline"]["cores"] == 16
+    assert line["prefill"]["metric"] == "prefill" and line["prefill"]["cpu_baseline"]["unit"] == "TFLOP/s"
+    assert [k for k in ("c1_prefill128", "c3_chunked", "c4_batched") if k in line] == ["c1_prefill128", "c3_chunked", "c4_batched"]
+    assert b._PARTIAL["pending"] == []
+
+    # the prefill shape as the headline: decode rides along; a single named configuration runs alone
+    monkeypatch.setattr(sys, "argv", ["bench.py", "--workload", "prefill_c5", "--no-cpu"])
+    b.main()
+    line = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert line["metric"] == "prefill" and line["decode"]["metric"] == "decode" and "cpu_baseline" not in line
+    monkeypatch.setattr(sys, "argv", ["bench.py", "--workload", "c4_batched"])
+    b.main()
+    line = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert line["metric"] == "batched" and "prefill" not in line and "decode" not in line and "c4_batched" not in line
