@@ -925,7 +925,8 @@ def main():
     other_name = "prefill" if args.workload == "decode_c2" else "decode"
     # the remaining configurations ride along as objects of their own: the other headline shape, the two chunked-prefill
     # shapes on one GPU (they are replicas at N > 1) and the sequence-sharded batched decode at every N
-    rest = [] if args.no_secondary else [other_name] + (["c1_prefill128", "c3_chunked"] if world == 1 else []) + ["c4_batched"]
+    # (at N > 1 the workload without a data-path exchange runs before the one with the fused gather)
+    rest = [] if args.no_secondary else ([other_name, "c1_prefill128", "c3_chunked", "c4_batched"] if world == 1 else ["c4_batched", other_name])
     _PARTIAL["pending"] = list(rest)
     _PARTIAL["line"] = out
     if world > 1:

@@ -130,3 +130,33 @@ def test_main_assembles_one_line_from_the_workloads(monkeypatch, capsys):
     b.main()
     line = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
     assert line["metric"] == "batched" and "prefill" not in line and "decode" not in line and "c4_batched" not in line
+
+
+def test_main_at_two_ranks_runs_the_batched_decode_before_the_gathering_prefill(monkeypatch, capsys):
+    import json
+    import torch.distributed as dist
+    b = _load_bench()
+    order = []
+
+    def leg(name, unit):
+        inner = _fake_leg(name, unit)
+
+        def run(args, rank, world, *rest):
+            order.append((name, list(b._PARTIAL["pending"])))
+            return inner(args, rank, world)
+        return run
+
+    monkeypatch.setattr(b, "dist_setup", lambda n: (0, 2, 0))
+    monkeypatch.setattr(b, "start_watchdog", lambda world: None)
+    monkeypatch.setattr(b, "run_decode", leg("decode", "GB/s"))
+    monkeypatch.setattr(b, "run_prefill", leg("prefill", "TFLOP/s"))
+    monkeypatch.setattr(b, "run_batched_decode", leg("batched", "GB/s"))
+    monkeypatch.setattr(dist, "barrier", lambda *a, **k: None)
+    monkeypatch.setattr(dist, "destroy_process_group", lambda *a, **k: None)
+    monkeypatch.setattr(sys, "argv", ["bench.py", "--gpus", "2"])
+    b.main()
+    line = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    # the headline first (nothing pending yet), then the workload without an exchange, then the one with the fused gather
+    assert order == [("decode", []), ("batched", ["c4_batched", "prefill"]), ("prefill", ["prefill"])]
+    assert line["n_gpus"] == 2 and "cpu_baseline" not in line and "c1_prefill128" not in line
+    assert line["c4_batched"]["metric"] == "batched" and line["prefill"]["metric"] == "prefill"
