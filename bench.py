@@ -150,6 +150,10 @@ def dist_setup(n_gpus):
         import datetime
         import torch.distributed as dist
         torch.cuda.set_device(local)
+        # NCCL only carries barriers, one-element reductions and the one-time all-gather check here, so in-switch reduction buys
+        # nothing; without it no rank's memory is bound to an NVLink multicast object, which matters because the watchdog and the
+        # collective time-out below can end ranks at slightly different times. (Set NCCL_NVLS_ENABLE=1 to override.)
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         # a collective that a rank never joins ends with an error after this long instead of the default ten minutes (long
         # enough for the slowest rank of a fresh machine to get through its imports)
         limit = datetime.timedelta(seconds=float(os.environ.get("INGOT_BENCH_PG_TIMEOUT_S", "300")))
