@@ -112,33 +112,77 @@ class ClockSampler:
 _PARTIAL = {"line": None, "pending": []}
 
 
+_LAST_STAGE = [time.time()]
+
+
 def stage(msg):
     """Progress marker on stderr (every rank): if a multi-GPU run ever stalls, the log says where."""
+    _LAST_STAGE[0] = time.time()
     print(f"[bench rank {os.environ.get('RANK', '0')} +{time.time() - _T0:6.1f}s] {msg}", file=sys.stderr, flush=True)
 
 
+_BAIL_LOCK = None
+
+
+def bail(world, why):
+    """Ends this rank of a multi-rank run at once. Rank 0 first prints what it has: the finished headline line with an
+    `incomplete` key naming the workloads that did not finish (exit code 0), else an `error` object (exit code 3)."""
+    global _BAIL_LOCK
+    import threading
+    if _BAIL_LOCK is None:
+        _BAIL_LOCK = threading.Lock()
+    if not _BAIL_LOCK.acquire(blocking=False):  # another thread is already on its way out
+        time.sleep(30)
+        os._exit(3)
+    stage(f"giving up: {why}")
+    why = f"bench.py --gpus {world} {why} (see the stage markers on stderr)"
+    rank0 = os.environ.get("RANK", "0") == "0"
+    done = _PARTIAL.get("line")
+    if rank0:
+        if done is not None:  # the headline workload was measured in full: report it and say what is missing
+            print(json.dumps(dict(done, incomplete=f"{why}; not finished: {', '.join(_PARTIAL['pending'])}")), flush=True)
+        else:
+            print(json.dumps({"error": why}), flush=True)
+    os._exit(0 if done is not None or not rank0 else 3)
+
+
 def start_watchdog(world):
-    """A multi-rank run that has not finished after INGOT_BENCH_LIMIT_S seconds (default 540) ends itself with a message
-    instead of occupying the GPUs until somebody else's limit: a stalled collective would otherwise wait for ever."""
+    """Keeps a multi-rank run from occupying the GPUs until somebody else's limit (a stalled collective would otherwise wait
+    for ever) and from ending without a line. The run ends itself through bail() when it has not finished after
+    INGOT_BENCH_LIMIT_S seconds (default 540), when no stage marker has been written for INGOT_BENCH_STALL_S seconds
+    (default 180; a healthy stage takes well under a minute), or when the launcher sends SIGTERM (another rank failed, or an
+    outer time limit ran out) - the last also while the main thread sits inside a collective, through a wake-up pipe."""
     if world <= 1:
         return
+    import signal
     import threading
     limit = float(os.environ.get("INGOT_BENCH_LIMIT_S", "540"))
+    stall = float(os.environ.get("INGOT_BENCH_STALL_S", "180"))
+    _LAST_STAGE[0] = time.time()
 
-    def bail():
-        stage(f"watchdog: not finished after {limit:.0f} s - giving up")
-        why = f"bench.py --gpus {world} did not finish within {limit:.0f} s (see the stage markers on stderr)"
-        done = _PARTIAL.get("line")
-        if os.environ.get("RANK", "0") == "0":
-            if done is not None:  # the headline workload was measured in full: report it and say what is missing
-                print(json.dumps(dict(done, incomplete=f"{why}; not finished: {', '.join(_PARTIAL['pending'])}")), flush=True)
-            else:
-                print(json.dumps({"error": why}), flush=True)
-        os._exit(0 if done is not None or os.environ.get("RANK", "0") != "0" else 3)
+    def watch():
+        while True:
+            time.sleep(0.25)
+            now = time.time()
+            if now - _T0 > limit:
+                bail(world, f"did not finish within {limit:.0f} s")
+            if now - _LAST_STAGE[0] > stall:
+                bail(world, f"made no progress for {stall:.0f} s")
 
-    t = threading.Timer(limit, bail)
-    t.daemon = True
-    t.start()
+    threading.Thread(target=watch, daemon=True).start()
+    if threading.current_thread() is threading.main_thread():
+        r, w = os.pipe()
+        os.set_blocking(w, False)
+        signal.signal(signal.SIGTERM, lambda signum, frame: bail(world, "was told to stop (SIGTERM)"))
+        signal.set_wakeup_fd(w, warn_on_full_buffer=False)
+
+        def on_signal():
+            while True:
+                data = os.read(r, 16)
+                if not data or signal.SIGTERM in data:
+                    bail(world, "was told to stop (SIGTERM)")
+
+        threading.Thread(target=on_signal, daemon=True).start()
 
 
 def dist_setup(n_gpus):
@@ -903,8 +947,8 @@ def main():
         print(json.dumps(run_e2e_model(args)), flush=True)
         return
 
+    start_watchdog(int(os.environ.get("WORLD_SIZE", "1")))  # before the process group comes up: its set-up can stall too
     rank, world, _ = dist_setup(args.gpus)
-    start_watchdog(world)
     from ingot_b200 import workloads as W
     others = {
         "c1_prefill128": lambda a, r, w: run_chunked(a, r, w, W.c1_prefill128(), "configs[0]: 128-token prefill at position 0"),
@@ -969,4 +1013,12 @@ def main():
 
 
 if __name__ == "__main__":
-    main()
+    try:
+        main()
+    except Exception as exc:  # noqa: BLE001
+        n_ranks = int(os.environ.get("WORLD_SIZE", "1"))
+        if n_ranks <= 1:
+            raise
+        import traceback
+        traceback.print_exc()
+        bail(n_ranks, f"stopped with {type(exc).__name__}: {exc}")

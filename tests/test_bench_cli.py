@@ -28,7 +28,7 @@ def test_watchdog_ends_a_stalled_multi_rank_run_with_a_message():
     r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=120, env=env)
     assert r.returncode == 3
     assert '"error"' in r.stdout and "did not finish within 1 s" in r.stdout and "not reached" not in r.stdout
-    assert "[bench rank 0" in r.stderr and "started" in r.stderr and "watchdog" in r.stderr
+    assert "[bench rank 0" in r.stderr and "started" in r.stderr and "giving up" in r.stderr
 
 
 def test_watchdog_reports_a_finished_headline_when_a_later_workload_stalls():
@@ -46,6 +46,46 @@ def test_watchdog_reports_a_finished_headline_when_a_later_workload_stalls():
     import json
     line = json.loads(r.stdout.strip().splitlines()[-1])
     assert line["value"] == 1.5 and "prefill, c4_batched" in line["incomplete"] and "error" not in line
+
+
+def _run_snippet(body, **env):
+    code = ("import importlib.util, time\n"
+            f"spec = importlib.util.spec_from_file_location('bench', {BENCH!r})\n"
+            "b = importlib.util.module_from_spec(spec); spec.loader.exec_module(b)\n" + body)
+    return subprocess.Popen([sys.executable, "-c", code], stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True,
+                            env=dict(os.environ, RANK="0", **env))
+
+
+def test_watchdog_ends_a_run_that_stops_writing_stage_markers():
+    p = _run_snippet("b.start_watchdog(2)\nb.stage('one')\ntime.sleep(0.5)\nb.stage('two')\ntime.sleep(30)\n",
+                     INGOT_BENCH_LIMIT_S="600", INGOT_BENCH_STALL_S="2")
+    out, err = p.communicate(timeout=120)
+    assert p.returncode == 3 and "made no progress for 2 s" in out and "two" in err
+
+
+import pytest  # noqa: E402
+
+# what the main thread is doing when the signal arrives: something Python can interrupt, or a C call that never returns
+# (a second lock of a plain pthread mutex: the stand-in for a thread waiting inside a collective)
+_WAITS = {"sleep": "time.sleep(60)\n",
+          "stuck_in_c": "import ctypes\nlibc = ctypes.CDLL(None)\nm = ctypes.create_string_buffer(128)\n"
+                        "libc.pthread_mutex_init(m, None)\nlibc.pthread_mutex_lock(m)\nprint('ready', flush=True)\n"
+                        "libc.pthread_mutex_lock(m)\n"}
+
+
+@pytest.mark.parametrize("wait", ["sleep", "stuck_in_c"])
+def test_sigterm_from_the_launcher_still_gets_the_headline_out(wait):
+    import json
+    import signal
+    import time
+    p = _run_snippet("b._PARTIAL['line'] = {'metric': 'm', 'value': 2.5}\nb._PARTIAL['pending'] = ['prefill']\n"
+                     "b.start_watchdog(2)\n" + ("print('ready', flush=True)\n" if wait == "sleep" else "") + _WAITS[wait])
+    assert p.stdout.readline().strip() == "ready"
+    time.sleep(0.2)
+    p.send_signal(signal.SIGTERM)
+    out, err = p.communicate(timeout=120)
+    line = json.loads(out.strip().splitlines()[-1])
+    assert p.returncode == 0 and line["value"] == 2.5 and "SIGTERM" in line["incomplete"] and "prefill" in line["incomplete"]
 
 
 def _agree_worker(rank, world, port, ret):
