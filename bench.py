@@ -173,7 +173,7 @@ def start_watchdog(world):
     if threading.current_thread() is threading.main_thread():
         r, w = os.pipe()
         os.set_blocking(w, False)
-        signal.signal(signal.SIGTERM, lambda signum, frame: bail(world, "was told to stop (SIGTERM)"))
+        signal.signal(signal.SIGTERM, lambda signum, frame: None)  # the work is done by the thread below, whatever the main thread is in
         signal.set_wakeup_fd(w, warn_on_full_buffer=False)
 
         def on_signal():
