@@ -13,6 +13,7 @@
 
 #include <cstdint>
 #include <memory>
+#include <string>
 
 #include "gguf.h"
 #include "model.h"
@@ -35,3 +36,10 @@ public:
 // max_seqs sequences of up to n_ctx_per_seq positions each share one paged cache (16-token blocks handed out on
 // demand). Throws like make_cuda_backend.
 std::unique_ptr<BatchedBackend> make_cuda_batched_backend(const gguf::File& file, const Model& model, int n_ctx_per_seq, int max_seqs);
+
+// The batched interface over a named backend. "cuda" (or "metal", the name the reference's engine knows its GPU
+// backend by) is make_cuda_batched_backend. Any other name the reference's make_backend accepts ("cpu") gets one
+// single-sequence backend instance per sequence slot, stepped one after another: no sharing of launches, but the
+// same interface and the same results, e.g. to run a serving loop written against forward_multi without a GPU.
+std::unique_ptr<BatchedBackend> make_batched_backend(const std::string& name, const gguf::File& file, const Model& model,
+                                                     int n_ctx_per_seq, int max_seqs);

@@ -6,9 +6,11 @@
 #include <chrono>
 #include <cmath>
 #include <cstdint>
+#include <stdexcept>
 #include <string>
 #include <vector>
 
+#include "batch_scheduler.h"
 #include "batched_backend.h"
 #include "engine.h"
 #include "metal_backend.h"
@@ -136,6 +138,53 @@ int ingot_e2e_multi_greedy(const char* gguf_path, const int32_t* prompts, const 
                 if (made[s] >= n_gen) backend->release_sequence(s);
             }
         }
+        return 0;
+    } catch (const std::exception& e) {
+        g_err = e.what();
+        return -1;
+    }
+}
+
+// Greedy generation of n_req requests through BatchScheduler on a backend with max_seqs sequence slots ("cpu": one
+// reference CpuBackend per slot; "metal" / "cuda": the paged CUDA backend). Request r is submitted before step
+// arrival_step[r] (null: all at the start), so later requests join while earlier ones are running and take over the
+// slots of finished ones. A reply ends before stop_token (pass -1 for none) or after max_tokens[r] tokens.
+// out_ids [n_req][max_out] receives the replies, out_counts their lengths, out_finish 1 for "stop" and 0 for
+// "length"; stats (may be null) receives the number of forward_multi calls and the tokens they carried.
+// Returns 0, or -1 with ingot_e2e_last_error() set.
+int ingot_e2e_sched_greedy(const char* gguf_path, const char* backend_name, const int32_t* prompts, const int32_t* prompt_lens,
+                           const int32_t* max_tokens, const int32_t* arrival_step, int n_req, int max_seqs, int n_ctx_per_seq,
+                           int stop_token, int32_t* out_ids, int max_out, int32_t* out_counts, int32_t* out_finish, long long* stats) {
+    try {
+        gguf::File f = gguf::File::open(gguf_path);
+        Model model = Model::load(f);
+        auto backend = make_batched_backend(backend_name, f, model, n_ctx_per_seq, max_seqs);
+        BatchScheduler sched(*backend, model.cfg.n_vocab);
+        std::vector<int> id(static_cast<size_t>(n_req), -1);
+        std::vector<const int32_t*> prompt(static_cast<size_t>(n_req), nullptr);
+        for (int r = 0, off = 0; r < n_req; off += prompt_lens[r], r++) prompt[size_t(r)] = prompts + off;
+        int submitted = 0;
+        for (long long step = 0;; step++) {
+            for (int r = 0; r < n_req; r++) {
+                if (id[size_t(r)] >= 0 || (arrival_step && arrival_step[r] > step)) continue;
+                BatchScheduler::Request q;
+                q.prompt.assign(prompt[size_t(r)], prompt[size_t(r)] + prompt_lens[r]);
+                q.max_tokens = max_tokens[r];
+                q.is_stop = [stop_token](int32_t t) { return t == stop_token; };
+                id[size_t(r)] = sched.submit(std::move(q));
+                submitted++;
+            }
+            if (!sched.step() && submitted == n_req) break;  // idle steps while waiting for an arrival cost nothing
+        }
+        for (int r = 0; r < n_req; r++) {
+            const BatchScheduler::Result& res = sched.result(id[size_t(r)]);
+            if (!res.finish) throw std::runtime_error("scheduler: a request was left unfinished");
+            if (int(res.tokens.size()) > max_out) throw std::runtime_error("scheduler: reply longer than the output rows");
+            out_counts[r] = int32_t(res.tokens.size());
+            out_finish[r] = std::string(res.finish) == "stop" ? 1 : 0;
+            std::copy(res.tokens.begin(), res.tokens.end(), out_ids + size_t(r) * size_t(max_out));
+        }
+        if (stats) { stats[0] = sched.steps(); stats[1] = sched.rows(); }
         return 0;
     } catch (const std::exception& e) {
         g_err = e.what();
