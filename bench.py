@@ -112,12 +112,12 @@ class ClockSampler:
 _PARTIAL = {"line": None, "pending": []}
 
 
-_LAST_STAGE = [time.time()]
+_LAST_STAGE = [time.time(), 0]  # when the last stage marker was written, and how many there have been
 
 
 def stage(msg):
     """Progress marker on stderr (every rank): if a multi-GPU run ever stalls, the log says where."""
-    _LAST_STAGE[0] = time.time()
+    _LAST_STAGE[0], _LAST_STAGE[1] = time.time(), _LAST_STAGE[1] + 1
     print(f"[bench rank {os.environ.get('RANK', '0')} +{time.time() - _T0:6.1f}s] {msg}", file=sys.stderr, flush=True)
 
 
@@ -150,7 +150,7 @@ def start_watchdog(world):
     """Keeps a multi-rank run from occupying the GPUs until somebody else's limit (a stalled collective would otherwise wait
     for ever) and from ending without a line. The run ends itself through bail() when it has not finished after
     INGOT_BENCH_LIMIT_S seconds (default 540), when no stage marker has been written for INGOT_BENCH_STALL_S seconds
-    (default 180; a healthy stage takes well under a minute), or when the launcher sends SIGTERM (another rank failed, or an
+    (default 180; a healthy stage takes well under a minute; twice that before the first marker), or when the launcher sends SIGTERM (another rank failed, or an
     outer time limit ran out) - the last also while the main thread sits inside a collective, through a wake-up pipe."""
     if world <= 1:
         return
@@ -158,7 +158,7 @@ def start_watchdog(world):
     import threading
     limit = float(os.environ.get("INGOT_BENCH_LIMIT_S", "540"))
     stall = float(os.environ.get("INGOT_BENCH_STALL_S", "180"))
-    _LAST_STAGE[0] = time.time()
+    _LAST_STAGE[0], _LAST_STAGE[1] = time.time(), 0
 
     def watch():
         while True:
@@ -166,8 +166,10 @@ def start_watchdog(world):
             now = time.time()
             if now - _T0 > limit:
                 bail(world, f"did not finish within {limit:.0f} s")
-            if now - _LAST_STAGE[0] > stall:
-                bail(world, f"made no progress for {stall:.0f} s")
+            # until the first marker (the process group is up) twice the time: a cold machine pages the libraries in first
+            patience = stall if _LAST_STAGE[1] > 0 else 2 * stall
+            if now - _LAST_STAGE[0] > patience:
+                bail(world, f"made no progress for {patience:.0f} s")
 
     threading.Thread(target=watch, daemon=True).start()
     if threading.current_thread() is threading.main_thread():
