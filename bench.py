@@ -146,6 +146,12 @@ def bail(world, why):
     os._exit(0 if done is not None or not rank0 else 3)
 
 
+def mark(world, msg):
+    """stage() for multi-rank runs only (a single-GPU run keeps stderr quiet)."""
+    if world > 1:
+        stage(msg)
+
+
 def start_watchdog(world):
     """Keeps a multi-rank run from occupying the GPUs until somebody else's limit (a stalled collective would otherwise wait
     for ever) and from ending without a line. The run ends itself through bail() when it has not finished after
@@ -327,6 +333,7 @@ def run_decode(args, rank, world):
             kv.layer_view(l, "k").copy_(torch.randn(HKV, DECODE_KEYS, D, device="cuda").half())
             kv.layer_view(l, "v").copy_(torch.randn(HKV, DECODE_KEYS, D, device="cuda").half())
     out = torch.zeros(N_LAYER, 1, H, D, device="cuda")
+    mark(world, "decode: caches ready")
 
     def launch_layers():
         ib.attn_decode_layers(kv, 0, q, out, max_seq_len=DECODE_KEYS, chunk_keys=args.chunk_keys)
@@ -338,6 +345,7 @@ def run_decode(args, rank, world):
     with ClockSampler(torch.cuda.current_device()) as clk:  # clocks are sampled while the timed region runs
         t = timed(step, args.steps, args.warmup, world, 0.0 if args.no_graph else MIN_TIMED_S)
     ms = t["ms"]
+    mark(world, "decode: timed")
 
     # Parity of what was just timed, outside the timed region: three of the 28 layers against the CPU reference.
     torch.cuda.synchronize()
@@ -379,6 +387,7 @@ def run_decode(args, rank, world):
         roofline["in_backend_us_per_layer"] = round(us, 3)
         roofline["in_backend_gbs"] = round(bytes_step / N_LAYER / (us * 1e-6) / 1e9, 1)
 
+    mark(world, "decode: parity and per-layer form done")
     # End to end through the host-buffer C-ABI call: per layer q/k/v rows host->device, RoPE+append,
     # decode at position 4095 (4096 keys), output device->host; one synchronisation per step.
     inv = torch.from_numpy(inv_freq_table()).cuda()
@@ -460,6 +469,7 @@ def run_prefill(args, rank, world):
                   torch.from_numpy(np.ascontiguousarray(c5.v[:, rank * hkv_l:(rank + 1) * hkv_l])).cuda(), 0)
     q = torch.from_numpy(np.ascontiguousarray(c5.q[:, rank * h_l:(rank + 1) * h_l])).cuda().bfloat16()
     out = torch.empty(S, h_l, D, device="cuda", dtype=torch.float16)
+    mark(world, "prefill: inputs ready")
     gathered = torch.empty(world * S, h_l, D, device="cuda", dtype=torch.float16) if world > 1 else None  # rank-major
     # N > 1: the gather of head outputs is fused into the kernel's epilogue - every rank stores its rows straight
     # into all ranks' token-major [S][24][128] buffers (symmetric memory, plain peer stores over NVLink) and then
@@ -526,6 +536,7 @@ def run_prefill(args, rank, world):
     tk = t if world == 1 else timed(step_kernel_only, steps, 3, world, min(0.1, MIN_TIMED_S))
     ms_kernel = tk["ms"]
     assert kv.status() == 0
+    mark(world, "prefill: timed")
 
     # Parity of the timed call's output, outside the timed region: row 0, the last row and 14 random rows (all 24
     # heads; at N > 1 read from the gathered buffer) against the CPU reference.
@@ -554,6 +565,7 @@ def run_prefill(args, rank, world):
                 "frac_of_nominal_2250": round(per_gpu / 2250.0, 4), "ms_per_launch": round(ms_kernel / steps, 4),
                 "best_block_tflops": round(flops / world * steps / (tk["ms_best"] * 1e-3) / 1e12, 1)}
 
+    mark(world, "prefill: parity done")
     # End to end with host buffers through the C ABI (ingot_attn_prefill_host): this rank's q slice in pinned host
     # memory in, its output rows in pinned host memory out; the call cuts the rows into chunks of three CTA waves and overlaps
     # the copy in of the next chunk, the attention of the current one and the copy out of the previous one.
