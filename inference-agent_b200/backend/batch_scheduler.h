@@ -36,7 +36,7 @@ public:
     };
     struct Result {
         std::vector<int32_t> tokens;             // the reply so far
-        const char* finish = nullptr;            // nullptr while queued or running, then "stop" or "length"
+        const char* finish = nullptr;            // nullptr while queued or running, then "stop", "length" or "cancelled"
     };
 
     BatchScheduler(BatchedBackend& backend, int n_vocab)
@@ -111,6 +111,17 @@ public:
     }
 
     void run() { while (step()) {} }
+
+    // Ends a request between steps (its client went away): a queued one never starts, a running one gives its slot
+    // and cache blocks back. What it has generated so far stays readable; finish becomes "cancelled".
+    void cancel(int id) {
+        Result& out = results_.at(size_t(id));
+        if (out.finish) return;
+        for (auto it = queue_.begin(); it != queue_.end(); ++it)
+            if (*it == id) { queue_.erase(it); out.finish = "cancelled"; return; }
+        for (Slot& slot : slots_)
+            if (slot.request == id) { finish(slot, out, "cancelled"); return; }
+    }
 
     const Result& result(int id) const { return results_.at(size_t(id)); }
     int queued() const { return int(queue_.size()); }

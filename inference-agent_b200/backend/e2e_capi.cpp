@@ -149,8 +149,9 @@ int ingot_e2e_multi_greedy(const char* gguf_path, const int32_t* prompts, const 
 // reference CpuBackend per slot; "metal" / "cuda": the paged CUDA backend). Request r is submitted before step
 // arrival_step[r] (null: all at the start), so later requests join while earlier ones are running and take over the
 // slots of finished ones. A reply ends before stop_token (pass -1 for none) or after max_tokens[r] tokens.
-// out_ids [n_req][max_out] receives the replies, out_counts their lengths, out_finish 1 for "stop" and 0 for
-// "length"; stats (may be null) receives the number of forward_multi calls and the tokens they carried.
+// A negative max_tokens[r] = -(k + 1) stands for a client that goes away: no limit of its own, cancelled before step k.
+// out_ids [n_req][max_out] receives the replies, out_counts their lengths, out_finish 0 for "length", 1 for "stop"
+// and 2 for "cancelled"; stats (may be null) receives the number of forward_multi calls and the tokens they carried.
 // Returns 0, or -1 with ingot_e2e_last_error() set.
 int ingot_e2e_sched_greedy(const char* gguf_path, const char* backend_name, const int32_t* prompts, const int32_t* prompt_lens,
                            const int32_t* max_tokens, const int32_t* arrival_step, int n_req, int max_seqs, int n_ctx_per_seq,
@@ -169,11 +170,14 @@ int ingot_e2e_sched_greedy(const char* gguf_path, const char* backend_name, cons
                 if (id[size_t(r)] >= 0 || (arrival_step && arrival_step[r] > step)) continue;
                 BatchScheduler::Request q;
                 q.prompt.assign(prompt[size_t(r)], prompt[size_t(r)] + prompt_lens[r]);
-                q.max_tokens = max_tokens[r];
+                q.max_tokens = max_tokens[r] < 0 ? (1 << 20) : max_tokens[r];
                 q.is_stop = [stop_token](int32_t t) { return t == stop_token; };
                 id[size_t(r)] = sched.submit(std::move(q));
                 submitted++;
             }
+            // a negative max_tokens[r] = -(k + 1) means: limit 1 << 20, and the client of request r goes away after step k
+            for (int r = 0; r < n_req; r++)
+                if (id[size_t(r)] >= 0 && max_tokens[r] < 0 && step == -(max_tokens[r] + 1)) sched.cancel(id[size_t(r)]);
             if (!sched.step() && submitted == n_req) break;  // idle steps while waiting for an arrival cost nothing
         }
         for (int r = 0; r < n_req; r++) {
@@ -181,7 +185,7 @@ int ingot_e2e_sched_greedy(const char* gguf_path, const char* backend_name, cons
             if (!res.finish) throw std::runtime_error("scheduler: a request was left unfinished");
             if (int(res.tokens.size()) > max_out) throw std::runtime_error("scheduler: reply longer than the output rows");
             out_counts[r] = int32_t(res.tokens.size());
-            out_finish[r] = std::string(res.finish) == "stop" ? 1 : 0;
+            out_finish[r] = std::string(res.finish) == "stop" ? 1 : std::string(res.finish) == "cancelled" ? 2 : 0;
             std::copy(res.tokens.begin(), res.tokens.end(), out_ids + size_t(r) * size_t(max_out));
         }
         if (stats) { stats[0] = sched.steps(); stats[1] = sched.rows(); }

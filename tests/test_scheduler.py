@@ -48,9 +48,10 @@ def alone(lib, path, prompt, n_gen):
 
 
 def scheduled(lib, path, prompts, max_tokens, arrivals, max_seqs, n_ctx, stop_token, backend=b"cpu"):
+    """max_tokens[r] = -(k + 1): request r has no limit of its own and is cancelled before step k."""
     n = len(prompts)
     lens = np.array([len(p) for p in prompts], dtype=np.int32)
-    max_out = int(max(max_tokens))
+    max_out = n_ctx if min(max_tokens) < 0 else int(max(max_tokens))
     out = np.full((n, max_out), -1, dtype=np.int32)
     counts, finish = np.zeros(n, dtype=np.int32), np.zeros(n, dtype=np.int32)
     stats = (C.c_longlong * 2)()
@@ -115,6 +116,19 @@ def test_limits_follow_the_reference_server(model):
     rc, out, counts, finish, (steps, rows) = scheduled(lib, model, [p, p], [0, 3], None, 2, 64, -1)
     assert rc == 0 and counts[0] == 0 and finish[0] == 0 and counts[1] == 3
     assert rows == len(p) + 2 and steps == rows  # only the second request ever reached the backend
+
+
+def test_cancelled_requests_free_their_slot_and_keep_what_they_had(model):
+    lib = engine()
+    rng = np.random.default_rng(13)
+    a, b, c = (rng.integers(0, N_VOCAB, size=n).astype(np.int32) for n in (4, 6, 3))
+    # one slot: a runs first and its client goes away before step 9 (steps 0..8 done: 4 prompt tokens fed in steps 0..3, the
+    # first reply token sampled in step 3, so 6 tokens by then); b is cancelled while still queued; c then gets the slot
+    rc, out, counts, finish, (steps, rows) = scheduled(lib, model, [a, b, c], [-(9 + 1), -(2 + 1), 5], None, 1, 64, -1)
+    assert rc == 0, lib.ingot_e2e_last_error()
+    assert list(finish) == [2, 2, 0] and list(counts) == [6, 0, 5]
+    assert np.array_equal(out[0, :6], alone(lib, model, a, 6)) and np.array_equal(out[2, :5], alone(lib, model, c, 5))
+    assert steps == rows == 9 + (3 + 5 - 1)  # b never reached the backend
 
 
 @pytest.mark.gpu
