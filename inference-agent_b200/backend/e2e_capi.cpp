@@ -145,17 +145,63 @@ int ingot_e2e_multi_greedy(const char* gguf_path, const int32_t* prompts, const 
     }
 }
 
-// Greedy generation of n_req requests through BatchScheduler on a backend with max_seqs sequence slots ("cpu": one
+// sampling: null for greedy defaults, else {temperature, top_k, top_p, repeat_penalty, repeat_last_n, seed} (src/sampler.h:8-15).
+static SamplerParams sampler_params(const double* sampling) {
+    SamplerParams sp;
+    sp.temperature = 0.0f;
+    if (sampling) {
+        sp.temperature = float(sampling[0]);
+        sp.top_k = int(sampling[1]);
+        sp.top_p = float(sampling[2]);
+        sp.repeat_penalty = float(sampling[3]);
+        sp.repeat_last_n = int(sampling[4]);
+        sp.seed = uint64_t(sampling[5]);
+    }
+    return sp;
+}
+
+// One request the way the reference's server runs it (src/server.cpp:164-184): prefill, then sample from the logits with
+// the request's own Sampler over prompt + reply, stop before stop_token (-1: none), at most max_tokens tokens, the last
+// one not fed back. Writes the reply to out_ids (room for max_tokens) and returns its length, or -1 with
+// ingot_e2e_last_error() set.
+int ingot_e2e_generate(const char* gguf_path, const char* backend_name, const int32_t* prompt, int n_prompt, int max_tokens,
+                       int n_batch, const double* sampling, int stop_token, int32_t* out_ids) {
+    try {
+        gguf::File f = gguf::File::open(gguf_path);
+        Model model = Model::load(f);
+        auto backend = make_backend(backend_name, f, model, n_prompt + max_tokens + 8, n_batch);
+        Sampler sampler(sampler_params(sampling), model.cfg.n_vocab);
+        std::vector<int32_t> history(prompt, prompt + n_prompt);
+        int pos = 0;
+        const float* logits = prefill(*backend, history, pos, n_batch);
+        int generated = 0;
+        while (generated < max_tokens) {
+            const int32_t next = sampler.sample(const_cast<float*>(logits), history);
+            if (next == stop_token) break;
+            history.push_back(next);
+            out_ids[generated++] = next;
+            if (generated < max_tokens) logits = backend->forward(next, pos++);
+        }
+        return generated;
+    } catch (const std::exception& e) {
+        g_err = e.what();
+        return -1;
+    }
+}
+
+// Generation of n_req requests through BatchScheduler on a backend with max_seqs sequence slots ("cpu": one
 // reference CpuBackend per slot; "metal" / "cuda": the paged CUDA backend). Request r is submitted before step
 // arrival_step[r] (null: all at the start), so later requests join while earlier ones are running and take over the
 // slots of finished ones. A reply ends before stop_token (pass -1 for none) or after max_tokens[r] tokens.
 // A negative max_tokens[r] = -(k + 1) stands for a client that goes away: no limit of its own, cancelled before step k.
 // out_ids [n_req][max_out] receives the replies, out_counts their lengths, out_finish 0 for "length", 1 for "stop"
-// and 2 for "cancelled"; stats (may be null) receives the number of forward_multi calls and the tokens they carried.
+// and 2 for "cancelled"; stats (may be null) receives the number of forward_multi calls and the tokens they carried;
+// sampling (may be null: greedy) is what ingot_e2e_generate takes.
 // Returns 0, or -1 with ingot_e2e_last_error() set.
 int ingot_e2e_sched_greedy(const char* gguf_path, const char* backend_name, const int32_t* prompts, const int32_t* prompt_lens,
                            const int32_t* max_tokens, const int32_t* arrival_step, int n_req, int max_seqs, int n_ctx_per_seq,
-                           int stop_token, int32_t* out_ids, int max_out, int32_t* out_counts, int32_t* out_finish, long long* stats) {
+                           int stop_token, int32_t* out_ids, int max_out, int32_t* out_counts, int32_t* out_finish, long long* stats,
+                           const double* sampling) {
     try {
         gguf::File f = gguf::File::open(gguf_path);
         Model model = Model::load(f);
@@ -172,6 +218,7 @@ int ingot_e2e_sched_greedy(const char* gguf_path, const char* backend_name, cons
                 q.prompt.assign(prompt[size_t(r)], prompt[size_t(r)] + prompt_lens[r]);
                 q.max_tokens = max_tokens[r] < 0 ? (1 << 20) : max_tokens[r];
                 q.is_stop = [stop_token](int32_t t) { return t == stop_token; };
+                q.sampling = sampler_params(sampling);  // every request seeds its own sampler, as every server request does
                 id[size_t(r)] = sched.submit(std::move(q));
                 submitted++;
             }

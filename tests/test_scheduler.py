@@ -26,7 +26,8 @@ def engine():
     lib = C.CDLL(ENGINE)
     lib.ingot_e2e_greedy.argtypes = [C.c_char_p, C.c_char_p, i32p, C.c_int, C.c_int, C.c_int, i32p, f32p]
     lib.ingot_e2e_sched_greedy.argtypes = [C.c_char_p, C.c_char_p, i32p, i32p, i32p, C.c_void_p, C.c_int, C.c_int, C.c_int,
-                                           C.c_int, i32p, C.c_int, i32p, i32p, C.c_void_p]
+                                           C.c_int, i32p, C.c_int, i32p, i32p, C.c_void_p, C.c_void_p]
+    lib.ingot_e2e_generate.argtypes = [C.c_char_p, C.c_char_p, i32p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int, i32p]
     lib.ingot_e2e_last_error.restype = C.c_char_p
     return lib
 
@@ -47,8 +48,24 @@ def alone(lib, path, prompt, n_gen):
     return ids
 
 
-def scheduled(lib, path, prompts, max_tokens, arrivals, max_seqs, n_ctx, stop_token, backend=b"cpu"):
+def _sampling(params):
+    """{temperature, top_k, top_p, repeat_penalty, repeat_last_n, seed} as the C entries take it (None: greedy)."""
+    return None if params is None else np.asarray(params, dtype=np.float64)
+
+
+def served_alone(lib, path, prompt, max_tokens, sampling, stop_token):
+    """The reply of one request through the reference server's loop (prefill, Sampler over prompt + reply, stop token)."""
+    ids = np.zeros(max_tokens, dtype=np.int32)
+    sp = _sampling(sampling)
+    n = lib.ingot_e2e_generate(path.encode(), b"cpu", prompt, len(prompt), max_tokens, 512, None if sp is None else sp.ctypes.data,
+                               stop_token, ids)
+    assert n >= 0, lib.ingot_e2e_last_error()
+    return ids[:n]
+
+
+def scheduled(lib, path, prompts, max_tokens, arrivals, max_seqs, n_ctx, stop_token, backend=b"cpu", sampling=None):
     """max_tokens[r] = -(k + 1): request r has no limit of its own and is cancelled before step k."""
+    sp = _sampling(sampling)
     n = len(prompts)
     lens = np.array([len(p) for p in prompts], dtype=np.int32)
     max_out = n_ctx if min(max_tokens) < 0 else int(max(max_tokens))
@@ -58,7 +75,8 @@ def scheduled(lib, path, prompts, max_tokens, arrivals, max_seqs, n_ctx, stop_to
     arr = None if arrivals is None else np.ascontiguousarray(arrivals, dtype=np.int32)
     rc = lib.ingot_e2e_sched_greedy(path.encode(), backend, np.concatenate(prompts).astype(np.int32), lens,
                                     np.asarray(max_tokens, dtype=np.int32), None if arr is None else arr.ctypes.data, n, max_seqs, n_ctx,
-                                    stop_token, out, max_out, counts, finish, C.cast(stats, C.c_void_p))
+                                    stop_token, out, max_out, counts, finish, C.cast(stats, C.c_void_p),
+                                    None if sp is None else sp.ctypes.data)
     return rc, out, counts, finish, (stats[0], stats[1])
 
 
@@ -116,6 +134,28 @@ def test_limits_follow_the_reference_server(model):
     rc, out, counts, finish, (steps, rows) = scheduled(lib, model, [p, p], [0, 3], None, 2, 64, -1)
     assert rc == 0 and counts[0] == 0 and finish[0] == 0 and counts[1] == 3
     assert rows == len(p) + 2 and steps == rows  # only the second request ever reached the backend
+
+
+@pytest.mark.parametrize("sampling", [
+    (0.0, 40, 0.95, 1.5, 8, 7),     # greedy with a repetition penalty over the last 8 tokens of prompt + reply
+    (0.9, 20, 0.9, 1.2, 64, 1234),  # temperature, top-k, top-p, penalty: every request seeds its own generator
+])
+def test_sampling_and_repetition_penalty_follow_the_reference_server_loop(model, sampling):
+    """The sampler sees what the server's sees: this request's prompt + reply as history, its own seeded generator."""
+    lib = engine()
+    rng = np.random.default_rng(14)
+    prompts = [rng.integers(0, 40, size=int(n)).astype(np.int32) for n in (5, 17, 2, 9)]  # a small alphabet: repeats happen
+    max_tokens = [10, 6, 12, 8]
+    stop = 3
+    want = [served_alone(lib, model, p, m, sampling, stop) for p, m in zip(prompts, max_tokens)]
+    rc, out, counts, finish, _ = scheduled(lib, model, prompts, max_tokens, [0, 0, 2, 6], 2, 64, stop, sampling=sampling)
+    assert rc == 0, lib.ingot_e2e_last_error()
+    for r in range(4):
+        assert np.array_equal(out[r, :counts[r]], want[r]), (r, out[r, :counts[r]], want[r])
+        assert finish[r] == (1 if len(want[r]) < max_tokens[r] else 0)
+    # the penalty changes the replies (otherwise this test would not see a wrong history)
+    plain = [served_alone(lib, model, p, m, None, stop) for p, m in zip(prompts, max_tokens)]
+    assert any(not np.array_equal(a, b) for a, b in zip(plain, want))
 
 
 def test_cancelled_requests_free_their_slot_and_keep_what_they_had(model):
